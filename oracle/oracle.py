@@ -1,0 +1,177 @@
+"""ctypes front end of the CPU oracle (oracle/ckks_oracle.c).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
+benchmark's CPU-baseline leg.  The product package never imports this module.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+from .build import LIB, build_oracle
+
+_U64P = np.ctypeslib.ndpointer(dtype=np.uint64, flags="C_CONTIGUOUS")
+_I64P = np.ctypeslib.ndpointer(dtype=np.int64, flags="C_CONTIGUOUS")
+_F32P = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB):
+            build_oracle()
+        L = C.CDLL(LIB)
+        L.orc_num_threads.restype = C.c_int
+        for name in ("orc_mulmod", "orc_powmod"):
+            getattr(L, name).restype = C.c_uint64
+            getattr(L, name).argtypes = [C.c_uint64] * 3
+        L.orc_invmod.restype = C.c_uint64
+        L.orc_invmod.argtypes = [C.c_uint64] * 2
+        L.orc_shoup.restype = C.c_uint64
+        L.orc_shoup.argtypes = [C.c_uint64] * 2
+        L.orc_find_primitive_root.restype = C.c_uint64
+        L.orc_find_primitive_root.argtypes = [C.c_uint64]
+        L.orc_find_mth_root.restype = C.c_uint64
+        L.orc_find_mth_root.argtypes = [C.c_uint64, C.c_uint64]
+        L.orc_barrett_mu.argtypes = [C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+        L.orc_fill_tables.argtypes = [C.c_uint64, C.c_uint64, C.c_uint32, _U64P, _U64P, _U64P, _U64P]
+        L.orc_ntt_batch.argtypes = [_U64P, C.c_uint32, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                    _U64P, _U64P, _U64P, C.c_int]
+        L.orc_ntt_bruteforce.argtypes = [_U64P, _U64P, C.c_uint32, C.c_uint64, C.c_uint64]
+        L.orc_modup.argtypes = [_U64P, _U64P, C.c_uint32, _U64P, C.c_int, _U64P, C.c_int, C.c_int,
+                                C.c_int, C.c_int]
+        L.orc_ppmm.argtypes = [_F32P, C.POINTER(C.c_void_p), _U64P, C.c_int, C.c_int, C.c_long,
+                               C.c_int, _U64P, C.c_double, C.c_int, C.c_int]
+        L.orc_rlwe_decompose.argtypes = [_U64P, _U64P, C.POINTER(C.c_void_p), C.c_long, C.c_int,
+                                         C.c_int, C.c_int, C.c_int, _U64P]
+        L.orc_ring_down.argtypes = [_I64P, _I64P, C.c_long, C.c_int, C.c_int]
+        L.orc_mlwe_decrypt.argtypes = [_U64P, _I64P, _U64P, C.c_int, C.c_int, C.c_uint64]
+        L.orc_negacyclic_mul_small.argtypes = [_U64P, _I64P, _U64P, C.c_long, C.c_uint64]
+        _lib = L
+    return _lib
+
+
+def num_threads():
+    return lib().orc_num_threads()
+
+
+def find_psi(two_n, q):
+    """2N-th root of unity the reference would pick (Utils.cuh:99-109)."""
+    return int(lib().orc_find_mth_root(int(two_n), int(q)))
+
+
+def barrett_mu(q):
+    hi, lo = C.c_uint64(), C.c_uint64()
+    lib().orc_barrett_mu(int(q), C.byref(hi), C.byref(lo))
+    return hi.value, lo.value
+
+
+class NttTables:
+    """psi tables [mod][n] for a list of moduli, the layout of
+    psi_table_device / psiinv_table_device (Context_23.cuh:481-521)."""
+
+    def __init__(self, n, moduli):
+        self.n = int(n)
+        self.moduli = np.ascontiguousarray(moduli, dtype=np.uint64)
+        k = len(self.moduli)
+        self.psi_root = np.zeros(k, dtype=np.uint64)
+        self.psi = np.zeros((k, n), dtype=np.uint64)
+        self.psiinv = np.zeros((k, n), dtype=np.uint64)
+        self.psi_shoup = np.zeros((k, n), dtype=np.uint64)
+        self.psiinv_shoup = np.zeros((k, n), dtype=np.uint64)
+        for i, q in enumerate(self.moduli):
+            r = find_psi(2 * n, int(q))
+            if r == 2 ** 64 - 1:
+                raise ValueError(f"modulus {int(q)} is not 1 mod {2 * n}")
+            self.psi_root[i] = r
+            lib().orc_fill_tables(r, int(q), n, self.psi[i], self.psiinv[i],
+                                  self.psi_shoup[i], self.psiinv_shoup[i])
+
+
+def ntt_batch(data, tables, start_limb_off, start_mod_idx, poly_num, mod_num, poly_mod_len,
+              inverse=False):
+    """In-place batched transform, arguments as Context_23::ToNTTInplace /
+    FromNTTInplace (Context_23.cuh:847-889)."""
+    assert data.dtype == np.uint64 and data.flags.c_contiguous
+    tab = tables.psiinv if inverse else tables.psi
+    tabs = tables.psiinv_shoup if inverse else tables.psi_shoup
+    lib().orc_ntt_batch(data.reshape(-1), tables.n, start_limb_off, start_mod_idx, poly_num,
+                        mod_num, poly_mod_len, tables.moduli, tab.reshape(-1), tabs.reshape(-1),
+                        1 if inverse else 0)
+    return data
+
+
+def ntt_bruteforce(a, q, psi):
+    a = np.ascontiguousarray(a, dtype=np.uint64)
+    out = np.zeros_like(a)
+    lib().orc_ntt_bruteforce(a, out, len(a), int(q), int(psi))
+    return out
+
+
+def modup(inp, n, q, t, alpha, l, batch):
+    """modUpQjtoT_23 (BasisConv.cuh:84-179): in [batch][q_num][n] ->
+    out [batch][blocks][t_num][n]."""
+    q = np.ascontiguousarray(q, dtype=np.uint64)
+    t = np.ascontiguousarray(t, dtype=np.uint64)
+    blocks = (l + 1 + alpha - 1) // alpha
+    out = np.zeros((batch, blocks, len(t), n), dtype=np.uint64)
+    lib().orc_modup(out.reshape(-1), np.ascontiguousarray(inp).reshape(-1), n, q, len(q), t,
+                    len(t), alpha, l, batch)
+    return out
+
+
+def ppmm(W, X, q, scaler, m0=0, m1=None):
+    """PPMM (PPMM_kernel.cuh:93-252).  W fp32 [M][K]; X uint64 [K][limbs][C] (one
+    contiguous array, or a list of K arrays [limbs][C]); returns [M][limbs][C] with
+    rows outside [m0, m1) left zero."""
+    W = np.ascontiguousarray(W, dtype=np.float32)
+    M, K = W.shape
+    q = np.ascontiguousarray(q, dtype=np.uint64)
+    limbs = len(q)
+    rows = [np.ascontiguousarray(X[n], dtype=np.uint64) for n in range(K)]
+    Cw = rows[0].shape[-1]
+    assert all(r.shape == (limbs, Cw) for r in rows)
+    ptrs = (C.c_void_p * K)(*[r.ctypes.data for r in rows])
+    out = np.zeros((M, limbs, Cw), dtype=np.uint64)
+    m1 = M if m1 is None else m1
+    lib().orc_ppmm(W, ptrs, out.reshape(-1), M, K, Cw, limbs, q, float(scaler), m0, m1)
+    return out
+
+
+def rlwe_decompose(rlwe_a, rlwe_b, N1, k, mlwe_num, q):
+    """rlweCipherDecompose_kernel (PCMM_Scheme.cuh:51-88) on coefficient-domain
+    limbs [limbs][N]; returns [mlwe_num][limbs][k+1][N1]."""
+    q = np.ascontiguousarray(q, dtype=np.uint64)
+    limbs, N = rlwe_a.shape
+    out = np.zeros((mlwe_num, limbs, k + 1, N1), dtype=np.uint64)
+    ptrs = (C.c_void_p * mlwe_num)(*[out[i].ctypes.data for i in range(mlwe_num)])
+    lib().orc_rlwe_decompose(np.ascontiguousarray(rlwe_a).reshape(-1),
+                             np.ascontiguousarray(rlwe_b).reshape(-1), ptrs, N, N1, k, mlwe_num,
+                             limbs, q)
+    return out
+
+
+def ring_down(S, N1, k):
+    S = np.ascontiguousarray(S, dtype=np.int64)
+    out = np.zeros_like(S)
+    lib().orc_ring_down(S, out, len(S), N1, k)
+    return out.reshape(k, N1)
+
+
+def mlwe_decrypt(ct_limb, s_mlwe, q):
+    """ct_limb [(k+1)][N1] for one limb -> message residues [N1]."""
+    kp1, N1 = ct_limb.shape
+    m = np.zeros(N1, dtype=np.uint64)
+    lib().orc_mlwe_decrypt(np.ascontiguousarray(ct_limb).reshape(-1),
+                           np.ascontiguousarray(s_mlwe, dtype=np.int64).reshape(-1), m, N1,
+                           kp1 - 1, int(q))
+    return m
+
+
+def negacyclic_mul_small(a, s, q):
+    a = np.ascontiguousarray(a, dtype=np.uint64)
+    c = np.zeros_like(a)
+    lib().orc_negacyclic_mul_small(a, np.ascontiguousarray(s, dtype=np.int64), c, len(a), int(q))
+    return c
