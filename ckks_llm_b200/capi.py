@@ -1,0 +1,86 @@
+"""ctypes binding of the C ABI declared in include/ckks_b200.h.
+
+Loading fails loudly when the CUDA library has not been built: there is no CPU path.
+"""
+import ctypes as C
+import os
+
+from ._build import LIB
+
+OK = 0
+ERR_ARG, ERR_SHAPE, ERR_UNSUPPORTED, ERR_CUDA, ERR_NOMEM, ERR_RANGE, ERR_TIMEOUT = range(1, 8)
+PCMM_AUTO, PCMM_TENSOR, PCMM_SIMT = 0, 1, 2
+
+# every symbol include/ckks_b200.h declares
+SYMBOLS = [
+    "ckks_b200_version", "ckks_b200_status_string", "ckks_b200_last_error",
+    "ckks_b200_context_create", "ckks_b200_context_destroy", "ckks_b200_context_psi",
+    "ckks_b200_context_table",
+    "ckks_b200_ntt_forward", "ckks_b200_ntt_inverse",
+    "ckks_b200_ntt_forward_host", "ckks_b200_ntt_inverse_host",
+    "ckks_b200_modup_qj_to_t", "ckks_b200_modup_qj_to_t_host",
+    "ckks_b200_pcmm_create", "ckks_b200_pcmm_destroy", "ckks_b200_pcmm_ppmm",
+    "ckks_b200_pcmm_ppmm_host", "ckks_b200_pcmm_copy_back", "ckks_b200_pcmm_check", "ckks_b200_pcmm_last_timing",
+    "ckks_b200_kernel_launches",
+]
+
+
+class CkksB200Error(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"ckks_b200 status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+_lib = None
+
+
+def load():
+    """Load libckks_b200.so (built in-tree by ckks_llm_b200._build.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB):
+        raise ImportError(
+            f"{LIB} is missing: build it with `python -m ckks_llm_b200._build` "
+            "(nvcc, sm_100a).  This package has no CPU implementation.")
+    L = C.CDLL(LIB)
+    vp, i, u64p, dbl, lng = C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.c_double, C.c_long
+    L.ckks_b200_version.restype = i
+    L.ckks_b200_status_string.restype = C.c_char_p
+    L.ckks_b200_status_string.argtypes = [i]
+    L.ckks_b200_last_error.restype = C.c_char_p
+    L.ckks_b200_context_create.argtypes = [C.POINTER(vp), i, i, u64p, i, u64p, i, u64p, i]
+    L.ckks_b200_context_destroy.argtypes = [vp]
+    L.ckks_b200_context_psi.argtypes = [vp, i, u64p]
+    L.ckks_b200_context_table.argtypes = [vp, i, i, vp]
+    for name in ("ckks_b200_ntt_forward", "ckks_b200_ntt_inverse"):
+        getattr(L, name).argtypes = [vp, vp, i, i, i, i, i, vp]
+    for name in ("ckks_b200_ntt_forward_host", "ckks_b200_ntt_inverse_host"):
+        getattr(L, name).argtypes = [vp, vp, i, i, i, i, i]
+    L.ckks_b200_modup_qj_to_t.argtypes = [vp, vp, vp, i, i, vp]
+    L.ckks_b200_modup_qj_to_t_host.argtypes = [vp, vp, vp, i, i]
+    L.ckks_b200_pcmm_create.argtypes = [C.POINTER(vp), i, i, i, u64p, i]
+    L.ckks_b200_pcmm_destroy.argtypes = [vp]
+    L.ckks_b200_pcmm_ppmm.argtypes = [vp, vp, C.POINTER(vp), vp, i, i, i, i, dbl, lng, lng, i, vp]
+    L.ckks_b200_pcmm_ppmm_host.argtypes = [vp, vp, vp, vp, i, i, i, i, dbl, i]
+    L.ckks_b200_pcmm_copy_back.argtypes = [vp, vp, C.POINTER(vp), i, i, vp]
+    L.ckks_b200_pcmm_check.argtypes = [vp, vp]
+    L.ckks_b200_pcmm_last_timing.argtypes = [vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+    L.ckks_b200_kernel_launches.restype = lng
+    for name in SYMBOLS:
+        f = getattr(L, name)
+        if f.restype is C.c_int and name not in ("ckks_b200_version",):
+            f.restype = i
+    _lib = L
+    return L
+
+
+def check(status):
+    if status != OK:
+        raise CkksB200Error(status, load().ckks_b200_last_error().decode())
+
+
+def u64_array(values):
+    arr = (C.c_uint64 * len(values))(*[int(v) for v in values])
+    return arr

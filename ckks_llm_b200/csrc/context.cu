@@ -1,0 +1,284 @@
+// Context creation: host-side table construction and upload.
+#include <math.h>
+#include <stdarg.h>
+
+#include <atomic>
+
+#include "context.cuh"
+
+namespace ckb {
+
+static thread_local char g_err[512] = "";
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+const char* get_error() { return g_err; }
+
+std::atomic<long> g_launches{0};
+
+static uint32_t bitrev(uint32_t x, int bits) {
+    uint32_t r = 0;
+    for (int i = 0; i < bits; i++) r |= ((x >> i) & 1u) << (bits - 1 - i);
+    return r;
+}
+
+// The reference searches for a generator by trial: it collects the divisors it finds
+// for q-1 by trial division with the bound "i < sqrt(remaining cofactor)" and adds
+// the remaining cofactor when it exceeds 2 (src/ckks/include/Utils.cuh:63-97).  The
+// bound is strict, so a cofactor that is the square of a prime enters the set as the
+// square.  The same set is built here so the same generator, hence the same psi and
+// the same NTT output order, results.
+static std::vector<u64> divisor_set(u64 n) {
+    std::vector<u64> s;
+    if ((n & 1) == 0) {
+        s.push_back(2);
+        while ((n & 1) == 0) n >>= 1;
+    }
+    for (u64 d = 3; (double)d < sqrt((double)n); d++) {
+        if (n % d) continue;
+        s.push_back(d);
+        do n /= d; while (n % d == 0);
+    }
+    if (n > 2) {
+        bool seen = false;
+        for (u64 v : s) seen |= (v == n);
+        if (!seen) s.push_back(n);
+    }
+    return s;
+}
+
+u64 find_mth_root(u64 M, u64 q) {
+    if ((q - 1) % M) return 0;
+    const u64 phi = q - 1;
+    std::vector<u64> fs = divisor_set(phi);
+    for (u64 g = 2; g <= phi; g++) {
+        bool generator = true;
+        for (u64 f : fs)
+            if (h_powmod(g, phi / f, q) == 1) { generator = false; break; }
+        if (generator) return h_powmod(g, phi / M, q);
+    }
+    return 0;
+}
+
+// tab[bitrev(e)] = psi^e, tabinv[bitrev(e)] = psi^-e, then tabinv[1] *= n^-1
+// (src/ckks/include/Utils.cuh:190-201).
+void fill_psi_tables(u64 psi, u64 q, uint32_t n, std::vector<u64>& tab, std::vector<u64>& tabinv) {
+    int logn = 0;
+    while ((1u << logn) < n) logn++;
+    tab.assign(n, 0);
+    tabinv.assign(n, 0);
+    const u64 psiinv = h_invmod(psi, q);
+    u64 pw = 1, pwi = 1;
+    for (uint32_t e = 0; e < n; e++) {
+        uint32_t at = bitrev(e, logn);
+        tab[at] = pw;
+        tabinv[at] = pwi;
+        pw = h_mulmod(pw, psi, q);
+        pwi = h_mulmod(pwi, psiinv, q);
+    }
+    tabinv[1] = h_mulmod(tabinv[1], h_invmod(n % q, q), q);
+}
+
+int ensure_buf(u64** buf, size_t* cap, size_t words) {
+    if (*cap >= words) return CKKS_B200_OK;
+    if (*buf) cudaFree(*buf);
+    *buf = nullptr;
+    *cap = 0;
+    if (cudaMalloc(buf, words * sizeof(u64)) != cudaSuccess) {
+        set_error("cudaMalloc of %zu bytes failed", words * sizeof(u64));
+        return CKKS_B200_ERR_NOMEM;
+    }
+    *cap = words;
+    return CKKS_B200_OK;
+}
+
+static bool is_prime(u64 n) {
+    if (n < 4) return n >= 2;
+    if ((n & 1) == 0) return false;
+    u64 d = n - 1;
+    int r = 0;
+    while ((d & 1) == 0) { d >>= 1; r++; }
+    const u64 bases[] = {2, 3, 5, 7, 11, 13, 17, 19, 23, 29, 31, 37};
+    for (u64 a : bases) {
+        if (a % n == 0) continue;
+        u64 x = h_powmod(a, d, n);
+        if (x == 1 || x == n - 1) continue;
+        bool comp = true;
+        for (int i = 1; i < r; i++) {
+            x = h_mulmod(x, x, n);
+            if (x == n - 1) { comp = false; break; }
+        }
+        if (comp) return false;
+    }
+    return true;
+}
+
+}  // namespace ckb
+
+using namespace ckb;
+
+template <class T>
+static int upload(T** dst, const std::vector<T>& src) {
+    if (src.empty()) { *dst = nullptr; return CKKS_B200_OK; }
+    CKB_CUDA(cudaMalloc(dst, src.size() * sizeof(T)));
+    CKB_CUDA(cudaMemcpy(*dst, src.data(), src.size() * sizeof(T), cudaMemcpyHostToDevice));
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int logN,
+                                        const uint64_t* p, int p_num, const uint64_t* q, int q_num,
+                                        const uint64_t* t, int t_num) {
+    CKB_REQUIRE(out != nullptr, CKKS_B200_ERR_ARG, "out is null");
+    *out = nullptr;
+    CKB_REQUIRE(logN >= 12 && logN <= 16, CKKS_B200_ERR_UNSUPPORTED,
+                "logN=%d outside the supported range [12,16]", logN);
+    CKB_REQUIRE(p_num >= 0 && q_num >= 1 && t_num >= 0, CKKS_B200_ERR_ARG, "bad modulus counts");
+    CKB_REQUIRE((p_num == 0 || p) && q && (t_num == 0 || t), CKKS_B200_ERR_ARG, "null modulus list");
+    CKB_REQUIRE(p_num <= 16, CKKS_B200_ERR_UNSUPPORTED, "alpha=p_num=%d exceeds 16", p_num);
+    int ndev = 0;
+    CKB_CUDA(cudaGetDeviceCount(&ndev));
+    CKB_REQUIRE(device >= 0 && device < ndev, CKKS_B200_ERR_ARG, "device %d of %d", device, ndev);
+    DeviceGuard guard(device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", device);
+
+    ckks_b200_context* c = new (std::nothrow) ckks_b200_context();
+    CKB_REQUIRE(c != nullptr, CKKS_B200_ERR_NOMEM, "host allocation failed");
+    c->device = device;
+    c->logN = logN;
+    c->N = 1u << logN;
+    c->p_num = p_num; c->q_num = q_num; c->t_num = t_num;
+    c->mod_num = p_num + q_num + t_num;
+    c->alpha = p_num > 0 ? p_num : 1;
+    c->blocks_max = (q_num + c->alpha - 1) / c->alpha;
+    for (int i = 0; i < p_num; i++) c->moduli.push_back(p[i]);
+    for (int i = 0; i < q_num; i++) c->moduli.push_back(q[i]);
+    for (int i = 0; i < t_num; i++) c->moduli.push_back(t[i]);
+
+    const uint32_t N = c->N;
+    const u64 M = 2ull * N;
+    for (int i = 0; i < c->mod_num; i++) {
+        u64 m = c->moduli[i];
+        if (!(m < (1ull << 62)) || !is_prime(m) || (m - 1) % M) {
+            set_error("modulus %d (%llu) must be a prime = 1 mod 2N below 2^62", i, m);
+            delete c;
+            return CKKS_B200_ERR_ARG;
+        }
+    }
+
+    std::vector<ulonglong2> fwd((size_t)c->mod_num * N), inv((size_t)c->mod_num * N), ninv(c->mod_num);
+    c->h_psi_tab.resize(c->mod_num);
+    c->h_psiinv_tab.resize(c->mod_num);
+    for (int i = 0; i < c->mod_num; i++) {
+        u64 m = c->moduli[i];
+        u64 root = find_mth_root(M, m);
+        c->psi.push_back(root);
+        fill_psi_tables(root, m, N, c->h_psi_tab[i], c->h_psiinv_tab[i]);
+        for (uint32_t j = 0; j < N; j++) {
+            u64 w = c->h_psi_tab[i][j], wi = c->h_psiinv_tab[i][j];
+            fwd[(size_t)i * N + j] = make_ulonglong2(w, h_shoup(w, m));
+            inv[(size_t)i * N + j] = make_ulonglong2(wi, h_shoup(wi, m));
+        }
+        u64 ni = h_invmod(N % m, m);
+        ninv[i] = make_ulonglong2(ni, h_shoup(ni, m));
+    }
+
+    // ModUp tables per level (src/ckks/include/Context_23.cuh:286-351).
+    const int A = c->alpha, B = c->blocks_max, T = t_num;
+    std::vector<ulonglong2> hat_inv((size_t)q_num * B * A, make_ulonglong2(0, 0));
+    std::vector<u64> hat_mod_t((size_t)q_num * B * (T ? T : 1) * A, 0), blk_mod_t((size_t)q_num * B * (T ? T : 1), 0);
+    std::vector<ulonglong2> t_mu(T ? T : 1);
+    const u64* qv = c->moduli.data() + p_num;
+    const u64* tv = c->moduli.data() + p_num + q_num;
+    for (int l = 0; l < q_num && T > 0; l++) {
+        int blocks = (l + 1 + A - 1) / A;
+        for (int b = 0; b < blocks; b++) {
+            int cnt = std::min(A, l + 1 - b * A);
+            for (int j = 0; j < cnt; j++) {
+                u64 qj = qv[b * A + j], prod = 1;
+                for (int jj = 0; jj < cnt; jj++)
+                    if (jj != j) prod = h_mulmod(prod, qv[b * A + jj] % qj, qj);
+                u64 iv = h_invmod(prod, qj);
+                hat_inv[((size_t)l * B + b) * A + j] = make_ulonglong2(iv, h_shoup(iv, qj));
+            }
+            for (int k = 0; k < T; k++) {
+                u64 tk = tv[k], full = 1;
+                for (int j = 0; j < cnt; j++) {
+                    u64 prod = 1;
+                    for (int jj = 0; jj < cnt; jj++)
+                        if (jj != j) prod = h_mulmod(prod, qv[b * A + jj] % tk, tk);
+                    hat_mod_t[(((size_t)l * B + b) * T + k) * A + j] = prod;
+                    full = h_mulmod(full, qv[b * A + j] % tk, tk);
+                }
+                blk_mod_t[((size_t)l * B + b) * T + k] = full;
+            }
+        }
+    }
+    for (int k = 0; k < T; k++) {
+        u64 hi, lo;
+        h_barrett_mu(tv[k], &hi, &lo);
+        t_mu[k] = make_ulonglong2(hi, lo);
+    }
+
+    int st = CKKS_B200_OK;
+    std::vector<u64> mods(c->moduli.begin(), c->moduli.end());
+    if (!st) st = upload(&c->tw_fwd, fwd);
+    if (!st) st = upload(&c->tw_inv, inv);
+    if (!st) st = upload(&c->d_moduli, mods);
+    if (!st) st = upload(&c->d_ninv, ninv);
+    if (!st) st = upload(&c->mu_hat_inv, hat_inv);
+    if (!st) st = upload(&c->mu_hat_mod_t, hat_mod_t);
+    if (!st) st = upload(&c->mu_blk_mod_t, blk_mod_t);
+    if (!st) st = upload(&c->d_t_mu, t_mu);
+    if (st) { ckks_b200_context_destroy(c); return st; }
+    *out = c;
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_context_destroy(ckks_b200_context* c) {
+    if (!c) return CKKS_B200_OK;
+    DeviceGuard guard(c->device);
+    cudaFree(c->tw_fwd); cudaFree(c->tw_inv); cudaFree(c->d_moduli); cudaFree(c->d_ninv);
+    cudaFree(c->mu_hat_inv); cudaFree(c->mu_hat_mod_t); cudaFree(c->mu_blk_mod_t);
+    cudaFree(c->d_t_mu); cudaFree(c->h2d_buf); cudaFree(c->h2d_buf2);
+    delete c;
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_context_psi(const ckks_b200_context* c, int mod_idx, uint64_t* psi) {
+    CKB_REQUIRE(c && psi, CKKS_B200_ERR_ARG, "null argument");
+    CKB_REQUIRE(mod_idx >= 0 && mod_idx < c->mod_num, CKKS_B200_ERR_ARG, "mod_idx %d out of range", mod_idx);
+    *psi = c->psi[mod_idx];
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_context_table(const ckks_b200_context* c, int mod_idx, int inverse,
+                                       uint64_t* h_table) {
+    CKB_REQUIRE(c && h_table, CKKS_B200_ERR_ARG, "null argument");
+    CKB_REQUIRE(mod_idx >= 0 && mod_idx < c->mod_num, CKKS_B200_ERR_ARG, "mod_idx %d out of range", mod_idx);
+    const std::vector<u64>& t = inverse ? c->h_psiinv_tab[mod_idx] : c->h_psi_tab[mod_idx];
+    for (uint32_t j = 0; j < c->N; j++) h_table[j] = t[j];
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_version(void) { return 100; }
+
+extern "C" const char* ckks_b200_status_string(int s) {
+    switch (s) {
+        case CKKS_B200_OK: return "ok";
+        case CKKS_B200_ERR_ARG: return "invalid argument";
+        case CKKS_B200_ERR_SHAPE: return "shape rule violated";
+        case CKKS_B200_ERR_UNSUPPORTED: return "unsupported size";
+        case CKKS_B200_ERR_CUDA: return "CUDA error";
+        case CKKS_B200_ERR_NOMEM: return "out of memory";
+        case CKKS_B200_ERR_RANGE: return "weight out of range";
+        case CKKS_B200_ERR_TIMEOUT: return "device-side wait timed out";
+    }
+    return "unknown status";
+}
+
+extern "C" const char* ckks_b200_last_error(void) { return ckb::get_error(); }
+
+extern "C" long ckks_b200_kernel_launches(void) { return ckb::g_launches.load(); }

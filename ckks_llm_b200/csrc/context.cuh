@@ -1,0 +1,48 @@
+// Context handle: moduli, NTT twiddle tables and ModUp tables resident in HBM.
+#pragma once
+#include <vector>
+
+#include "common.cuh"
+
+struct ckks_b200_context {
+    int device = 0;
+    int logN = 0;
+    uint32_t N = 0;
+    int p_num = 0, q_num = 0, t_num = 0, mod_num = 0;
+    int alpha = 0;          // limbs per digit (= p_num)
+    int blocks_max = 0;     // ceil(q_num / alpha)
+
+    std::vector<u64> moduli;                 // [p | q | t]
+    std::vector<u64> psi;                    // 2N-th root per modulus
+    std::vector<std::vector<u64>> h_psi_tab, h_psiinv_tab;   // kept for ckks_b200_context_table
+
+    // Device tables.  Twiddles are interleaved {w, floor(w*2^64/q)} pairs so one
+    // 128-bit load fetches both: tw_fwd/tw_inv are [mod_num][N] ulonglong2.
+    ulonglong2* tw_fwd = nullptr;
+    ulonglong2* tw_inv = nullptr;
+    u64* d_moduli = nullptr;                 // [mod_num]
+    ulonglong2* d_ninv = nullptr;            // [mod_num] {N^-1, shoup}
+
+    // ModUp tables, one group per level l in [0, q_num):
+    //   hat_inv   [l][blocks_max*alpha]           {inv, shoup} of (Qblk/q_j)^-1 mod q_j
+    //   hat_mod_t [l][blocks_max][t_num][alpha]   (Qblk/q_j) mod t_k
+    //   blk_mod_t [l][blocks_max][t_num]          Qblk mod t_k
+    ulonglong2* mu_hat_inv = nullptr;
+    u64* mu_hat_mod_t = nullptr;
+    u64* mu_blk_mod_t = nullptr;
+    ulonglong2* d_t_mu = nullptr;            // [t_num] Barrett mu {hi, lo}
+
+    // Scratch for the *_host entry points, grown on demand.
+    u64* h2d_buf = nullptr;
+    size_t h2d_cap = 0;
+    u64* h2d_buf2 = nullptr;
+    size_t h2d_cap2 = 0;
+};
+
+namespace ckb {
+// Smallest r >= 2 with r^((q-1)/f) != 1 for every f in the factor set the reference
+// derives for q-1, raised to (q-1)/M: the same root the reference would pick.
+u64 find_mth_root(u64 M, u64 q);
+void fill_psi_tables(u64 psi, u64 q, uint32_t n, std::vector<u64>& tab, std::vector<u64>& tabinv);
+int ensure_buf(u64** buf, size_t* cap, size_t words);
+}  // namespace ckb

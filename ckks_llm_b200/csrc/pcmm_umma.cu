@@ -1,0 +1,528 @@
+// PCMM on the 5th-generation tensor cores (tcgen05, sm_100a).
+//
+// out[m][i][c] = (sum_n w[m][n] * X[n][i][c]) mod q_i is an exact integer GEMM per limb.
+// Both operands are cut into 8-bit planes: w (int64, two's complement) into SW planes of
+// which the top one is signed, X (residues below 2^(8*SC)) into SC unsigned planes.  The
+// product of weight plane a and ciphertext plane b carries weight 2^(8(a+b)), so all
+// plane pairs with the same d = a+b may share one s32 accumulator ("diagonal").
+//
+// Mapping onto one UMMA (M=128, K=32, kind::i8): operand A is a 128-row tile of weight
+// plane a; operand B is the 32-column ciphertext tile of all SC planes stacked
+// (N = 32*SC rows); the destination is placed at TMEM column 32*a, so plane pair (a,b)
+// lands in columns [32(a+b), 32(a+b)+32) and equal diagonals accumulate in place.
+// A tile therefore costs SW instructions per 32-deep K step and (SW+SC-1)*32 TMEM
+// columns.  The epilogue reads the diagonals back, recombines them into a 128-bit
+// signed integer, adds a multiple of q to make it positive, Barrett-reduces, applies the
+// reference's rescale by the last limb, and stores.
+//
+// Operands reach shared memory by bulk asynchronous copies (the TMA engine) of
+// contiguous blobs that two pre-pass kernels have laid out in exactly the core-matrix
+// order the MMA descriptors expect (K-major, no swizzle: 8 rows x 16 bytes per core
+// matrix, 128 B between the two K halves, 256 B between 8-row groups).
+//
+// Roles inside a CTA (persistent, one per SM): warp 0 issues the copies, warp 1 owns
+// TMEM and issues the MMAs, warps 2..9 are the epilogue.  Every wait on an mbarrier is
+// bounded by a clock budget; a wait that runs out raises a flag the host turns into
+// CKKS_B200_ERR_TIMEOUT, and the CTA drains and exits.
+#include "pcmm.cuh"
+
+using namespace ckb;
+
+namespace {
+
+constexpr int TM = 128;            // rows of W per tile (UMMA M)
+constexpr int TC = 32;             // ciphertext columns per tile
+constexpr int KB = 64;             // contraction depth per pipeline stage
+constexpr int KS = KB / 32;        // UMMA K steps per stage
+constexpr int A_PLANE_STEP = TM * 32;   // bytes of one weight plane, one K step
+constexpr int B_PLANE_STEP = TC * 32;   // bytes of one ciphertext plane, one K step
+constexpr int NUM_EPI_WARPS = 8;
+constexpr int NUM_THREADS = 32 * (2 + NUM_EPI_WARPS);
+constexpr long long WAIT_BUDGET = 4000000000ll;   // clock cycles, about two seconds
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the budget ran out (the flag is raised).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* flags, int where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > WAIT_BUDGET) {
+            atomicExch(&flags[1], where);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 B,
+// 128 B from one K half to the next (leading offset), 256 B from one 8-row group to the
+// next (stride offset), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(256 >> 4) << 32) |
+           ((uint64_t)1 << 46);
+}
+// Instruction descriptor: s32 accumulate, A signed or unsigned 8-bit, B unsigned 8-bit,
+// both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool a_signed) {
+    return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | (0u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+}
+
+struct UmmaArgs {
+    const uint8_t* wplanes;    // [mt][kb][a][ks][4096]
+    const uint8_t* xplanes;    // [limb][ct][kb][ks][b][1024]
+    u64* out;                  // [M][limbs][C]
+    const PcmmLimb* limbs;
+    int* flags;
+    int M, limbs_n;
+    long C;
+    long col_begin, col_end;   // columns covered by xplanes: ct 0 starts at col_begin
+    int MT, CT, KBN;           // tiles in M, tiles in columns, pipeline stages per tile
+    int num_stages;
+};
+
+template <int SW, int SC>
+struct Cfg {
+    static constexpr int ND = SW + SC - 1;
+    static constexpr int A_STAGE = SW * KS * A_PLANE_STEP;
+    static constexpr int B_STAGE = SC * KS * B_PLANE_STEP;
+    static constexpr int STAGE = A_STAGE + B_STAGE;
+    static constexpr int TMEM_COLS = ND * TC <= 128 ? 128 : ND * TC <= 256 ? 256 : 512;
+    static constexpr int MAX_STAGES = (220 * 1024) / STAGE < 8 ? (220 * 1024) / STAGE : 8;
+};
+
+// ---------------------------------------------------------------------------
+// Pre-pass 1: weight planes.  One thread per (row, 16-wide K chunk) writes 16 bytes per
+// plane.  Rows and K beyond the matrix are zero.
+// ---------------------------------------------------------------------------
+__global__ void slice_weights_kernel(const long long* __restrict__ w, uint8_t* __restrict__ planes, int M,
+                                     int K, int MT, int KBN, int SW) {
+    const long chunks_per_row = (long)KBN * (KB / 16);
+    const long total = (long)MT * TM * chunks_per_row;
+    long id = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= total) return;
+    const int row = (int)(id % (MT * TM));      // rows fastest: consecutive threads fill one core matrix column
+    const long ch = id / (MT * TM);
+    const int kb = (int)(ch / (KB / 16)), k16 = (int)(ch % (KB / 16));
+    const int ks = k16 / 2, kc = k16 % 2;
+    const int mt = row / TM, r = row % TM;
+    long long v[16];
+#pragma unroll
+    for (int e = 0; e < 16; e++) {
+        int n = kb * KB + k16 * 16 + e;
+        v[e] = (row < M && n < K) ? w[(size_t)row * K + n] : 0;
+    }
+    for (int a = 0; a < SW; a++) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int wd = 0; wd < 4; wd++) {
+            uint32_t x = 0;
+#pragma unroll
+            for (int e = 0; e < 4; e++) x |= (uint32_t)((v[wd * 4 + e] >> (8 * a)) & 0xff) << (8 * e);
+            pk[wd] = x;
+        }
+        size_t off = ((((size_t)mt * KBN + kb) * SW + a) * KS + ks) * A_PLANE_STEP + (size_t)(r / 8) * 256 +
+                     kc * 128 + (r % 8) * 16;
+        *reinterpret_cast<uint4*>(planes + off) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+}
+
+// Pre-pass 2: ciphertext planes for columns [col_begin, col_begin + CT*32).  One thread
+// per (limb, column, 16-wide K chunk); lanes run over columns so every ciphertext read is
+// coalesced.
+__global__ void slice_cipher_kernel(const u64* const* __restrict__ X, uint8_t* __restrict__ planes, int K,
+                                    long C, int limbs_n, long col_begin, long col_end, int CT, int KBN, int SC) {
+    const long ncol = (long)CT * TC;
+    const long col = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= ncol) return;
+    const int k16g = blockIdx.y;                 // global 16-chunk index along K
+    const int limb = blockIdx.z;
+    const int kb = k16g / (KB / 16), k16 = k16g % (KB / 16);
+    const int ks = k16 / 2, kc = k16 % 2;
+    const long c = col_begin + col;
+    u64 v[16];
+#pragma unroll
+    for (int e = 0; e < 16; e++) {
+        int n = k16g * 16 + e;
+        v[e] = (n < K && c < col_end) ? X[n][(size_t)limb * C + c] : 0;
+    }
+    const int ct = (int)(col / TC), cc = (int)(col % TC);
+    for (int b = 0; b < SC; b++) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int wd = 0; wd < 4; wd++) {
+            uint32_t x = 0;
+#pragma unroll
+            for (int e = 0; e < 4; e++) x |= (uint32_t)((v[wd * 4 + e] >> (8 * b)) & 0xff) << (8 * e);
+            pk[wd] = x;
+        }
+        size_t off = (((((size_t)limb * CT + ct) * KBN + kb) * KS + ks) * SC + b) * B_PLANE_STEP +
+                     (size_t)(cc / 8) * 256 + kc * 128 + (cc % 8) * 16;
+        *reinterpret_cast<uint4*>(planes + off) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Main kernel
+// ---------------------------------------------------------------------------
+template <int SW, int SC>
+__global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
+    using C_ = Cfg<SW, SC>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ uint64_t bars[2 * 8 + 2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int NS = P.num_stages;
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t full_bar = smem_u32(&bars[0]);          // [NS]
+    const uint32_t empty_bar = smem_u32(&bars[8]);         // [NS]
+    const uint32_t tmem_full_bar = smem_u32(&bars[16]);
+    const uint32_t tmem_empty_bar = smem_u32(&bars[17]);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; s++) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        mbar_init(tmem_full_bar, 1);
+        mbar_init(tmem_empty_bar, NUM_EPI_WARPS);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), C_::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const long num_items = (long)P.MT * P.CT;
+    const int limbs_n = P.limbs_n;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;           // running stage counter
+            bool ok = true;
+            for (long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                const int mt = (int)(item % P.MT);
+                const long ct = item / P.MT;
+                for (int limb = limbs_n - 1; limb >= 0 && ok; limb--) {
+                    const uint8_t* asrc = P.wplanes + (size_t)mt * P.KBN * C_::A_STAGE;
+                    const uint8_t* bsrc = P.xplanes + ((size_t)limb * P.CT + ct) * P.KBN * C_::B_STAGE;
+                    for (int kb = 0; kb < P.KBN; kb++, it++) {
+                        const int s = it % NS;
+                        const uint32_t ph = (it / NS) & 1;
+                        if (it >= (uint32_t)NS && !mbar_wait(empty_bar + 8 * s, ph ^ 1, P.flags, 1)) { ok = false; break; }
+                        if (*(volatile int*)&abort_flag) { ok = false; break; }
+                        const uint32_t dst = smem_base + s * C_::STAGE;
+                        mbar_arrive_expect_tx(full_bar + 8 * s, C_::STAGE);
+                        bulk_g2s(dst, asrc + (size_t)kb * C_::A_STAGE, C_::A_STAGE, full_bar + 8 * s);
+                        bulk_g2s(dst + C_::A_STAGE, bsrc + (size_t)kb * C_::B_STAGE, C_::B_STAGE, full_bar + 8 * s);
+                    }
+                }
+            }
+            if (!ok) atomicExch(&abort_flag, 1);
+            // Drain: every copy this thread issued must have landed before the CTA exits.
+            const uint32_t issued = it;
+            for (uint32_t j = issued > (uint32_t)NS ? issued - NS : 0; j < issued; j++)
+                mbar_wait(full_bar + 8 * (j % NS), (j / NS) & 1, P.flags, 2);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t it = 0, tile = 0;
+            bool ok = true;
+            constexpr uint32_t idesc_full_u = instr_desc(TC * SC, false);
+            constexpr uint32_t idesc_full_s = instr_desc(TC * SC, true);
+            constexpr uint32_t idesc_head_u = instr_desc(TC * (SC - 1), false);
+            constexpr uint32_t idesc_head_s = instr_desc(TC * (SC - 1), true);
+            constexpr uint32_t idesc_tail_u = instr_desc(TC, false);
+            constexpr uint32_t idesc_tail_s = instr_desc(TC, true);
+            for (long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                for (int limb = limbs_n - 1; limb >= 0 && ok; limb--, tile++) {
+                    if (tile > 0 && !mbar_wait(tmem_empty_bar, (tile - 1) & 1, P.flags, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    for (int kb = 0; kb < P.KBN; kb++, it++) {
+                        const int s = it % NS;
+                        if (!mbar_wait(full_bar + 8 * s, (it / NS) & 1, P.flags, 4)) { ok = false; break; }
+                        if (*(volatile int*)&abort_flag) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t a_base = smem_base + s * C_::STAGE;
+                        const uint32_t b_base = a_base + C_::A_STAGE;
+#pragma unroll
+                        for (int ks = 0; ks < KS; ks++) {
+                            const uint64_t bdesc = smem_desc(b_base + ks * SC * B_PLANE_STEP);
+                            const bool first = (kb == 0 && ks == 0);
+#pragma unroll
+                            for (int a = 0; a < SW; a++) {
+                                const uint64_t adesc = smem_desc(a_base + (a * KS + ks) * A_PLANE_STEP);
+                                const bool sgn = (a == SW - 1);
+                                const uint32_t d = tmem_base + a * TC;
+                                if (!first) {
+                                    umma_i8(d, adesc, bdesc, sgn ? idesc_full_s : idesc_full_u, 1);
+                                } else if (a == 0) {
+                                    umma_i8(d, adesc, bdesc, idesc_full_u, 0);
+                                } else {
+                                    // columns shared with earlier planes accumulate, the new
+                                    // top diagonal (ciphertext plane SC-1) is overwritten
+                                    umma_i8(d, adesc, bdesc, sgn ? idesc_head_s : idesc_head_u, 1);
+                                    const uint64_t btail = smem_desc(b_base + (ks * SC + SC - 1) * B_PLANE_STEP);
+                                    umma_i8(d + (SC - 1) * TC, adesc, btail, sgn ? idesc_tail_s : idesc_tail_u, 0);
+                                }
+                            }
+                        }
+                        umma_commit(empty_bar + 8 * s);
+                    }
+                    if (ok) umma_commit(tmem_full_bar);
+                }
+            }
+            if (!ok) atomicExch(&abort_flag, 1);
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int ew = warp - 2;
+        const int quarter = warp & 3;          // TMEM lanes this warp may read
+        const int half = ew >> 2;              // which 16 of the 32 columns
+        const int row = quarter * 32 + lane;
+        uint32_t tile = 0;
+        bool ok = true;
+        for (long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+            const int mt = (int)(item % P.MT);
+            const long ct = item / P.MT;
+            const int m = mt * TM + row;
+            const long c0 = P.col_begin + ct * TC + half * 16;
+            for (int limb = limbs_n - 1; limb >= 0 && ok; limb--, tile++) {
+                if (!mbar_wait(tmem_full_bar, tile & 1, P.flags, 5)) { ok = false; break; }
+                tc_fence_after();
+                unsigned __int128 acc[16];
+#pragma unroll
+                for (int g = 0; g < 2; g++) {
+                    int32_t v[C_::ND][8];
+#pragma unroll
+                    for (int d = 0; d < C_::ND; d++)
+                        tmem_ld8(tmem_base + ((uint32_t)(quarter * 32) << 16) + d * TC + half * 16 + g * 8, v[d]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        unsigned __int128 s = 0;
+#pragma unroll
+                        for (int d = 0; d < C_::ND; d++)
+                            s += (unsigned __int128)(__int128)v[d][e] << (8 * d);
+                        acc[g * 8 + e] = s;
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty_bar);
+
+                const PcmmLimb L = P.limbs[limb];
+                const unsigned __int128 off = ((unsigned __int128)L.off_hi << 64) | L.off_lo;
+                u64* orow = P.out + ((size_t)m * limbs_n + limb) * P.C;
+                const u64* lrow = P.out + ((size_t)m * limbs_n + (limbs_n - 1)) * P.C;
+#pragma unroll
+                for (int e = 0; e < 16; e++) {
+                    const long c = c0 + e;
+                    unsigned __int128 t = acc[e] + off;
+                    u64 res = barrett128((u64)t, (u64)(t >> 64), L.q, L.mu_hi, L.mu_lo);
+                    if (m < P.M && c < P.col_end) {
+                        if (limb != limbs_n - 1) {
+                            u64 tmp = res + L.q - lrow[c];
+                            res = shoup_mul(tmp, L.inv, L.inv_shoup, L.q);
+                        }
+                        orow[c] = res;
+                    }
+                }
+            }
+        }
+        if (!ok) atomicExch(&abort_flag, 1);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C_::TMEM_COLS);
+    }
+}
+
+template <int SW, int SC>
+int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, u64* d_out, int M, int K,
+           long col_begin, long col_end, cudaStream_t st) {
+    using C_ = Cfg<SW, SC>;
+    const int MT = (M + TM - 1) / TM;
+    const long ncol = col_end - col_begin;
+    const int CT = (int)((ncol + TC - 1) / TC);
+    const int KBN = (K + KB - 1) / KB;
+    const size_t wbytes = (size_t)MT * KBN * C_::A_STAGE;
+    const size_t xbytes = (size_t)pc->q_count * CT * KBN * C_::B_STAGE;
+    int rc = ensure_dev(&pc->d_wplanes, &pc->wplanes_cap, wbytes);
+    if (!rc) rc = ensure_dev(&pc->d_xplanes, &pc->xplanes_cap, xbytes);
+    if (rc) return rc;
+
+    CKB_CUDA(cudaEventRecord(pc->ev[0], st));
+    {
+        long total = (long)MT * TM * KBN * (KB / 16);
+        slice_weights_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d_w, pc->d_wplanes, M, K, MT, KBN, SW);
+        dim3 grid((unsigned)(((long)CT * TC + 127) / 128), KBN * (KB / 16), pc->q_count);
+        slice_cipher_kernel<<<grid, 128, 0, st>>>(d_xptrs, pc->d_xplanes, K, pc->C, pc->q_count, col_begin, col_end,
+                                                  CT, KBN, SC);
+        count_launch(2);
+        CKB_CUDA(cudaGetLastError());
+    }
+
+    int sms = 0;
+    CKB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, pc->device));
+    UmmaArgs P;
+    P.wplanes = pc->d_wplanes;
+    P.xplanes = pc->d_xplanes;
+    P.out = d_out;
+    P.limbs = pc->d_limbs;
+    P.flags = pc->d_flags;
+    P.M = M;
+    P.limbs_n = pc->q_count;
+    P.C = pc->C;
+    P.col_begin = col_begin;
+    P.col_end = col_end;
+    P.MT = MT;
+    P.CT = CT;
+    P.KBN = KBN;
+    P.num_stages = C_::MAX_STAGES;
+    const size_t smem = (size_t)C_::MAX_STAGES * C_::STAGE + 1024;
+    CKB_CUDA(cudaFuncSetAttribute(pcmm_umma_kernel<SW, SC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    long items = (long)MT * CT;
+    int grid = (int)(items < sms ? items : sms);
+    CKB_CUDA(cudaEventRecord(pc->ev[1], st));
+    pcmm_umma_kernel<SW, SC><<<grid, NUM_THREADS, smem, st>>>(P);
+    count_launch();
+    CKB_CUDA(cudaGetLastError());
+    CKB_CUDA(cudaEventRecord(pc->ev[2], st));
+    pc->ev_valid = true;
+    return CKKS_B200_OK;
+}
+
+}  // namespace
+
+namespace ckb {
+
+int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, u64* d_out, int M, int K,
+                long col_begin, long col_end, int w_bits, cudaStream_t st) {
+    int q_bits = 0;
+    for (u64 q : pc->q) {
+        int b = 64 - __builtin_clzll(q);
+        q_bits = b > q_bits ? b : q_bits;
+    }
+    const int sc = (q_bits + 7) / 8;
+    const int sw = (w_bits + 1 + 7) / 8 > 0 ? (w_bits + 1 + 7) / 8 : 1;
+    int klog = 0;
+    while ((1 << klog) < K) klog++;
+    CKB_REQUIRE(q_bits + w_bits + klog <= 110, CKKS_B200_ERR_UNSUPPORTED,
+                "sum of %d-bit weights times %d-bit residues over K=%d exceeds the 110-bit accumulator budget",
+                w_bits, q_bits, K);
+    struct Inst { int sw, sc; };
+    const Inst insts[] = {{4, 5}, {5, 7}, {6, 7}, {8, 8}};
+    for (const Inst& in : insts) {
+        if (sw > in.sw || sc > in.sc) continue;
+        const int pairs = in.sw < in.sc ? in.sw : in.sc;
+        // |sum| per accumulator <= pairs * K * 255 * 255 must stay below 2^31
+        if ((long long)pairs * ((K + KB - 1) / KB * KB) * 65025ll >= (1ll << 31)) continue;
+        if (in.sw == 4) return launch<4, 5>(pc, d_w, d_xptrs, d_out, M, K, col_begin, col_end, st);
+        if (in.sw == 5) return launch<5, 7>(pc, d_w, d_xptrs, d_out, M, K, col_begin, col_end, st);
+        if (in.sw == 6) return launch<6, 7>(pc, d_w, d_xptrs, d_out, M, K, col_begin, col_end, st);
+        return launch<8, 8>(pc, d_w, d_xptrs, d_out, M, K, col_begin, col_end, st);
+    }
+    set_error("no tensor-core configuration fits %d weight planes, %d residue planes and K=%d within s32 accumulators",
+              sw, sc, K);
+    return CKKS_B200_ERR_UNSUPPORTED;
+}
+
+}  // namespace ckb
+
+// Synchronise `stream` and report whether any bounded device-side wait of a tensor-core
+// launch on this handle ran out since the last check.
+extern "C" int ckks_b200_pcmm_check(ckks_b200_pcmm* pc, void* stream) {
+    CKB_REQUIRE(pc != nullptr, CKKS_B200_ERR_ARG, "null argument");
+    DeviceGuard guard(pc->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    CKB_CUDA(cudaMemcpyAsync(pc->h_flags, pc->d_flags, 8 * sizeof(int), cudaMemcpyDeviceToHost, st));
+    CKB_CUDA(cudaStreamSynchronize(st));
+    CKB_REQUIRE(pc->h_flags[1] == 0, CKKS_B200_ERR_TIMEOUT,
+                "a device-side wait ran out of its clock budget (site %d)", pc->h_flags[1]);
+    return CKKS_B200_OK;
+}
+
+// Device time of the latest tensor-core multiply on this handle: the two slicing
+// pre-pass kernels and the main kernel, in milliseconds (waits for them to finish).
+extern "C" int ckks_b200_pcmm_last_timing(ckks_b200_pcmm* pc, float* prepass_ms, float* main_ms) {
+    CKB_REQUIRE(pc && prepass_ms && main_ms, CKKS_B200_ERR_ARG, "null argument");
+    CKB_REQUIRE(pc->ev_valid, CKKS_B200_ERR_ARG, "no tensor-core multiply has run on this handle");
+    DeviceGuard guard(pc->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
+    CKB_CUDA(cudaEventSynchronize(pc->ev[2]));
+    CKB_CUDA(cudaEventElapsedTime(prepass_ms, pc->ev[0], pc->ev[1]));
+    CKB_CUDA(cudaEventElapsedTime(main_ms, pc->ev[1], pc->ev[2]));
+    return CKKS_B200_OK;
+}

@@ -1,0 +1,212 @@
+"""Host-side mirror of the reference's call surface for the hot path.
+
+Class and method names, argument order and error behaviour follow the reference's C++
+classes (Context_23, MLWECiphertext, PCMM_Context, PCMM_Scheme) so that a test written
+against this module reads like a reference driver.  Every method forwards to the C ABI
+(include/ckks_b200.h); device buffers are torch int64 tensors holding uint64 words
+(torch is used for device memory and streams only).
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import capi
+
+
+def _stream_ptr(device):
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def as_u64_tensor(array, device):
+    """uint64 numpy array -> int64 device tensor with the same bits."""
+    a = np.ascontiguousarray(array, dtype=np.uint64)
+    return torch.from_numpy(a.view(np.int64)).to(device)
+
+
+def to_u64_numpy(tensor):
+    return tensor.detach().cpu().contiguous().numpy().view(np.uint64)
+
+
+class Context_23:
+    """Tables and transforms of the reference's Context_23 that lie on the path
+    (src/ckks/include/Context_23.h:19-279): moduli [p | q | t], ToNTTInplace,
+    FromNTTInplace, modUpQjtoT_23."""
+
+    def __init__(self, logN, pVec, qVec, tVec=(), device=0):
+        self.lib = capi.load()
+        self.logN, self.N = int(logN), 1 << int(logN)
+        self.pVec, self.qVec, self.tVec = list(pVec), list(qVec), list(tVec)
+        self.p_num, self.q_num, self.t_num = len(self.pVec), len(self.qVec), len(self.tVec)
+        self.K, self.L = self.p_num, self.q_num - 1
+        self.device = torch.device("cuda", device)
+        self._h = C.c_void_p()
+        capi.check(self.lib.ckks_b200_context_create(
+            C.byref(self._h), device, self.logN, capi.u64_array(self.pVec), self.p_num,
+            capi.u64_array(self.qVec), self.q_num, capi.u64_array(self.tVec), self.t_num))
+
+    def close(self):
+        if self._h:
+            self.lib.ckks_b200_context_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def psi(self, mod_idx):
+        out = C.c_uint64()
+        capi.check(self.lib.ckks_b200_context_psi(self._h, mod_idx, C.byref(out)))
+        return out.value
+
+    def psi_table(self, mod_idx, inverse=False):
+        out = np.zeros(self.N, dtype=np.uint64)
+        capi.check(self.lib.ckks_b200_context_table(self._h, mod_idx, int(inverse), out.ctypes.data))
+        return out
+
+    # Context_23::ToNTTInplace, src/ckks/include/Context_23.cuh:847-866
+    def ToNTTInplace(self, device_a, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len):
+        capi.check(self.lib.ckks_b200_ntt_forward(
+            self._h, device_a.data_ptr(), start_poly_idx, start_mod_idx, poly_num, mod_num,
+            poly_mod_len, _stream_ptr(self.device)))
+
+    # Context_23::FromNTTInplace, src/ckks/include/Context_23.cuh:868-889
+    def FromNTTInplace(self, device_a, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len):
+        capi.check(self.lib.ckks_b200_ntt_inverse(
+            self._h, device_a.data_ptr(), start_poly_idx, start_mod_idx, poly_num, mod_num,
+            poly_mod_len, _stream_ptr(self.device)))
+
+    # Context_23::modUpQjtoT_23, src/ckks/include/BasisConv.cuh:161-179
+    def modUpQjtoT_23(self, output, input, l, batch_size):
+        capi.check(self.lib.ckks_b200_modup_qj_to_t(
+            self._h, output.data_ptr(), input.data_ptr(), l, batch_size, _stream_ptr(self.device)))
+
+    # host-buffer forms (numpy uint64 arrays, transformed in place / returned)
+    def ToNTTInplace_host(self, host_a, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len):
+        assert host_a.dtype == np.uint64 and host_a.flags.c_contiguous
+        capi.check(self.lib.ckks_b200_ntt_forward_host(
+            self._h, host_a.ctypes.data, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len))
+
+    def FromNTTInplace_host(self, host_a, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len):
+        assert host_a.dtype == np.uint64 and host_a.flags.c_contiguous
+        capi.check(self.lib.ckks_b200_ntt_inverse_host(
+            self._h, host_a.ctypes.data, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len))
+
+    def modUpQjtoT_23_host(self, host_in, l, batch_size):
+        assert host_in.dtype == np.uint64 and host_in.flags.c_contiguous
+        blocks = (l + 1 + self.p_num - 1) // self.p_num
+        out = np.zeros((batch_size, blocks, self.t_num, self.N), dtype=np.uint64)
+        capi.check(self.lib.ckks_b200_modup_qj_to_t_host(
+            self._h, out.ctypes.data, host_in.ctypes.data, l, batch_size))
+        return out
+
+
+class MLWECiphertext:
+    """Device buffer [L+1][k+1][N1] words (src/ckks/include/pcmm/MLWECiphertext.cuh:6-78)."""
+
+    def __init__(self, N1, L, l, k, scale, device=0, cipher=None):
+        self.N1, self.L, self.l, self.k, self.scale = N1, L, l, k, scale
+        if cipher is None:
+            cipher = torch.zeros((L + 1) * (k + 1) * N1, dtype=torch.int64, device=torch.device("cuda", device))
+        self.cipher_device = cipher
+
+
+class PCMM_Context:
+    """Parameter carrier of the ring packing (src/ckks/include/pcmm/PCMM_Context.h:14-90)."""
+
+    def __init__(self, N1, mlwe_rank, p_ringpack, q_ringpack, device=0):
+        self.lib = capi.load()
+        self.N1, self.mlwe_rank = int(N1), int(mlwe_rank)
+        self.p_ringpack, self.q_ringpack = list(p_ringpack), list(q_ringpack)
+        self.ringpack_p_count = len(self.p_ringpack)
+        self.ringpack_q_count = len(self.q_ringpack)
+        self.ringpack_pq_count = self.ringpack_p_count + self.ringpack_q_count
+        self.device = torch.device("cuda", device)
+        self._h = C.c_void_p()
+        capi.check(self.lib.ckks_b200_pcmm_create(
+            C.byref(self._h), device, self.N1, self.mlwe_rank, capi.u64_array(self.q_ringpack),
+            self.ringpack_q_count))
+
+    def close(self):
+        if self._h:
+            self.lib.ckks_b200_pcmm_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class PCMM_Scheme:
+    """PPMM of the reference's PCMM_Scheme (src/ckks/include/pcmm/PCMM_Scheme.h:12-48)."""
+
+    def __init__(self, pcmm_context, algo=capi.PCMM_AUTO):
+        self.pcmm_context = pcmm_context
+        self.lib = pcmm_context.lib
+        self.algo = algo
+        self.ppmm_output = None
+
+    def scaler_for(self, scale, target_scale=float(1 << 49)):
+        """scaler = (long)(q_ringpack[1] * target / scale), PPMM_kernel.cuh:283-284."""
+        q1 = self.pcmm_context.q_ringpack[1]
+        return float(int(q1 * target_scale / scale))
+
+    def PPMM(self, plain_mat, mlwe_cipher_decomposed, mat_M, mat_N, mat_K, mlwe_num, scaler=None,
+             col_begin=0, col_end=None, copy_back=True):
+        """PCMM_Scheme::PPMM (src/ckks/include/pcmm/PPMM_kernel.cuh:254-349).
+
+        plain_mat: fp32 device tensor [mat_M][mat_N].  Like the reference, a shape
+        violation prints its message and returns without computing.  `scaler` defaults to
+        the reference's choice.  The raw result stays in self.ppmm_output
+        ([mat_M][q_count][(k+1)*N1]); with copy_back the first limb of row i overwrites
+        ciphertext i and scales are updated as at :345-348."""
+        pc = self.pcmm_context
+        if scaler is None:
+            scaler = self.scaler_for(mlwe_cipher_decomposed[0].scale)
+        C_ = (pc.mlwe_rank + 1) * pc.N1
+        if col_end is None:
+            col_end = C_
+        need = mat_M * pc.ringpack_q_count * C_
+        if self.ppmm_output is None or self.ppmm_output.numel() < need:
+            self.ppmm_output = torch.empty(need, dtype=torch.int64, device=pc.device)
+        ptrs = (C.c_void_p * max(mlwe_num, 1))(*[c.cipher_device.data_ptr() for c in mlwe_cipher_decomposed[:mlwe_num]])
+        st = self.lib.ckks_b200_pcmm_ppmm(
+            pc._h, plain_mat.data_ptr(), ptrs, self.ppmm_output.data_ptr(), mat_M, mat_N, mat_K, mlwe_num,
+            float(scaler), col_begin, col_end, self.algo, _stream_ptr(pc.device))
+        if st == capi.ERR_SHAPE:
+            print(self.lib.ckks_b200_last_error().decode())
+            return None
+        capi.check(st)
+        out = self.ppmm_output[:need].view(mat_M, pc.ringpack_q_count, C_)
+        if copy_back:
+            capi.check(self.lib.ckks_b200_pcmm_copy_back(
+                pc._h, self.ppmm_output.data_ptr(), ptrs, min(mlwe_num, mat_M), 1, _stream_ptr(pc.device)))
+            q_last = pc.q_ringpack[-1]
+            for c in mlwe_cipher_decomposed[:mlwe_num]:
+                c.scale = c.scale * scaler / q_last
+        return out
+
+    def check(self):
+        capi.check(self.lib.ckks_b200_pcmm_check(self.pcmm_context._h, _stream_ptr(self.pcmm_context.device)))
+
+    def last_timing(self):
+        """(pre-pass ms, main kernel ms) of the latest tensor-core multiply."""
+        a, b = C.c_float(), C.c_float()
+        capi.check(self.lib.ckks_b200_pcmm_last_timing(self.pcmm_context._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def PPMM_host(self, plain_mat, X, mat_M, mat_N, mat_K, mlwe_num, scaler):
+        """Host-buffer call: numpy in, numpy out, copies inside."""
+        pc = self.pcmm_context
+        W = np.ascontiguousarray(plain_mat, dtype=np.float32)
+        X = np.ascontiguousarray(X, dtype=np.uint64)
+        C_ = (pc.mlwe_rank + 1) * pc.N1
+        out = np.empty((mat_M, pc.ringpack_q_count, C_), dtype=np.uint64)
+        capi.check(self.lib.ckks_b200_pcmm_ppmm_host(
+            pc._h, W.ctypes.data, X.ctypes.data, out.ctypes.data, mat_M, mat_N, mat_K, mlwe_num,
+            float(scaler), self.algo))
+        return out

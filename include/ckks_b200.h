@@ -1,0 +1,139 @@
+/*
+ * ckks_b200.h -- C ABI of the B200-native CKKS hot path: batched negacyclic RNS
+ * NTT/INTT, Q-digit -> T basis conversion (ModUp) and the ring-packed
+ * plaintext x ciphertext matrix multiply (PPMM/PCMM).
+ *
+ * The reference (haozetao/ckks_llm) is a header-only CUDA/C++ unity build with no
+ * C interface; each entry point below names the reference C++ member it stands in
+ * for (file:line relative to the reference root).  All functions return 0 on
+ * success or a CKKS_B200_ERR_* code, never throw and never print; a description of
+ * the last failure on the calling thread is available from ckks_b200_last_error().
+ * Pointers named d_* are device pointers on the handle's device, h_* are host
+ * pointers.  `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ * No entry point falls back to a CPU implementation: without a CUDA device every
+ * compute call fails with CKKS_B200_ERR_CUDA.
+ */
+#ifndef CKKS_B200_H
+#define CKKS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CKKS_B200_OK 0
+#define CKKS_B200_ERR_ARG 1         /* null pointer, negative count, bad index */
+#define CKKS_B200_ERR_SHAPE 2       /* shape rule of the reference violated */
+#define CKKS_B200_ERR_UNSUPPORTED 3 /* size outside what the kernels were built for */
+#define CKKS_B200_ERR_CUDA 4        /* a CUDA runtime call failed */
+#define CKKS_B200_ERR_NOMEM 5       /* device or host allocation failed */
+#define CKKS_B200_ERR_RANGE 6       /* scaled weight does not fit the byte planes */
+#define CKKS_B200_ERR_TIMEOUT 7     /* a bounded device-side wait ran out */
+
+typedef struct ckks_b200_context ckks_b200_context;
+typedef struct ckks_b200_pcmm ckks_b200_pcmm;
+
+int ckks_b200_version(void);
+const char* ckks_b200_status_string(int status);
+const char* ckks_b200_last_error(void);
+
+/* ---- context ---------------------------------------------------------------
+ * Tables the path needs from Context_23: moduli in the order [p | q | t]
+ * (src/ckks/include/Context_23.cuh:56-113), 2N-th roots and psi / psi^-1 power
+ * tables with Shoup companions (Utils.cuh:99-109,190-210; upload
+ * Context_23.cuh:481-521), N^-1 (Context_23.cuh:140-157) and the Q-digit -> T
+ * conversion tables for every level (Context_23.cuh:286-351).  alpha (limbs per
+ * digit) equals p_num as in the reference (Context_23.cuh:31-32).
+ * logN in [12,16]; every modulus is an odd prime = 1 mod 2N below 2^62. */
+int ckks_b200_context_create(ckks_b200_context** out, int device, int logN,
+                             const uint64_t* p, int p_num,
+                             const uint64_t* q, int q_num,
+                             const uint64_t* t, int t_num);
+int ckks_b200_context_destroy(ckks_b200_context* ctx);
+/* 2N-th root of unity chosen for modulus index mod_idx (index into [p|q|t]). */
+int ckks_b200_context_psi(const ckks_b200_context* ctx, int mod_idx, uint64_t* psi);
+/* Copy of the psi (inverse=0) or psi^-1 (inverse=1) table of one modulus, N words,
+ * bit-reversed exponent order, n^-1 folded into psiinv[1] (Utils.cuh:190-201). */
+int ckks_b200_context_table(const ckks_b200_context* ctx, int mod_idx, int inverse,
+                            uint64_t* h_table);
+
+/* ---- NTT / INTT ------------------------------------------------------------
+ * Context_23::ToNTTInplace / FromNTTInplace (Context_23.cuh:847-889): in place on
+ * [poly_num][poly_mod_len][N] words; limb i of the call (i < mod_num) lives at limb
+ * offset start_limb_off+i and uses modulus index start_mod_idx+i.  Forward takes
+ * natural order to bit-reversed order, inverse the opposite and includes N^-1;
+ * outputs are canonical residues in [0,q). */
+int ckks_b200_ntt_forward(ckks_b200_context* ctx, uint64_t* d_data, int start_limb_off,
+                          int start_mod_idx, int poly_num, int mod_num, int poly_mod_len,
+                          void* stream);
+int ckks_b200_ntt_inverse(ckks_b200_context* ctx, uint64_t* d_data, int start_limb_off,
+                          int start_mod_idx, int poly_num, int mod_num, int poly_mod_len,
+                          void* stream);
+/* Same transforms on a host buffer: copy in, transform, copy out, synchronise. */
+int ckks_b200_ntt_forward_host(ckks_b200_context* ctx, uint64_t* h_data, int start_limb_off,
+                               int start_mod_idx, int poly_num, int mod_num, int poly_mod_len);
+int ckks_b200_ntt_inverse_host(ckks_b200_context* ctx, uint64_t* h_data, int start_limb_off,
+                               int start_mod_idx, int poly_num, int mod_num, int poly_mod_len);
+
+/* ---- ModUp -----------------------------------------------------------------
+ * Context_23::modUpQjtoT_23 (BasisConv.cuh:84-179): for level l, every digit of
+ * alpha consecutive Q-limbs of in[batch][q_num][N] (coefficient domain) is extended
+ * to the t_num limbs of T: out[batch][ceil((l+1)/alpha)][t_num][N]. */
+int ckks_b200_modup_qj_to_t(ckks_b200_context* ctx, uint64_t* d_out, const uint64_t* d_in,
+                            int l, int batch, void* stream);
+int ckks_b200_modup_qj_to_t_host(ckks_b200_context* ctx, uint64_t* h_out, const uint64_t* h_in,
+                                 int l, int batch);
+
+/* ---- PCMM ------------------------------------------------------------------
+ * Parameter carrier of PCMM_Context for the multiply (pcmm/PCMM_Context.cuh:7-57):
+ * MLWE degree N1, rank k, and the ring-pack q moduli the product runs over
+ * (any odd q < 2^62; the reference uses {q0,q1}). */
+int ckks_b200_pcmm_create(ckks_b200_pcmm** out, int device, int N1, int mlwe_rank,
+                          const uint64_t* q_ringpack, int q_count);
+int ckks_b200_pcmm_destroy(ckks_b200_pcmm* pc);
+
+#define CKKS_B200_PCMM_AUTO 0   /* tensor-core path (tcgen05) */
+#define CKKS_B200_PCMM_TENSOR 1 /* same, explicit */
+#define CKKS_B200_PCMM_SIMT 2   /* 64-bit CUDA-core path, the reference's formulation */
+
+/* PCMM_Scheme::PPMM (pcmm/PPMM_kernel.cuh:254-349) and its kernel (:93-252):
+ *   out[m][i][c] = rescale_i( sum_n a(m,n,i) * X[n][i][c] mod q_i )
+ * with w = (int64)((double)W[m][n]*scaler) truncated toward zero, a = w>0 ? w : q_i+w,
+ * limbs processed last to first and every limb but the last rescaled by the last
+ * (:213-249).  d_W is fp32 [mat_M][mat_N] row-major; h_X_ptrs is a HOST array of
+ * mlwe_num device pointers, ciphertext n laid out [q_count][(k+1)*N1]
+ * (pcmm/MLWECiphertext.cuh:8-10); d_out is [mat_M][q_count][(k+1)*N1], the
+ * reference's ppmm_output.  Shape rules of the reference are kept: mat_K == N1 and
+ * mat_N == mlwe_num, else CKKS_B200_ERR_SHAPE (:256-263).  Only columns
+ * [col_begin, col_end) of every row are computed (multiples of 32, or the full
+ * width); pass 0 and (k+1)*N1 for the whole product.  The call is asynchronous on
+ * `stream`. */
+int ckks_b200_pcmm_ppmm(ckks_b200_pcmm* pc, const float* d_W, const uint64_t* const* h_X_ptrs,
+                        uint64_t* d_out, int mat_M, int mat_N, int mat_K, int mlwe_num,
+                        double scaler, long col_begin, long col_end, int algo, void* stream);
+/* Host-buffer form: h_W fp32 [M][N], h_X contiguous [mlwe_num][q_count][(k+1)*N1],
+ * h_out [M][q_count][(k+1)*N1]; copies in, multiplies, copies out, synchronises. */
+int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, const uint64_t* h_X,
+                             uint64_t* h_out, int mat_M, int mat_N, int mat_K, int mlwe_num,
+                             double scaler, int algo);
+/* The copy-back PPMM ends with (:345-348): row i of d_out, first `limbs` limbs, is
+ * copied over ciphertext i for i < mlwe_num (the reference hard-codes limbs = 2). */
+int ckks_b200_pcmm_copy_back(ckks_b200_pcmm* pc, const uint64_t* d_out,
+                             uint64_t* const* h_X_ptrs, int mlwe_num, int limbs, void* stream);
+/* Waits for `stream` and reports CKKS_B200_ERR_TIMEOUT if a bounded device-side wait
+ * of a tensor-core multiply on this handle gave up since the last check (no reference
+ * counterpart: the reference never checks a CUDA status). */
+int ckks_b200_pcmm_check(ckks_b200_pcmm* pc, void* stream);
+/* Device time in milliseconds of the latest tensor-core multiply on this handle, split
+ * into its slicing pre-pass and its main kernel; waits for them.  Stands in for the
+ * CUDATimer the reference wraps around its kernel (PPMM_kernel.cuh:301-343). */
+int ckks_b200_pcmm_last_timing(ckks_b200_pcmm* pc, float* prepass_ms, float* main_ms);
+/* Number of kernels this library has launched on the calling process so far. */
+long ckks_b200_kernel_launches(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CKKS_B200_H */

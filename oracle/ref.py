@@ -1,0 +1,81 @@
+"""ctypes front end of oracle/_ref/libref_driver.so: the REAL reference's host table
+builders and CUDA kernels (see oracle/ref_driver.cu).  TEST INFRASTRUCTURE ONLY."""
+import ctypes as C
+import os
+
+import numpy as np
+
+from .build_ref import LIB, build_ref
+
+_U64P = np.ctypeslib.ndpointer(dtype=np.uint64, flags="C_CONTIGUOUS")
+_F32P = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+_lib = None
+
+
+def available():
+    return build_ref() is not None and os.path.exists(LIB)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not available():
+            raise RuntimeError("reference driver library is not built")
+        L = C.CDLL(LIB)
+        L.ref_find_mth_root.restype = C.c_uint64
+        L.ref_find_mth_root.argtypes = [C.c_uint64, C.c_uint64]
+        L.ref_fill_tables.argtypes = [C.c_uint64, C.c_uint64, C.c_uint, _U64P, _U64P, _U64P, _U64P]
+        L.ref_ntt.argtypes = [_U64P, C.c_int, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
+        L.ref_modup.argtypes = [_U64P, _U64P, C.c_int, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                _U64P, _U64P, _U64P, _U64P]
+        L.ref_ppmm.argtypes = [_F32P, _U64P, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _U64P,
+                               C.c_double, _U64P, _U64P]
+        _lib = L
+    return _lib
+
+
+def find_psi(two_n, q):
+    return int(lib().ref_find_mth_root(int(two_n), int(q)))
+
+
+def fill_tables(psi, q, n):
+    out = [np.zeros(n, dtype=np.uint64) for _ in range(4)]
+    lib().ref_fill_tables(int(psi), int(q), int(n), *out)
+    return out  # psi, psiinv, psi_shoup, psiinv_shoup
+
+
+def ntt(data, logN, pqt, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len, inverse=False):
+    d = np.ascontiguousarray(data, dtype=np.uint64).copy()
+    pqt = np.ascontiguousarray(pqt, dtype=np.uint64)
+    rc = lib().ref_ntt(d.reshape(-1), logN, pqt, len(pqt), start_poly_idx, start_mod_idx, poly_num, mod_num,
+                       poly_mod_len, int(inverse))
+    if rc:
+        raise RuntimeError(f"ref_ntt failed with {rc}")
+    return d
+
+
+def modup(inp, logN, p, q, t, l, batch, tables):
+    """tables = (hat_inv, hat_inv_shoup, hat_mod_t, blk_mod_t) for level l."""
+    pqt = np.ascontiguousarray(list(p) + list(q) + list(t), dtype=np.uint64)
+    alpha = len(p)
+    blocks = (l + 1 + alpha - 1) // alpha
+    out = np.zeros((batch, blocks, len(t), 1 << logN), dtype=np.uint64)
+    rc = lib().ref_modup(out.reshape(-1), np.ascontiguousarray(inp, dtype=np.uint64).reshape(-1), logN, pqt,
+                         len(p), len(q), len(t), l, batch, *[np.ascontiguousarray(x, dtype=np.uint64) for x in tables])
+    if rc:
+        raise RuntimeError(f"ref_modup failed with {rc}")
+    return out
+
+
+def ppmm(W, X, N1, rank, q, scaler, qinv, qinv_shoup):
+    W = np.ascontiguousarray(W, dtype=np.float32)
+    X = np.ascontiguousarray(X, dtype=np.uint64)
+    M, K = W.shape
+    limbs = len(q)
+    out = np.zeros((M, limbs, (rank + 1) * N1), dtype=np.uint64)
+    rc = lib().ref_ppmm(W, X.reshape(-1), out.reshape(-1), M, K, N1, rank, limbs,
+                        np.ascontiguousarray(q, dtype=np.uint64), float(scaler),
+                        np.ascontiguousarray(qinv, dtype=np.uint64), np.ascontiguousarray(qinv_shoup, dtype=np.uint64))
+    if rc:
+        raise RuntimeError(f"ref_ppmm failed with {rc}")
+    return out

@@ -1,0 +1,211 @@
+// Thin driver around the REAL reference (haozetao/ckks_llm), compiled from the reference
+// sources where they lie (never copied into this repository) into oracle/_ref/.
+//
+// TEST INFRASTRUCTURE ONLY.  It exposes, through a few extern "C" entry points,
+//   * the reference's own host table builders (findMthRootOfUnity,
+//     fillTablePsi128_special, fillTablePsi_shoup128: src/ckks/include/Utils.cuh), and
+//   * the reference's own CUDA kernels for the hot path, launched by the reference's own
+//     host launchers where those need no big-number state:
+//     Context_23::ToNTTInplace / FromNTTInplace (src/ckks/include/Context_23.cuh:847-889),
+//     Context_23::modUpQjtoT_23 (src/ckks/include/BasisConv.cuh:161-179), and
+//     pcmm_cuda_core_kernel<mat_N> with the launch shape of PCMM_Scheme::PPMM
+//     (src/ckks/include/pcmm/PPMM_kernel.cuh:294-329).
+// The reference's constructors need the NTL big-number library, which is absent; the
+// driver therefore fills the handful of plain-integer members those launchers read on a
+// zero-initialised Context_23 object and uploads tables passed in by the caller.  NTL
+// itself is replaced by the do-nothing stand-in under oracle/ref_shim/.
+#include <iostream>
+#include <string>
+#include <sstream>
+#include <vector>
+#include <cmath>
+using namespace std;
+
+#include "Context_23.cuh"
+#include "Scheme_23.cuh"
+#include "TimeUtils.cuh"
+#include "pcmm/PCMM_Context.cuh"
+#include "pcmm/PCMM_Scheme.cuh"
+
+#define RD_CUDA(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { fprintf(stderr, "ref_driver: %s -> %s\n", #x, cudaGetErrorString(e_)); return 100 + (int)e_; } } while (0)
+
+extern "C" unsigned long long ref_find_mth_root(unsigned long long M, unsigned long long q) {
+    return findMthRootOfUnity(M, q);
+}
+
+extern "C" void ref_fill_tables(unsigned long long psi, unsigned long long q, unsigned n,
+                                unsigned long long* psi_tab, unsigned long long* psiinv_tab,
+                                unsigned long long* psi_shoup, unsigned long long* psiinv_shoup) {
+    uint64_tt psiinv = modinv128(psi, q);
+    uint64_tt ninv = modinv128(n, q);
+    fillTablePsi128_special(psi, q, psiinv, psi_tab, psiinv_tab, n, ninv);
+    fillTablePsi_shoup128(psi_tab, q, psiinv_tab, psi_shoup, psiinv_shoup, n);
+}
+
+static Context_23* fake_context() {
+    // No constructor runs: only plain-integer and pointer members are used below.
+    return (Context_23*)calloc(1, sizeof(Context_23));
+}
+
+static int upload_pqt(const unsigned long long* pqt, int n_mod) {
+    std::vector<uint64_tt> m(pqt, pqt + n_mod), m2(n_mod), mh(n_mod), ml(n_mod);
+    for (int i = 0; i < n_mod; i++) {
+        m2[i] = m[i] * 2;
+        unsigned __int128 mu = (~(unsigned __int128)0) / m[i];
+        mh[i] = (uint64_tt)(mu >> 64);
+        ml[i] = (uint64_tt)mu;
+    }
+    RD_CUDA(cudaMemcpyToSymbol(pqt_cons, m.data(), 8 * n_mod));
+    RD_CUDA(cudaMemcpyToSymbol(pqt2_cons, m2.data(), 8 * n_mod));
+    RD_CUDA(cudaMemcpyToSymbol(pqt_mu_cons_high, mh.data(), 8 * n_mod));
+    RD_CUDA(cudaMemcpyToSymbol(pqt_mu_cons_low, ml.data(), 8 * n_mod));
+    return 0;
+}
+
+// Forward / inverse NTT of h_data [poly_num][poly_mod_len][N] with the reference kernels.
+extern "C" int ref_ntt(unsigned long long* h_data, int logN, const unsigned long long* pqt, int n_mod,
+                       int start_poly_idx, int start_mod_idx, int poly_num, int mod_num,
+                       int poly_mod_len, int inverse) {
+    if (n_mod > max_pqt_num) return 1;
+    const long N = 1L << logN;
+    int rc = upload_pqt(pqt, n_mod);
+    if (rc) return rc;
+    std::vector<uint64_tt> psi((size_t)n_mod * N), psiinv((size_t)n_mod * N), psis((size_t)n_mod * N),
+        psiinvs((size_t)n_mod * N), ninv(n_mod), ninvs(n_mod);
+    for (int i = 0; i < n_mod; i++) {
+        uint64_tt root = findMthRootOfUnity(2 * N, pqt[i]);
+        ref_fill_tables(root, pqt[i], (unsigned)N, (unsigned long long*)&psi[(size_t)i * N],
+                        (unsigned long long*)&psiinv[(size_t)i * N], (unsigned long long*)&psis[(size_t)i * N],
+                        (unsigned long long*)&psiinvs[(size_t)i * N]);
+        ninv[i] = modinv128(N, pqt[i]);
+        ninvs[i] = x_Shoup(ninv[i], pqt[i]);
+    }
+    Context_23* c = fake_context();
+    c->N = N;
+    c->logN = logN;
+    size_t tb = sizeof(uint64_tt) * n_mod * N;
+    RD_CUDA(cudaMalloc(&c->psi_table_device, tb));
+    RD_CUDA(cudaMalloc(&c->psiinv_table_device, tb));
+    RD_CUDA(cudaMalloc(&c->psi_shoup_table_device, tb));
+    RD_CUDA(cudaMalloc(&c->psiinv_shoup_table_device, tb));
+    RD_CUDA(cudaMalloc(&c->n_inv_device, 8 * n_mod));
+    RD_CUDA(cudaMalloc(&c->n_inv_shoup_device, 8 * n_mod));
+    RD_CUDA(cudaMemcpy(c->psi_table_device, psi.data(), tb, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(c->psiinv_table_device, psiinv.data(), tb, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(c->psi_shoup_table_device, psis.data(), tb, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(c->psiinv_shoup_table_device, psiinvs.data(), tb, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(c->n_inv_device, ninv.data(), 8 * n_mod, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(c->n_inv_shoup_device, ninvs.data(), 8 * n_mod, cudaMemcpyHostToDevice));
+    uint64_tt* d = nullptr;
+    size_t db = sizeof(uint64_tt) * (size_t)poly_num * poly_mod_len * N;
+    RD_CUDA(cudaMalloc(&d, db));
+    RD_CUDA(cudaMemcpy(d, h_data, db, cudaMemcpyHostToDevice));
+    if (inverse) c->FromNTTInplace(d, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len);
+    else c->ToNTTInplace(d, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len);
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    RD_CUDA(cudaMemcpy(h_data, d, db, cudaMemcpyDeviceToHost));
+    cudaFree(d);
+    cudaFree(c->psi_table_device); cudaFree(c->psiinv_table_device);
+    cudaFree(c->psi_shoup_table_device); cudaFree(c->psiinv_shoup_table_device);
+    cudaFree(c->n_inv_device); cudaFree(c->n_inv_shoup_device);
+    free(c);
+    return 0;
+}
+
+// modUpQjtoT_23 at level l.  Tables are for level l only, in the reference's layout:
+// hat_inv[blk*p_num+j], hat_mod_t[(blk*t_num+k)*p_num+j], blk_mod_t[blk*t_num+k].
+extern "C" int ref_modup(unsigned long long* h_out, const unsigned long long* h_in, int logN,
+                         const unsigned long long* pqt, int p_num, int q_num, int t_num, int l, int batch,
+                         const unsigned long long* hat_inv, const unsigned long long* hat_inv_shoup,
+                         const unsigned long long* hat_mod_t, const unsigned long long* blk_mod_t) {
+    const int n_mod = p_num + q_num + t_num;
+    if (n_mod > max_pqt_num || p_num > max_p_num || t_num > max_tnum) return 1;
+    const long N = 1L << logN;
+    int rc = upload_pqt(pqt, n_mod);
+    if (rc) return rc;
+    Context_23* c = fake_context();
+    c->N = N;
+    c->p_num = p_num; c->q_num = q_num; c->t_num = t_num;
+    c->gamma = 0;
+    c->Qj_blockNum = (q_num + p_num - 1) / p_num;
+    const int B = c->Qj_blockNum;
+    const int blocks = (l + 1 + p_num - 1) / p_num;
+    // the launcher offsets each table by l * (size of one level); allocate so that offset
+    // lands on the level passed in
+    size_t s_inv = (size_t)B * p_num, s_hat = (size_t)B * t_num * p_num, s_blk = (size_t)B * t_num;
+    RD_CUDA(cudaMalloc(&c->QjHatInvVecModQj_23_device, 8 * s_inv * (l + 1)));
+    RD_CUDA(cudaMalloc(&c->QjHatInvVecModQj_23_shoup_device, 8 * s_inv * (l + 1)));
+    RD_CUDA(cudaMalloc(&c->QjHatVecModT_23_device, 8 * s_hat * (l + 1)));
+    RD_CUDA(cudaMalloc(&c->Qjmodti_device, 8 * s_blk * (l + 1)));
+    RD_CUDA(cudaMemcpy(c->QjHatInvVecModQj_23_device + s_inv * l, hat_inv, 8 * (size_t)blocks * p_num, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(c->QjHatInvVecModQj_23_shoup_device + s_inv * l, hat_inv_shoup, 8 * (size_t)blocks * p_num, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(c->QjHatVecModT_23_device + s_hat * l, hat_mod_t, 8 * (size_t)blocks * t_num * p_num, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(c->Qjmodti_device + s_blk * l, blk_mod_t, 8 * (size_t)blocks * t_num, cudaMemcpyHostToDevice));
+    uint64_tt *din = nullptr, *dout = nullptr;
+    size_t ib = 8 * (size_t)batch * q_num * N, ob = 8 * (size_t)batch * blocks * t_num * N;
+    RD_CUDA(cudaMalloc(&din, ib));
+    RD_CUDA(cudaMalloc(&dout, ob));
+    RD_CUDA(cudaMemcpy(din, h_in, ib, cudaMemcpyHostToDevice));
+    c->modUpQjtoT_23(dout, din, l, batch);
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    RD_CUDA(cudaMemcpy(h_out, dout, ob, cudaMemcpyDeviceToHost));
+    cudaFree(din); cudaFree(dout);
+    cudaFree(c->QjHatInvVecModQj_23_device); cudaFree(c->QjHatInvVecModQj_23_shoup_device);
+    cudaFree(c->QjHatVecModT_23_device); cudaFree(c->Qjmodti_device);
+    free(c);
+    return 0;
+}
+
+// pcmm_cuda_core_kernel<mat_N> with the grid/block of PCMM_Scheme::PPMM.
+// h_X is [mat_N][limbs][C] contiguous, h_out [mat_M][limbs][C]; qinv[i] = q_last^-1 mod q_i.
+extern "C" int ref_ppmm(const float* h_W, const unsigned long long* h_X, unsigned long long* h_out, int mat_M,
+                        int mat_N, int N1, int mlwe_rank, int limbs, const unsigned long long* q, double scaler,
+                        const unsigned long long* qinv, const unsigned long long* qinv_shoup) {
+    if (limbs > 4 || mat_M % 32 || ((long)N1 * (mlwe_rank + 1)) % 32) return 1;
+    std::vector<uint64_tt> mh(limbs), ml(limbs), qq(q, q + limbs);
+    for (int i = 0; i < limbs; i++) {
+        unsigned __int128 mu = (~(unsigned __int128)0) / q[i];
+        mh[i] = (uint64_tt)(mu >> 64);
+        ml[i] = (uint64_tt)mu;
+    }
+    RD_CUDA(cudaMemcpyToSymbol(ringpack_pq_cons, qq.data(), 8 * limbs));
+    RD_CUDA(cudaMemcpyToSymbol(ringpack_pq_mu_high_cons, mh.data(), 8 * limbs));
+    RD_CUDA(cudaMemcpyToSymbol(ringpack_pq_mu_low_cons, ml.data(), 8 * limbs));
+    const size_t C = (size_t)N1 * (mlwe_rank + 1);
+    float* dW = nullptr;
+    uint64_tt *dX = nullptr, *dout = nullptr, *dinv = nullptr, *dinvs = nullptr;
+    uint64_tt** dptr = nullptr;
+    RD_CUDA(cudaMalloc(&dW, sizeof(float) * mat_M * mat_N));
+    RD_CUDA(cudaMalloc(&dX, 8 * C * limbs * mat_N));
+    RD_CUDA(cudaMalloc(&dout, 8 * C * limbs * mat_M));
+    RD_CUDA(cudaMalloc(&dinv, 8 * limbs));
+    RD_CUDA(cudaMalloc(&dinvs, 8 * limbs));
+    RD_CUDA(cudaMalloc(&dptr, sizeof(uint64_tt*) * mat_N));
+    std::vector<uint64_tt*> ptrs(mat_N);
+    for (int n = 0; n < mat_N; n++) ptrs[n] = dX + C * limbs * n;
+    RD_CUDA(cudaMemcpy(dW, h_W, sizeof(float) * mat_M * mat_N, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(dX, h_X, 8 * C * limbs * mat_N, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(dptr, ptrs.data(), sizeof(uint64_tt*) * mat_N, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(dinv, qinv, 8 * limbs, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(dinvs, qinv_shoup, 8 * limbs, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemset(dout, 0, 8 * C * limbs * mat_M));
+    dim3 ppmm_block(mat_M / TILE_WIDTH_M, N1 * (mlwe_rank + 1) / TILE_WIDTH_K);
+    dim3 ppmm_thread(32, (TILE_WIDTH_M * TILE_WIDTH_K) / (16 * 16));
+    int SMem_size = (TILE_WIDTH_M * TILE_WIDTH_N * (sizeof(int64_tt)) + TILE_WIDTH_N * TILE_WIDTH_K * sizeof(uint64_tt)) * 2;
+#define RD_LAUNCH(NN)                                                                                         \
+    cudaFuncSetAttribute(&pcmm_cuda_core_kernel<NN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMem_size); \
+    pcmm_cuda_core_kernel<NN><<<ppmm_block, ppmm_thread, SMem_size>>>(dW, dptr, dout, N1, mlwe_rank, limbs, 0, scaler, dinv, dinvs)
+    if (mat_N == 128) { RD_LAUNCH(128); }
+    else if (mat_N == 256) { RD_LAUNCH(256); }
+    else if (mat_N == 512) { RD_LAUNCH(512); }
+    else if (mat_N == 768) { RD_LAUNCH(768); }
+    else if (mat_N == 3072) { RD_LAUNCH(3072); }
+    else return 2;
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    RD_CUDA(cudaMemcpy(h_out, dout, 8 * C * limbs * mat_M, cudaMemcpyDeviceToHost));
+    cudaFree(dW); cudaFree(dX); cudaFree(dout); cudaFree(dinv); cudaFree(dinvs); cudaFree(dptr);
+    return 0;
+}

@@ -1,0 +1,199 @@
+"""GPU parity of PPMM (tensor-core and CUDA-core paths) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+from ckks_llm_b200 import capi, params
+from ckks_llm_b200.host import MLWECiphertext, PCMM_Context, PCMM_Scheme, as_u64_tensor, to_u64_numpy
+
+pytestmark = pytest.mark.gpu
+
+ALGOS = [capi.PCMM_SIMT, capi.PCMM_TENSOR]
+
+
+def _ciphers(rng, q, K, N1, rank, device):
+    Cw = (rank + 1) * N1
+    X = np.stack([H.uniform_residues(rng, q, (Cw,)) for _ in range(K)])     # [K][limbs][C]
+    cts = [MLWECiphertext(N1, len(q) - 1, len(q) - 1, rank, float(1 << 49),
+                          cipher=as_u64_tensor(X[n], device).reshape(-1)) for n in range(K)]
+    return X, cts
+
+
+def _run(oracle, algo, q, M, K, N1, rank, scaler, seed, wdist="uniform", rows=None):
+    pc = PCMM_Context(N1, rank, [], q)
+    sch = PCMM_Scheme(pc, algo=algo)
+    rng = np.random.default_rng(seed)
+    if wdist == "uniform":
+        W = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    else:
+        W = rng.normal(0, 0.02, (M, K)).astype(np.float32)
+    W[0, 0] = 0.0
+    X, cts = _ciphers(rng, q, K, N1, rank, pc.device)
+    Wd = torch.from_numpy(W).to(pc.device)
+    out = sch.PPMM(Wd, cts, M, K, N1, K, scaler=scaler, copy_back=False)
+    sch.check()
+    got = to_u64_numpy(out)
+    rows = range(M) if rows is None else rows
+    for m in rows:
+        exp = oracle.ppmm(W, X, q, scaler, m0=m, m1=m + 1)
+        assert np.array_equal(got[m], exp[m]), (m, algo)
+    pc.close()
+    return got
+
+
+@pytest.mark.parametrize("algo", ALGOS, ids=["simt", "tensor"])
+def test_config1_shape(oracle, cuda_device, algo):
+    """Configuration 1 shape: N1=64, rank 64, 64x64 weights at 2^30, three 36-bit limbs."""
+    _run(oracle, algo, H.cfg1_moduli(), 64, 64, 64, 64, float(1 << 30), seed=0)
+
+
+@pytest.mark.parametrize("algo", ALGOS, ids=["simt", "tensor"])
+def test_reference_native_two_limbs(oracle, cuda_device, algo):
+    """The reference's own setting: q_ringpack = {q0, q1} of its logN=16 chain, scaler = q1
+    (scale 2^49), weights uniform +-0.1 (test_rlwe_decomp.cu:36-37,83-86)."""
+    q = params.REF_LOGN16_Q[:2]
+    pc_scaler = float(q[1])
+    rng = np.random.default_rng(1)
+    M = K = 128
+    N1, rank = 128, 7
+    pc = PCMM_Context(N1, rank, [], q)
+    sch = PCMM_Scheme(pc, algo=algo)
+    W = rng.uniform(-0.1, 0.1, (M, K)).astype(np.float32)
+    X, cts = _ciphers(rng, q, K, N1, rank, pc.device)
+    assert sch.scaler_for(float(1 << 49)) == pc_scaler
+    out = sch.PPMM(torch.from_numpy(W).to(pc.device), cts, M, K, N1, K, copy_back=True)
+    sch.check()
+    got = to_u64_numpy(out)
+    exp = oracle.ppmm(W, X, q, pc_scaler)
+    assert np.array_equal(got, exp)
+    # copy-back: limb 0 of row i replaces ciphertext i (PPMM_kernel.cuh:345-348)
+    Cw = (rank + 1) * N1
+    for i in (0, 5, K - 1):
+        assert np.array_equal(to_u64_numpy(cts[i].cipher_device)[:Cw], exp[i, 0])
+    pc.close()
+
+
+@pytest.mark.parametrize("algo", ALGOS, ids=["simt", "tensor"])
+def test_ragged_shapes(oracle, cuda_device, algo):
+    """M and K that are not multiples of the tile sizes, four limbs."""
+    q = params.ntt_primes(50, 1 << 13, 4)
+    _run(oracle, algo, q, 40, 72, 32, 3, float(1 << 40), seed=2, wdist="normal")
+    _run(oracle, algo, q[:1], 130, 100, 64, 1, float(1 << 40), seed=3, wdist="normal")
+
+
+@pytest.mark.parametrize("algo", ALGOS, ids=["simt", "tensor"])
+def test_wide_moduli_and_weights(oracle, cuda_device, algo):
+    """60-bit limbs and 2^40-scaled weights exercise the widest plane configuration."""
+    q = params.ntt_primes(60, 1 << 13, 2)
+    _run(oracle, algo, q, 32, 64, 32, 1, float(1 << 40), seed=4)
+
+
+def test_bert_shape_sampled_rows(oracle, cuda_device):
+    """Configuration 4 geometry at reduced limb count: K=768, N1=128, rank 512 would need
+    8 GB per operand at 20 limbs; 2 limbs keep it to 0.8 GB.  Tensor path vs CUDA-core path
+    on every word, and vs the oracle on sampled rows."""
+    q = params.ntt_primes(50, 1 << 17, 2)
+    N1, rank, M, K = 128, 512, 768, 768
+    pc = PCMM_Context(N1, rank, [], q)
+    rng = np.random.default_rng(0)
+    W = rng.normal(0, 0.02, (M, K)).astype(np.float32)
+    Cw = (rank + 1) * N1
+    Xd = torch.empty((K, 2, Cw), dtype=torch.int64, device=pc.device)
+    g = torch.Generator(device=pc.device).manual_seed(0)
+    for i, qi in enumerate(q):
+        Xd[:, i, :] = torch.randint(0, qi, (K, Cw), generator=g, device=pc.device, dtype=torch.int64)
+    cts = [MLWECiphertext(N1, 1, 1, rank, 1.0, cipher=Xd[n].reshape(-1)) for n in range(K)]
+    Wd = torch.from_numpy(W).to(pc.device)
+    outs = {}
+    for algo in ALGOS:
+        sch = PCMM_Scheme(pc, algo=algo)
+        o = sch.PPMM(Wd, cts, M, K, N1, K, scaler=float(1 << 40), copy_back=False)
+        sch.check()
+        outs[algo] = o.clone()
+    assert torch.equal(outs[capi.PCMM_SIMT], outs[capi.PCMM_TENSOR])
+    X = to_u64_numpy(Xd)
+    got = to_u64_numpy(outs[capi.PCMM_TENSOR])
+    for m in (0, 383, 767):
+        exp = oracle.ppmm(W, X, q, float(1 << 40), m0=m, m1=m + 1)
+        assert np.array_equal(got[m], exp[m])
+    pc.close()
+
+
+def test_column_range(oracle, cuda_device):
+    """Only the requested column range is written (the unit multi-GPU sharding uses)."""
+    q = params.ntt_primes(50, 1 << 13, 2)
+    N1, rank, M, K = 64, 3, 64, 64
+    Cw = (rank + 1) * N1
+    rng = np.random.default_rng(9)
+    W = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    for algo in ALGOS:
+        pc = PCMM_Context(N1, rank, [], q)
+        sch = PCMM_Scheme(pc, algo=algo)
+        X, cts = _ciphers(np.random.default_rng(9), q, K, N1, rank, pc.device)
+        sch.ppmm_output = torch.full((M * 2 * Cw,), -1, dtype=torch.int64, device=pc.device)
+        out = sch.PPMM(torch.from_numpy(W).to(pc.device), cts, M, K, N1, K, scaler=float(1 << 30),
+                       col_begin=64, col_end=160, copy_back=False)
+        sch.check()
+        got = to_u64_numpy(out)
+        exp = oracle.ppmm(W, X, q, float(1 << 30))
+        assert np.array_equal(got[:, :, 64:160], exp[:, :, 64:160])
+        assert (got[:, :, :64] == np.uint64(2 ** 64 - 1)).all() and (got[:, :, 160:] == np.uint64(2 ** 64 - 1)).all()
+        pc.close()
+
+
+def test_shape_rules_and_errors(cuda_device, capsys):
+    q = params.ntt_primes(50, 1 << 13, 2)
+    pc = PCMM_Context(64, 3, [], q)
+    sch = PCMM_Scheme(pc)
+    cts = [MLWECiphertext(64, 1, 1, 3, 1.0) for _ in range(4)]
+    W = torch.zeros((4, 4), dtype=torch.float32, device=pc.device)
+    assert sch.PPMM(W, cts, 4, 4, 32, 4, scaler=1.0) is None          # mat_K != N1
+    assert "matrix K should be equal to N1!" in capsys.readouterr().out
+    assert sch.PPMM(W, cts, 4, 4, 64, 3, scaler=1.0) is None          # mat_N != mlwe_num
+    assert "matrix N should be equal to mlwe number!" in capsys.readouterr().out
+    Wbad = torch.full((4, 4), float("inf"), dtype=torch.float32, device=pc.device)
+    with pytest.raises(capi.CkksB200Error) as e:
+        sch.PPMM(Wbad, cts, 4, 4, 64, 4, scaler=1.0)
+    assert e.value.status == capi.ERR_RANGE
+    pc.close()
+
+
+def test_host_buffer_entry_point(oracle, cuda_device):
+    q = H.cfg1_moduli()
+    rng = np.random.default_rng(12)
+    N1, rank, M, K = 64, 1, 32, 32
+    W = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    X = np.stack([H.uniform_residues(rng, q, ((rank + 1) * N1,)) for _ in range(K)])
+    pc = PCMM_Context(N1, rank, [], q)
+    for algo in ALGOS:
+        got = PCMM_Scheme(pc, algo=algo).PPMM_host(W, X, M, K, N1, K, float(1 << 30))
+        assert np.array_equal(got, oracle.ppmm(W, X, q, float(1 << 30)))
+    pc.close()
+
+
+def test_config1_decrypt_through_gpu(oracle, cuda_device):
+    """Configuration 1 end to end with the GPU multiply in the middle: decrypted output
+    within 2^-20 of the fp64 matmul, residues bit-exact vs the oracle."""
+    N, N1, k = 1 << 12, 64, 64
+    moduli = H.cfg1_moduli()
+    rng = np.random.default_rng(0)
+    W = rng.uniform(-1, 1, (64, 64)).astype(np.float32)
+    Xf = rng.uniform(-1, 1, (64, 64))
+    delta = float(1 << 30)
+    msg = H.encode_coeffs(H.pack_message(Xf, k), delta, moduli)
+    s = H.sparse_ternary(rng, N, 192)
+    a, b = H.rlwe_encrypt(oracle, rng, msg, s, moduli)
+    X = oracle.rlwe_decompose(a, b, N1, k, 64, moduli).reshape(64, 3, (k + 1) * N1)
+    pc = PCMM_Context(N1, k, [], moduli)
+    out = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR).PPMM_host(W, X, 64, 64, N1, 64, delta)
+    assert np.array_equal(out, oracle.ppmm(W, X, moduli, delta))
+    s_mlwe = oracle.ring_down(s, N1, k)
+    expect = W.astype(np.float64) @ Xf
+    scale_out = delta * delta / moduli[-1]
+    worst = 0.0
+    for m in range(64):
+        dec = oracle.mlwe_decrypt(out[m, 0].reshape(k + 1, N1), s_mlwe, moduli[0])
+        worst = max(worst, np.abs(H.centered(dec, moduli[0]) / scale_out - expect[m]).max())
+    assert worst / np.abs(expect).max() < 2.0 ** -20
+    pc.close()

@@ -1,0 +1,95 @@
+"""Pins the oracle AND the library to the REAL reference kernels run on this GPU.
+
+oracle/_ref/libref_driver.so holds the reference's own NTT, ModUp and PPMM kernels,
+compiled for sm_100a from the reference sources (oracle/ref_driver.cu).  The tests are
+skipped when that library was not built."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+from ckks_llm_b200 import capi, params
+from ckks_llm_b200.host import Context_23, PCMM_Context, PCMM_Scheme, as_u64_tensor, to_u64_numpy
+from oracle import ref as R
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not R.available(), reason="reference driver library not built")]
+
+
+@pytest.mark.parametrize("logN", [14, 16])
+def test_reference_ntt_kernels(oracle, cuda_device, logN):
+    N = 1 << logN
+    if logN == 16:
+        pqt = params.REF_LOGN16_P[:1] + params.REF_LOGN16_Q[:3] + params.REF_LOGN16_T[:2]
+    else:
+        pqt = params.ntt_primes(50, 2 * N, 4) + params.ntt_primes(60, 2 * N, 2)
+    rng = np.random.default_rng(logN)
+    polys = 2
+    data = np.stack([H.uniform_residues(rng, pqt, (N,)) for _ in range(polys)])
+    ref_fwd = R.ntt(data, logN, pqt, 0, 0, polys, len(pqt), len(pqt))
+    T = oracle.NttTables(N, pqt)
+    orc = data.copy()
+    oracle.ntt_batch(orc, T, 0, 0, polys, len(pqt), len(pqt))
+    assert np.array_equal(orc, ref_fwd)                       # oracle == reference kernels
+    ctx = Context_23(logN, [], pqt, [])
+    d = as_u64_tensor(data, ctx.device)
+    ctx.ToNTTInplace(d, 0, 0, polys, len(pqt), len(pqt))
+    assert np.array_equal(to_u64_numpy(d), ref_fwd)           # library == reference kernels
+    ref_inv = R.ntt(data, logN, pqt, 0, 0, polys, len(pqt), len(pqt), inverse=True)
+    orc = data.copy()
+    oracle.ntt_batch(orc, T, 0, 0, polys, len(pqt), len(pqt), inverse=True)
+    assert np.array_equal(orc, ref_inv)
+    d = as_u64_tensor(data, ctx.device)
+    ctx.FromNTTInplace(d, 0, 0, polys, len(pqt), len(pqt))
+    assert np.array_equal(to_u64_numpy(d), ref_inv)
+    ctx.close()
+
+
+def test_reference_modup_kernel(oracle, cuda_device):
+    logN, N = 14, 1 << 14
+    p = params.ntt_primes(51, 2 * N, 4)
+    q = params.ntt_primes(50, 2 * N, 10)
+    t = params.ntt_primes(60, 2 * N, 6)
+    l, batch, alpha = 9, 2, 4
+    rng = np.random.default_rng(5)
+    inp = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(batch)])
+    blocks = (l + 1 + alpha - 1) // alpha
+    hat_inv = np.zeros(blocks * alpha, dtype=np.uint64)
+    hat_inv_s = np.zeros_like(hat_inv)
+    hat_mod_t = np.zeros(blocks * len(t) * alpha, dtype=np.uint64)
+    blk_mod_t = np.zeros(blocks * len(t), dtype=np.uint64)
+    qa, ta = np.array(q, dtype=np.uint64), np.array(t, dtype=np.uint64)
+    L = oracle.lib()
+    L.orc_modup_tables.argtypes = [np.ctypeslib.ndpointer(np.uint64), C.c_int, np.ctypeslib.ndpointer(np.uint64),
+                                   C.c_int, C.c_int, C.c_int] + [np.ctypeslib.ndpointer(np.uint64)] * 4
+    L.orc_modup_tables(qa, len(q), ta, len(t), alpha, l, hat_inv, hat_inv_s, hat_mod_t, blk_mod_t)
+    ref_out = R.modup(inp, logN, p, q, t, l, batch, (hat_inv, hat_inv_s, hat_mod_t, blk_mod_t))
+    assert np.array_equal(oracle.modup(inp, N, q, t, alpha, l, batch), ref_out)
+    ctx = Context_23(logN, p, q, t)
+    out = torch.empty(batch * blocks * len(t) * N, dtype=torch.int64, device=ctx.device)
+    ctx.modUpQjtoT_23(out, as_u64_tensor(inp, ctx.device), l, batch)
+    assert np.array_equal(to_u64_numpy(out).reshape(ref_out.shape), ref_out)
+    ctx.close()
+
+
+@pytest.mark.parametrize("limbs", [2, 3])
+def test_reference_ppmm_kernel(oracle, cuda_device, limbs):
+    """pcmm_cuda_core_kernel<128> of the reference at its native moduli {q0,q1(,q2)} and
+    scaler = q1, against the oracle and both library paths."""
+    q = params.REF_LOGN16_Q[:limbs]
+    N1, rank, M, K = 64, 7, 64, 128
+    rng = np.random.default_rng(limbs)
+    W = rng.uniform(-0.1, 0.1, (M, K)).astype(np.float32)
+    W[3, 3] = 0.0
+    X = np.stack([H.uniform_residues(rng, q, ((rank + 1) * N1,)) for _ in range(K)])
+    scaler = float(q[1])
+    qinv = [pow(q[-1], -1, qi) if i < limbs - 1 else 0 for i, qi in enumerate(q)]
+    qinv_s = [(v << 64) // qi for v, qi in zip(qinv, q)]
+    ref_out = R.ppmm(W, X, N1, rank, q, scaler, qinv, qinv_s)
+    assert np.array_equal(oracle.ppmm(W, X, q, scaler), ref_out)
+    pc = PCMM_Context(N1, rank, [], q)
+    for algo in (capi.PCMM_SIMT, capi.PCMM_TENSOR):
+        got = PCMM_Scheme(pc, algo=algo).PPMM_host(W, X, M, K, N1, K, scaler)
+        assert np.array_equal(got, ref_out), algo
+    pc.close()
