@@ -1,0 +1,412 @@
+"""Benchmark of the hot path on B200: PCMM ct-rows/s (headline) with NTT / INTT
+limb-transforms/s and ModUp polynomials/s measured in the same run.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload pcmm|ntt|modup]
+                    [--impl b200|reference]
+
+A step is one pass of the named kernel family over one batch of seeded synthetic input
+resident in HBM.  Default workload: the BERT-base-shaped PCMM (768x768 weights ~N(0,0.02)
+at scale 2^40, 768 feature ciphertexts, N=2^16, N1=128, rank 512, 20 limbs of 50-bit
+primes, ciphertext words uniform in [0,q_i)).  With N>1 ranks (torchrun) every rank
+multiplies its own block of 128 tokens: no data-path collective, weak scaling.
+Prints one JSON line (rank 0).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+PCMM_CFG = dict(logN=16, N1=128, rank=512, M=768, K=768, limbs=20, q_bits=50, w_std=0.02, scaler=float(1 << 40))
+NTT_CFG = dict(logN=16, limbs=40, q_bits=50, polys=32)
+MODUP_CFG = dict(logN=16, q_num=24, q_bits=50, t_num=12, t_bits=60, alpha=8, batch=32)
+SW, SC = 5, 7          # byte planes the PCMM workload needs: 40-bit signed weights, 50-bit residues
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, smax, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def pcmm_inputs(torch, device, seed):
+    from ckks_llm_b200 import params
+    c = PCMM_CFG
+    q = params.ntt_primes(c["q_bits"], 2 << c["logN"], c["limbs"])
+    Cw = (c["rank"] + 1) * c["N1"]
+    g = torch.Generator(device=device).manual_seed(seed)
+    X = torch.empty((c["K"], c["limbs"], Cw), dtype=torch.int64, device=device)
+    for i, qi in enumerate(q):
+        X[:, i, :] = torch.randint(0, qi, (c["K"], Cw), generator=g, device=device, dtype=torch.int64)
+    W = (torch.randn((c["M"], c["K"]), generator=g, device=device, dtype=torch.float32) * c["w_std"])
+    return q, X, W, Cw
+
+
+def cpu_pcmm_sample(q, X, W, Cw, rows=16, cols=4096):
+    """Oracle PPMM on `rows` output rows x `cols` columns x all limbs of the same workload."""
+    from oracle import oracle as O
+    c = PCMM_CFG
+    Xs = np.ascontiguousarray(X[:, :, :cols].cpu().numpy().view(np.uint64))
+    Wh = W.cpu().numpy()
+    t0 = time.perf_counter()
+    O.ppmm(Wh, Xs, q, c["scaler"], m0=0, m1=rows)
+    dt = time.perf_counter() - t0
+    frac_rows = rows * (cols / Cw)           # ct-rows worth of work
+    return frac_rows / dt, dt, O.num_threads(), f"{rows} rows x {cols} of {Cw} columns x {c['limbs']} limbs, K={c['K']}"
+
+
+def run_reference(args):
+    """The reference has no CPU implementation of this path and its CUDA build needs NTL;
+    the CPU restatement (oracle/) is timed instead, on all host threads, on a bounded
+    sample of the same workload per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from ckks_llm_b200 import params
+    from oracle import oracle as O
+    c = PCMM_CFG
+    if args.workload == "pcmm":
+        q = params.ntt_primes(c["q_bits"], 2 << c["logN"], c["limbs"])
+        Cw = (c["rank"] + 1) * c["N1"]
+        rows, cols = 16, 4096
+        rng = np.random.default_rng(0)
+        Xs = np.stack([np.stack([rng.integers(0, qi, cols, dtype=np.uint64) for qi in q]) for _ in range(c["K"])])
+        Wh = (rng.standard_normal((c["M"], c["K"])) * c["w_std"]).astype(np.float32)
+        times = []
+        for it in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            O.ppmm(Wh, Xs, q, c["scaler"], m0=0, m1=rows)
+            if it >= args.warmup:
+                times.append(time.perf_counter() - t0)
+        dt = float(np.mean(times))
+        value = rows * (cols / Cw) / dt
+        metric, unit = "pcmm_ct_rows_per_sec", "ct-rows/s"
+        sample = f"{rows} rows x {cols} of {Cw} columns x {c['limbs']} limbs, K={c['K']} per step"
+        workload = "bert-base 768x768 PCMM, N=2^16, N1=128, 20x50-bit limbs"
+    else:
+        n = NTT_CFG
+        N = 1 << n["logN"]
+        q = params.ntt_primes(n["q_bits"], 2 * N, n["limbs"])
+        T = O.NttTables(N, q)
+        rng = np.random.default_rng(0)
+        polys = 2
+        data = np.stack([np.stack([rng.integers(0, qi, N, dtype=np.uint64) for qi in q]) for _ in range(polys)])
+        times = []
+        for it in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            O.ntt_batch(data, T, 0, 0, polys, n["limbs"], n["limbs"], inverse=(it % 2 == 1))
+            if it >= args.warmup:
+                times.append(time.perf_counter() - t0)
+        dt = float(np.mean(times))
+        value = polys * n["limbs"] / dt
+        metric, unit = "ntt_limb_xforms_per_sec", "limb-xforms/s"
+        sample = f"{polys} polys x {n['limbs']} limbs per step"
+        workload = "batched NTT N=2^16, 40x50-bit limbs"
+    line = {
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+        "config": {"workload": workload},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": O.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference CUDA build needs NTL (absent) and the reference has no CPU path; the CPU restatement is timed",
+    }
+    print(json.dumps(line))
+
+
+def bench_ntt(torch, device, steps, warmup, peaks):
+    from ckks_llm_b200 import params
+    from ckks_llm_b200.host import Context_23
+    n = NTT_CFG
+    N = 1 << n["logN"]
+    q = params.ntt_primes(n["q_bits"], 2 * N, n["limbs"])
+    ctx = Context_23(n["logN"], [], q, [], device=device.index)
+    g = torch.Generator(device=device).manual_seed(1)
+    data = torch.empty((n["polys"], n["limbs"], N), dtype=torch.int64, device=device)
+    for i, qi in enumerate(q):
+        data[:, i, :] = torch.randint(0, qi, (n["polys"], N), generator=g, device=device, dtype=torch.int64)
+    xforms = n["polys"] * n["limbs"]
+    res = {}
+    for name, fn in (("forward", ctx.ToNTTInplace), ("inverse", ctx.FromNTTInplace)):
+        for _ in range(warmup):
+            fn(data, 0, 0, n["polys"], n["limbs"], n["limbs"])
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn(data, 0, 0, n["polys"], n["limbs"], n["limbs"])
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms = e0.elapsed_time(e1) / steps
+        gbs = xforms * 16 * N / (ms * 1e-3) / 1e9
+        res[name] = {"limb_xforms_per_sec": xforms / (ms * 1e-3), "ms_per_step": ms,
+                     "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                  "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                                  "note": "two kernels per transform; achieved = 16*N bytes per limb-xform / time"}}
+    ctx.close()
+    res["config"] = {"workload": "batched NTT N=2^16, 40x50-bit limbs, 16 ciphertexts x 2 polys",
+                     "bytes_resident": int(data.numel() * 8), "l2_policy": "inputs (671 MB) larger than L2"}
+    return res
+
+
+def bench_modup(torch, device, steps, warmup, peaks):
+    from ckks_llm_b200 import params
+    from ckks_llm_b200.host import Context_23
+    m = MODUP_CFG
+    N = 1 << m["logN"]
+    p = params.ntt_primes(m["q_bits"] + 1, 2 * N, m["alpha"])
+    q = params.ntt_primes(m["q_bits"], 2 * N, m["q_num"])
+    t = params.ntt_primes(m["t_bits"], 2 * N, m["t_num"])
+    ctx = Context_23(m["logN"], p, q, t, device=device.index)
+    g = torch.Generator(device=device).manual_seed(2)
+    inp = torch.empty((m["batch"], m["q_num"], N), dtype=torch.int64, device=device)
+    for i, qi in enumerate(q):
+        inp[:, i, :] = torch.randint(0, qi, (m["batch"], N), generator=g, device=device, dtype=torch.int64)
+    blocks = m["q_num"] // m["alpha"]
+    out = torch.empty((m["batch"], blocks, m["t_num"], N), dtype=torch.int64, device=device)
+    for _ in range(warmup):
+        ctx.modUpQjtoT_23(out, inp, m["q_num"] - 1, m["batch"])
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        ctx.modUpQjtoT_23(out, inp, m["q_num"] - 1, m["batch"])
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1) / steps
+    bytes_per_poly = (m["q_num"] + blocks * m["t_num"]) * 8 * N
+    gbs = m["batch"] * bytes_per_poly / (ms * 1e-3) / 1e9
+    ctx.close()
+    return {"polys_per_sec": m["batch"] / (ms * 1e-3), "ms_per_step": ms,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None},
+            "config": {"workload": "ModUp N=2^16, 24x50-bit Q limbs in 3 digits -> 12x60-bit T limbs, batch 32",
+                       "l2_policy": "input+output (1 GB) larger than L2"}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", choices=["pcmm", "ntt", "modup"], default="pcmm")
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from ckks_llm_b200 import capi
+    from ckks_llm_b200.host import MLWECiphertext, PCMM_Context, PCMM_Scheme
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU path")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    capi.load()
+    peaks = measured_peaks()
+    launches0 = capi.load().ckks_b200_kernel_launches()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    c = PCMM_CFG
+    extra = {}
+    if args.workload == "pcmm":
+        q, X, W, Cw = pcmm_inputs(torch, device, seed=rank)
+        pc = PCMM_Context(c["N1"], c["rank"], [], q, device=local_rank)
+        sch = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR)
+        cts = [MLWECiphertext(c["N1"], c["limbs"] - 1, c["limbs"] - 1, c["rank"], 1.0, cipher=X[n].reshape(-1))
+               for n in range(c["K"])]
+
+        def step():
+            return sch.PPMM(W, cts, c["M"], c["K"], c["N1"], c["K"], scaler=c["scaler"], copy_back=False)
+
+        for _ in range(args.warmup):
+            step()
+        sch.check()
+        sampler = ClockSampler(local_rank)
+        barrier()
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        main_ms, pre_ms = [], []
+        l_before = capi.load().ckks_b200_kernel_launches()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+            p_ms, m_ms = sch.last_timing()
+            pre_ms.append(p_ms)
+            main_ms.append(m_ms)
+        e1.record()
+        l_after = capi.load().ckks_b200_kernel_launches()
+        barrier()
+        clocks = sampler.stop() if rank == 0 else None
+        sch.check()
+        ms = e0.elapsed_time(e1) / args.steps
+        if world > 1:
+            tt = torch.tensor([ms], device=device)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        launches_timed = int(l_after - l_before)
+        value = world * c["M"] / (ms * 1e-3)
+        macs = c["M"] * c["K"] * Cw * c["limbs"]
+        int8_ops = 2.0 * SW * SC * macs
+        main = float(np.mean(main_ms))
+        achieved = int8_ops / (main * 1e-3) / 1e12
+        peak = 2.0 * peaks["bf16_tflops"]
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s (int8)", "frac": achieved / peak,
+                "traffic": None, "kernel": "pcmm_umma_kernel<5,7>", "kernel_ms": main, "prepass_ms": float(np.mean(pre_ms)),
+                "peak_source": f"2 x bf16 dense {peaks['bf16_tflops']} TFLOP/s ({peaks['source']}); int8 dense is nominally 2x bf16",
+                "algorithmic_ops": "2*5*7 int8 ops per modular MAC x M*K*(N+N1)*limbs"}
+        metric, unit = "pcmm_ct_rows_per_sec", "ct-rows/s"
+        workload = ("bert-base PCMM 768x768 (W~N(0,0.02) at 2^40), 768 ciphertexts x 20 limbs x 65664 words, "
+                    "N=2^16, N1=128, rank 512, 50-bit limbs")
+        cfg = {"workload": workload, "tokens_per_gpu": c["N1"], "sharding": "one 128-token block per GPU, no collective",
+               "l2_policy": "inputs (8.07 GB ciphertext + 8.07 GB output) larger than L2"}
+
+        e2e = None
+        if rank == 0 and not args.no_e2e and world == 1:
+            # same call through the C ABI with HOST buffers: H2D of W and X and D2H of the result per step
+            Xh = torch.empty(X.shape, dtype=torch.int64).pin_memory()
+            Xh.copy_(X)
+            Wh = W.cpu().pin_memory()
+            outh = torch.empty((c["M"], c["limbs"], Cw), dtype=torch.int64).pin_memory()
+            del cts, X
+            sch.ppmm_output = None
+            torch.cuda.empty_cache()
+            L = capi.load()
+
+            def host_step():
+                capi.check(L.ckks_b200_pcmm_ppmm_host(pc._h, Wh.data_ptr(), Xh.data_ptr(), outh.data_ptr(), c["M"], c["K"],
+                                                      c["N1"], c["K"], c["scaler"], capi.PCMM_TENSOR))
+            host_step()
+            n_e2e = max(1, min(args.steps, 3))
+            t0 = time.perf_counter()
+            for _ in range(n_e2e):
+                host_step()
+            dt = (time.perf_counter() - t0) / n_e2e
+            e2e = {"value": c["M"] / dt, "unit": unit, "h2d_bytes_per_step": int(Xh.numel() * 8 + Wh.numel() * 4),
+                   "d2h_bytes_per_step": int(outh.numel() * 8), "ms_per_step": dt * 1e3, "steps": n_e2e,
+                   "call": "ckks_b200_pcmm_ppmm_host (pinned host buffers)"}
+            cpu = None
+            if not args.no_cpu:
+                Xd = Xh[:, :, :4096].contiguous()
+                v, dt_cpu, cores, sample = cpu_pcmm_sample(q, Xd, Wh, Cw)
+                cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample, "seconds": dt_cpu}
+        else:
+            cpu = None
+        pc.close()
+        if rank == 0 and world == 1:
+            try:
+                extra["ntt"] = bench_ntt(torch, device, max(args.steps, 10), args.warmup, peaks)
+                extra["modup"] = bench_modup(torch, device, max(args.steps, 10), args.warmup, peaks)
+            except Exception as ex:           # the headline stays valid without the side measurements
+                extra["side_error"] = repr(ex)
+    else:
+        sampler = ClockSampler(local_rank)
+        barrier()
+        if rank == 0:
+            sampler.start()
+        if args.workload == "ntt":
+            r = bench_ntt(torch, device, args.steps, args.warmup, peaks)
+            ms = r["forward"]["ms_per_step"]
+            value = world * r["forward"]["limb_xforms_per_sec"]
+            roof = r["forward"]["roofline"]
+            extra["ntt"] = r
+            metric, unit, cfg = "ntt_limb_xforms_per_sec", "limb-xforms/s", r["config"]
+        else:
+            r = bench_modup(torch, device, args.steps, args.warmup, peaks)
+            ms = r["ms_per_step"]
+            value = world * r["polys_per_sec"]
+            roof = r["roofline"]
+            metric, unit, cfg = "modup_polys_per_sec", "polys/s", r["config"]
+        barrier()
+        clocks = sampler.stop() if rank == 0 else None
+        launches_timed = None
+        e2e, cpu = None, None
+
+    if rank == 0:
+        line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "u64 (int8 planes on tensor cores, s32 accumulate)" if args.workload == "pcmm" else "u64",
+                "data": "synthetic", "config": cfg, "roofline": roof, "clocks": clocks,
+                "gpu_launches": launches_timed if launches_timed is not None else int(capi.load().ckks_b200_kernel_launches() - launches0),
+                "e2e": e2e, "cpu_baseline": cpu}
+        line.update(extra)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

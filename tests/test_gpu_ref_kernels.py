@@ -64,7 +64,12 @@ def test_reference_modup_kernel(oracle, cuda_device):
     L.orc_modup_tables.argtypes = [np.ctypeslib.ndpointer(np.uint64), C.c_int, np.ctypeslib.ndpointer(np.uint64),
                                    C.c_int, C.c_int, C.c_int] + [np.ctypeslib.ndpointer(np.uint64)] * 4
     L.orc_modup_tables(qa, len(q), ta, len(t), alpha, l, hat_inv, hat_inv_s, hat_mod_t, blk_mod_t)
-    ref_out = R.modup(inp, logN, p, q, t, l, batch, (hat_inv, hat_inv_s, hat_mod_t, blk_mod_t))
+    # The reference only ever converts one polynomial per call (batch_size 1 at every call
+    # site); for a batch index b > 0 its kernel indexes the Qblk-mod-t table with an extra
+    # offset of b*Qj_blockNum*t_num (BasisConv.cuh:142,153) and so reads another level's row.
+    # Each polynomial is therefore pinned as a batch of one.
+    ref_out = np.concatenate([R.modup(inp[b:b + 1], logN, p, q, t, l, 1, (hat_inv, hat_inv_s, hat_mod_t, blk_mod_t))
+                              for b in range(batch)])
     assert np.array_equal(oracle.modup(inp, N, q, t, alpha, l, batch), ref_out)
     ctx = Context_23(logN, p, q, t)
     out = torch.empty(batch * blocks * len(t) * N, dtype=torch.int64, device=ctx.device)
