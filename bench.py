@@ -98,7 +98,7 @@ def pcmm_inputs(torch, device, seed):
     return q, X, W, Cw
 
 
-def cpu_pcmm_sample(q, X, W, Cw, rows=16, cols=4096):
+def cpu_pcmm_sample(q, X, W, Cw, rows=128, cols=16384):
     """Oracle PPMM on `rows` output rows x `cols` columns x all limbs of the same workload."""
     from oracle import oracle as O
     c = PCMM_CFG
@@ -124,7 +124,7 @@ def run_reference(args):
     if args.workload == "pcmm":
         q = params.ntt_primes(c["q_bits"], 2 << c["logN"], c["limbs"])
         Cw = (c["rank"] + 1) * c["N1"]
-        rows, cols = 16, 4096
+        rows, cols = 128, 16384
         rng = np.random.default_rng(0)
         Xs = np.stack([np.stack([rng.integers(0, qi, cols, dtype=np.uint64) for qi in q]) for _ in range(c["K"])])
         Wh = (rng.standard_normal((c["M"], c["K"])) * c["w_std"]).astype(np.float32)
@@ -249,8 +249,15 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-side", action="store_true", help="skip the NTT / ModUp side measurements")
+    ap.add_argument("--small", action="store_true",
+                    help="profiling-sized case: PCMM with 2 limbs, NTT with 8 polys, ModUp batch 8 (not a bench value)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.small:
+        PCMM_CFG["limbs"] = 2
+        NTT_CFG["polys"] = 8
+        MODUP_CFG["batch"] = 8
 
     if args.impl == "reference":
         run_reference(args)
@@ -360,13 +367,13 @@ def main():
                    "call": "ckks_b200_pcmm_ppmm_host (pinned host buffers)"}
             cpu = None
             if not args.no_cpu:
-                Xd = Xh[:, :, :4096].contiguous()
+                Xd = Xh[:, :, :16384].contiguous()
                 v, dt_cpu, cores, sample = cpu_pcmm_sample(q, Xd, Wh, Cw)
                 cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample, "seconds": dt_cpu}
         else:
             cpu = None
         pc.close()
-        if rank == 0 and world == 1:
+        if rank == 0 and world == 1 and not args.no_side:
             try:
                 extra["ntt"] = bench_ntt(torch, device, max(args.steps, 10), args.warmup, peaks)
                 extra["modup"] = bench_modup(torch, device, max(args.steps, 10), args.warmup, peaks)
@@ -399,7 +406,7 @@ def main():
         line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "u64 (int8 planes on tensor cores, s32 accumulate)" if args.workload == "pcmm" else "u64",
-                "data": "synthetic", "config": cfg, "roofline": roof, "clocks": clocks,
+                "data": "synthetic", "config": dict(cfg, small=True) if args.small else cfg, "roofline": roof, "clocks": clocks,
                 "gpu_launches": launches_timed if launches_timed is not None else int(capi.load().ckks_b200_kernel_launches() - launches0),
                 "e2e": e2e, "cpu_baseline": cpu}
         line.update(extra)
