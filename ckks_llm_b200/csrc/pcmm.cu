@@ -110,12 +110,12 @@ int prepare(ckks_b200_pcmm* pc, const float* d_W, const u64* const* h_X_ptrs, in
     rc = ensure_dev(&pc->d_xptrs, &pc->xptrs_cap, (size_t)K);
     if (rc) return rc;
     CKB_CUDA(cudaMemcpyAsync((void*)pc->d_xptrs, h_X_ptrs, sizeof(u64*) * K, cudaMemcpyHostToDevice, st));
-    CKB_CUDA(cudaMemsetAsync(pc->d_flags, 0, 8 * sizeof(int), st));
+    CKB_CUDA(cudaMemsetAsync(pc->d_flags, 0, 16 * sizeof(int), st));
     size_t count = (size_t)M * K;
     scale_weights_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(d_W, pc->d_w, count, scaler, pc->d_flags);
     count_launch();
     CKB_CUDA(cudaGetLastError());
-    CKB_CUDA(cudaMemcpyAsync(pc->h_flags, pc->d_flags, 8 * sizeof(int), cudaMemcpyDeviceToHost, st));
+    CKB_CUDA(cudaMemcpyAsync(pc->h_flags, pc->d_flags, 16 * sizeof(int), cudaMemcpyDeviceToHost, st));
     CKB_CUDA(cudaStreamSynchronize(st));
     CKB_REQUIRE(pc->h_flags[2] == 0, CKKS_B200_ERR_RANGE,
                 "a scaled weight is not finite or exceeds 2^62 in magnitude");
@@ -174,8 +174,8 @@ extern "C" int ckks_b200_pcmm_create(ckks_b200_pcmm** out, int device, int N1, i
     pc->q.assign(q_ringpack, q_ringpack + q_count);
     cudaError_t e = cudaMalloc(&pc->d_limbs, sizeof(PcmmLimb) * q_count);
     if (e == cudaSuccess) e = cudaMemcpy(pc->d_limbs, L.data(), sizeof(PcmmLimb) * q_count, cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMalloc(&pc->d_flags, 8 * sizeof(int));
-    if (e == cudaSuccess) e = cudaMallocHost(&pc->h_flags, 8 * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&pc->d_flags, 16 * sizeof(int));
+    if (e == cudaSuccess) e = cudaMallocHost(&pc->h_flags, 16 * sizeof(int));
     for (int i = 0; i < 3 && e == cudaSuccess; i++) e = cudaEventCreate(&pc->ev[i]);
     if (e != cudaSuccess) {
         set_error("allocating the PCMM handle failed: %s", cudaGetErrorString(e));

@@ -32,12 +32,20 @@ namespace {
 
 constexpr int TM = 128;            // rows of W per tile (UMMA M)
 constexpr int TC = 32;             // ciphertext columns per tile
-constexpr int KB = 64;             // contraction depth per pipeline stage
+#ifndef CKB_KB
+#define CKB_KB 64
+#endif
+constexpr int KB = CKB_KB;         // contraction depth per pipeline stage
 constexpr int KS = KB / 32;        // UMMA K steps per stage
 constexpr int A_PLANE_STEP = TM * 32;   // bytes of one weight plane, one K step
 constexpr int B_PLANE_STEP = TC * 32;   // bytes of one ciphertext plane, one K step
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = 32 * (2 + NUM_EPI_WARPS);
+// Per-warp staging tile of the epilogue: 32 rows x 16 words, rows padded to 144 bytes so
+// that both the row-per-lane writes and the row-contiguous reads are bank-conflict free.
+constexpr int STG_ROW = 144;
+constexpr int STG_WARP = 32 * STG_ROW;
+constexpr int STG_BYTES = NUM_EPI_WARPS * STG_WARP;
 constexpr long long WAIT_BUDGET = 4000000000ll;   // clock cycles, about two seconds
 
 // ---------------------------------------------------------------------------
@@ -66,6 +74,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+#ifdef CKB_PROFILE
+#define CKB_PROF_DECL long long prof_t0_ = 0, prof_acc_[4] = {0, 0, 0, 0};
+#define CKB_PROF_BEGIN() prof_t0_ = clock64()
+#define CKB_PROF_END(i) prof_acc_[i] += clock64() - prof_t0_
+#define CKB_PROF_FLUSH(base) if (blockIdx.x == 0) { for (int i_ = 0; i_ < 4; i_++) P.flags[(base) + i_] = (int)(prof_acc_[i_] >> 10); }
+#else
+#define CKB_PROF_DECL
+#define CKB_PROF_BEGIN()
+#define CKB_PROF_END(i)
+#define CKB_PROF_FLUSH(base)
+#endif
+
 // Bounded wait.  Returns false when the budget ran out (the flag is raised).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* flags, int where) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -146,7 +166,8 @@ struct Cfg {
     static constexpr int B_STAGE = SC * KS * B_PLANE_STEP;
     static constexpr int STAGE = A_STAGE + B_STAGE;
     static constexpr int TMEM_COLS = ND * TC <= 128 ? 128 : ND * TC <= 256 ? 256 : 512;
-    static constexpr int MAX_STAGES = (220 * 1024) / STAGE < 8 ? (220 * 1024) / STAGE : 8;
+    static constexpr int SMEM_BUDGET = 227 * 1024 - 2048 - STG_BYTES;
+    static constexpr int MAX_STAGES = SMEM_BUDGET / STAGE < 8 ? SMEM_BUDGET / STAGE : 8;
 };
 
 // ---------------------------------------------------------------------------
@@ -295,6 +316,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
         if (lane == 0) {
             uint32_t it = 0, tile = 0;
             bool ok = true;
+            CKB_PROF_DECL
+            const long long prof_start = clock64();
+            (void)prof_start;
             constexpr uint32_t idesc_full_u = instr_desc(TC * SC, false);
             constexpr uint32_t idesc_full_s = instr_desc(TC * SC, true);
             constexpr uint32_t idesc_head_u = instr_desc(TC * (SC - 1), false);
@@ -303,11 +327,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
             constexpr uint32_t idesc_tail_s = instr_desc(TC, true);
             for (long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 for (int limb = limbs_n - 1; limb >= 0 && ok; limb--, tile++) {
+                    CKB_PROF_BEGIN();
                     if (tile > 0 && !mbar_wait(tmem_empty_bar, (tile - 1) & 1, P.flags, 3)) { ok = false; break; }
+                    CKB_PROF_END(0);
                     tc_fence_after();
                     for (int kb = 0; kb < P.KBN; kb++, it++) {
                         const int s = it % NS;
+                        CKB_PROF_BEGIN();
                         if (!mbar_wait(full_bar + 8 * s, (it / NS) & 1, P.flags, 4)) { ok = false; break; }
+                        CKB_PROF_END(1);
                         if (*(volatile int*)&abort_flag) { ok = false; break; }
                         tc_fence_after();
                         const uint32_t a_base = smem_base + s * C_::STAGE;
@@ -340,23 +368,33 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                 }
             }
             if (!ok) atomicExch(&abort_flag, 1);
+#ifdef CKB_PROFILE
+            prof_acc_[2] = clock64() - prof_start;
+            prof_acc_[3] = tile;
+            if (blockIdx.x == 0) { P.flags[8] = (int)(prof_acc_[0] >> 10); P.flags[9] = (int)(prof_acc_[1] >> 10); P.flags[10] = (int)(prof_acc_[2] >> 10); P.flags[11] = (int)tile; }
+#endif
         }
     } else {
         // ---------------- epilogue ----------------
         const int ew = warp - 2;
         const int quarter = warp & 3;          // TMEM lanes this warp may read
         const int half = ew >> 2;              // which 16 of the 32 columns
-        const int row = quarter * 32 + lane;
+        uint8_t* stg = smem + (size_t)NS * C_::STAGE + (size_t)ew * STG_WARP;
+        u64 last[16];
+        const bool vec_ok = (P.C & 1) == 0 && (reinterpret_cast<uintptr_t>(P.out) & 15) == 0;   // 16-byte stores stay aligned
         uint32_t tile = 0;
         bool ok = true;
+        CKB_PROF_DECL
         for (long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
             const int mt = (int)(item % P.MT);
             const long ct = item / P.MT;
-            const int m = mt * TM + row;
             const long c0 = P.col_begin + ct * TC + half * 16;
             for (int limb = limbs_n - 1; limb >= 0 && ok; limb--, tile++) {
+                CKB_PROF_BEGIN();
                 if (!mbar_wait(tmem_full_bar, tile & 1, P.flags, 5)) { ok = false; break; }
+                CKB_PROF_END(0);
                 tc_fence_after();
+                CKB_PROF_BEGIN();
                 unsigned __int128 acc[16];
 #pragma unroll
                 for (int g = 0; g < 2; g++) {
@@ -367,36 +405,75 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                     tmem_ld_wait();
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
-                        unsigned __int128 s = 0;
+                        // sum_d v_d * 2^(8d): groups of four diagonals fit a signed 64-bit word
+                        // (|v_d| < 2^31, top shift 24), and the groups sit 32 bits apart
+                        long long grp[(C_::ND + 3) / 4];
 #pragma unroll
-                        for (int d = 0; d < C_::ND; d++)
-                            s += (unsigned __int128)(__int128)v[d][e] << (8 * d);
-                        acc[g * 8 + e] = s;
+                        for (int gi = 0; gi < (C_::ND + 3) / 4; gi++) {
+                            long long t = 0;
+#pragma unroll
+                            for (int k = 3; k >= 0; k--)
+                                if (gi * 4 + k < C_::ND) t = t * 256 + (long long)v[gi * 4 + k][e];
+                            grp[gi] = t;
+                        }
+                        __int128 s = 0;
+#pragma unroll
+                        for (int gi = (C_::ND + 3) / 4 - 1; gi >= 0; gi--) s = s * ((__int128)1 << 32) + grp[gi];
+                        acc[g * 8 + e] = (unsigned __int128)s;
                     }
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tmem_empty_bar);
+                CKB_PROF_END(1);
+                CKB_PROF_BEGIN();
 
                 const PcmmLimb L = P.limbs[limb];
                 const unsigned __int128 off = ((unsigned __int128)L.off_hi << 64) | L.off_lo;
-                u64* orow = P.out + ((size_t)m * limbs_n + limb) * P.C;
-                const u64* lrow = P.out + ((size_t)m * limbs_n + (limbs_n - 1)) * P.C;
+                u64 res[16];
 #pragma unroll
                 for (int e = 0; e < 16; e++) {
-                    const long c = c0 + e;
                     unsigned __int128 t = acc[e] + off;
-                    u64 res = barrett128((u64)t, (u64)(t >> 64), L.q, L.mu_hi, L.mu_lo);
-                    if (m < P.M && c < P.col_end) {
-                        if (limb != limbs_n - 1) {
-                            u64 tmp = res + L.q - lrow[c];
-                            res = shoup_mul(tmp, L.inv, L.inv_shoup, L.q);
+                    u64 r = barrett128((u64)t, (u64)(t >> 64), L.q, L.mu_hi, L.mu_lo);
+                    if (limb == limbs_n - 1) {
+                        last[e] = r;                              // kept in registers for the other limbs
+                    } else {
+                        u64 tmp = r + L.q - last[e];              // wraps mod 2^64 like the reference
+                        r = shoup_mul(tmp, L.inv, L.inv_shoup, L.q);
+                    }
+                    res[e] = r;
+                }
+                // Transpose through the warp's staging tile so that every store instruction
+                // writes whole 128-byte lines: lane = row while writing the tile, lanes run
+                // along a row while reading it back.
+                __syncwarp();
+#pragma unroll
+                for (int e = 0; e < 8; e++)
+                    *reinterpret_cast<ulonglong2*>(stg + lane * STG_ROW + e * 16) = make_ulonglong2(res[2 * e], res[2 * e + 1]);
+                __syncwarp();
+                const int sub_r = lane >> 3, pair = lane & 7;
+                const long c = c0 + pair * 2;
+#pragma unroll
+                for (int it = 0; it < 8; it++) {
+                    const int r = it * 4 + sub_r;
+                    const int mm = mt * TM + quarter * 32 + r;
+                    const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(stg + r * STG_ROW + pair * 16);
+                    if (mm < P.M) {
+                        u64* dst = P.out + ((size_t)mm * limbs_n + limb) * P.C + c;
+                        if (vec_ok && c + 1 < P.col_end) {
+                            *reinterpret_cast<ulonglong2*>(dst) = v;
+                        } else {
+                            if (c < P.col_end) dst[0] = v.x;
+                            if (c + 1 < P.col_end) dst[1] = v.y;
                         }
-                        orow[c] = res;
                     }
                 }
+                CKB_PROF_END(2);
             }
         }
+#ifdef CKB_PROFILE
+        if (blockIdx.x == 0 && warp == 2 && lane == 0) { P.flags[12] = (int)(prof_acc_[0] >> 10); P.flags[13] = (int)(prof_acc_[1] >> 10); P.flags[14] = (int)(prof_acc_[2] >> 10); }
+#endif
         if (!ok) atomicExch(&abort_flag, 1);
     }
 
@@ -450,7 +527,7 @@ int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, 
     P.CT = CT;
     P.KBN = KBN;
     P.num_stages = C_::MAX_STAGES;
-    const size_t smem = (size_t)C_::MAX_STAGES * C_::STAGE + 1024;
+    const size_t smem = (size_t)C_::MAX_STAGES * C_::STAGE + STG_BYTES;
     CKB_CUDA(cudaFuncSetAttribute(pcmm_umma_kernel<SW, SC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     long items = (long)MT * CT;
     int grid = (int)(items < sms ? items : sms);
@@ -507,8 +584,12 @@ extern "C" int ckks_b200_pcmm_check(ckks_b200_pcmm* pc, void* stream) {
     DeviceGuard guard(pc->device);
     CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
     cudaStream_t st = (cudaStream_t)stream;
-    CKB_CUDA(cudaMemcpyAsync(pc->h_flags, pc->d_flags, 8 * sizeof(int), cudaMemcpyDeviceToHost, st));
+    CKB_CUDA(cudaMemcpyAsync(pc->h_flags, pc->d_flags, 16 * sizeof(int), cudaMemcpyDeviceToHost, st));
     CKB_CUDA(cudaStreamSynchronize(st));
+#ifdef CKB_PROFILE
+    fprintf(stderr, "[prof] mma: wait_tmem_empty=%d wait_full=%d total=%d (kcycles) tiles=%d | epi: wait_full=%d drain=%d math+store=%d\n",
+            pc->h_flags[8], pc->h_flags[9], pc->h_flags[10], pc->h_flags[11], pc->h_flags[12], pc->h_flags[13], pc->h_flags[14]);
+#endif
     CKB_REQUIRE(pc->h_flags[1] == 0, CKKS_B200_ERR_TIMEOUT,
                 "a device-side wait ran out of its clock budget (site %d)", pc->h_flags[1]);
     return CKKS_B200_OK;
