@@ -1,0 +1,158 @@
+// C++ classes with the reference's names and signatures for the hot path, forwarding to
+// the C ABI (ckks_b200.h).  For callers that want Context_23 / MLWECiphertext /
+// PCMM_Context / PCMM_Scheme without the rest of the reference tree.
+//
+// Mirrors (paths relative to the reference root):
+//   Context_23::ToNTTInplace / FromNTTInplace   src/ckks/include/Context_23.cuh:847-889
+//   Context_23::modUpQjtoT_23                   src/ckks/include/BasisConv.cuh:161-179
+//   MLWECiphertext                              src/ckks/include/pcmm/MLWECiphertext.cuh:6-78
+//   PCMM_Context                                src/ckks/include/pcmm/PCMM_Context.h:14-90
+//   PCMM_Scheme::PPMM                           src/ckks/include/pcmm/PPMM_kernel.cuh:254-349
+// Differences: `NTL::RR scale` is `long double`; constructors take the modulus lists
+// explicitly (the reference hard-codes them per logN in Params.cuh); CUDA errors surface as
+// std::runtime_error instead of being ignored; shape violations print the reference's
+// message and return, as the reference does.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <iostream>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../ckks_b200.h"
+
+namespace ckks_b200 {
+
+typedef unsigned long long uint64_tt;
+
+inline void check(int status) {
+    if (status != CKKS_B200_OK) throw std::runtime_error(std::string("ckks_b200: ") + ckks_b200_last_error());
+}
+
+class Context_23 {
+public:
+    int logN;
+    long N;
+    int L, K, p_num, q_num, t_num;
+    std::vector<uint64_tt> pVec, qVec, tVec;
+    ckks_b200_context* b200 = nullptr;
+
+    Context_23(int logN_, std::vector<uint64_tt> p, std::vector<uint64_tt> q, std::vector<uint64_tt> t, int device = 0)
+        : logN(logN_), N(1L << logN_), pVec(std::move(p)), qVec(std::move(q)), tVec(std::move(t)) {
+        p_num = (int)pVec.size(); q_num = (int)qVec.size(); t_num = (int)tVec.size();
+        K = p_num; L = q_num - 1;
+        check(ckks_b200_context_create(&b200, device, logN, (const uint64_t*)pVec.data(), p_num,
+                                       (const uint64_t*)qVec.data(), q_num, (const uint64_t*)tVec.data(), t_num));
+    }
+    Context_23(const Context_23&) = delete;
+    Context_23& operator=(const Context_23&) = delete;
+    ~Context_23() { ckks_b200_context_destroy(b200); }
+
+    void ToNTTInplace(uint64_tt* device_a, int start_poly_idx, int start_mod_idx, int poly_num, int mod_num,
+                      int poly_mod_len, cudaStream_t stream = 0) {
+        check(ckks_b200_ntt_forward(b200, (uint64_t*)device_a, start_poly_idx, start_mod_idx, poly_num, mod_num,
+                                    poly_mod_len, stream));
+    }
+    void FromNTTInplace(uint64_tt* device_a, int start_poly_idx, int start_mod_idx, int poly_num, int mod_num,
+                        int poly_mod_len, cudaStream_t stream = 0) {
+        check(ckks_b200_ntt_inverse(b200, (uint64_t*)device_a, start_poly_idx, start_mod_idx, poly_num, mod_num,
+                                    poly_mod_len, stream));
+    }
+    void modUpQjtoT_23(uint64_tt* output, uint64_tt* input, int l, int batch_size, cudaStream_t stream = 0) {
+        check(ckks_b200_modup_qj_to_t(b200, (uint64_t*)output, (const uint64_t*)input, l, batch_size, stream));
+    }
+};
+
+// One cudaMalloc per object, freed in the destructor, deep copy on copy: the reference's
+// ownership rules (MLWECiphertext.cuh:26-77).
+class MLWECiphertext {
+public:
+    uint64_tt* cipher_device = nullptr;
+    int N1 = 0, L = 0, l = 0, k = 0;
+    long double scale = 0;
+
+    MLWECiphertext() {}
+    MLWECiphertext(int N1_, int L_, int l_, int k_, long double scale_) : N1(N1_), L(L_), l(l_), k(k_), scale(scale_) {
+        if (cudaMalloc(&cipher_device, bytes()) != cudaSuccess) throw std::runtime_error("cudaMalloc failed");
+    }
+    MLWECiphertext(const MLWECiphertext& c) : N1(c.N1), L(c.L), l(c.l), k(c.k), scale(c.scale) {
+        if (cudaMalloc(&cipher_device, bytes()) != cudaSuccess) throw std::runtime_error("cudaMalloc failed");
+        if (c.cipher_device) cudaMemcpy(cipher_device, c.cipher_device, bytes(), cudaMemcpyDeviceToDevice);
+    }
+    MLWECiphertext& operator=(const MLWECiphertext& c) {
+        if (this == &c) return *this;
+        if (cipher_device && bytes() != c.bytes()) { cudaFree(cipher_device); cipher_device = nullptr; }
+        N1 = c.N1; L = c.L; l = c.l; k = c.k; scale = c.scale;
+        if (!cipher_device && cudaMalloc(&cipher_device, bytes()) != cudaSuccess) throw std::runtime_error("cudaMalloc failed");
+        if (c.cipher_device) cudaMemcpy(cipher_device, c.cipher_device, bytes(), cudaMemcpyDeviceToDevice);
+        return *this;
+    }
+    virtual ~MLWECiphertext() {
+        if (cipher_device) { cudaFree(cipher_device); cipher_device = nullptr; }
+    }
+    size_t bytes() const { return sizeof(uint64_tt) * (size_t)N1 * (L + 1) * (k + 1); }
+};
+
+class PCMM_Context {
+public:
+    int N1, mlwe_rank;
+    int ringpack_p_count, ringpack_q_count, ringpack_pq_count;
+    std::vector<uint64_tt> p_ringpack, q_ringpack, pq_ringpack;
+    ckks_b200_pcmm* b200 = nullptr;
+
+    PCMM_Context(int N1_, int mlwe_rank_, std::vector<uint64_tt> p, std::vector<uint64_tt> q, int device = 0)
+        : N1(N1_), mlwe_rank(mlwe_rank_), p_ringpack(std::move(p)), q_ringpack(std::move(q)) {
+        for (auto v : p_ringpack) pq_ringpack.push_back(v);
+        for (auto v : q_ringpack) pq_ringpack.push_back(v);
+        ringpack_p_count = (int)p_ringpack.size();
+        ringpack_q_count = (int)q_ringpack.size();
+        ringpack_pq_count = (int)pq_ringpack.size();
+        check(ckks_b200_pcmm_create(&b200, device, N1, mlwe_rank, (const uint64_t*)q_ringpack.data(), ringpack_q_count));
+    }
+    PCMM_Context(const PCMM_Context&) = delete;
+    PCMM_Context& operator=(const PCMM_Context&) = delete;
+    ~PCMM_Context() { ckks_b200_pcmm_destroy(b200); }
+};
+
+class PCMM_Scheme {
+public:
+    PCMM_Context& pcmm_context;
+    uint64_tt* ppmm_output = nullptr;     // [rows][q_count][(k+1)*N1], grown on demand
+    size_t ppmm_output_rows = 0;
+    int algo = CKKS_B200_PCMM_AUTO;
+
+    explicit PCMM_Scheme(PCMM_Context& ctx) : pcmm_context(ctx) {}
+    ~PCMM_Scheme() { if (ppmm_output) cudaFree(ppmm_output); }
+
+    void PPMM(float* plain_mat, std::vector<MLWECiphertext*> mlwe_cipher_decomposed, int mat_M, int mat_N, int mat_K,
+              int mlwe_num, cudaStream_t stream = 0) {
+        if (mat_K != pcmm_context.N1) { std::cout << "matrix K should be equal to N1!" << std::endl; return; }
+        if (mat_N != mlwe_num) { std::cout << "matrix N should be equal to mlwe number!" << std::endl; return; }
+        const long C = (long)(pcmm_context.mlwe_rank + 1) * pcmm_context.N1;
+        if (ppmm_output_rows < (size_t)mat_M) {
+            if (ppmm_output) cudaFree(ppmm_output);
+            if (cudaMalloc(&ppmm_output, sizeof(uint64_tt) * C * pcmm_context.ringpack_q_count * mat_M) != cudaSuccess)
+                throw std::runtime_error("cudaMalloc failed");
+            ppmm_output_rows = mat_M;
+        }
+        std::vector<const uint64_t*> ptrs(mlwe_num);
+        std::vector<uint64_t*> wptrs(mlwe_num);
+        for (int i = 0; i < mlwe_num; i++) {
+            ptrs[i] = (const uint64_t*)mlwe_cipher_decomposed[i]->cipher_device;
+            wptrs[i] = (uint64_t*)mlwe_cipher_decomposed[i]->cipher_device;
+        }
+        // scaler = (long)(q_ringpack[1] * 2^49 / scale)   (PPMM_kernel.cuh:283-284)
+        const long double q_div = (long double)pcmm_context.q_ringpack[pcmm_context.ringpack_q_count > 1 ? 1 : 0];
+        const long scaler = (long)(q_div * (long double)(1LL << 49) / mlwe_cipher_decomposed[0]->scale);
+        check(ckks_b200_pcmm_ppmm(pcmm_context.b200, plain_mat, ptrs.data(), (uint64_t*)ppmm_output, mat_M, mat_N, mat_K,
+                                  mlwe_num, (double)scaler, 0, C, algo, stream));
+        const int rows_back = mlwe_num < mat_M ? mlwe_num : mat_M;
+        check(ckks_b200_pcmm_copy_back(pcmm_context.b200, (const uint64_t*)ppmm_output, wptrs.data(), rows_back, 1, stream));
+        for (int i = 0; i < mlwe_num; i++)
+            mlwe_cipher_decomposed[i]->scale = mlwe_cipher_decomposed[i]->scale * scaler / q_div;
+    }
+};
+
+}  // namespace ckks_b200

@@ -1,0 +1,68 @@
+"""Host-side multi-rank logic on CPU: two gloo ranks split a PPMM by column range, compute
+their shards with the oracle, gather, and must reproduce the unsharded result."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import helpers as H
+from ckks_llm_b200 import params, shard
+
+
+def test_column_ranges_cover_and_align():
+    for width, world in [(65664, 8), (4160, 2), (96, 8), (67584, 8), (33, 2)]:
+        rs = shard.column_ranges(width, world)
+        assert rs[0][0] == 0 and rs[-1][1] == width
+        for (a, b), (c, d) in zip(rs, rs[1:]):
+            assert b == c
+        for a, b in rs:
+            assert a % 32 == 0 and (b % 32 == 0 or b == width) and a <= b
+        widths = [b - a for a, b in rs if b > a]
+        assert max(widths) - min(widths) <= 32 + 31
+    assert shard.unit_ranges(20, 8) == [(0, 3), (3, 6), (6, 9), (9, 12), (12, 14), (14, 16), (16, 18), (18, 20)]
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle import oracle as O
+    q = params.ntt_primes(50, 1 << 13, 3)
+    rng = np.random.default_rng(0)                 # same inputs on both ranks
+    M, K, N1, k = 8, 16, 32, 2                     # width 96: three tiles over two ranks (ragged)
+    Cw = (k + 1) * N1
+    W = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    X = np.stack([H.uniform_residues(rng, q, (Cw,)) for _ in range(K)])
+    ranges = shard.column_ranges(Cw, world)
+    c0, c1 = ranges[rank]
+    out = torch.zeros((M, len(q), Cw), dtype=torch.int64)
+    part = O.ppmm(W, np.ascontiguousarray(X[:, :, c0:c1]), q, float(1 << 40))
+    out[:, :, c0:c1] = torch.from_numpy(part.view(np.int64))
+    shard.gather_output(out, ranges)
+    full = O.ppmm(W, X, q, float(1 << 40))
+    ret[rank] = bool(np.array_equal(out.numpy().view(np.uint64), full))
+    dist.destroy_process_group()
+
+
+def test_two_ranks_column_sharded_ppmm_gloo():
+    world = 2
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert all(ret[r] for r in range(world))
