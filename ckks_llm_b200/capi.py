@@ -20,7 +20,7 @@ SYMBOLS = [
     "ckks_b200_ntt_forward_host", "ckks_b200_ntt_inverse_host",
     "ckks_b200_modup_qj_to_t", "ckks_b200_modup_qj_to_t_host",
     "ckks_b200_pcmm_create", "ckks_b200_pcmm_destroy", "ckks_b200_pcmm_ppmm",
-    "ckks_b200_pcmm_ppmm_host", "ckks_b200_pcmm_copy_back", "ckks_b200_pcmm_check", "ckks_b200_pcmm_last_timing",
+    "ckks_b200_pcmm_ppmm_host", "ckks_b200_pcmm_copy_back", "ckks_b200_pcmm_check", "ckks_b200_pcmm_last_timing", "ckks_b200_pcmm_ppmm_static",
     "ckks_b200_kernel_launches",
 ]
 
@@ -40,11 +40,12 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB):
+    lib_path = os.environ.get("CKKS_B200_LIB", LIB)      # development override of the library path
+    if not os.path.exists(lib_path):
         raise ImportError(
             f"{LIB} is missing: build it with `python -m ckks_llm_b200._build` "
             "(nvcc, sm_100a).  This package has no CPU implementation.")
-    L = C.CDLL(LIB)
+    L = C.CDLL(lib_path)
     vp, i, u64p, dbl, lng = C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.c_double, C.c_long
     L.ckks_b200_version.restype = i
     L.ckks_b200_status_string.restype = C.c_char_p
@@ -67,6 +68,7 @@ def load():
     L.ckks_b200_pcmm_copy_back.argtypes = [vp, vp, C.POINTER(vp), i, i, vp]
     L.ckks_b200_pcmm_check.argtypes = [vp, vp]
     L.ckks_b200_pcmm_last_timing.argtypes = [vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+    L.ckks_b200_pcmm_ppmm_static.argtypes = [vp, C.POINTER(vp), vp, i, i, i, i, i, i, u64p, i, dbl, vp]
     L.ckks_b200_kernel_launches.restype = lng
     for name in SYMBOLS:
         f = getattr(L, name)

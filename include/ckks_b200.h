@@ -130,6 +130,20 @@ int ckks_b200_pcmm_check(ckks_b200_pcmm* pc, void* stream);
  * into its slicing pre-pass and its main kernel; waits for them.  Stands in for the
  * CUDATimer the reference wraps around its kernel (PPMM_kernel.cuh:301-343). */
 int ckks_b200_pcmm_last_timing(ckks_b200_pcmm* pc, float* prepass_ms, float* main_ms);
+/* No counterpart in the reference.  PPMM for callers that are not allowed to allocate
+ * device memory (a serving process whose pool owns the GPU, a real-time loop, a sandboxed
+ * plug-in): the same product as ckks_b200_pcmm_ppmm on the CUDA-core kernel, with no
+ * handle and with all working memory (flags, ciphertext pointer table, scaled weights)
+ * in one fixed array inside the library image, about 8 MB on every GPU that loads the
+ * library.  Runs on the CURRENT device.  Limits: mat_N <= 4096, mat_M*mat_N <= 2^20,
+ * q_count <= 24; larger sizes return CKKS_B200_ERR_UNSUPPORTED.  It calls no allocator.
+ * The array is shared by all calls: calls whose work overlaps on one GPU race and must be
+ * serialised by the caller.  The first call on each device looks up the array's address
+ * and should be made outside any stream capture.  The stream is synchronised once inside
+ * the call (to read the weight range flag). */
+int ckks_b200_pcmm_ppmm_static(const float* d_W, const uint64_t* const* h_X_ptrs, uint64_t* d_out,
+                               int mat_M, int mat_N, int mat_K, int mlwe_num, int N1, int mlwe_rank,
+                               const uint64_t* q_ringpack, int q_count, double scaler, void* stream);
 /* Number of kernels this library has launched on the calling process so far. */
 long ckks_b200_kernel_launches(void);
 
