@@ -104,10 +104,14 @@ __device__ __forceinline__ u64 barrett128(u64 lo, u64 hi, u64 q, u64 mu_hi, u64 
     return csub(lo - qhat * q, q);
 }
 
+// (hi:lo) += a * b, one carry chain
 __device__ __forceinline__ void mac128(u64& lo, u64& hi, u64 a, u64 b) {
-    u64 pl = a * b, ph = __umul64hi(a, b);
-    lo += pl;
-    hi += ph + (lo < pl);
+    asm("{\n\t"
+        "mad.lo.cc.u64 %0, %2, %3, %0;\n\t"
+        "madc.hi.u64 %1, %2, %3, %1;\n\t"
+        "}"
+        : "+l"(lo), "+l"(hi)
+        : "l"(a), "l"(b));
 }
 #endif
 

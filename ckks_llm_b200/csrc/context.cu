@@ -228,6 +228,9 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
     if (!st) st = upload(&c->tw_inv, inv);
     if (!st) st = upload(&c->d_moduli, mods);
     if (!st) st = upload(&c->d_ninv, ninv);
+    std::vector<u64> qinv64(c->mod_num);
+    for (int i = 0; i < c->mod_num; i++) qinv64[i] = (u64)((((u128)1) << 64) / c->moduli[i]);
+    if (!st) st = upload(&c->d_qinv64, qinv64);
     if (!st) st = upload(&c->mu_hat_inv, hat_inv);
     if (!st) st = upload(&c->mu_hat_mod_t, hat_mod_t);
     if (!st) st = upload(&c->mu_blk_mod_t, blk_mod_t);
@@ -240,7 +243,7 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
 extern "C" int ckks_b200_context_destroy(ckks_b200_context* c) {
     if (!c) return CKKS_B200_OK;
     DeviceGuard guard(c->device);
-    cudaFree(c->tw_fwd); cudaFree(c->tw_inv); cudaFree(c->d_moduli); cudaFree(c->d_ninv);
+    cudaFree(c->tw_fwd); cudaFree(c->tw_inv); cudaFree(c->d_moduli); cudaFree(c->d_ninv); cudaFree(c->d_qinv64);
     cudaFree(c->mu_hat_inv); cudaFree(c->mu_hat_mod_t); cudaFree(c->mu_blk_mod_t);
     cudaFree(c->d_t_mu); cudaFree(c->h2d_buf); cudaFree(c->h2d_buf2);
     delete c;

@@ -22,6 +22,7 @@ struct ckks_b200_context {
     ulonglong2* tw_inv = nullptr;
     u64* d_moduli = nullptr;                 // [mod_num]
     ulonglong2* d_ninv = nullptr;            // [mod_num] {N^-1, shoup}
+    u64* d_qinv64 = nullptr;                 // [mod_num] floor(2^64 / q)
 
     // ModUp tables, one group per level l in [0, q_num):
     //   hat_inv   [l][blocks_max*alpha]           {inv, shoup} of (Qblk/q_j)^-1 mod q_j

@@ -25,6 +25,7 @@ struct NttArgs {
     const ulonglong2* tw;     // [mod][N] {w, w_shoup}
     const u64* moduli;        // [mod]
     const ulonglong2* ninv;   // [mod] {N^-1, shoup}
+    const u64* qinv64;        // [mod] floor(2^64 / q)
     int logN;
     int start_limb_off, start_mod_idx, poly_mod_len;
 };
@@ -32,9 +33,14 @@ struct NttArgs {
 __device__ __forceinline__ ulonglong2 ldtw(const ulonglong2* p) { return __ldg(p); }
 
 // Harvey butterflies.  Forward keeps values in [0, 4q), inverse in [0, 2q).
+// With LAZY the forward butterfly skips the conditional subtraction: values then grow by
+// at most 2q per stage, (2*logN+1)*q < 2^64 after all stages when q < 2^58, and the Shoup
+// product is exact for any 64-bit input; one reduction at the very end restores [0, q).
+template <bool LAZY>
 __device__ __forceinline__ void ct_bfly(u64& a, u64& b, ulonglong2 w, u64 q, u64 q2) {
     u64 t = shoup_lazy(b, w.x, w.y, q);       // [0, 2q)
-    u64 s = a >= q2 ? a - q2 : a;             // [0, 2q)
+    u64 s = a;
+    if (!LAZY) s = a >= q2 ? a - q2 : a;      // [0, 2q)
     a = s + t;
     b = s + q2 - t;
 }
@@ -48,26 +54,26 @@ __device__ __forceinline__ void gs_bfly(u64& a, u64& b, ulonglong2 w, u64 q, u64
 // Three forward stages on a[0..7]; a[j] sits at index base | (j << fb).  S0..S1 select
 // which of the three (stage 0 pairs on the top bit of the window).  widx is the
 // twiddle index of stage 0 for this thread's group.
-template <int S0, int S1>
+template <int S0, int S1, bool LAZY>
 __device__ __forceinline__ void fwd8(u64 (&a)[8], const ulonglong2* tw, uint32_t widx, u64 q, u64 q2) {
     if (S0 <= 0 && 0 < S1) {
         ulonglong2 w = ldtw(tw + widx);
 #pragma unroll
-        for (int j = 0; j < 4; j++) ct_bfly(a[j], a[j + 4], w, q, q2);
+        for (int j = 0; j < 4; j++) ct_bfly<LAZY>(a[j], a[j + 4], w, q, q2);
     }
     if (S0 <= 1 && 1 < S1) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             ulonglong2 w = ldtw(tw + 2 * widx + h);
-            ct_bfly(a[4 * h], a[4 * h + 2], w, q, q2);
-            ct_bfly(a[4 * h + 1], a[4 * h + 3], w, q, q2);
+            ct_bfly<LAZY>(a[4 * h], a[4 * h + 2], w, q, q2);
+            ct_bfly<LAZY>(a[4 * h + 1], a[4 * h + 3], w, q, q2);
         }
     }
     if (S0 <= 2 && 2 < S1) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             ulonglong2 w = ldtw(tw + 4 * widx + i);
-            ct_bfly(a[2 * i], a[2 * i + 1], w, q, q2);
+            ct_bfly<LAZY>(a[2 * i], a[2 * i + 1], w, q, q2);
         }
     }
 }
@@ -97,11 +103,11 @@ __device__ __forceinline__ void inv8(u64 (&a)[8], const ulonglong2* tw, uint32_t
     }
 }
 
-template <int NST>
+template <int NST, bool LAZY>
 __device__ __forceinline__ void fwd_n(u64 (&a)[8], const ulonglong2* tw, uint32_t widx, u64 q, u64 q2) {
-    if (NST == 3) fwd8<0, 3>(a, tw, widx, q, q2);
-    else if (NST == 2) fwd8<0, 2>(a, tw, widx, q, q2);
-    else fwd8<0, 1>(a, tw, widx, q, q2);
+    if (NST == 3) fwd8<0, 3, LAZY>(a, tw, widx, q, q2);
+    else if (NST == 2) fwd8<0, 2, LAZY>(a, tw, widx, q, q2);
+    else fwd8<0, 1, LAZY>(a, tw, widx, q, q2);
 }
 template <int NST>
 __device__ __forceinline__ void inv_n(u64 (&a)[8], const ulonglong2* tw, uint32_t widx, u64 q, u64 q2) {
@@ -123,8 +129,11 @@ constexpr int kChunk = 256;
 constexpr int kChunksPerCta = 16;
 constexpr int kThreadsB = 32 * kChunksPerCta;
 
-__global__ void __launch_bounds__(kThreadsB) ntt_fwd_contig(NttArgs P) {
-    __shared__ u64 S[kChunk * kChunksPerCta];
+// Moduli below this bound take the lazy forward butterflies (see ct_bfly).
+constexpr u64 kLazyBound = 1ull << 58;
+
+template <bool LAZY>
+__device__ __forceinline__ void ntt_fwd_contig_body(const NttArgs& P, u64* S) {
     const int lane = threadIdx.x & 31, v = threadIdx.x >> 5;
     const int limb = blockIdx.y, poly = blockIdx.z;
     const int mod = P.start_mod_idx + limb;
@@ -139,7 +148,7 @@ __global__ void __launch_bounds__(kThreadsB) ntt_fwd_contig(NttArgs P) {
     // window bits 7..5: p = j*32 + lane
 #pragma unroll
     for (int j = 0; j < 8; j++) a[j] = g[j * 32 + lane];
-    fwd8<0, 3>(a, tw, (N + x0) >> 8, q, q2);
+    fwd8<0, 3, LAZY>(a, tw, (N + x0) >> 8, q, q2);
 #pragma unroll
     for (int j = 0; j < 8; j++) s[swz(j * 32 + lane)] = a[j];
     __syncwarp();
@@ -149,7 +158,7 @@ __global__ void __launch_bounds__(kThreadsB) ntt_fwd_contig(NttArgs P) {
         const uint32_t lo = lane & 3, hi = lane >> 2;
 #pragma unroll
         for (int j = 0; j < 8; j++) a[j] = s[swz(hi * 32 + j * 4 + lo)];
-        fwd8<0, 3>(a, tw, ((N + x0) >> 5) + hi, q, q2);
+        fwd8<0, 3, LAZY>(a, tw, ((N + x0) >> 5) + hi, q, q2);
 #pragma unroll
         for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = a[j];
     }
@@ -158,15 +167,29 @@ __global__ void __launch_bounds__(kThreadsB) ntt_fwd_contig(NttArgs P) {
     // window bits 2..0, stages on bits 1 and 0 only: p = lane*8 + j
 #pragma unroll
     for (int j = 0; j < 8; j++) a[j] = s[swz(lane * 8 + j)];
-    fwd8<1, 3>(a, tw, ((N + x0) >> 3) + lane, q, q2);
+    fwd8<1, 3, LAZY>(a, tw, ((N + x0) >> 3) + lane, q, q2);
+    if (LAZY) {
+        // values are below (2*logN+1)*q: one Barrett-style step with floor(2^64/q) brings them to [0, 2q)
+        const u64 qinv64 = P.qinv64[mod];
 #pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = csub(csub(a[j], q2), q);
+        for (int j = 0; j < 8; j++) a[j] = csub(a[j] - __umul64hi(a[j], qinv64) * q, q);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) a[j] = csub(csub(a[j], q2), q);
+    }
     ulonglong2* go = reinterpret_cast<ulonglong2*>(g + lane * 8);
 #pragma unroll
     for (int j = 0; j < 4; j++) go[j] = make_ulonglong2(a[2 * j], a[2 * j + 1]);
 }
 
-__global__ void __launch_bounds__(kThreadsB) ntt_inv_contig(NttArgs P) {
+__global__ void __launch_bounds__(kThreadsB, 2) ntt_fwd_contig(NttArgs P) {
+    __shared__ u64 S[kChunk * kChunksPerCta];
+    const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
+    if (q < kLazyBound) ntt_fwd_contig_body<true>(P, S);
+    else ntt_fwd_contig_body<false>(P, S);
+}
+
+__global__ void __launch_bounds__(kThreadsB, 2) ntt_inv_contig(NttArgs P) {
     __shared__ u64 S[kChunk * kChunksPerCta];
     const int lane = threadIdx.x & 31, v = threadIdx.x >> 5;
     const int limb = blockIdx.y, poly = blockIdx.z;
@@ -229,14 +252,14 @@ __device__ __forceinline__ uint32_t strided_base(uint32_t tid) {
     return ((tid >> fb) << (fb + 3)) | (tid & ((1u << fb) - 1));
 }
 
-template <int SA, int WIN, bool INV>
+template <int SA, int WIN, bool INV, bool LAZY = false>
 __device__ __forceinline__ void strided_window(u64 (&a)[8], const ulonglong2* tw, uint32_t base, u64 q, u64 q2) {
     using C = StridedCfg<SA>;
     constexpr int fb = C::T - 3 * (WIN + 1);
     constexpr int nst = (SA - 3 * WIN) < 3 ? (SA - 3 * WIN) : 3;
     const uint32_t widx = ((1u << C::T) + base) >> (fb + 3);
     if (INV) inv_n<nst>(a, tw, widx, q, q2);
-    else fwd_n<nst>(a, tw, widx, q, q2);
+    else fwd_n<nst, LAZY>(a, tw, widx, q, q2);
 }
 
 template <int SA>
@@ -270,10 +293,9 @@ __device__ __forceinline__ void strided_st_gmem(const u64 (&a)[8], u64* g, uint3
     for (int j = 0; j < 8; j++) *strided_gptr<SA>(g, base | (j << fb)) = a[j];
 }
 
-template <int SA>
-__global__ void __launch_bounds__(StridedCfg<SA>::THREADS) ntt_fwd_strided(NttArgs P) {
+template <int SA, bool LAZY>
+__device__ __forceinline__ void ntt_fwd_strided_body(const NttArgs& P, u64* S) {
     using C = StridedCfg<SA>;
-    __shared__ u64 S[C::NWIN > 1 ? (1 << C::T) : 1];
     const uint32_t tid = threadIdx.x;
     const int limb = blockIdx.y, poly = blockIdx.z;
     const int mod = P.start_mod_idx + limb;
@@ -284,20 +306,29 @@ __global__ void __launch_bounds__(StridedCfg<SA>::THREADS) ntt_fwd_strided(NttAr
     u64 a[8];
     uint32_t base = strided_base<SA, 0>(tid);
     strided_ld_gmem<SA, 0>(a, g, base);
-    strided_window<SA, 0, false>(a, tw, base, q, q2);
+    strided_window<SA, 0, false, LAZY>(a, tw, base, q, q2);
     if (C::NWIN == 1) { strided_st_gmem<SA, 0>(a, g, base); return; }
     strided_st_smem<SA, 0>(a, S, base);
     __syncthreads();
     base = strided_base<SA, 1>(tid);
     strided_ld_smem<SA, 1>(a, S, base);
-    strided_window<SA, 1, false>(a, tw, base, q, q2);
+    strided_window<SA, 1, false, LAZY>(a, tw, base, q, q2);
     if (C::NWIN == 2) { strided_st_gmem<SA, 1>(a, g, base); return; }
     strided_st_smem<SA, 1>(a, S, base);
     __syncthreads();
     base = strided_base<SA, 2>(tid);
     strided_ld_smem<SA, 2>(a, S, base);
-    strided_window<SA, 2, false>(a, tw, base, q, q2);
+    strided_window<SA, 2, false, LAZY>(a, tw, base, q, q2);
     strided_st_gmem<SA, 2>(a, g, base);
+}
+
+template <int SA>
+__global__ void __launch_bounds__(StridedCfg<SA>::THREADS, 2) ntt_fwd_strided(NttArgs P) {
+    using C = StridedCfg<SA>;
+    __shared__ u64 S[C::NWIN > 1 ? (1 << C::T) : 1];
+    const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
+    if (q < kLazyBound) ntt_fwd_strided_body<SA, true>(P, S);
+    else ntt_fwd_strided_body<SA, false>(P, S);
 }
 
 // Final scaling of the inverse transform: the last stage's twiddle psiinv[1] already
@@ -312,7 +343,7 @@ __device__ __forceinline__ void inv_finish(u64 (&a)[8], ulonglong2 ninv, u64 q) 
 }
 
 template <int SA>
-__global__ void __launch_bounds__(StridedCfg<SA>::THREADS) ntt_inv_strided(NttArgs P) {
+__global__ void __launch_bounds__(StridedCfg<SA>::THREADS, 2) ntt_inv_strided(NttArgs P) {
     using C = StridedCfg<SA>;
     __shared__ u64 S[C::NWIN > 1 ? (1 << C::T) : 1];
     const uint32_t tid = threadIdx.x;
@@ -378,6 +409,7 @@ int run_ntt(ckks_b200_context* c, u64* d_data, int start_limb_off, int start_mod
     P.tw = inverse ? c->tw_inv : c->tw_fwd;
     P.moduli = c->d_moduli;
     P.ninv = c->d_ninv;
+    P.qinv64 = c->d_qinv64;
     P.logN = c->logN;
     P.start_limb_off = start_limb_off;
     P.start_mod_idx = start_mod_idx;
