@@ -169,6 +169,7 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
     }
 
     std::vector<ulonglong2> fwd((size_t)c->mod_num * N), inv((size_t)c->mod_num * N), ninv(c->mod_num);
+    std::vector<double> fwd_d((size_t)c->mod_num * N), inv_d((size_t)c->mod_num * N);
     c->h_psi_tab.resize(c->mod_num);
     c->h_psiinv_tab.resize(c->mod_num);
     for (int i = 0; i < c->mod_num; i++) {
@@ -180,6 +181,9 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
             u64 w = c->h_psi_tab[i][j], wi = c->h_psiinv_tab[i][j];
             fwd[(size_t)i * N + j] = make_ulonglong2(w, h_shoup(w, m));
             inv[(size_t)i * N + j] = make_ulonglong2(wi, h_shoup(wi, m));
+            // centred representatives for the FP64 back end
+            fwd_d[(size_t)i * N + j] = w > m / 2 ? -(double)(m - w) : (double)w;
+            inv_d[(size_t)i * N + j] = wi > m / 2 ? -(double)(m - wi) : (double)wi;
         }
         u64 ni = h_invmod(N % m, m);
         ninv[i] = make_ulonglong2(ni, h_shoup(ni, m));
@@ -226,6 +230,8 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
     std::vector<u64> mods(c->moduli.begin(), c->moduli.end());
     if (!st) st = upload(&c->tw_fwd, fwd);
     if (!st) st = upload(&c->tw_inv, inv);
+    if (!st) st = upload(&c->tw_fwd_d, fwd_d);
+    if (!st) st = upload(&c->tw_inv_d, inv_d);
     if (!st) st = upload(&c->d_moduli, mods);
     if (!st) st = upload(&c->d_ninv, ninv);
     std::vector<u64> qinv64(c->mod_num);
@@ -243,7 +249,7 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
 extern "C" int ckks_b200_context_destroy(ckks_b200_context* c) {
     if (!c) return CKKS_B200_OK;
     DeviceGuard guard(c->device);
-    cudaFree(c->tw_fwd); cudaFree(c->tw_inv); cudaFree(c->d_moduli); cudaFree(c->d_ninv); cudaFree(c->d_qinv64);
+    cudaFree(c->tw_fwd); cudaFree(c->tw_inv); cudaFree(c->tw_fwd_d); cudaFree(c->tw_inv_d); cudaFree(c->d_moduli); cudaFree(c->d_ninv); cudaFree(c->d_qinv64);
     cudaFree(c->mu_hat_inv); cudaFree(c->mu_hat_mod_t); cudaFree(c->mu_blk_mod_t);
     cudaFree(c->d_t_mu); cudaFree(c->h2d_buf); cudaFree(c->h2d_buf2);
     delete c;

@@ -20,6 +20,8 @@ struct ckks_b200_context {
     // 128-bit load fetches both: tw_fwd/tw_inv are [mod_num][N] ulonglong2.
     ulonglong2* tw_fwd = nullptr;
     ulonglong2* tw_inv = nullptr;
+    double* tw_fwd_d = nullptr;              // [mod_num][N] the same twiddles as centred doubles (FP64 back end)
+    double* tw_inv_d = nullptr;
     u64* d_moduli = nullptr;                 // [mod_num]
     ulonglong2* d_ninv = nullptr;            // [mod_num] {N^-1, shoup}
     u64* d_qinv64 = nullptr;                 // [mod_num] floor(2^64 / q)

@@ -14,6 +14,22 @@
 // (N + x) >> (b + 1).  Outputs are canonical.  Semantics follow
 // Context_23::ToNTTInplace / FromNTTInplace of the reference
 // (src/ckks/include/Context_23.cuh:847-889, butterflies ntt_60bit.cuh:293-318).
+//
+// Three arithmetic back ends compute the same residues and are chosen per limb from the
+// size of its modulus:
+//   F64   (q < 2^50)  values are exact integers held in doubles; a product with a twiddle
+//                     is one error-free multiplication (mul + fma), a quotient estimate
+//                     rounded to an integer with the 1.5*2^52 trick, and an exact fma
+//                     remainder: six FP64 operations, against one 64-bit high product
+//                     and two 64-bit low products on the integer pipes, which on this GPU
+//                     issue at a fraction of the FP64 rate (measured: 61 dfma vs 6.8
+//                     umul64hi lane-operations per clock per SM).
+//   LAZY  (q < 2^57)  64-bit Harvey butterflies without per-stage corrections and with a
+//                     three-partial-product quotient estimate.
+//   EXACT (otherwise) 64-bit Harvey butterflies, values in [0,4q) / [0,2q).
+// Between the two kernels of a transform the in-place buffer holds the back end's lazy
+// representation (for F64 the bit pattern of the double); the last kernel restores
+// canonical residues.
 #include "context.cuh"
 
 using namespace ckb;
@@ -23,6 +39,7 @@ namespace {
 struct NttArgs {
     u64* data;
     const ulonglong2* tw;     // [mod][N] {w, w_shoup}
+    const double* tw_d;       // [mod][N] w as double (exact below 2^53)
     const u64* moduli;        // [mod]
     const ulonglong2* ninv;   // [mod] {N^-1, shoup}
     const u64* qinv64;        // [mod] floor(2^64 / q)
@@ -30,90 +47,191 @@ struct NttArgs {
     int start_limb_off, start_mod_idx, poly_mod_len;
 };
 
-__device__ __forceinline__ ulonglong2 ldtw(const ulonglong2* p) { return __ldg(p); }
+constexpr u64 kF64Bound = 1ull << 50;
+constexpr u64 kLazyBound = 1ull << 57;
 
-// Harvey butterflies.  Forward keeps values in [0, 4q), inverse in [0, 2q).
-// With LAZY the forward butterfly skips the conditional subtraction: values then grow by
-// at most 2q per stage, (2*logN+1)*q < 2^64 after all stages when q < 2^58, and the Shoup
-// product is exact for any 64-bit input; one reduction at the very end restores [0, q).
+// ---------------------------------------------------------------------------
+// Arithmetic back ends.  V is the in-flight value type (64 bits wide), TW the twiddle.
+// ct<R>: forward butterfly; gs<R>: inverse butterfly.  R asks the F64 back end for its
+// extra range reduction on that stage; the integer back ends ignore it.
+// ---------------------------------------------------------------------------
 template <bool LAZY>
-__device__ __forceinline__ void ct_bfly(u64& a, u64& b, ulonglong2 w, u64 q, u64 q2) {
-    u64 t = shoup_lazy(b, w.x, w.y, q);       // [0, 2q)
-    u64 s = a;
-    if (!LAZY) s = a >= q2 ? a - q2 : a;      // [0, 2q)
-    a = s + t;
-    b = s + q2 - t;
-}
-__device__ __forceinline__ void gs_bfly(u64& a, u64& b, ulonglong2 w, u64 q, u64 q2) {
-    u64 t = a + q2 - b;
-    u64 s = a + b;
-    a = s >= q2 ? s - q2 : s;
-    b = shoup_lazy(t, w.x, w.y, q);
-}
+struct IntArith {
+    typedef u64 V;
+    typedef ulonglong2 TW;
+    u64 q, q2, qinv64;
+    ulonglong2 ninv;
+    const ulonglong2* tw;
+    __device__ __forceinline__ void init(const NttArgs& P, int mod) {
+        q = P.moduli[mod];
+        q2 = 2 * q;
+        qinv64 = P.qinv64[mod];
+        ninv = P.ninv[mod];
+        tw = P.tw + ((size_t)mod << P.logN);
+    }
+    __device__ __forceinline__ TW twiddle(uint32_t i) const { return __ldg(tw + i); }
+    __device__ __forceinline__ V from_word(u64 x) const { return x; }
+    __device__ __forceinline__ u64 to_word(V x) const { return x; }
+    __device__ __forceinline__ V from_canonical(u64 x) const { return x; }
+    template <bool R>
+    __device__ __forceinline__ void ct(V& a, V& b, TW w) const {
+        if (LAZY) {
+            // no correction: values grow by at most 4q per stage, (4*logN+1)*q < 2^64
+            u64 t = shoup_lazy4(b, w.x, w.y, q);
+            b = a + 2 * q2 - t;
+            a = a + t;
+        } else {
+            u64 t = shoup_lazy(b, w.x, w.y, q);      // [0, 2q)
+            u64 s = a >= q2 ? a - q2 : a;            // [0, 2q)
+            a = s + t;
+            b = s + q2 - t;                          // both in [0, 4q)
+        }
+    }
+    template <bool R>
+    __device__ __forceinline__ void gs(V& a, V& b, TW w) const {
+        if (LAZY) {                                  // values in [0, 4q)
+            const u64 q4 = 2 * q2;
+            u64 t = a + q4 - b, s = a + b;
+            a = s >= q4 ? s - q4 : s;
+            b = shoup_lazy4(t, w.x, w.y, q);
+        } else {                                     // values in [0, 2q)
+            u64 t = a + q2 - b, s = a + b;
+            a = s >= q2 ? s - q2 : s;
+            b = shoup_lazy(t, w.x, w.y, q);
+        }
+    }
+    // any lazy forward value -> [0, q)
+    __device__ __forceinline__ u64 canonical_fwd(V x) const {
+        if (LAZY) return csub(x - __umul64hi(x, qinv64) * q, q);
+        return csub(csub(x, q2), q);
+    }
+    // last inverse stage: the lower half still needs N^-1, the upper half got it with psiinv[1]
+    __device__ __forceinline__ u64 canonical_inv_lo(V x) const { return shoup_mul(x, ninv.x, ninv.y, q); }
+    __device__ __forceinline__ u64 canonical_inv_hi(V x) const {
+        if (LAZY) x = csub(x, q2);
+        return csub(x, q);
+    }
+};
 
-// Three forward stages on a[0..7]; a[j] sits at index base | (j << fb).  S0..S1 select
-// which of the three (stage 0 pairs on the top bit of the window).  widx is the
-// twiddle index of stage 0 for this thread's group.
-template <int S0, int S1, bool LAZY>
-__device__ __forceinline__ void fwd8(u64 (&a)[8], const ulonglong2* tw, uint32_t widx, u64 q, u64 q2) {
+struct F64Arith {
+    typedef double V;
+    typedef double TW;
+    double q, u, ninv;
+    const double* tw;
+    __device__ __forceinline__ void init(const NttArgs& P, int mod) {
+        const u64 qi = P.moduli[mod];
+        q = (double)qi;
+        u = __drcp_rn(q);
+        const u64 ni = P.ninv[mod].x;
+        ninv = ni > qi / 2 ? -(double)(qi - ni) : (double)ni;
+        tw = P.tw_d + ((size_t)mod << P.logN);
+    }
+    __device__ __forceinline__ TW twiddle(uint32_t i) const { return __ldg(tw + i); }
+    __device__ __forceinline__ V from_word(u64 x) const { return __longlong_as_double((long long)x); }
+    __device__ __forceinline__ u64 to_word(V x) const { return (u64)__double_as_longlong(x); }
+    // exact for x < 2^52
+    __device__ __forceinline__ V from_canonical(u64 x) const {
+        return __dadd_rn(__longlong_as_double((long long)(x | 0x4330000000000000ull)), -4503599627370496.0);
+    }
+    // x - rint(x/q)*q, exact; |result| <= q/2 + tiny for |x| < 2^52.  1.5*2^52 rounds to an integer.
+    __device__ __forceinline__ V reduce(V x) const {
+        double c = __dadd_rn(__fma_rn(x, u, 6755399441055744.0), -6755399441055744.0);
+        return __fma_rn(-c, q, x);
+    }
+    // b*w - c*q for an integer c near b*w/q, computed without error: h + l = b*w exactly,
+    // h - c*q is exact because it is a small integer, and adding l stays below 2^53.
+    // Twiddles are stored centred, |w| <= q/2 < 2^49, which halves both error terms:
+    // |b| < 2^52  ->  |result| <= q/2 + 3|b|/16 for q up to 2^50.
+    __device__ __forceinline__ V mulmod(V b, V w) const {
+        double h = __dmul_rn(b, w);
+        double l = __fma_rn(b, w, -h);
+        double c = __dadd_rn(__fma_rn(h, u, 6755399441055744.0), -6755399441055744.0);
+        double d = __fma_rn(-c, q, h);
+        return __dadd_rn(d, l);
+    }
+    // Forward: a is reduced on one stage in three (R); with bound B on the inputs a stage
+    // yields B + T(B) without and 0.51q + T(B) with the reduction, T(B) = q/2 + 3B/16, so
+    // the cycle (R, -, -) keeps every value below 3.5q < 2^52.
+    template <bool R>
+    __device__ __forceinline__ void ct(V& a, V& b, TW w) const {
+        double t = mulmod(b, w);
+        double s = R ? reduce(a) : a;
+        a = __dadd_rn(s, t);
+        b = __dadd_rn(s, -t);
+    }
+    // Inverse: the sum is reduced on every stage; products then stay below 0.8q and
+    // differences below 1.6q.
+    template <bool R>
+    __device__ __forceinline__ void gs(V& a, V& b, TW w) const {
+        double s = __dadd_rn(a, b), d = __dadd_rn(a, -b);
+        a = reduce(s);
+        b = mulmod(d, w);
+    }
+    __device__ __forceinline__ u64 canonical(V x) const {
+        x = reduce(x);
+        if (x < 0.0) x = __dadd_rn(x, q);
+        return (u64)__double_as_longlong(__dadd_rn(x, 4503599627370496.0)) & 0x000FFFFFFFFFFFFFull;
+    }
+    __device__ __forceinline__ u64 canonical_fwd(V x) const { return canonical(x); }
+    __device__ __forceinline__ u64 canonical_inv_lo(V x) const { return canonical(mulmod(x, ninv)); }
+    __device__ __forceinline__ u64 canonical_inv_hi(V x) const { return canonical(x); }
+};
+
+// ---------------------------------------------------------------------------
+// Three stages on v[0..7]; v[j] sits at index base | (j << fb).  Stage s of the window
+// pairs on window bit 2-s; S0..S1 selects which stages run.  widx is the twiddle index
+// of stage 0 for this thread's group.
+// ---------------------------------------------------------------------------
+// RM: bit s set = stage s applies the back end's range reduction.
+template <int S0, int S1, int RM, class A>
+__device__ __forceinline__ void fwd8(const A& ar, typename A::V (&v)[8], uint32_t widx) {
     if (S0 <= 0 && 0 < S1) {
-        ulonglong2 w = ldtw(tw + widx);
+        typename A::TW w = ar.twiddle(widx);
 #pragma unroll
-        for (int j = 0; j < 4; j++) ct_bfly<LAZY>(a[j], a[j + 4], w, q, q2);
+        for (int j = 0; j < 4; j++) ar.template ct<(RM & 1) != 0>(v[j], v[j + 4], w);
     }
     if (S0 <= 1 && 1 < S1) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            ulonglong2 w = ldtw(tw + 2 * widx + h);
-            ct_bfly<LAZY>(a[4 * h], a[4 * h + 2], w, q, q2);
-            ct_bfly<LAZY>(a[4 * h + 1], a[4 * h + 3], w, q, q2);
+            typename A::TW w = ar.twiddle(2 * widx + h);
+            ar.template ct<(RM & 2) != 0>(v[4 * h], v[4 * h + 2], w);
+            ar.template ct<(RM & 2) != 0>(v[4 * h + 1], v[4 * h + 3], w);
         }
     }
     if (S0 <= 2 && 2 < S1) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            ulonglong2 w = ldtw(tw + 4 * widx + i);
-            ct_bfly<LAZY>(a[2 * i], a[2 * i + 1], w, q, q2);
+            typename A::TW w = ar.twiddle(4 * widx + i);
+            ar.template ct<(RM & 4) != 0>(v[2 * i], v[2 * i + 1], w);
         }
     }
 }
 
-// The same three stages undone, bottom bit first.
-template <int S0, int S1>
-__device__ __forceinline__ void inv8(u64 (&a)[8], const ulonglong2* tw, uint32_t widx, u64 q, u64 q2) {
+// The same stages undone, bottom bit first.  K is the number, within its kernel, of the
+// first stage this call executes; odd-numbered stages set R.
+template <int S0, int S1, int K, class A>
+__device__ __forceinline__ void inv8(const A& ar, typename A::V (&v)[8], uint32_t widx) {
+    constexpr int first = S1 - 1;       // window stage executed first
     if (S0 <= 2 && 2 < S1) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            ulonglong2 w = ldtw(tw + 4 * widx + i);
-            gs_bfly(a[2 * i], a[2 * i + 1], w, q, q2);
+            typename A::TW w = ar.twiddle(4 * widx + i);
+            ar.template gs<((K + first - 2) & 1) == 1>(v[2 * i], v[2 * i + 1], w);
         }
     }
     if (S0 <= 1 && 1 < S1) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            ulonglong2 w = ldtw(tw + 2 * widx + h);
-            gs_bfly(a[4 * h], a[4 * h + 2], w, q, q2);
-            gs_bfly(a[4 * h + 1], a[4 * h + 3], w, q, q2);
+            typename A::TW w = ar.twiddle(2 * widx + h);
+            ar.template gs<((K + first - 1) & 1) == 1>(v[4 * h], v[4 * h + 2], w);
+            ar.template gs<((K + first - 1) & 1) == 1>(v[4 * h + 1], v[4 * h + 3], w);
         }
     }
     if (S0 <= 0 && 0 < S1) {
-        ulonglong2 w = ldtw(tw + widx);
+        typename A::TW w = ar.twiddle(widx);
 #pragma unroll
-        for (int j = 0; j < 4; j++) gs_bfly(a[j], a[j + 4], w, q, q2);
+        for (int j = 0; j < 4; j++) ar.template gs<((K + first - 0) & 1) == 1>(v[j], v[j + 4], w);
     }
-}
-
-template <int NST, bool LAZY>
-__device__ __forceinline__ void fwd_n(u64 (&a)[8], const ulonglong2* tw, uint32_t widx, u64 q, u64 q2) {
-    if (NST == 3) fwd8<0, 3, LAZY>(a, tw, widx, q, q2);
-    else if (NST == 2) fwd8<0, 2, LAZY>(a, tw, widx, q, q2);
-    else fwd8<0, 1, LAZY>(a, tw, widx, q, q2);
-}
-template <int NST>
-__device__ __forceinline__ void inv_n(u64 (&a)[8], const ulonglong2* tw, uint32_t widx, u64 q, u64 q2) {
-    if (NST == 3) inv8<0, 3>(a, tw, widx, q, q2);
-    else if (NST == 2) inv8<0, 2>(a, tw, widx, q, q2);
-    else inv8<0, 1>(a, tw, widx, q, q2);
 }
 
 // ---------------------------------------------------------------------------
@@ -129,105 +247,99 @@ constexpr int kChunk = 256;
 constexpr int kChunksPerCta = 16;
 constexpr int kThreadsB = 32 * kChunksPerCta;
 
-// Moduli below this bound take the lazy forward butterflies (see ct_bfly).
-constexpr u64 kLazyBound = 1ull << 58;
-
-template <bool LAZY>
-__device__ __forceinline__ void ntt_fwd_contig_body(const NttArgs& P, u64* S) {
-    const int lane = threadIdx.x & 31, v = threadIdx.x >> 5;
+template <class A>
+__device__ __forceinline__ void fwd_contig_body(const NttArgs& P, u64* S) {
+    typedef typename A::V V;
+    const int lane = threadIdx.x & 31, vv = threadIdx.x >> 5;
     const int limb = blockIdx.y, poly = blockIdx.z;
-    const int mod = P.start_mod_idx + limb;
-    const u64 q = P.moduli[mod], q2 = 2 * q;
+    A ar;
+    ar.init(P, P.start_mod_idx + limb);
     const uint32_t N = 1u << P.logN;
-    const ulonglong2* tw = P.tw + ((size_t)mod << P.logN);
-    const uint32_t x0 = (blockIdx.x * kChunksPerCta + v) * kChunk;   // position of the chunk
+    const uint32_t x0 = (blockIdx.x * kChunksPerCta + vv) * kChunk;   // position of the chunk
     u64* g = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN) + x0;
-    u64* s = S + v * kChunk;
-    u64 a[8];
+    u64* s = S + vv * kChunk;
+    V a[8];
 
     // window bits 7..5: p = j*32 + lane
 #pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = g[j * 32 + lane];
-    fwd8<0, 3, LAZY>(a, tw, (N + x0) >> 8, q, q2);
+    for (int j = 0; j < 8; j++) a[j] = ar.from_word(g[j * 32 + lane]);
+    fwd8<0, 3, 1>(ar, a, (N + x0) >> 8);             // kernel stages 0 (reducing), 1, 2
 #pragma unroll
-    for (int j = 0; j < 8; j++) s[swz(j * 32 + lane)] = a[j];
+    for (int j = 0; j < 8; j++) s[swz(j * 32 + lane)] = ar.to_word(a[j]);
     __syncwarp();
 
     // window bits 4..2: p = hi*32 + j*4 + lo, lane = hi*4 + lo
     {
         const uint32_t lo = lane & 3, hi = lane >> 2;
 #pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = s[swz(hi * 32 + j * 4 + lo)];
-        fwd8<0, 3, LAZY>(a, tw, ((N + x0) >> 5) + hi, q, q2);
+        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(hi * 32 + j * 4 + lo)]);
+        fwd8<0, 3, 1>(ar, a, ((N + x0) >> 5) + hi);  // stages 3 (reducing), 4, 5
 #pragma unroll
-        for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = a[j];
+        for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = ar.to_word(a[j]);
     }
     __syncwarp();
 
     // window bits 2..0, stages on bits 1 and 0 only: p = lane*8 + j
 #pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = s[swz(lane * 8 + j)];
-    fwd8<1, 3, LAZY>(a, tw, ((N + x0) >> 3) + lane, q, q2);
-    if (LAZY) {
-        // values are below (2*logN+1)*q: one Barrett-style step with floor(2^64/q) brings them to [0, 2q)
-        const u64 qinv64 = P.qinv64[mod];
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = csub(a[j] - __umul64hi(a[j], qinv64) * q, q);
-    } else {
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = csub(csub(a[j], q2), q);
-    }
+    for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(lane * 8 + j)]);
+    fwd8<1, 3, 2>(ar, a, ((N + x0) >> 3) + lane);    // stages 6 (reducing), 7
     ulonglong2* go = reinterpret_cast<ulonglong2*>(g + lane * 8);
 #pragma unroll
-    for (int j = 0; j < 4; j++) go[j] = make_ulonglong2(a[2 * j], a[2 * j + 1]);
+    for (int j = 0; j < 4; j++) go[j] = make_ulonglong2(ar.canonical_fwd(a[2 * j]), ar.canonical_fwd(a[2 * j + 1]));
 }
 
-__global__ void __launch_bounds__(kThreadsB, 2) ntt_fwd_contig(NttArgs P) {
-    __shared__ u64 S[kChunk * kChunksPerCta];
-    const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
-    if (q < kLazyBound) ntt_fwd_contig_body<true>(P, S);
-    else ntt_fwd_contig_body<false>(P, S);
-}
-
-__global__ void __launch_bounds__(kThreadsB, 2) ntt_inv_contig(NttArgs P) {
-    __shared__ u64 S[kChunk * kChunksPerCta];
-    const int lane = threadIdx.x & 31, v = threadIdx.x >> 5;
+template <class A>
+__device__ __forceinline__ void inv_contig_body(const NttArgs& P, u64* S) {
+    typedef typename A::V V;
+    const int lane = threadIdx.x & 31, vv = threadIdx.x >> 5;
     const int limb = blockIdx.y, poly = blockIdx.z;
-    const int mod = P.start_mod_idx + limb;
-    const u64 q = P.moduli[mod], q2 = 2 * q;
+    A ar;
+    ar.init(P, P.start_mod_idx + limb);
     const uint32_t N = 1u << P.logN;
-    const ulonglong2* tw = P.tw + ((size_t)mod << P.logN);
-    const uint32_t x0 = (blockIdx.x * kChunksPerCta + v) * kChunk;
+    const uint32_t x0 = (blockIdx.x * kChunksPerCta + vv) * kChunk;
     u64* g = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN) + x0;
-    u64* s = S + v * kChunk;
-    u64 a[8];
+    u64* s = S + vv * kChunk;
+    V a[8];
 
     const ulonglong2* gi = reinterpret_cast<const ulonglong2*>(g + lane * 8);
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         ulonglong2 t = gi[j];
-        a[2 * j] = t.x;
-        a[2 * j + 1] = t.y;
+        a[2 * j] = ar.from_canonical(t.x);
+        a[2 * j + 1] = ar.from_canonical(t.y);
     }
-    inv8<1, 3>(a, tw, ((N + x0) >> 3) + lane, q, q2);
+    inv8<1, 3, 0>(ar, a, ((N + x0) >> 3) + lane);            // stages 0, 1 of this kernel
 #pragma unroll
-    for (int j = 0; j < 8; j++) s[swz(lane * 8 + j)] = a[j];
+    for (int j = 0; j < 8; j++) s[swz(lane * 8 + j)] = ar.to_word(a[j]);
     __syncwarp();
     {
         const uint32_t lo = lane & 3, hi = lane >> 2;
 #pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = s[swz(hi * 32 + j * 4 + lo)];
-        inv8<0, 3>(a, tw, ((N + x0) >> 5) + hi, q, q2);
+        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(hi * 32 + j * 4 + lo)]);
+        inv8<0, 3, 2>(ar, a, ((N + x0) >> 5) + hi);          // stages 2, 3, 4
 #pragma unroll
-        for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = a[j];
+        for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = ar.to_word(a[j]);
     }
     __syncwarp();
 #pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = s[swz(j * 32 + lane)];
-    inv8<0, 3>(a, tw, (N + x0) >> 8, q, q2);
-    // values stay in [0, 2q); the strided phase finishes the transform
+    for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(j * 32 + lane)]);
+    inv8<0, 3, 5>(ar, a, (N + x0) >> 8);                      // stages 5, 6, 7
+    // values stay lazy; the strided phase finishes the transform
 #pragma unroll
-    for (int j = 0; j < 8; j++) g[j * 32 + lane] = a[j];
+    for (int j = 0; j < 8; j++) g[j * 32 + lane] = ar.to_word(a[j]);
+}
+
+template <bool INV>
+__global__ void __launch_bounds__(kThreadsB, 2) ntt_contig(NttArgs P) {
+    __shared__ u64 S[kChunk * kChunksPerCta];
+    const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
+    if (q < kF64Bound) {
+        if (INV) inv_contig_body<F64Arith>(P, S); else fwd_contig_body<F64Arith>(P, S);
+    } else if (q < kLazyBound) {
+        if (INV) inv_contig_body<IntArith<true>>(P, S); else fwd_contig_body<IntArith<true>>(P, S);
+    } else {
+        if (INV) inv_contig_body<IntArith<false>>(P, S); else fwd_contig_body<IntArith<false>>(P, S);
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -247,144 +359,124 @@ struct StridedCfg {
 };
 
 template <int SA, int WIN>
-__device__ __forceinline__ uint32_t strided_base(uint32_t tid) {
-    constexpr int fb = StridedCfg<SA>::T - 3 * (WIN + 1);
-    return ((tid >> fb) << (fb + 3)) | (tid & ((1u << fb) - 1));
-}
-
-template <int SA, int WIN, bool INV, bool LAZY = false>
-__device__ __forceinline__ void strided_window(u64 (&a)[8], const ulonglong2* tw, uint32_t base, u64 q, u64 q2) {
-    using C = StridedCfg<SA>;
-    constexpr int fb = C::T - 3 * (WIN + 1);
-    constexpr int nst = (SA - 3 * WIN) < 3 ? (SA - 3 * WIN) : 3;
-    const uint32_t widx = ((1u << C::T) + base) >> (fb + 3);
-    if (INV) inv_n<nst>(a, tw, widx, q, q2);
-    else fwd_n<nst, LAZY>(a, tw, widx, q, q2);
-}
-
-template <int SA>
-__device__ __forceinline__ u64* strided_gptr(u64* g, uint32_t idx) {
-    using C = StridedCfg<SA>;
-    return g + ((size_t)(idx >> C::LOGCW) << 8) + (idx & (C::CW - 1));
-}
-
-template <int SA, int WIN>
-__device__ __forceinline__ void strided_ld_smem(u64 (&a)[8], const u64* S, uint32_t base) {
-    constexpr int fb = StridedCfg<SA>::T - 3 * (WIN + 1);
-#pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = S[base | (j << fb)];
-}
-template <int SA, int WIN>
-__device__ __forceinline__ void strided_st_smem(const u64 (&a)[8], u64* S, uint32_t base) {
-    constexpr int fb = StridedCfg<SA>::T - 3 * (WIN + 1);
-#pragma unroll
-    for (int j = 0; j < 8; j++) S[base | (j << fb)] = a[j];
-}
-template <int SA, int WIN>
-__device__ __forceinline__ void strided_ld_gmem(u64 (&a)[8], u64* g, uint32_t base) {
-    constexpr int fb = StridedCfg<SA>::T - 3 * (WIN + 1);
-#pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = *strided_gptr<SA>(g, base | (j << fb));
-}
-template <int SA, int WIN>
-__device__ __forceinline__ void strided_st_gmem(const u64 (&a)[8], u64* g, uint32_t base) {
-    constexpr int fb = StridedCfg<SA>::T - 3 * (WIN + 1);
-#pragma unroll
-    for (int j = 0; j < 8; j++) *strided_gptr<SA>(g, base | (j << fb)) = a[j];
-}
-
-template <int SA, bool LAZY>
-__device__ __forceinline__ void ntt_fwd_strided_body(const NttArgs& P, u64* S) {
-    using C = StridedCfg<SA>;
-    const uint32_t tid = threadIdx.x;
-    const int limb = blockIdx.y, poly = blockIdx.z;
-    const int mod = P.start_mod_idx + limb;
-    const u64 q = P.moduli[mod], q2 = 2 * q;
-    const ulonglong2* tw = P.tw + ((size_t)mod << P.logN);
-    u64* g = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN) +
-             (size_t)blockIdx.x * C::CW;
-    u64 a[8];
-    uint32_t base = strided_base<SA, 0>(tid);
-    strided_ld_gmem<SA, 0>(a, g, base);
-    strided_window<SA, 0, false, LAZY>(a, tw, base, q, q2);
-    if (C::NWIN == 1) { strided_st_gmem<SA, 0>(a, g, base); return; }
-    strided_st_smem<SA, 0>(a, S, base);
-    __syncthreads();
-    base = strided_base<SA, 1>(tid);
-    strided_ld_smem<SA, 1>(a, S, base);
-    strided_window<SA, 1, false, LAZY>(a, tw, base, q, q2);
-    if (C::NWIN == 2) { strided_st_gmem<SA, 1>(a, g, base); return; }
-    strided_st_smem<SA, 1>(a, S, base);
-    __syncthreads();
-    base = strided_base<SA, 2>(tid);
-    strided_ld_smem<SA, 2>(a, S, base);
-    strided_window<SA, 2, false, LAZY>(a, tw, base, q, q2);
-    strided_st_gmem<SA, 2>(a, g, base);
-}
-
-template <int SA>
-__global__ void __launch_bounds__(StridedCfg<SA>::THREADS, 2) ntt_fwd_strided(NttArgs P) {
-    using C = StridedCfg<SA>;
-    __shared__ u64 S[C::NWIN > 1 ? (1 << C::T) : 1];
-    const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
-    if (q < kLazyBound) ntt_fwd_strided_body<SA, true>(P, S);
-    else ntt_fwd_strided_body<SA, false>(P, S);
-}
-
-// Final scaling of the inverse transform: the last stage's twiddle psiinv[1] already
-// carries N^-1 for the upper half (a[4..7] of the top window); the lower half is
-// multiplied by N^-1 here (src/ckks/include/ntt_60bit.cuh:890-898).
-__device__ __forceinline__ void inv_finish(u64 (&a)[8], ulonglong2 ninv, u64 q) {
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        a[j] = shoup_mul(a[j], ninv.x, ninv.y, q);
-        a[j + 4] = csub(a[j + 4], q);
+struct Win {
+    typedef StridedCfg<SA> C;
+    static constexpr int fb = C::T - 3 * (WIN + 1);
+    static constexpr int nst_raw = SA - 3 * WIN;
+    static constexpr int nst = nst_raw < 1 ? 1 : (nst_raw < 3 ? nst_raw : 3);
+    // stages executed before this window in the inverse kernel (windows run high to low)
+    static constexpr int inv_before = (SA - 3 * (WIN + 1)) > 0 ? (SA - 3 * (WIN + 1)) : 0;
+    __device__ static __forceinline__ uint32_t base(uint32_t tid) {
+        return ((tid >> fb) << (fb + 3)) | (tid & ((1u << fb) - 1));
     }
-}
+    __device__ static __forceinline__ uint32_t widx(uint32_t b) { return ((1u << C::T) + b) >> (fb + 3); }
+    __device__ static __forceinline__ u64* gptr(u64* g, uint32_t idx) {
+        return g + ((size_t)(idx >> C::LOGCW) << 8) + (idx & (C::CW - 1));
+    }
+};
 
-template <int SA>
-__global__ void __launch_bounds__(StridedCfg<SA>::THREADS, 2) ntt_inv_strided(NttArgs P) {
-    using C = StridedCfg<SA>;
-    __shared__ u64 S[C::NWIN > 1 ? (1 << C::T) : 1];
+template <int SA, class A>
+__device__ __forceinline__ void fwd_strided_body(const NttArgs& P, u64* S) {
+    typedef StridedCfg<SA> C;
+    typedef typename A::V V;
     const uint32_t tid = threadIdx.x;
     const int limb = blockIdx.y, poly = blockIdx.z;
-    const int mod = P.start_mod_idx + limb;
-    const u64 q = P.moduli[mod], q2 = 2 * q;
-    const ulonglong2* tw = P.tw + ((size_t)mod << P.logN);
-    const ulonglong2 ninv = P.ninv[mod];
+    A ar;
+    ar.init(P, P.start_mod_idx + limb);
     u64* g = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN) +
              (size_t)blockIdx.x * C::CW;
-    u64 a[8];
-    uint32_t base;
-    if (C::NWIN == 3) {
-        base = strided_base<SA, 2>(tid);
-        strided_ld_gmem<SA, 2>(a, g, base);
-        strided_window<SA, 2, true>(a, tw, base, q, q2);
-        strided_st_smem<SA, 2>(a, S, base);
+    V a[8];
+    uint32_t b = Win<SA, 0>::base(tid);
+#pragma unroll
+    for (int j = 0; j < 8; j++) a[j] = ar.from_canonical(*Win<SA, 0>::gptr(g, b | (j << Win<SA, 0>::fb)));
+    fwd8<0, Win<SA, 0>::nst, 4>(ar, a, Win<SA, 0>::widx(b));      // the third stage of a window reduces
+    if (C::NWIN >= 2) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) S[b | (j << Win<SA, 0>::fb)] = ar.to_word(a[j]);
         __syncthreads();
+        b = Win<SA, 1>::base(tid);
+#pragma unroll
+        for (int j = 0; j < 8; j++) a[j] = ar.from_word(S[b | (j << Win<SA, 1>::fb)]);
+        fwd8<0, Win<SA, 1>::nst, 4>(ar, a, Win<SA, 1>::widx(b));
+    }
+    if (C::NWIN >= 3) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) S[b | (j << Win<SA, 1>::fb)] = ar.to_word(a[j]);
+        __syncthreads();
+        b = Win<SA, 2>::base(tid);
+#pragma unroll
+        for (int j = 0; j < 8; j++) a[j] = ar.from_word(S[b | (j << Win<SA, 2>::fb)]);
+        fwd8<0, Win<SA, 2>::nst, 4>(ar, a, Win<SA, 2>::widx(b));
+    }
+    constexpr int LW = C::NWIN - 1;
+#pragma unroll
+    for (int j = 0; j < 8; j++) *Win<SA, LW>::gptr(g, b | (j << Win<SA, LW>::fb)) = ar.to_word(a[j]);
+}
+
+template <int SA, class A>
+__device__ __forceinline__ void inv_strided_body(const NttArgs& P, u64* S) {
+    typedef StridedCfg<SA> C;
+    typedef typename A::V V;
+    const uint32_t tid = threadIdx.x;
+    const int limb = blockIdx.y, poly = blockIdx.z;
+    A ar;
+    ar.init(P, P.start_mod_idx + limb);
+    u64* g = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN) +
+             (size_t)blockIdx.x * C::CW;
+    V a[8];
+    constexpr int LW = C::NWIN - 1;
+    uint32_t b = Win<SA, LW>::base(tid);
+#pragma unroll
+    for (int j = 0; j < 8; j++) a[j] = ar.from_word(*Win<SA, LW>::gptr(g, b | (j << Win<SA, LW>::fb)));
+    if (C::NWIN == 3) {
+        inv8<0, Win<SA, 2>::nst, Win<SA, 2>::inv_before>(ar, a, Win<SA, 2>::widx(b));
+#pragma unroll
+        for (int j = 0; j < 8; j++) S[b | (j << Win<SA, 2>::fb)] = ar.to_word(a[j]);
+        __syncthreads();
+        b = Win<SA, 1>::base(tid);
+#pragma unroll
+        for (int j = 0; j < 8; j++) a[j] = ar.from_word(S[b | (j << Win<SA, 1>::fb)]);
     }
     if (C::NWIN >= 2) {
-        base = strided_base<SA, 1>(tid);
-        if (C::NWIN == 2) strided_ld_gmem<SA, 1>(a, g, base);
-        else strided_ld_smem<SA, 1>(a, S, base);
-        strided_window<SA, 1, true>(a, tw, base, q, q2);
-        strided_st_smem<SA, 1>(a, S, base);
+        inv8<0, Win<SA, 1>::nst, Win<SA, 1>::inv_before>(ar, a, Win<SA, 1>::widx(b));
+#pragma unroll
+        for (int j = 0; j < 8; j++) S[b | (j << Win<SA, 1>::fb)] = ar.to_word(a[j]);
         __syncthreads();
+        b = Win<SA, 0>::base(tid);
+#pragma unroll
+        for (int j = 0; j < 8; j++) a[j] = ar.from_word(S[b | (j << Win<SA, 0>::fb)]);
     }
-    base = strided_base<SA, 0>(tid);
-    if (C::NWIN == 1) strided_ld_gmem<SA, 0>(a, g, base);
-    else strided_ld_smem<SA, 0>(a, S, base);
-    strided_window<SA, 0, true>(a, tw, base, q, q2);
-    inv_finish(a, ninv, q);
-    strided_st_gmem<SA, 0>(a, g, base);
+    inv8<0, Win<SA, 0>::nst, Win<SA, 0>::inv_before>(ar, a, Win<SA, 0>::widx(b));
+    // Final scaling: the last stage's twiddle psiinv[1] already carries N^-1 for the upper
+    // half (a[4..7] of the top window); the lower half is multiplied by N^-1 here
+    // (src/ckks/include/ntt_60bit.cuh:890-898).
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const u64 r = j < 4 ? ar.canonical_inv_lo(a[j]) : ar.canonical_inv_hi(a[j]);
+        *Win<SA, 0>::gptr(g, b | (j << Win<SA, 0>::fb)) = r;
+    }
+}
+
+template <int SA, bool INV>
+__global__ void __launch_bounds__(StridedCfg<SA>::THREADS, 2) ntt_strided(NttArgs P) {
+    typedef StridedCfg<SA> C;
+    __shared__ u64 S[C::NWIN > 1 ? (1 << C::T) : 1];
+    const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
+    if (q < kF64Bound) {
+        if (INV) inv_strided_body<SA, F64Arith>(P, S); else fwd_strided_body<SA, F64Arith>(P, S);
+    } else if (q < kLazyBound) {
+        if (INV) inv_strided_body<SA, IntArith<true>>(P, S); else fwd_strided_body<SA, IntArith<true>>(P, S);
+    } else {
+        if (INV) inv_strided_body<SA, IntArith<false>>(P, S); else fwd_strided_body<SA, IntArith<false>>(P, S);
+    }
 }
 
 template <int SA>
 void launch_strided(bool inverse, dim3 grid_lp, const NttArgs& P, cudaStream_t st) {
-    using C = StridedCfg<SA>;
+    typedef StridedCfg<SA> C;
     dim3 grid(256 / C::CW, grid_lp.y, grid_lp.z);
-    if (inverse) ntt_inv_strided<SA><<<grid, C::THREADS, 0, st>>>(P);
-    else ntt_fwd_strided<SA><<<grid, C::THREADS, 0, st>>>(P);
+    if (inverse) ntt_strided<SA, true><<<grid, C::THREADS, 0, st>>>(P);
+    else ntt_strided<SA, false><<<grid, C::THREADS, 0, st>>>(P);
 }
 
 int run_ntt(ckks_b200_context* c, u64* d_data, int start_limb_off, int start_mod_idx, int poly_num,
@@ -407,6 +499,7 @@ int run_ntt(ckks_b200_context* c, u64* d_data, int start_limb_off, int start_mod
     NttArgs P;
     P.data = d_data;
     P.tw = inverse ? c->tw_inv : c->tw_fwd;
+    P.tw_d = inverse ? c->tw_inv_d : c->tw_fwd_d;
     P.moduli = c->d_moduli;
     P.ninv = c->d_ninv;
     P.qinv64 = c->d_qinv64;
@@ -427,9 +520,9 @@ int run_ntt(ckks_b200_context* c, u64* d_data, int start_limb_off, int start_mod
     };
     if (!inverse) {
         strided();
-        ntt_fwd_contig<<<grid_c, kThreadsB, 0, st>>>(P);
+        ntt_contig<false><<<grid_c, kThreadsB, 0, st>>>(P);
     } else {
-        ntt_inv_contig<<<grid_c, kThreadsB, 0, st>>>(P);
+        ntt_contig<true><<<grid_c, kThreadsB, 0, st>>>(P);
         strided();
     }
     count_launch(2);
