@@ -193,6 +193,8 @@ extern "C" int ckks_b200_pcmm_destroy(ckks_b200_pcmm* pc) {
     if (pc->h_flags) cudaFreeHost(pc->h_flags);
     cudaFree(pc->d_wplanes); cudaFree(pc->d_xplanes);
     for (int i = 0; i < 3; i++) if (pc->ev[i]) cudaEventDestroy(pc->ev[i]);
+    for (int i = 0; i < 3; i++) if (pc->hs[i]) cudaStreamDestroy(pc->hs[i]);
+    for (cudaEvent_t e : pc->hev) cudaEventDestroy(e);
     cudaFree(pc->d_W_host); cudaFree(pc->d_X_host); cudaFree(pc->d_out_host);
     delete pc;
     return CKKS_B200_OK;
@@ -247,15 +249,49 @@ extern "C" int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, co
     if (!rc) rc = ensure_dev(&pc->d_X_host, &pc->X_host_cap, ct_words * mlwe_num);
     if (!rc) rc = ensure_dev(&pc->d_out_host, &pc->out_host_cap, ct_words * mat_M);
     if (rc) return rc;
-    CKB_CUDA(cudaMemcpyAsync(pc->d_W_host, h_W, sizeof(float) * mat_M * mat_N, cudaMemcpyHostToDevice, 0));
-    CKB_CUDA(cudaMemcpyAsync(pc->d_X_host, h_X, 8 * ct_words * mlwe_num, cudaMemcpyHostToDevice, 0));
+    // Column chunks are pipelined over three streams: while chunk i is multiplied, chunk i+1
+    // is on its way in and chunk i-1 on its way out (columns are independent of one another).
+    for (int i = 0; i < 3; i++)
+        if (!pc->hs[i]) CKB_CUDA(cudaStreamCreateWithFlags(&pc->hs[i], cudaStreamNonBlocking));
+    cudaStream_t s_in = pc->hs[0], s_mm = pc->hs[1], s_out = pc->hs[2];
+    const long tiles = (pc->C + 31) / 32;
+    const size_t total_bytes = 8 * ct_words * ((size_t)mlwe_num + mat_M);
+    int nchunk = total_bytes > ((size_t)2 << 30) ? 16 : total_bytes > ((size_t)256 << 20) ? 8 : 1;
+    if (nchunk > tiles) nchunk = (int)tiles;
+    while ((int)pc->hev.size() < 2 * nchunk) {
+        cudaEvent_t e;
+        CKB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        pc->hev.push_back(e);
+    }
+    CKB_CUDA(cudaMemcpyAsync(pc->d_W_host, h_W, sizeof(float) * mat_M * mat_N, cudaMemcpyHostToDevice, s_in));
     std::vector<const uint64_t*> ptrs(mlwe_num);
     for (int n = 0; n < mlwe_num; n++) ptrs[n] = (const uint64_t*)(pc->d_X_host + ct_words * n);
-    rc = ckks_b200_pcmm_ppmm(pc, pc->d_W_host, ptrs.data(), (uint64_t*)pc->d_out_host, mat_M, mat_N,
-                             mat_K, mlwe_num, scaler, 0, pc->C, algo, nullptr);
-    if (rc) return rc;
-    CKB_CUDA(cudaMemcpyAsync(h_out, pc->d_out_host, 8 * ct_words * mat_M, cudaMemcpyDeviceToHost, 0));
-    CKB_CUDA(cudaStreamSynchronize(0));
+    const size_t pitch = (size_t)pc->C * 8;
+    const long tbase = tiles / nchunk, textra = tiles % nchunk;   // the first chunks are the widest, so
+    long t0 = 0;                                                  // workspaces are sized once
+    for (int i = 0; i < nchunk; i++) {
+        const long t1 = t0 + tbase + (i < textra ? 1 : 0);
+        const long c0 = t0 * 32;
+        long c1 = t1 * 32;
+        t0 = t1;
+        if (c1 > pc->C) c1 = pc->C;
+        CKB_CUDA(cudaMemcpy2DAsync(pc->d_X_host + c0, pitch, h_X + c0, pitch, (size_t)(c1 - c0) * 8,
+                                   (size_t)mlwe_num * pc->q_count, cudaMemcpyHostToDevice, s_in));
+        CKB_CUDA(cudaEventRecord(pc->hev[2 * i], s_in));
+        CKB_CUDA(cudaStreamWaitEvent(s_mm, pc->hev[2 * i], 0));
+        rc = ckks_b200_pcmm_ppmm(pc, pc->d_W_host, ptrs.data(), (uint64_t*)pc->d_out_host, mat_M, mat_N, mat_K,
+                                 mlwe_num, scaler, c0, c1, algo, s_mm);
+        if (rc) return rc;
+        CKB_CUDA(cudaEventRecord(pc->hev[2 * i + 1], s_mm));
+        CKB_CUDA(cudaStreamWaitEvent(s_out, pc->hev[2 * i + 1], 0));
+        CKB_CUDA(cudaMemcpy2DAsync(h_out + c0, pitch, pc->d_out_host + c0, pitch, (size_t)(c1 - c0) * 8,
+                                   (size_t)mat_M * pc->q_count, cudaMemcpyDeviceToHost, s_out));
+    }
+    CKB_CUDA(cudaStreamSynchronize(s_out));
+    if (algo != CKKS_B200_PCMM_SIMT) {
+        rc = ckks_b200_pcmm_check(pc, s_mm);
+        if (rc) return rc;
+    }
     return CKKS_B200_OK;
 }
 

@@ -37,6 +37,10 @@ struct ckks_b200_pcmm {
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
     bool ev_valid = false;
 
+    // streams and events of the pipelined *_host entry point
+    cudaStream_t hs[3] = {nullptr, nullptr, nullptr};
+    std::vector<cudaEvent_t> hev;
+
     // staging for the *_host entry point
     float* d_W_host = nullptr;
     size_t W_host_cap = 0;

@@ -120,6 +120,31 @@ def test_bert_shape_sampled_rows(oracle, cuda_device):
     pc.close()
 
 
+def test_llama_contraction_depth(oracle, cuda_device):
+    """Configuration 5 contraction: K = 4096 at 2^40-scaled weights and 50-bit limbs is the
+    deepest sum the s32 accumulators take with five weight planes (5*4096*255^2 < 2^31).
+    Reduced to 256 rows, N1=32, rank 3, 3 limbs; every word vs the CUDA-core path, sampled
+    rows vs the oracle."""
+    q = params.ntt_primes(50, 1 << 17, 3)
+    N1, rank, M, K = 32, 3, 256, 4096
+    Cw = (rank + 1) * N1
+    rng = np.random.default_rng(5)
+    W = rng.normal(0, 0.02, (M, K)).astype(np.float32)
+    pc = PCMM_Context(N1, rank, [], q)
+    X, cts = _ciphers(rng, q, K, N1, rank, pc.device)
+    Wd = torch.from_numpy(W).to(pc.device)
+    outs = {}
+    for algo in ALGOS:
+        sch = PCMM_Scheme(pc, algo=algo)
+        outs[algo] = sch.PPMM(Wd, cts, M, K, N1, K, scaler=float(1 << 40), copy_back=False).clone()
+        sch.check()
+    assert torch.equal(outs[capi.PCMM_SIMT], outs[capi.PCMM_TENSOR])
+    got = to_u64_numpy(outs[capi.PCMM_TENSOR])
+    for m in (0, 100, 255):
+        assert np.array_equal(got[m], oracle.ppmm(W, X, q, float(1 << 40), m0=m, m1=m + 1)[m])
+    pc.close()
+
+
 def test_column_range(oracle, cuda_device):
     """Only the requested column range is written (the unit multi-GPU sharding uses)."""
     q = params.ntt_primes(50, 1 << 13, 2)
