@@ -40,6 +40,8 @@ struct ckks_b200_context {
     size_t h2d_cap = 0;
     u64* h2d_buf2 = nullptr;
     size_t h2d_cap2 = 0;
+    u64* ptr_buf = nullptr;                  // device copy of a caller's pointer table
+    size_t ptr_cap = 0;
 };
 
 namespace ckb {

@@ -256,7 +256,7 @@ extern "C" int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, co
     cudaStream_t s_in = pc->hs[0], s_mm = pc->hs[1], s_out = pc->hs[2];
     const long tiles = (pc->C + 31) / 32;
     const size_t total_bytes = 8 * ct_words * ((size_t)mlwe_num + mat_M);
-    int nchunk = total_bytes > ((size_t)2 << 30) ? 16 : total_bytes > ((size_t)256 << 20) ? 8 : 1;
+    int nchunk = total_bytes > ((size_t)256 << 20) ? 8 : 1;
     if (nchunk > tiles) nchunk = (int)tiles;
     while ((int)pc->hev.size() < 2 * nchunk) {
         cudaEvent_t e;

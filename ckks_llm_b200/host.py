@@ -103,6 +103,17 @@ class Context_23:
         return out
 
 
+class Ciphertext:
+    """RLWE ciphertext buffer: a limbs then b limbs, each [L+1][N] words, NTT domain at rest
+    (src/ckks/include/Ciphertext.cuh:5-100)."""
+
+    def __init__(self, N, L, l, slots, scale, device=0, cipher=None):
+        self.N, self.L, self.l, self.slots, self.scale = N, L, l, slots, scale
+        if cipher is None:
+            cipher = torch.zeros(2 * (L + 1) * N, dtype=torch.int64, device=torch.device("cuda", device))
+        self.cipher_device = cipher
+
+
 class MLWECiphertext:
     """Device buffer [L+1][k+1][N1] words (src/ckks/include/pcmm/MLWECiphertext.cuh:6-78)."""
 
@@ -144,8 +155,9 @@ class PCMM_Context:
 class PCMM_Scheme:
     """PPMM of the reference's PCMM_Scheme (src/ckks/include/pcmm/PCMM_Scheme.h:12-48)."""
 
-    def __init__(self, pcmm_context, algo=capi.PCMM_AUTO):
+    def __init__(self, pcmm_context, algo=capi.PCMM_AUTO, context=None):
         self.pcmm_context = pcmm_context
+        self.context = context              # Context_23, needed by rlweCipherDecompose
         self.lib = pcmm_context.lib
         self.algo = algo
         self.ppmm_output = None
@@ -189,6 +201,20 @@ class PCMM_Scheme:
             for c in mlwe_cipher_decomposed[:mlwe_num]:
                 c.scale = c.scale * scaler / q_last
         return out
+
+    def rlweCipherDecompose(self, rlwe_cipher, mlwe_cipher_decomposed, mlwe_num, offset, ntt_domain=True):
+        """PCMM_Scheme::rlweCipherDecompose (src/ckks/include/pcmm/PCMM_Scheme.cuh:90-125): fills
+        mlwe_cipher_decomposed[offset : offset+mlwe_num] from the RLWE ciphertext.  Like the
+        reference, asking for more ciphertexts than the rank prints a message and returns."""
+        pc, ctx = self.pcmm_context, self.context
+        ptrs = (C.c_void_p * max(mlwe_num, 1))(
+            *[c.cipher_device.data_ptr() for c in mlwe_cipher_decomposed[offset:offset + mlwe_num]])
+        st = self.lib.ckks_b200_rlwe_decompose(ctx._h, rlwe_cipher.cipher_device.data_ptr(), rlwe_cipher.L, rlwe_cipher.l,
+                                               ptrs, mlwe_num, pc.N1, pc.mlwe_rank, int(ntt_domain), _stream_ptr(pc.device))
+        if st == capi.ERR_SHAPE:
+            print(self.lib.ckks_b200_last_error().decode())
+            return
+        capi.check(st)
 
     def check(self):
         capi.check(self.lib.ckks_b200_pcmm_check(self.pcmm_context._h, _stream_ptr(self.pcmm_context.device)))

@@ -86,6 +86,19 @@ int ckks_b200_modup_qj_to_t(ckks_b200_context* ctx, uint64_t* d_out, const uint6
 int ckks_b200_modup_qj_to_t_host(ckks_b200_context* ctx, uint64_t* h_out, const uint64_t* h_in,
                                  int l, int batch);
 
+/* ---- ring packing, RLWE -> MLWE ---------------------------------------------
+ * PCMM_Scheme::rlweCipherDecompose (pcmm/PCMM_Scheme.cuh:51-125): d_rlwe is the
+ * reference's Ciphertext buffer, a limbs then b limbs, each [L+1][N]; limbs 0..l are
+ * used with q moduli 0..l of the context.  MLWE ciphertext i is written to
+ * h_mlwe_ptrs[i] (HOST array of device pointers) as [l+1][(k+1)*N1] with k = mlwe_rank =
+ * N/N1 and gap = k/mlwe_num between extracted combs.  With ntt_domain != 0 the RLWE
+ * ciphertext is taken out of and put back into the NTT domain around the gather, as the
+ * reference does (:107,:124); with 0 it is read as coefficients and left untouched.
+ * mlwe_num > mlwe_rank is the reference's error case (:103-106) -> CKKS_B200_ERR_SHAPE. */
+int ckks_b200_rlwe_decompose(ckks_b200_context* ctx, uint64_t* d_rlwe, int L, int l,
+                             uint64_t* const* h_mlwe_ptrs, int mlwe_num, int N1, int mlwe_rank,
+                             int ntt_domain, void* stream);
+
 /* ---- PCMM ------------------------------------------------------------------
  * Parameter carrier of PCMM_Context for the multiply (pcmm/PCMM_Context.cuh:7-57):
  * MLWE degree N1, rank k, and the ring-pack q moduli the product runs over

@@ -30,6 +30,7 @@ def lib():
                                 _U64P, _U64P, _U64P, _U64P]
         L.ref_ppmm.argtypes = [_F32P, _U64P, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _U64P,
                                C.c_double, _U64P, _U64P]
+        L.ref_decompose.argtypes = [_U64P, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _U64P]
         _lib = L
     return _lib
 
@@ -78,4 +79,15 @@ def ppmm(W, X, N1, rank, q, scaler, qinv, qinv_shoup):
                         np.ascontiguousarray(qinv, dtype=np.uint64), np.ascontiguousarray(qinv_shoup, dtype=np.uint64))
     if rc:
         raise RuntimeError(f"ref_ppmm failed with {rc}")
+    return out
+
+
+def decompose(rlwe, logN, N1, rank, mlwe_num, L, l, q):
+    """rlwe [2][L+1][N] coefficient domain -> [mlwe_num][l+1][(rank+1)*N1] by the reference kernel."""
+    rlwe = np.ascontiguousarray(rlwe, dtype=np.uint64)
+    out = np.zeros((mlwe_num, l + 1, (rank + 1) * N1), dtype=np.uint64)
+    rc = lib().ref_decompose(rlwe.reshape(-1), out.reshape(-1), logN, N1, rank, mlwe_num, L, l,
+                             np.ascontiguousarray(q, dtype=np.uint64))
+    if rc:
+        raise RuntimeError(f"ref_decompose failed with {rc}")
     return out

@@ -209,3 +209,36 @@ extern "C" int ref_ppmm(const float* h_W, const unsigned long long* h_X, unsigne
     cudaFree(dW); cudaFree(dX); cudaFree(dout); cudaFree(dinv); cudaFree(dinvs); cudaFree(dptr);
     return 0;
 }
+
+// rlweCipherDecompose_kernel<mlwe_rank> with the launch shape of PCMM_Scheme::rlweCipherDecompose
+// (src/ckks/include/pcmm/PCMM_Scheme.cuh:51-125), on coefficient-domain input.
+// h_rlwe is [2][L+1][N]; h_mlwe receives mlwe_num ciphertexts of [l+1][(rank+1)*N1] back to back.
+extern "C" int ref_decompose(const unsigned long long* h_rlwe, unsigned long long* h_mlwe, int logN, int N1,
+                             int mlwe_rank, int mlwe_num, int L, int l, const unsigned long long* q) {
+    if (mlwe_rank != 256 && mlwe_rank != 512) return 1;
+    if (N1 % ringSwitch_block) return 2;
+    const long N = 1L << logN;
+    int rc = upload_pqt(q, L + 1);          // p_num = 0: modulus index = limb index
+    if (rc) return rc;
+    const size_t ct_words = (size_t)(l + 1) * (mlwe_rank + 1) * N1;
+    uint64_tt *d_rlwe = nullptr, *d_mlwe = nullptr;
+    uint64_tt** d_ptr = nullptr;
+    RD_CUDA(cudaMalloc(&d_rlwe, 8 * 2 * (size_t)(L + 1) * N));
+    RD_CUDA(cudaMalloc(&d_mlwe, 8 * ct_words * mlwe_num));
+    RD_CUDA(cudaMalloc(&d_ptr, sizeof(uint64_tt*) * mlwe_num));
+    RD_CUDA(cudaMemcpy(d_rlwe, h_rlwe, 8 * 2 * (size_t)(L + 1) * N, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemset(d_mlwe, 0xff, 8 * ct_words * mlwe_num));
+    std::vector<uint64_tt*> ptrs(mlwe_num);
+    for (int i = 0; i < mlwe_num; i++) ptrs[i] = d_mlwe + ct_words * i;
+    RD_CUDA(cudaMemcpy(d_ptr, ptrs.data(), sizeof(uint64_tt*) * mlwe_num, cudaMemcpyHostToDevice));
+    dim3 grid(N1 / ringSwitch_block, l + 1, mlwe_num);
+    if (mlwe_rank == 256)
+        rlweCipherDecompose_kernel<256><<<grid, ringSwitch_block>>>(d_rlwe, d_ptr, (int)N, N1, mlwe_num, l, L, 0);
+    else
+        rlweCipherDecompose_kernel<512><<<grid, ringSwitch_block>>>(d_rlwe, d_ptr, (int)N, N1, mlwe_num, l, L, 0);
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    RD_CUDA(cudaMemcpy(h_mlwe, d_mlwe, 8 * ct_words * mlwe_num, cudaMemcpyDeviceToHost));
+    cudaFree(d_rlwe); cudaFree(d_mlwe); cudaFree(d_ptr);
+    return 0;
+}

@@ -1,0 +1,93 @@
+"""GPU parity of the RLWE -> MLWE decomposition against the oracle and the reference kernel."""
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+from ckks_llm_b200 import capi, params
+from ckks_llm_b200.host import (Ciphertext, Context_23, MLWECiphertext, PCMM_Context, PCMM_Scheme, as_u64_tensor,
+                                to_u64_numpy)
+from oracle import ref as R
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(logN, N1, L, seed, p_num=1):
+    N = 1 << logN
+    p = params.ntt_primes(51, 2 * N, p_num)
+    q = params.ntt_primes(50, 2 * N, L + 1)
+    ctx = Context_23(logN, p, q, [])
+    rng = np.random.default_rng(seed)
+    rlwe = np.stack([H.uniform_residues(rng, q, (N,)), H.uniform_residues(rng, q, (N,))])     # [2][L+1][N]
+    return N, q, ctx, rlwe
+
+
+@pytest.mark.parametrize("logN,N1,mlwe_num", [(12, 64, 64), (12, 64, 16), (13, 32, 5), (15, 128, 8)])
+def test_decompose_coefficient_domain(oracle, cuda_device, logN, N1, mlwe_num):
+    L = l = 2
+    N, q, ctx, rlwe = _setup(logN, N1, L, seed=logN + mlwe_num)
+    k = N // N1
+    pc = PCMM_Context(N1, k, [], q)
+    sch = PCMM_Scheme(pc, context=ctx)
+    ct = Ciphertext(N, L, l, N // 2, 1.0, cipher=as_u64_tensor(rlwe, ctx.device).reshape(-1))
+    mlwe = [MLWECiphertext(N1, L, l, k, 1.0) for _ in range(mlwe_num + 2)]
+    sch.rlweCipherDecompose(ct, mlwe, mlwe_num, 2, ntt_domain=False)
+    exp = oracle.rlwe_decompose(rlwe[0], rlwe[1], N1, k, mlwe_num, q)          # [num][limbs][k+1][N1]
+    for i in range(mlwe_num):
+        got = to_u64_numpy(mlwe[i + 2].cipher_device).reshape(L + 1, k + 1, N1)
+        assert np.array_equal(got, exp[i]), i
+    assert np.array_equal(to_u64_numpy(ct.cipher_device).reshape(rlwe.shape), rlwe)     # input untouched
+    assert not to_u64_numpy(mlwe[0].cipher_device).any()                                 # offset respected
+    pc.close(); ctx.close()
+
+
+def test_decompose_from_ntt_domain_and_level(oracle, cuda_device):
+    """The reference's call: ciphertext at rest in the NTT domain, level l below L."""
+    logN, N1, L, l = 13, 64, 3, 1
+    N, q, ctx, rlwe = _setup(logN, N1, L, seed=7, p_num=2)
+    k = N // N1
+    T = oracle.NttTables(N, ctx.pVec + ctx.qVec)
+    ntt = rlwe.copy()
+    oracle.ntt_batch(ntt, T, 0, ctx.p_num, 2, l + 1, L + 1)            # limbs 0..l of a and b into the NTT domain
+    pc = PCMM_Context(N1, k, [], q[:l + 1])
+    sch = PCMM_Scheme(pc, context=ctx)
+    ct = Ciphertext(N, L, l, N // 2, 1.0, cipher=as_u64_tensor(ntt, ctx.device).reshape(-1))
+    mlwe = [MLWECiphertext(N1, l, l, k, 1.0) for _ in range(4)]
+    sch.rlweCipherDecompose(ct, mlwe, 4, 0)
+    exp = oracle.rlwe_decompose(rlwe[0, :l + 1], rlwe[1, :l + 1], N1, k, 4, q[:l + 1])
+    for i in range(4):
+        assert np.array_equal(to_u64_numpy(mlwe[i].cipher_device).reshape(l + 1, k + 1, N1), exp[i])
+    assert np.array_equal(to_u64_numpy(ct.cipher_device).reshape(ntt.shape), ntt)      # back in the NTT domain
+    pc.close(); ctx.close()
+
+
+def test_decompose_error_message(cuda_device, capsys):
+    N, q, ctx, rlwe = _setup(12, 64, 0, seed=1)
+    pc = PCMM_Context(64, 64, [], q)
+    sch = PCMM_Scheme(pc, context=ctx)
+    ct = Ciphertext(N, 0, 0, N // 2, 1.0, cipher=as_u64_tensor(rlwe, ctx.device).reshape(-1))
+    mlwe = [MLWECiphertext(64, 0, 0, 64, 1.0) for _ in range(65)]
+    sch.rlweCipherDecompose(ct, mlwe, 65, 0)
+    assert "extract number muse <= mlwe_rank" in capsys.readouterr().out
+    pc.close(); ctx.close()
+
+
+@pytest.mark.skipif(not R.available(), reason="reference driver library not built")
+def test_decompose_matches_reference_kernel(oracle, cuda_device):
+    """rlweCipherDecompose_kernel<256> of the reference (N=2^15, N1=128, rank 256)."""
+    if not hasattr(R.lib(), "ref_decompose"):
+        pytest.skip("reference driver built without the decomposition entry")
+    logN, N1, L, l, mlwe_num = 15, 128, 1, 1, 8
+    N, q, ctx, rlwe = _setup(logN, N1, L, seed=3, p_num=0)
+    k = N // N1
+    ref_out = R.decompose(rlwe, logN, N1, k, mlwe_num, L, l, q)
+    exp = oracle.rlwe_decompose(rlwe[0], rlwe[1], N1, k, mlwe_num, q).reshape(ref_out.shape)
+    assert np.array_equal(exp, ref_out)
+    pc = PCMM_Context(N1, k, [], q)
+    sch = PCMM_Scheme(pc, context=ctx)
+    ct = Ciphertext(N, L, l, N // 2, 1.0, cipher=as_u64_tensor(rlwe, ctx.device).reshape(-1))
+    mlwe = [MLWECiphertext(N1, L, l, k, 1.0) for _ in range(mlwe_num)]
+    sch.rlweCipherDecompose(ct, mlwe, mlwe_num, 0, ntt_domain=False)
+    for i in range(mlwe_num):
+        assert np.array_equal(to_u64_numpy(mlwe[i].cipher_device).reshape(l + 1, -1), ref_out[i])
+    pc.close(); ctx.close()
