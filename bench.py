@@ -101,6 +101,7 @@ def pcmm_inputs(torch, device, seed):
 def cpu_pcmm_sample(q, X, W, Cw, rows=128, cols=16384):
     """Oracle PPMM on `rows` output rows x `cols` columns x all limbs of the same workload."""
     from oracle import oracle as O
+    O.set_threads(os.cpu_count() or 1)
     c = PCMM_CFG
     Xs = np.ascontiguousarray(X[:, :, :cols].cpu().numpy().view(np.uint64))
     Wh = W.cpu().numpy()
@@ -120,6 +121,7 @@ def run_reference(args):
         return
     from ckks_llm_b200 import params
     from oracle import oracle as O
+    O.set_threads(os.cpu_count() or 1)       # torchrun exports OMP_NUM_THREADS=1 to its workers
     c = PCMM_CFG
     if args.workload == "pcmm":
         q = params.ntt_primes(c["q_bits"], 2 << c["logN"], c["limbs"])
@@ -341,8 +343,22 @@ def main():
         cfg = {"workload": workload, "tokens_per_gpu": c["N1"], "sharding": "one 128-token block per GPU, no collective",
                "l2_policy": "inputs (8.07 GB ciphertext + 8.07 GB output) larger than L2"}
 
-        e2e = None
-        if rank == 0 and not args.no_e2e and world == 1:
+        e2e, cpu = None, None
+        do_e2e = not args.no_e2e
+        if do_e2e:
+            # every rank needs 16 GB of pinned host memory; skip (and say so) if the host cannot give it
+            try:
+                import psutil
+                need = (X.numel() * 8 + c["M"] * c["limbs"] * Cw * 8) * world * 1.25
+                if psutil.virtual_memory().available < need:
+                    do_e2e = False
+            except ImportError:
+                pass
+            if world > 1:
+                flag = torch.tensor([1 if do_e2e else 0], device=device)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                do_e2e = bool(flag.item())
+        if do_e2e:
             # same call through the C ABI with HOST buffers: H2D of W and X and D2H of the result per step
             Xh = torch.empty(X.shape, dtype=torch.int64).pin_memory()
             Xh.copy_(X)
@@ -358,20 +374,23 @@ def main():
                                                       c["N1"], c["K"], c["scaler"], capi.PCMM_TENSOR))
             host_step()
             n_e2e = max(1, min(args.steps, 3))
+            barrier()
             t0 = time.perf_counter()
             for _ in range(n_e2e):
                 host_step()
+            barrier()
             dt = (time.perf_counter() - t0) / n_e2e
-            e2e = {"value": c["M"] / dt, "unit": unit, "h2d_bytes_per_step": int(Xh.numel() * 8 + Wh.numel() * 4),
+            if world > 1:
+                tt = torch.tensor([dt], device=device, dtype=torch.float64)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                dt = float(tt.item())
+            e2e = {"value": world * c["M"] / dt, "unit": unit, "h2d_bytes_per_step": int(Xh.numel() * 8 + Wh.numel() * 4),
                    "d2h_bytes_per_step": int(outh.numel() * 8), "ms_per_step": dt * 1e3, "steps": n_e2e,
-                   "call": "ckks_b200_pcmm_ppmm_host (pinned host buffers)"}
-            cpu = None
-            if not args.no_cpu:
+                   "call": "ckks_b200_pcmm_ppmm_host (pinned host buffers, per rank)"}
+            if rank == 0 and world == 1 and not args.no_cpu:
                 Xd = Xh[:, :, :16384].contiguous()
                 v, dt_cpu, cores, sample = cpu_pcmm_sample(q, Xd, Wh, Cw)
                 cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample, "seconds": dt_cpu}
-        else:
-            cpu = None
         pc.close()
         if rank == 0 and world == 1 and not args.no_side:
             try:

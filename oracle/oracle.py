@@ -24,6 +24,7 @@ def lib():
             build_oracle()
         L = C.CDLL(LIB)
         L.orc_num_threads.restype = C.c_int
+        L.orc_set_threads.argtypes = [C.c_int]
         for name in ("orc_mulmod", "orc_powmod"):
             getattr(L, name).restype = C.c_uint64
             getattr(L, name).argtypes = [C.c_uint64] * 3
@@ -55,6 +56,10 @@ def lib():
 
 def num_threads():
     return lib().orc_num_threads()
+
+
+def set_threads(n):
+    lib().orc_set_threads(int(n))
 
 
 def find_psi(two_n, q):
