@@ -251,7 +251,7 @@ extern "C" int ckks_b200_context_destroy(ckks_b200_context* c) {
     DeviceGuard guard(c->device);
     cudaFree(c->tw_fwd); cudaFree(c->tw_inv); cudaFree(c->tw_fwd_d); cudaFree(c->tw_inv_d); cudaFree(c->d_moduli); cudaFree(c->d_ninv); cudaFree(c->d_qinv64);
     cudaFree(c->mu_hat_inv); cudaFree(c->mu_hat_mod_t); cudaFree(c->mu_blk_mod_t);
-    cudaFree(c->d_t_mu); cudaFree(c->h2d_buf); cudaFree(c->h2d_buf2); cudaFree(c->ptr_buf);
+    cudaFree(c->d_t_mu); cudaFree(c->h2d_buf); cudaFree(c->h2d_buf2); cudaFree(c->ptr_buf); cudaFree(c->pack_buf);
     delete c;
     return CKKS_B200_OK;
 }

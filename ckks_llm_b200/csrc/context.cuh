@@ -42,6 +42,8 @@ struct ckks_b200_context {
     size_t h2d_cap2 = 0;
     u64* ptr_buf = nullptr;                  // device copy of a caller's pointer table
     size_t ptr_cap = 0;
+    u64* pack_buf = nullptr;                 // embedded MLWE polynomials and key products of the packing
+    size_t pack_cap = 0;
 };
 
 namespace ckb {

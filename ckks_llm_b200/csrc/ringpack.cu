@@ -56,7 +56,123 @@ __global__ void __launch_bounds__(256) rlwe_decompose_kernel(const u64* __restri
     mlwe[i][(size_t)limb * C + w] = v;
 }
 
+// ---------------------------------------------------------------------------
+// MLWE -> RLWE packing (PCMM_Scheme::mlweCipherPacking, PCMM_Scheme.cuh:362-430), for the
+// reference's ring-pack shape: one special prime p and one packing limb q0.  Buffers hold
+// the limbs in the order [p, q0].
+// ---------------------------------------------------------------------------
+
+// mlweCipherEmbedding_new_kernel (:312-359): coefficient g of polynomial r of ciphertext i
+// goes to position g*k + i*gap of embedded polynomial r; the p limb gets the centred lift.
+// E: (k+1) polynomials of [2][N], zeroed beforehand.
+__global__ void __launch_bounds__(256) pack_embed_kernel(const u64* const* __restrict__ mlwe, u64* __restrict__ E, long N,
+                                                         int N1, int k, int mlwe_num, u64 p, u64 q0) {
+    const long C = (long)(k + 1) * N1;
+    const long w = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (w >= C) return;
+    const int i = blockIdx.y;
+    const int r = (int)(w / N1), g = (int)(w % N1);
+    const int gap = k / mlwe_num;
+    const u64 v = mlwe[i][w];                                   // limb 0 of ciphertext i
+    const long pos = (long)g * k + (long)i * gap;
+    u64* poly = E + (size_t)r * 2 * N;
+    poly[N + pos] = v;
+    poly[pos] = v > (q0 >> 1) ? (p - (q0 - v)) % p : v;
+}
+
+// mlweCipherMultRepackingKey_kernel (:261-289): (A, B) = sum_i E_i * key_i in the NTT domain.
+// keys: [k][2 (a,b)][2 limbs][N]; O: [2 (a,b)][2 limbs][N].
+__global__ void __launch_bounds__(128) pack_keymac_kernel(const u64* __restrict__ E, const u64* __restrict__ keys,
+                                                          u64* __restrict__ O, long N, int k, u64 m0, u64 m0_mu_hi,
+                                                          u64 m0_mu_lo, u64 m1, u64 m1_mu_hi, u64 m1_mu_lo) {
+    const long n = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int m = blockIdx.y;
+    if (n >= N) return;
+    u64 alo = 0, ahi = 0, blo = 0, bhi = 0;
+#pragma unroll 4
+    for (int i = 0; i < k; i++) {
+        const u64 c = E[((size_t)i * 2 + m) * N + n];
+        const u64* key = keys + (size_t)i * 4 * N;
+        mac128(alo, ahi, c, __ldg(key + (size_t)m * N + n));
+        mac128(blo, bhi, c, __ldg(key + (size_t)(m + 2) * N + n));
+    }
+    const u64 mod = m ? m1 : m0, mh = m ? m1_mu_hi : m0_mu_hi, ml = m ? m1_mu_lo : m0_mu_lo;
+    O[(size_t)m * N + n] = barrett128(alo, ahi, mod, mh, ml);
+    O[(size_t)(2 + m) * N + n] = barrett128(blo, bhi, mod, mh, ml);
+}
+
+// ringpacking_ModDown_kernel (:291-308) followed by the addition of the embedded b
+// (:426): out_c = (x_q + q - (x_p mod q)) * p^-1 mod q; b additionally + b_embedded mod q.
+__global__ void __launch_bounds__(256) pack_moddown_kernel(const u64* __restrict__ O, const u64* __restrict__ b_embedded,
+                                                           u64* __restrict__ out_a, u64* __restrict__ out_b, long N,
+                                                           u64 q0, u64 pinv, u64 pinv_shoup) {
+    const long n = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    const int c = blockIdx.y;
+    u64 ra = O[((size_t)c * 2) * N + n] % q0;
+    ra = q0 - ra + O[((size_t)c * 2 + 1) * N + n];
+    u64 r = shoup_mul(ra, pinv, pinv_shoup, q0);
+    if (c == 0) {
+        out_a[n] = r;
+    } else {
+        r += b_embedded[n];
+        out_b[n] = csub(r, q0);
+    }
+}
+
 }  // namespace
+
+extern "C" int ckks_b200_mlwe_packing(ckks_b200_context* c, uint64_t* d_rlwe, int L, uint64_t* const* h_mlwe_ptrs,
+                                      int mlwe_num, int N1, int mlwe_rank, const uint64_t* d_keys, void* stream) {
+    CKB_REQUIRE(c && d_rlwe && h_mlwe_ptrs && d_keys, CKKS_B200_ERR_ARG, "null argument");
+    CKB_REQUIRE(c->p_num >= 1, CKKS_B200_ERR_ARG, "packing needs a special prime p in the context");
+    CKB_REQUIRE(N1 >= 1 && mlwe_rank >= 1 && (long)N1 * mlwe_rank == (long)c->N, CKKS_B200_ERR_SHAPE,
+                "N1 * rank must equal N (%d * %d vs %u)", N1, mlwe_rank, c->N);
+    CKB_REQUIRE(mlwe_num >= 1 && mlwe_num <= mlwe_rank && mlwe_num <= 65535, CKKS_B200_ERR_SHAPE,
+                "mlwe_num %d outside [1, rank]", mlwe_num);
+    CKB_REQUIRE(L >= 0 && L < c->q_num, CKKS_B200_ERR_ARG, "L=%d outside the %d q moduli", L, c->q_num);
+    for (int i = 0; i < mlwe_num; i++)
+        CKB_REQUIRE(h_mlwe_ptrs[i] != nullptr, CKKS_B200_ERR_ARG, "MLWE pointer %d is null", i);
+    DeviceGuard guard(c->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", c->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const long N = c->N;
+    const int k = mlwe_rank;
+    const u64 p = c->moduli[c->p_num - 1], q0 = c->moduli[c->p_num];
+    CKB_REQUIRE(p > q0, CKKS_B200_ERR_ARG, "the special prime must exceed q0 (centred lift, PCMM_Scheme.cuh:334)");
+    int rc = ensure_buf(&c->ptr_buf, &c->ptr_cap, (size_t)mlwe_num);
+    if (!rc) rc = ensure_buf(&c->pack_buf, &c->pack_cap, (size_t)(k + 1) * 2 * N + 4 * N);
+    if (rc) return rc;
+    u64* E = c->pack_buf;
+    u64* O = E + (size_t)(k + 1) * 2 * N;
+    CKB_CUDA(cudaMemcpyAsync(c->ptr_buf, h_mlwe_ptrs, sizeof(u64*) * mlwe_num, cudaMemcpyHostToDevice, st));
+    CKB_CUDA(cudaMemsetAsync(E, 0, sizeof(u64) * (size_t)(k + 1) * 2 * N, st));                       // :397
+    const long C = (long)(k + 1) * N1;
+    pack_embed_kernel<<<dim3((unsigned)((C + 255) / 256), mlwe_num), 256, 0, st>>>((const u64* const*)c->ptr_buf, E, N, N1,
+                                                                                  k, mlwe_num, p, q0);
+    count_launch();
+    CKB_CUDA(cudaGetLastError());
+    // the k a-polynomials to the NTT domain over [p, q0] (:401)
+    rc = ckks_b200_ntt_forward(c, (uint64_t*)E, 0, c->p_num - 1, k, 2, 2, stream);
+    if (rc) return rc;
+    u64 mu[4];
+    h_barrett_mu(p, &mu[0], &mu[1]);
+    h_barrett_mu(q0, &mu[2], &mu[3]);
+    pack_keymac_kernel<<<dim3((unsigned)((N + 127) / 128), 2), 128, 0, st>>>(E, (const u64*)d_keys, O, N, k, p, mu[0], mu[1],
+                                                                            q0, mu[2], mu[3]);
+    count_launch();
+    CKB_CUDA(cudaGetLastError());
+    rc = ckks_b200_ntt_inverse(c, (uint64_t*)O, 0, c->p_num - 1, 2, 2, 2, stream);                                   // :416
+    if (rc) return rc;
+    const u64 pinv = h_invmod(p % q0, q0);
+    u64* out_a = (u64*)d_rlwe;
+    u64* out_b = (u64*)d_rlwe + (size_t)N * (L + 1);
+    pack_moddown_kernel<<<dim3((unsigned)((N + 255) / 256), 2), 256, 0, st>>>(O, E + (size_t)k * 2 * N + N, out_a, out_b, N, q0,
+                                                                             pinv, h_shoup(pinv, q0));
+    count_launch();
+    CKB_CUDA(cudaGetLastError());
+    return ckks_b200_ntt_forward(c, d_rlwe, 0, c->p_num, 2, 1, L + 1, stream);                            // :428
+}
 
 extern "C" int ckks_b200_rlwe_decompose(ckks_b200_context* c, uint64_t* d_rlwe, int L, int l,
                                         uint64_t* const* h_mlwe_ptrs, int mlwe_num, int N1, int mlwe_rank,

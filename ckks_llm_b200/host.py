@@ -216,6 +216,22 @@ class PCMM_Scheme:
             return
         capi.check(st)
 
+    def addRepakcingKey(self, keys_device):
+        """The reference generates the keys itself (PCMM_Scheme.cuh:152-223); key generation is
+        out of scope here, so the caller hands over the finished block [k][2][2][N]."""
+        self.repackingKeys = keys_device
+
+    def mlweCipherPacking(self, rlwe_cipher, mlwe_cipher_decomposed, mlwe_num, offset):
+        """PCMM_Scheme::mlweCipherPacking (src/ckks/include/pcmm/PCMM_Scheme.cuh:362-430)."""
+        pc, ctx = self.pcmm_context, self.context
+        ptrs = (C.c_void_p * max(mlwe_num, 1))(
+            *[c.cipher_device.data_ptr() for c in mlwe_cipher_decomposed[offset:offset + mlwe_num]])
+        capi.check(self.lib.ckks_b200_mlwe_packing(ctx._h, rlwe_cipher.cipher_device.data_ptr(), rlwe_cipher.L, ptrs,
+                                                   mlwe_num, pc.N1, pc.mlwe_rank, self.repackingKeys.data_ptr(),
+                                                   _stream_ptr(pc.device)))
+        rlwe_cipher.l = pc.ringpack_q_count - 1 - 1                      # :418-420
+        rlwe_cipher.scale = mlwe_cipher_decomposed[0].scale
+
     def check(self):
         capi.check(self.lib.ckks_b200_pcmm_check(self.pcmm_context._h, _stream_ptr(self.pcmm_context.device)))
 

@@ -99,6 +99,21 @@ int ckks_b200_rlwe_decompose(ckks_b200_context* ctx, uint64_t* d_rlwe, int L, in
                              uint64_t* const* h_mlwe_ptrs, int mlwe_num, int N1, int mlwe_rank,
                              int ntt_domain, void* stream);
 
+/* ---- ring packing, MLWE -> RLWE ---------------------------------------------
+ * PCMM_Scheme::mlweCipherPacking (pcmm/PCMM_Scheme.cuh:362-430) with its kernels
+ * (:261-359): limb 0 of the mlwe_num MLWE ciphertexts in h_mlwe_ptrs (HOST array of
+ * device pointers, each [..][(k+1)*N1]) is embedded into degree N with the centred lift
+ * q0 -> p*q0, the k a-polynomials go through the NTT, are multiplied with the repacking
+ * keys and summed, and the result comes back through INTT, ModDown by p, + b and NTT into
+ * limb 0 of d_rlwe (a limbs then b limbs, each [L+1][N]; the caller sets l = 0 and the scale
+ * as at :418-420).  As in the reference the ring-pack moduli are one special prime p (the
+ * LAST p of the context) and one packing limb q0 (the FIRST q), with p > q0.
+ * d_keys: the reference's contiguous key block, [k][2 (a,b)][2 limbs (p,q0)][N], NTT
+ * domain (Key.cuh:20-25 with addRepakcingKey's sizes, PCMM_Scheme.cuh:170-186). */
+int ckks_b200_mlwe_packing(ckks_b200_context* ctx, uint64_t* d_rlwe, int L,
+                           uint64_t* const* h_mlwe_ptrs, int mlwe_num, int N1, int mlwe_rank,
+                           const uint64_t* d_keys, void* stream);
+
 /* ---- PCMM ------------------------------------------------------------------
  * Parameter carrier of PCMM_Context for the multiply (pcmm/PCMM_Context.cuh:7-57):
  * MLWE degree N1, rank k, and the ring-pack q moduli the product runs over

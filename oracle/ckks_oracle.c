@@ -534,3 +534,68 @@ ORC_API void orc_negacyclic_mul_small(const u64 *a, const i64 *s, u64 *c, long N
         c[j] = p >= ng ? p - ng : p + q - ng;
     }
 }
+
+/* ---------------------------------------------------------------------------
+ * MLWE -> RLWE packing, stage by stage (PCMM_Scheme::mlweCipherPacking,
+ * src/ckks/include/pcmm/PCMM_Scheme.cuh:362-430).  The reference's kernels are written
+ * for one special prime p and one packing limb q0 (ring-pack moduli {p | q0, q1}); the
+ * same restriction holds here.  Limb order in every buffer: [p, q0].
+ * ------------------------------------------------------------------------- */
+
+/* mlweCipherEmbedding_new_kernel (:312-359) after the memset of :397.
+ *   mlwe[i] : MLWE ciphertext i, limb 0 = [(k+1)][N1]
+ *   E       : (k+1) polynomials (a_0..a_{k-1}, b), each [2 limbs][N]
+ * coefficient g of ciphertext i lands at position g*k + i*gap; the p limb receives the
+ * centred lift of the q0 residue. */
+ORC_API void orc_pack_embed(const u64 *const *mlwe, u64 *E, long N, int N1, int k, int mlwe_num,
+                            u64 p, u64 q0)
+{
+    int gap = k / mlwe_num;
+    memset(E, 0, sizeof(u64) * (size_t)(k + 1) * 2 * N);
+    for (int i = 0; i < mlwe_num; i++)
+        for (int r = 0; r <= k; r++)
+            for (int g = 0; g < N1; g++) {
+                u64 v = mlwe[i][(size_t)r * N1 + g];
+                long pos = (long)g * k + (long)i * gap;
+                u64 *poly = E + (size_t)r * 2 * N;
+                poly[N + pos] = v;
+                poly[pos] = v > (q0 / 2) ? (p - (q0 - v)) % p : v;
+            }
+}
+
+/* mlweCipherMultRepackingKey_kernel (:261-289): E_ntt is the first k polynomials of E in the
+ * NTT domain; keys [k][2 (a,b)][2 limbs][N]; O [2 (a,b)][2 limbs][N]. */
+ORC_API void orc_pack_keymac(const u64 *E_ntt, const u64 *keys, u64 *O, long N, int k, const u64 *mods)
+{
+    for (int m = 0; m < 2; m++) {
+        u64 mu_hi, mu_lo;
+        orc_barrett_mu(mods[m], &mu_hi, &mu_lo);
+#pragma omp parallel for
+        for (long n = 0; n < N; n++) {
+            u128 acc_a = 0, acc_b = 0;
+            for (int i = 0; i < k; i++) {
+                u64 c = E_ntt[((size_t)i * 2 + m) * N + n];
+                const u64 *key = keys + (size_t)i * 4 * N;
+                acc_a += (u128)c * key[(size_t)m * N + n];
+                acc_b += (u128)c * key[(size_t)(m + 2) * N + n];
+            }
+            O[(size_t)m * N + n] = barrett128(acc_a, mods[m], mu_hi, mu_lo);
+            O[(size_t)(2 + m) * N + n] = barrett128(acc_b, mods[m], mu_hi, mu_lo);
+        }
+    }
+}
+
+/* ringpacking_ModDown_kernel (:291-308) on coefficient-domain O [2][2 limbs][N]:
+ * out_c = (x_q + q - (x_p mod q)) * p^-1 mod q  (no centring of x_p), c in {a, b}. */
+ORC_API void orc_pack_moddown(const u64 *O, u64 *out_a, u64 *out_b, long N, u64 p, u64 q0)
+{
+    u64 pinv = orc_invmod(p % q0, q0), pinv_s = orc_shoup(pinv, q0);
+    for (int c = 0; c < 2; c++) {
+        u64 *out = c ? out_b : out_a;
+        for (long n = 0; n < N; n++) {
+            u64 ra = O[((size_t)c * 2) * N + n] % q0;
+            ra = q0 - ra + O[((size_t)c * 2 + 1) * N + n];
+            out[n] = mulmod_shoup(ra, pinv, pinv_s, q0);
+        }
+    }
+}

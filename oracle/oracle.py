@@ -50,6 +50,10 @@ def lib():
         L.orc_ring_down.argtypes = [_I64P, _I64P, C.c_long, C.c_int, C.c_int]
         L.orc_mlwe_decrypt.argtypes = [_U64P, _I64P, _U64P, C.c_int, C.c_int, C.c_uint64]
         L.orc_negacyclic_mul_small.argtypes = [_U64P, _I64P, _U64P, C.c_long, C.c_uint64]
+        L.orc_pack_embed.argtypes = [C.POINTER(C.c_void_p), _U64P, C.c_long, C.c_int, C.c_int, C.c_int,
+                                     C.c_uint64, C.c_uint64]
+        L.orc_pack_keymac.argtypes = [_U64P, _U64P, _U64P, C.c_long, C.c_int, _U64P]
+        L.orc_pack_moddown.argtypes = [_U64P, _U64P, _U64P, C.c_long, C.c_uint64, C.c_uint64]
         _lib = L
     return _lib
 
@@ -180,3 +184,36 @@ def negacyclic_mul_small(a, s, q):
     c = np.zeros_like(a)
     lib().orc_negacyclic_mul_small(a, np.ascontiguousarray(s, dtype=np.int64), c, len(a), int(q))
     return c
+
+
+def mlwe_packing(mlwe, keys, N1, k, p, q0, tables):
+    """PCMM_Scheme::mlweCipherPacking (PCMM_Scheme.cuh:362-430) for ring-pack moduli {p | q0, q1}.
+
+    mlwe: [mlwe_num][(k+1)][N1] limb-0 words of the MLWE ciphertexts; keys: [k][2][2][N] repacking
+    keys (a, b) x (p, q0) in the NTT domain; tables: NttTables over [p, q0].  Returns the packed
+    RLWE ciphertext (a, b) mod q0 in the NTT domain plus the intermediate stages."""
+    mlwe = np.ascontiguousarray(mlwe, dtype=np.uint64)
+    keys = np.ascontiguousarray(keys, dtype=np.uint64)
+    mlwe_num = mlwe.shape[0]
+    N = N1 * k
+    E = np.zeros((k + 1, 2, N), dtype=np.uint64)
+    ptrs = (C.c_void_p * mlwe_num)(*[mlwe[i].ctypes.data for i in range(mlwe_num)])
+    lib().orc_pack_embed(ptrs, E.reshape(-1), N, N1, k, mlwe_num, int(p), int(q0))
+    stages = {"embed": E.copy()}
+    ntt_batch(E, tables, 0, 0, k, 2, 2)                      # the k a-polynomials only (:401)
+    O = np.zeros((2, 2, N), dtype=np.uint64)
+    lib().orc_pack_keymac(E.reshape(-1), keys.reshape(-1), O.reshape(-1), N, k,
+                          np.array([p, q0], dtype=np.uint64))
+    stages["keymac"] = O.copy()
+    ntt_batch(O, tables, 0, 0, 2, 2, 2, inverse=True)        # :416
+    out = np.zeros((2, N), dtype=np.uint64)
+    lib().orc_pack_moddown(O.reshape(-1), out[0], out[1], N, int(p), int(q0))
+    stages["moddown"] = out.copy()
+    out[1] = (out[1] + E[k, 1]) % np.uint64(q0)              # + embedded b, coefficient domain (:426)
+    res = out[:, None, :].copy()                             # [2][1 limb][N]
+    sub = NttTables.__new__(NttTables)
+    sub.n, sub.moduli = tables.n, tables.moduli[1:2].copy()
+    sub.psi, sub.psiinv = tables.psi[1:2].copy(), tables.psiinv[1:2].copy()
+    sub.psi_shoup, sub.psiinv_shoup = tables.psi_shoup[1:2].copy(), tables.psiinv_shoup[1:2].copy()
+    ntt_batch(res, sub, 0, 0, 2, 1, 1)                       # :428
+    return res[:, 0, :], stages

@@ -100,3 +100,30 @@ def ppmm_python(W, X, q, scaler):
                     res.append(tmp * inv % qi)
                 out[m, i] = np.array(res, dtype=np.uint64)
     return out
+
+
+def repacking_keys(oracle, rng, s, N1, k, p, q0, tables, sigma=3.2):
+    """Repacking keys of PCMM_Scheme::addRepakcingKey (PCMM_Scheme.cuh:152-223): for every MLWE
+    secret component i, (a_i, b_i = -a_i*s + e_i + p*iota(s_i)) over the limbs [p, q0] in the NTT
+    domain, iota placing coefficient j at j*k (:149).  Returns [k][2][2][N]."""
+    N = N1 * k
+    mods = [p, q0]
+    s_mlwe = oracle.ring_down(s, N1, k)                       # [k][N1]
+    s_res = np.stack([np.where(s >= 0, s, s + np.int64(m)).astype(np.uint64) for m in mods])[None].copy()
+    oracle.ntt_batch(s_res, tables, 0, 0, 1, 2, 2)            # s in the NTT domain, both limbs
+    keys = np.zeros((k, 2, 2, N), dtype=np.uint64)
+    for i in range(k):
+        e = np.rint(rng.normal(0.0, sigma, size=N)).astype(np.int64)
+        iota = np.zeros(N, dtype=np.int64)
+        iota[::k] = s_mlwe[i]
+        msg = np.zeros((1, 2, N), dtype=np.uint64)
+        for m, mod in enumerate(mods):
+            t = (e.astype(object) + int(p) * iota.astype(object)) % int(mod)
+            msg[0, m] = np.array(t, dtype=np.uint64)
+        oracle.ntt_batch(msg, tables, 0, 0, 1, 2, 2)
+        for m, mod in enumerate(mods):
+            a = rng.integers(0, mod, N, dtype=np.uint64)
+            a_s = np.array([(int(x) * int(y)) % int(mod) for x, y in zip(a, s_res[0, m])], dtype=np.uint64)
+            keys[i, 0, m] = a
+            keys[i, 1, m] = (msg[0, m] + np.uint64(mod) - a_s) % np.uint64(mod)
+    return keys

@@ -91,3 +91,42 @@ def test_decompose_matches_reference_kernel(oracle, cuda_device):
     for i in range(mlwe_num):
         assert np.array_equal(to_u64_numpy(mlwe[i].cipher_device).reshape(l + 1, -1), ref_out[i])
     pc.close(); ctx.close()
+
+
+def test_packing_bit_exact_and_decrypts(oracle, cuda_device):
+    """mlweCipherPacking on the GPU: every word equal to the oracle's, and the packed RLWE
+    ciphertext decrypts to the message that went through decompose -> pack."""
+    N1, k = 64, 64
+    logN, N = 12, 4096
+    q = params.ntt_primes(50, 2 * N, 2)                       # q0, q1 (q1 only sizes the buffers)
+    p = params.ntt_primes(51, 2 * N, 2)                       # the LAST p is the ring-pack prime
+    ctx = Context_23(logN, p, q, [])
+    T = oracle.NttTables(N, [p[-1], q[0]])
+    rng = np.random.default_rng(4)
+    s = H.sparse_ternary(rng, N, 64)
+    vals = rng.uniform(-1, 1, N)
+    delta = float(1 << 30)
+    a, b = H.rlwe_encrypt(oracle, rng, H.encode_coeffs(vals, delta, q[:1]), s, q[:1])
+    for mlwe_num in (k, 16):
+        mlwe = oracle.rlwe_decompose(a, b, N1, k, mlwe_num, q[:1])[:, 0]          # [num][(k+1)][N1]
+        keys = H.repacking_keys(oracle, np.random.default_rng(5), s, N1, k, p[-1], q[0], T)
+        exp, stages = oracle.mlwe_packing(mlwe, keys, N1, k, p[-1], q[0], T)
+        pc = PCMM_Context(N1, k, [p[-1]], q)
+        sch = PCMM_Scheme(pc, context=ctx)
+        sch.addRepakcingKey(as_u64_tensor(keys, ctx.device).reshape(-1))
+        L = 1
+        cts = [MLWECiphertext(N1, L, 0, k, delta, cipher=as_u64_tensor(
+            np.concatenate([mlwe[i].reshape(-1), np.zeros((k + 1) * N1, dtype=np.uint64)]), ctx.device)) for i in range(mlwe_num)]
+        out = Ciphertext(N, L, L, N // 2, 1.0)
+        sch.mlweCipherPacking(out, cts, mlwe_num, 0)
+        got = to_u64_numpy(out.cipher_device).reshape(2, L + 1, N)
+        assert np.array_equal(got[:, 0], exp)
+        assert out.l == 0 and out.scale == delta
+        if mlwe_num == k:
+            sub = oracle.NttTables(N, q[:1])
+            coeff = got[:, :1].copy()
+            oracle.ntt_batch(coeff, sub, 0, 0, 2, 1, 1, inverse=True)
+            dec = (coeff[1, 0] + oracle.negacyclic_mul_small(coeff[0, 0], s, q[0])) % np.uint64(q[0])
+            assert np.abs(H.centered(dec, q[0]) / delta - vals).max() < 2.0 ** -20
+        pc.close()
+    ctx.close()
