@@ -91,3 +91,44 @@ def decompose(rlwe, logN, N1, rank, mlwe_num, L, l, q):
     if rc:
         raise RuntimeError(f"ref_decompose failed with {rc}")
     return out
+
+
+def _pack_fns():
+    L = lib()
+    if not hasattr(L, "ref_pack_embed"):
+        return None
+    L.ref_pack_embed.argtypes = [_U64P, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_uint64]
+    L.ref_pack_keymac.argtypes = [_U64P, _U64P, _U64P, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_uint64]
+    L.ref_pack_moddown.argtypes = [_U64P, _U64P, C.c_int, C.c_uint64, C.c_uint64]
+    return L
+
+
+def pack_embed(mlwe, logN, N1, rank, p, q0):
+    """mlwe [num][(rank+1)*N1] -> E [(rank+1)][2][N] by mlweCipherEmbedding_new_kernel."""
+    L = _pack_fns()
+    mlwe = np.ascontiguousarray(mlwe, dtype=np.uint64)
+    E = np.zeros((rank + 1, 2, 1 << logN), dtype=np.uint64)
+    rc = L.ref_pack_embed(mlwe.reshape(-1), E.reshape(-1), logN, N1, rank, mlwe.shape[0], int(p), int(q0))
+    if rc:
+        raise RuntimeError(f"ref_pack_embed failed with {rc}")
+    return E
+
+
+def pack_keymac(E_ntt, keys, logN, N1, rank, p, q0):
+    L = _pack_fns()
+    O = np.zeros((2, 2, 1 << logN), dtype=np.uint64)
+    rc = L.ref_pack_keymac(np.ascontiguousarray(E_ntt, dtype=np.uint64).reshape(-1),
+                           np.ascontiguousarray(keys, dtype=np.uint64).reshape(-1), O.reshape(-1), logN, N1, rank,
+                           int(p), int(q0))
+    if rc:
+        raise RuntimeError(f"ref_pack_keymac failed with {rc}")
+    return O
+
+
+def pack_moddown(O, logN, p, q0):
+    L = _pack_fns()
+    out = np.zeros((2, 1 << logN), dtype=np.uint64)
+    rc = L.ref_pack_moddown(np.ascontiguousarray(O, dtype=np.uint64).reshape(-1), out.reshape(-1), logN, int(p), int(q0))
+    if rc:
+        raise RuntimeError(f"ref_pack_moddown failed with {rc}")
+    return out

@@ -242,3 +242,92 @@ extern "C" int ref_decompose(const unsigned long long* h_rlwe, unsigned long lon
     cudaFree(d_rlwe); cudaFree(d_mlwe); cudaFree(d_ptr);
     return 0;
 }
+
+// The three kernels of PCMM_Scheme::mlweCipherPacking (src/ckks/include/pcmm/PCMM_Scheme.cuh:261-359),
+// each on its own so that every stage of the oracle can be pinned.  Ring-pack moduli [p | q0, q1].
+static int upload_ringpack(unsigned long long p, unsigned long long q0) {
+    uint64_tt m[2] = {p, q0}, mh[2], ml[2];
+    for (int i = 0; i < 2; i++) {
+        unsigned __int128 mu = (~(unsigned __int128)0) / m[i];
+        mh[i] = (uint64_tt)(mu >> 64);
+        ml[i] = (uint64_tt)mu;
+    }
+    RD_CUDA(cudaMemcpyToSymbol(ringpack_pq_cons, m, 16));
+    RD_CUDA(cudaMemcpyToSymbol(ringpack_pq_mu_high_cons, mh, 16));
+    RD_CUDA(cudaMemcpyToSymbol(ringpack_pq_mu_low_cons, ml, 16));
+    return 0;
+}
+
+// h_mlwe: mlwe_num ciphertexts, limb 0 only, [(rank+1)*N1] each; h_E: (rank+1) polynomials of [2][N].
+extern "C" int ref_pack_embed(const unsigned long long* h_mlwe, unsigned long long* h_E, int logN, int N1, int mlwe_rank,
+                              int mlwe_num, unsigned long long p, unsigned long long q0) {
+    if (N1 % ringSwitch_block) return 2;
+    const long N = 1L << logN;
+    int rc = upload_ringpack(p, q0);
+    if (rc) return rc;
+    const size_t ct = (size_t)(mlwe_rank + 1) * N1, eb = 8 * (size_t)(mlwe_rank + 1) * 2 * N;
+    uint64_tt *d_mlwe = nullptr, *d_E = nullptr;
+    uint64_tt** d_ptr = nullptr;
+    RD_CUDA(cudaMalloc(&d_mlwe, 8 * ct * mlwe_num));
+    RD_CUDA(cudaMalloc(&d_E, eb));
+    RD_CUDA(cudaMalloc(&d_ptr, sizeof(uint64_tt*) * mlwe_num));
+    RD_CUDA(cudaMemcpy(d_mlwe, h_mlwe, 8 * ct * mlwe_num, cudaMemcpyHostToDevice));
+    std::vector<uint64_tt*> ptrs(mlwe_num);
+    for (int i = 0; i < mlwe_num; i++) ptrs[i] = d_mlwe + ct * i;
+    RD_CUDA(cudaMemcpy(d_ptr, ptrs.data(), sizeof(uint64_tt*) * mlwe_num, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemset(d_E, 0, eb));                                                   // :397
+    dim3 grid(N1 / ringSwitch_block, 1, mlwe_num);
+    mlweCipherEmbedding_new_kernel<<<grid, ringSwitch_block>>>(d_E, d_ptr, N1, (int)N, mlwe_rank, mlwe_num, 1, 2);
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    RD_CUDA(cudaMemcpy(h_E, d_E, eb, cudaMemcpyDeviceToHost));
+    cudaFree(d_mlwe); cudaFree(d_E); cudaFree(d_ptr);
+    return 0;
+}
+
+// h_E: rank polynomials of [2][N] in the NTT domain; h_keys [rank][2][2][N]; h_O [2][2][N].
+extern "C" int ref_pack_keymac(const unsigned long long* h_E, const unsigned long long* h_keys, unsigned long long* h_O,
+                               int logN, int N1, int mlwe_rank, unsigned long long p, unsigned long long q0) {
+    if (mlwe_rank != 256 && mlwe_rank != 512) return 1;
+    const long N = 1L << logN;
+    int rc = upload_ringpack(p, q0);
+    if (rc) return rc;
+    uint64_tt *d_E = nullptr, *d_K = nullptr, *d_O = nullptr;
+    RD_CUDA(cudaMalloc(&d_E, 8 * (size_t)mlwe_rank * 2 * N));
+    RD_CUDA(cudaMalloc(&d_K, 8 * (size_t)mlwe_rank * 4 * N));
+    RD_CUDA(cudaMalloc(&d_O, 8 * 4 * N));
+    RD_CUDA(cudaMemcpy(d_E, h_E, 8 * (size_t)mlwe_rank * 2 * N, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(d_K, h_keys, 8 * (size_t)mlwe_rank * 4 * N, cudaMemcpyHostToDevice));
+    dim3 grid(N / ringSwitch_block, 2);
+    if (mlwe_rank == 256) mlweCipherMultRepackingKey_kernel<256><<<grid, ringSwitch_block>>>(d_O, d_E, d_K, N1, (int)N, 2);
+    else mlweCipherMultRepackingKey_kernel<512><<<grid, ringSwitch_block>>>(d_O, d_E, d_K, N1, (int)N, 2);
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    RD_CUDA(cudaMemcpy(h_O, d_O, 8 * 4 * N, cudaMemcpyDeviceToHost));
+    cudaFree(d_E); cudaFree(d_K); cudaFree(d_O);
+    return 0;
+}
+
+// h_O [2][2][N] coefficient domain -> h_out [2][N] (a, b) mod q0.
+extern "C" int ref_pack_moddown(const unsigned long long* h_O, unsigned long long* h_out, int logN, unsigned long long p,
+                                unsigned long long q0) {
+    const long N = 1L << logN;
+    int rc = upload_ringpack(p, q0);
+    if (rc) return rc;
+    uint64_tt pinv = modinv128(p, q0), pinv_s = x_Shoup(pinv, q0);
+    uint64_tt *d_O = nullptr, *d_out = nullptr, *d_pinv = nullptr, *d_pinvs = nullptr;
+    RD_CUDA(cudaMalloc(&d_O, 8 * 4 * N));
+    RD_CUDA(cudaMalloc(&d_out, 8 * 2 * N));
+    RD_CUDA(cudaMalloc(&d_pinv, 8));
+    RD_CUDA(cudaMalloc(&d_pinvs, 8));
+    RD_CUDA(cudaMemcpy(d_O, h_O, 8 * 4 * N, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(d_pinv, &pinv, 8, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(d_pinvs, &pinv_s, 8, cudaMemcpyHostToDevice));
+    dim3 grid(N / ringSwitch_block, 1, 2);
+    ringpacking_ModDown_kernel<<<grid, ringSwitch_block>>>(d_out, d_O, (int)N, 1, 2, 1, d_pinv, d_pinvs);
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    RD_CUDA(cudaMemcpy(h_out, d_out, 8 * 2 * N, cudaMemcpyDeviceToHost));
+    cudaFree(d_O); cudaFree(d_out); cudaFree(d_pinv); cudaFree(d_pinvs);
+    return 0;
+}

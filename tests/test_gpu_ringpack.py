@@ -130,3 +130,44 @@ def test_packing_bit_exact_and_decrypts(oracle, cuda_device):
             assert np.abs(H.centered(dec, q[0]) / delta - vals).max() < 2.0 ** -20
         pc.close()
     ctx.close()
+
+
+@pytest.mark.skipif(not R.available(), reason="reference driver library not built")
+def test_packing_stages_match_reference_kernels(oracle, cuda_device):
+    """mlweCipherEmbedding_new_kernel, mlweCipherMultRepackingKey_kernel<256> and
+    ringpacking_ModDown_kernel of the reference (N=2^15, N1=128, rank 256) against the oracle's
+    stages, and the library's end result against the oracle's."""
+    if R._pack_fns() is None:
+        pytest.skip("reference driver built without the packing entries")
+    import ctypes as C
+    logN, N1, k = 15, 128, 256
+    N = 1 << logN
+    q0 = params.REF_LOGN16_Q[0]                 # the reference's own q0 and special prime (both = 1 mod 2^17)
+    p = params.REF_LOGN16_P[-1]
+    rng = np.random.default_rng(8)
+    mlwe_num = 32
+    mlwe = rng.integers(0, q0, (mlwe_num, (k + 1) * N1), dtype=np.uint64)
+    keys = np.empty((k, 2, 2, N), dtype=np.uint64)
+    keys[:, :, 0] = rng.integers(0, p, (k, 2, N), dtype=np.uint64)
+    keys[:, :, 1] = rng.integers(0, q0, (k, 2, N), dtype=np.uint64)
+    T = oracle.NttTables(N, [p, q0])
+    exp, stages = oracle.mlwe_packing(mlwe.reshape(mlwe_num, k + 1, N1), keys, N1, k, p, q0, T)
+    E_ref = R.pack_embed(mlwe, logN, N1, k, p, q0)
+    assert np.array_equal(E_ref, stages["embed"])
+    E_ntt = stages["embed"][:k].copy()
+    oracle.ntt_batch(E_ntt, T, 0, 0, k, 2, 2)
+    O_ref = R.pack_keymac(E_ntt, keys, logN, N1, k, p, q0)
+    assert np.array_equal(O_ref, stages["keymac"])
+    O_c = stages["keymac"].copy()
+    oracle.ntt_batch(O_c, T, 0, 0, 2, 2, 2, inverse=True)
+    assert np.array_equal(R.pack_moddown(O_c, logN, p, q0), stages["moddown"])
+    # the library end to end on the same inputs
+    ctx = Context_23(logN, [p], [q0, params.REF_LOGN16_Q[1]], [])
+    pc = PCMM_Context(N1, k, [p], [q0, params.REF_LOGN16_Q[1]])
+    sch = PCMM_Scheme(pc, context=ctx)
+    sch.addRepakcingKey(as_u64_tensor(keys, ctx.device).reshape(-1))
+    cts = [MLWECiphertext(N1, 0, 0, k, 1.0, cipher=as_u64_tensor(mlwe[i], ctx.device)) for i in range(mlwe_num)]
+    out = Ciphertext(N, 1, 1, N // 2, 1.0)
+    sch.mlweCipherPacking(out, cts, mlwe_num, 0)
+    assert np.array_equal(to_u64_numpy(out.cipher_device).reshape(2, 2, N)[:, 0], exp)
+    pc.close(); ctx.close()
