@@ -9,9 +9,11 @@
  * host-side table builders restated here (root search, psi tables, Shoup companions)
  * are pinned against the reference's own functions, compiled from the reference
  * sources into oracle/_ref/ (see oracle/build_ref.py and tests/test_oracle_vs_ref_host.py),
- * and the NTT / INTT / ModUp restatements are pinned on a GPU against the reference's
- * own kernels compiled for sm_100a (tests/test_gpu_ref_kernels.py).  The PPMM
- * restatement is pinned the same way when the reference PPMM kernel could be built.
+ * and the NTT / INTT / ModUp / PPMM / decomposition / packing restatements are pinned
+ * on a GPU against the reference's own kernels compiled for sm_100a
+ * (tests/test_gpu_ref_kernels.py, tests/test_gpu_ringpack.py); digests of those
+ * reference-kernel outputs are committed under tests/golden/ and checked on any machine
+ * (tests/test_golden.py).
  *
  * Every function cites the reference file:line it follows (paths relative to the
  * reference project root).
