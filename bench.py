@@ -29,6 +29,11 @@ PCMM_CFG = dict(logN=16, N1=128, rank=512, M=768, K=768, limbs=20, q_bits=50, w_
 NTT_CFG = dict(logN=16, limbs=40, q_bits=50, polys=32)
 MODUP_CFG = dict(logN=16, q_num=24, q_bits=50, t_num=12, t_bits=60, alpha=8, batch=32)
 SW, SC = 5, 7          # byte planes the PCMM workload needs: 40-bit signed weights, 50-bit residues
+# DRAM traffic (bytes) from the ncu captures summarised under profiles/, per unit of work
+PCMM_TRAFFIC_PER_LIMB = (709.55e6 + 770.68e6) / 2                    # pcmm_umma_kernel<5,7>, 768x768, per limb
+NTT_TRAFFIC_PER_XFORM = {"forward": (167.90e6 + 111.49e6 + 194.98e6 + 112.24e6) / 320,
+                         "inverse": (197.69e6 + 116.77e6 + 167.91e6 + 109.20e6) / 320}
+MODUP_TRAFFIC_PER_POLY = (100.74e6 + 99.14e6) / 8
 
 
 def measured_peaks():
@@ -199,7 +204,9 @@ def bench_ntt(torch, device, steps, warmup, peaks):
         gbs = xforms * 16 * N / (ms * 1e-3) / 1e9
         res[name] = {"limb_xforms_per_sec": xforms / (ms * 1e-3), "ms_per_step": ms,
                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                  "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                                  "frac": gbs / peaks["hbm_gbs"],
+                                  "traffic": NTT_TRAFFIC_PER_XFORM[name] * xforms,
+                                  "traffic_note": "dram read+write of the two kernels in the ncu capture of 320 limb-transforms, scaled by units",
                                   "note": "two kernels per transform; achieved = 16*N bytes per limb-xform / time"}}
     ctx.close()
     res["config"] = {"workload": "batched NTT N=2^16, 40x50-bit limbs, 16 ciphertexts x 2 polys",
@@ -237,7 +244,8 @@ def bench_modup(torch, device, steps, warmup, peaks):
     ctx.close()
     return {"polys_per_sec": m["batch"] / (ms * 1e-3), "ms_per_step": ms,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": gbs / peaks["hbm_gbs"], "traffic": None},
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": MODUP_TRAFFIC_PER_POLY * m["batch"],
+                         "traffic_note": "dram read+write in the ncu capture of batch 8, scaled by units (part of the output was still dirty in L2)"},
             "config": {"workload": "ModUp N=2^16, 24x50-bit Q limbs in 3 digits -> 12x60-bit T limbs, batch 32",
                        "l2_policy": "input+output (1 GB) larger than L2"}}
 
@@ -334,7 +342,9 @@ def main():
         achieved = int8_ops / (main * 1e-3) / 1e12
         peak = 2.0 * peaks["bf16_tflops"]
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s (int8)", "frac": achieved / peak,
-                "traffic": None, "kernel": "pcmm_umma_kernel<5,7>", "kernel_ms": main, "prepass_ms": float(np.mean(pre_ms)),
+                "traffic": PCMM_TRAFFIC_PER_LIMB * c["limbs"],
+                "traffic_note": "dram read+write of the ncu capture of the 2-limb case, scaled by the limb count",
+                "kernel": "pcmm_umma_kernel<5,7>", "kernel_ms": main, "prepass_ms": float(np.mean(pre_ms)),
                 "peak_source": f"2 x bf16 dense {peaks['bf16_tflops']} TFLOP/s ({peaks['source']}); int8 dense is nominally 2x bf16",
                 "algorithmic_ops": "2*5*7 int8 ops per modular MAC x M*K*(N+N1)*limbs"}
         metric, unit = "pcmm_ct_rows_per_sec", "ct-rows/s"
