@@ -30,12 +30,9 @@
 // Between the two kernels of a transform the in-place buffer holds the back end's lazy
 // representation (for F64 the bit pattern of the double); the last kernel restores
 // canonical residues.
-#include <cooperative_groups.h>
-
 #include "context.cuh"
 
 using namespace ckb;
-namespace cg = cooperative_groups;
 
 namespace {
 
@@ -474,231 +471,6 @@ __global__ void __launch_bounds__(StridedCfg<SA>::THREADS, 2) ntt_strided(NttArg
     }
 }
 
-
-// ---------------------------------------------------------------------------
-// Fused transform for N >= 2^14: one thread-block cluster per limb-polynomial, one pass over
-// HBM.  CTA r of the cluster owns 8192 points.  Forward: it runs the strided phase on its
-// slice of columns (two half-tiles of 4096 points through a 32 KiB work buffer) and writes
-// the results straight into the 64 KiB receive buffer of the CTA that owns the row in the
-// contiguous phase (distributed shared memory, plain stores); after a cluster barrier every
-// CTA runs the contiguous phase on the 32 chunks it received and stores canonical residues.
-// The inverse mirrors this.
-// ---------------------------------------------------------------------------
-constexpr int kFusedThreads = 512;
-constexpr int kFusedWords = 8192;          // points per CTA
-
-template <int SA, class A>
-__device__ __forceinline__ void fused_fwd_body(const NttArgs& P, u64* S) {
-    typedef StridedCfg<SA> C;
-    typedef typename A::V V;
-    constexpr int LW = C::NWIN - 1;
-    cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t r = cluster.block_rank();
-    const uint32_t tid = threadIdx.x;
-    const int limb = blockIdx.y, poly = blockIdx.z;
-    A ar;
-    ar.init(P, P.start_mod_idx + limb);
-    const uint32_t N = 1u << P.logN;
-    u64* gl = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN);
-    u64* RX = S + 4096;      // receive buffer: the 32 chunks of the contiguous phase
-    cluster.sync();          // every CTA of the cluster is running: its shared memory may be written
-#pragma unroll 1
-    for (int u = 0; u < 2; u++) {
-        u64* g = gl + (size_t)(2 * r + u) * C::CW;
-        V a[8];
-        uint32_t b = Win<SA, 0>::base(tid);
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_canonical(*Win<SA, 0>::gptr(g, b | (j << Win<SA, 0>::fb)));
-        fwd8<0, Win<SA, 0>::nst, 4>(ar, a, Win<SA, 0>::widx(b));
-        if (C::NWIN >= 2) {
-            if (u == 1) __syncthreads();           // the first half is done with the work buffer
-#pragma unroll
-            for (int j = 0; j < 8; j++) S[b | (j << Win<SA, 0>::fb)] = ar.to_word(a[j]);
-            __syncthreads();
-            b = Win<SA, 1>::base(tid);
-#pragma unroll
-            for (int j = 0; j < 8; j++) a[j] = ar.from_word(S[b | (j << Win<SA, 1>::fb)]);
-            fwd8<0, Win<SA, 1>::nst, 4>(ar, a, Win<SA, 1>::widx(b));
-        }
-        if (C::NWIN >= 3) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) S[b | (j << Win<SA, 1>::fb)] = ar.to_word(a[j]);
-            __syncthreads();
-            b = Win<SA, 2>::base(tid);
-#pragma unroll
-            for (int j = 0; j < 8; j++) a[j] = ar.from_word(S[b | (j << Win<SA, 2>::fb)]);
-            fwd8<0, Win<SA, 2>::nst, 4>(ar, a, Win<SA, 2>::widx(b));
-        }
-        // straight into the receive buffer of the CTA that owns the row
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const uint32_t idx = b | (j << Win<SA, LW>::fb);
-            const uint32_t row = idx >> C::LOGCW, gcol = (2 * r + u) * C::CW + (idx & (C::CW - 1));
-            u64* dst = cluster.map_shared_rank(RX, row >> 5);
-            dst[(row & 31) * kChunk + swz(gcol)] = ar.to_word(a[j]);
-        }
-    }
-    cluster.sync();          // all 32 chunks of this CTA have arrived
-
-    const int lane = tid & 31, w = tid >> 5;
-#pragma unroll 1
-    for (int h = 0; h < 2; h++) {
-        const int vv = w + 16 * h;
-        const uint32_t x0 = (r * 32 + vv) * kChunk;
-        u64* s = RX + vv * kChunk;
-        V a[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(j * 32 + lane)]);
-        fwd8<0, 3, 1>(ar, a, (N + x0) >> 8);
-#pragma unroll
-        for (int j = 0; j < 8; j++) s[swz(j * 32 + lane)] = ar.to_word(a[j]);
-        __syncwarp();
-        {
-            const uint32_t lo = lane & 3, hi = lane >> 2;
-#pragma unroll
-            for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(hi * 32 + j * 4 + lo)]);
-            fwd8<0, 3, 1>(ar, a, ((N + x0) >> 5) + hi);
-#pragma unroll
-            for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = ar.to_word(a[j]);
-        }
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(lane * 8 + j)]);
-        fwd8<1, 3, 2>(ar, a, ((N + x0) >> 3) + lane);
-        ulonglong2* go = reinterpret_cast<ulonglong2*>(gl + x0 + lane * 8);
-#pragma unroll
-        for (int j = 0; j < 4; j++) go[j] = make_ulonglong2(ar.canonical_fwd(a[2 * j]), ar.canonical_fwd(a[2 * j + 1]));
-    }
-}
-
-template <int SA, class A>
-__device__ __forceinline__ void fused_inv_body(const NttArgs& P, u64* S) {
-    typedef StridedCfg<SA> C;
-    typedef typename A::V V;
-    constexpr int LW = C::NWIN - 1;
-    cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t r = cluster.block_rank();
-    const uint32_t tid = threadIdx.x;
-    const int limb = blockIdx.y, poly = blockIdx.z;
-    A ar;
-    ar.init(P, P.start_mod_idx + limb);
-    const uint32_t N = 1u << P.logN;
-    u64* gl = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN);
-    const int lane = tid & 31, w = tid >> 5;
-    u64* RX = S + 4096;      // receive buffer: the two half-tiles of the strided phase
-    cluster.sync();          // every CTA of the cluster is running: its shared memory may be written
-#pragma unroll 1
-    for (int h = 0; h < 2; h++) {
-        const int vv = w + 16 * h;
-        const uint32_t x0 = (r * 32 + vv) * kChunk;
-        u64* s = S + w * kChunk;                   // per-warp work area, reused by the second chunk
-        V a[8];
-        const ulonglong2* gi = reinterpret_cast<const ulonglong2*>(gl + x0 + lane * 8);
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            ulonglong2 t = gi[j];
-            a[2 * j] = ar.from_canonical(t.x);
-            a[2 * j + 1] = ar.from_canonical(t.y);
-        }
-        inv8<1, 3, 0>(ar, a, ((N + x0) >> 3) + lane);
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 8; j++) s[swz(lane * 8 + j)] = ar.to_word(a[j]);
-        __syncwarp();
-        {
-            const uint32_t lo = lane & 3, hi = lane >> 2;
-#pragma unroll
-            for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(hi * 32 + j * 4 + lo)]);
-            inv8<0, 3, 2>(ar, a, ((N + x0) >> 5) + hi);
-#pragma unroll
-            for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = ar.to_word(a[j]);
-        }
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(j * 32 + lane)]);
-        inv8<0, 3, 5>(ar, a, (N + x0) >> 8);
-        const uint32_t row = r * 32 + vv;
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const uint32_t gcol = j * 32 + lane;
-            const uint32_t half = gcol >> C::LOGCW;                   // half-tile number across the cluster
-            u64* dst = cluster.map_shared_rank(RX, half >> 1);
-            dst[(half & 1) * 4096 + (row << C::LOGCW) + (gcol & (C::CW - 1))] = ar.to_word(a[j]);
-        }
-    }
-    cluster.sync();          // both half-tiles of this CTA have arrived
-
-#pragma unroll 1
-    for (int u = 0; u < 2; u++) {
-        u64* T = RX + u * 4096;
-        u64* g = gl + (size_t)(2 * r + u) * C::CW;
-        V a[8];
-        uint32_t b = Win<SA, LW>::base(tid);
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(T[b | (j << Win<SA, LW>::fb)]);
-        if (C::NWIN == 3) {
-            inv8<0, Win<SA, 2>::nst, Win<SA, 2>::inv_before>(ar, a, Win<SA, 2>::widx(b));
-#pragma unroll
-            for (int j = 0; j < 8; j++) T[b | (j << Win<SA, 2>::fb)] = ar.to_word(a[j]);
-            __syncthreads();
-            b = Win<SA, 1>::base(tid);
-#pragma unroll
-            for (int j = 0; j < 8; j++) a[j] = ar.from_word(T[b | (j << Win<SA, 1>::fb)]);
-        }
-        if (C::NWIN >= 2) {
-            inv8<0, Win<SA, 1>::nst, Win<SA, 1>::inv_before>(ar, a, Win<SA, 1>::widx(b));
-            __syncthreads();
-#pragma unroll
-            for (int j = 0; j < 8; j++) T[b | (j << Win<SA, 1>::fb)] = ar.to_word(a[j]);
-            __syncthreads();
-            b = Win<SA, 0>::base(tid);
-#pragma unroll
-            for (int j = 0; j < 8; j++) a[j] = ar.from_word(T[b | (j << Win<SA, 0>::fb)]);
-        }
-        inv8<0, Win<SA, 0>::nst, Win<SA, 0>::inv_before>(ar, a, Win<SA, 0>::widx(b));
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const u64 res = j < 4 ? ar.canonical_inv_lo(a[j]) : ar.canonical_inv_hi(a[j]);
-            *Win<SA, 0>::gptr(g, b | (j << Win<SA, 0>::fb)) = res;
-        }
-    }
-}
-
-template <int SA, bool INV>
-__global__ void __launch_bounds__(kFusedThreads, 2) ntt_fused(NttArgs P) {
-    extern __shared__ __align__(16) u64 S_dyn[];
-    const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
-    if (q < kF64Bound) {
-        if (INV) fused_inv_body<SA, F64Arith>(P, S_dyn); else fused_fwd_body<SA, F64Arith>(P, S_dyn);
-    } else if (q < kLazyBound) {
-        if (INV) fused_inv_body<SA, IntArith<true>>(P, S_dyn); else fused_fwd_body<SA, IntArith<true>>(P, S_dyn);
-    } else {
-        if (INV) fused_inv_body<SA, IntArith<false>>(P, S_dyn); else fused_fwd_body<SA, IntArith<false>>(P, S_dyn);
-    }
-}
-
-template <int SA>
-cudaError_t launch_fused(bool inverse, int mod_num, int poly_num, const NttArgs& P, cudaStream_t st) {
-    constexpr int CS = (1 << (SA + 8)) / kFusedWords;           // CTAs per limb-polynomial
-    constexpr size_t smem = (4096 + kFusedWords) * sizeof(u64);   // work buffer + receive buffer
-    auto kf = inverse ? ntt_fused<SA, true> : ntt_fused<SA, false>;
-    cudaError_t e = cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(CS, mod_num, poly_num);
-    cfg.blockDim = dim3(kFusedThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = CS;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kf, P);
-}
-
 template <int SA>
 void launch_strided(bool inverse, dim3 grid_lp, const NttArgs& P, cudaStream_t st) {
     typedef StridedCfg<SA> C;
@@ -736,19 +508,6 @@ int run_ntt(ckks_b200_context* c, u64* d_data, int start_limb_off, int start_mod
     P.start_mod_idx = start_mod_idx;
     P.poly_mod_len = poly_mod_len;
 
-    static const bool use_fused = getenv("CKKS_B200_NTT_TWO_PASS") == nullptr;
-    if (use_fused && c->logN >= 14) {
-        cudaError_t e = cudaSuccess;
-        switch (c->logN - 8) {
-            case 6: e = launch_fused<6>(inverse, mod_num, poly_num, P, st); break;
-            case 7: e = launch_fused<7>(inverse, mod_num, poly_num, P, st); break;
-            case 8: e = launch_fused<8>(inverse, mod_num, poly_num, P, st); break;
-        }
-        count_launch(1);
-        CKB_CUDA(e);
-        CKB_CUDA(cudaGetLastError());
-        return CKKS_B200_OK;
-    }
     dim3 grid_c(c->N / (kChunk * kChunksPerCta), mod_num, poly_num);
     auto strided = [&]() {
         switch (c->logN - 8) {
