@@ -30,6 +30,8 @@
 // Between the two kernels of a transform the in-place buffer holds the back end's lazy
 // representation (for F64 the bit pattern of the double); the last kernel restores
 // canonical residues.
+#include <cuda_pipeline_primitives.h>
+
 #include "context.cuh"
 
 using namespace ckb;
@@ -247,98 +249,131 @@ constexpr int kChunk = 256;
 constexpr int kChunksPerCta = 16;
 constexpr int kThreadsB = 32 * kChunksPerCta;
 
-template <class A>
-__device__ __forceinline__ void fwd_contig_body(const NttArgs& P, u64* S) {
-    typedef typename A::V V;
-    const int lane = threadIdx.x & 31, vv = threadIdx.x >> 5;
-    const int limb = blockIdx.y, poly = blockIdx.z;
-    A ar;
-    ar.init(P, P.start_mod_idx + limb);
-    const uint32_t N = 1u << P.logN;
-    const uint32_t x0 = (blockIdx.x * kChunksPerCta + vv) * kChunk;   // position of the chunk
-    u64* g = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN) + x0;
-    u64* s = S + vv * kChunk;
-    V a[8];
-
-    // window bits 7..5: p = j*32 + lane
+// A CTA walks over `tiles` consecutive tiles of 16 chunks; warp v owns chunk v of every tile.
+// While a chunk is in the butterflies the next one is already on its way into the warp's
+// other shared-memory buffer (asynchronous 8-byte copies straight to the swizzled positions),
+// so loads stay in flight through the compute phases.
+__device__ __forceinline__ void prefetch_chunk(u64* sbuf, const u64* g, int lane) {
 #pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = ar.from_word(g[j * 32 + lane]);
-    fwd8<0, 3, 1>(ar, a, (N + x0) >> 8);             // kernel stages 0 (reducing), 1, 2
-#pragma unroll
-    for (int j = 0; j < 8; j++) s[swz(j * 32 + lane)] = ar.to_word(a[j]);
-    __syncwarp();
-
-    // window bits 4..2: p = hi*32 + j*4 + lo, lane = hi*4 + lo
-    {
-        const uint32_t lo = lane & 3, hi = lane >> 2;
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(hi * 32 + j * 4 + lo)]);
-        fwd8<0, 3, 1>(ar, a, ((N + x0) >> 5) + hi);  // stages 3 (reducing), 4, 5
-#pragma unroll
-        for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = ar.to_word(a[j]);
+    for (int j = 0; j < 8; j++) {
+        const uint32_t p = j * 32 + lane;
+        __pipeline_memcpy_async(sbuf + swz(p), g + p, 8);
     }
-    __syncwarp();
-
-    // window bits 2..0, stages on bits 1 and 0 only: p = lane*8 + j
-#pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(lane * 8 + j)]);
-    fwd8<1, 3, 2>(ar, a, ((N + x0) >> 3) + lane);    // stages 6 (reducing), 7
-    ulonglong2* go = reinterpret_cast<ulonglong2*>(g + lane * 8);
-#pragma unroll
-    for (int j = 0; j < 4; j++) go[j] = make_ulonglong2(ar.canonical_fwd(a[2 * j]), ar.canonical_fwd(a[2 * j + 1]));
+    __pipeline_commit();
 }
 
 template <class A>
-__device__ __forceinline__ void inv_contig_body(const NttArgs& P, u64* S) {
+__device__ __forceinline__ void fwd_contig_body(const NttArgs& P, u64* S, int tiles) {
     typedef typename A::V V;
     const int lane = threadIdx.x & 31, vv = threadIdx.x >> 5;
     const int limb = blockIdx.y, poly = blockIdx.z;
     A ar;
     ar.init(P, P.start_mod_idx + limb);
     const uint32_t N = 1u << P.logN;
-    const uint32_t x0 = (blockIdx.x * kChunksPerCta + vv) * kChunk;
-    u64* g = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN) + x0;
-    u64* s = S + vv * kChunk;
+    u64* gl = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN);
+    const uint32_t xfirst = (blockIdx.x * tiles * kChunksPerCta + vv) * kChunk;
+    u64* sbuf = S + vv * 2 * kChunk;            // two buffers per warp
     V a[8];
+    prefetch_chunk(sbuf, gl + xfirst, lane);
+    for (int t = 0; t < tiles; t++) {
+        const uint32_t x0 = xfirst + t * kChunksPerCta * kChunk;      // position of the chunk
+        u64* s = sbuf + (t & 1) * kChunk;
+        __syncwarp();                            // every lane is done with the other buffer
+        if (t + 1 < tiles) {
+            prefetch_chunk(sbuf + ((t + 1) & 1) * kChunk, gl + x0 + kChunksPerCta * kChunk, lane);
+            __pipeline_wait_prior(1);
+        } else {
+            __pipeline_wait_prior(0);
+        }
+        __syncwarp();
 
-    const ulonglong2* gi = reinterpret_cast<const ulonglong2*>(g + lane * 8);
+        // window bits 7..5: p = j*32 + lane
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        ulonglong2 t = gi[j];
-        a[2 * j] = ar.from_canonical(t.x);
-        a[2 * j + 1] = ar.from_canonical(t.y);
+        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(j * 32 + lane)]);
+        fwd8<0, 3, 1>(ar, a, (N + x0) >> 8);             // kernel stages 0 (reducing), 1, 2
+#pragma unroll
+        for (int j = 0; j < 8; j++) s[swz(j * 32 + lane)] = ar.to_word(a[j]);
+        __syncwarp();
+
+        // window bits 4..2: p = hi*32 + j*4 + lo, lane = hi*4 + lo
+        {
+            const uint32_t lo = lane & 3, hi = lane >> 2;
+#pragma unroll
+            for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(hi * 32 + j * 4 + lo)]);
+            fwd8<0, 3, 1>(ar, a, ((N + x0) >> 5) + hi);  // stages 3 (reducing), 4, 5
+#pragma unroll
+            for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = ar.to_word(a[j]);
+        }
+        __syncwarp();
+
+        // window bits 2..0, stages on bits 1 and 0 only: p = lane*8 + j
+#pragma unroll
+        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(lane * 8 + j)]);
+        fwd8<1, 3, 2>(ar, a, ((N + x0) >> 3) + lane);    // stages 6 (reducing), 7
+        ulonglong2* go = reinterpret_cast<ulonglong2*>(gl + x0 + lane * 8);
+#pragma unroll
+        for (int j = 0; j < 4; j++) go[j] = make_ulonglong2(ar.canonical_fwd(a[2 * j]), ar.canonical_fwd(a[2 * j + 1]));
     }
-    inv8<1, 3, 0>(ar, a, ((N + x0) >> 3) + lane);            // stages 0, 1 of this kernel
+}
+
+template <class A>
+__device__ __forceinline__ void inv_contig_body(const NttArgs& P, u64* S, int tiles) {
+    typedef typename A::V V;
+    const int lane = threadIdx.x & 31, vv = threadIdx.x >> 5;
+    const int limb = blockIdx.y, poly = blockIdx.z;
+    A ar;
+    ar.init(P, P.start_mod_idx + limb);
+    const uint32_t N = 1u << P.logN;
+    u64* gl = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN);
+    const uint32_t xfirst = (blockIdx.x * tiles * kChunksPerCta + vv) * kChunk;
+    u64* sbuf = S + vv * 2 * kChunk;
+    V a[8];
+    prefetch_chunk(sbuf, gl + xfirst, lane);
+    for (int t = 0; t < tiles; t++) {
+        const uint32_t x0 = xfirst + t * kChunksPerCta * kChunk;
+        u64* s = sbuf + (t & 1) * kChunk;
+        __syncwarp();
+        if (t + 1 < tiles) {
+            prefetch_chunk(sbuf + ((t + 1) & 1) * kChunk, gl + x0 + kChunksPerCta * kChunk, lane);
+            __pipeline_wait_prior(1);
+        } else {
+            __pipeline_wait_prior(0);
+        }
+        __syncwarp();
 #pragma unroll
-    for (int j = 0; j < 8; j++) s[swz(lane * 8 + j)] = ar.to_word(a[j]);
-    __syncwarp();
-    {
-        const uint32_t lo = lane & 3, hi = lane >> 2;
+        for (int j = 0; j < 8; j++) a[j] = ar.from_canonical(s[swz(lane * 8 + j)]);
+        inv8<1, 3, 0>(ar, a, ((N + x0) >> 3) + lane);            // stages 0, 1 of this kernel
 #pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(hi * 32 + j * 4 + lo)]);
-        inv8<0, 3, 2>(ar, a, ((N + x0) >> 5) + hi);          // stages 2, 3, 4
+        for (int j = 0; j < 8; j++) s[swz(lane * 8 + j)] = ar.to_word(a[j]);
+        __syncwarp();
+        {
+            const uint32_t lo = lane & 3, hi = lane >> 2;
 #pragma unroll
-        for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = ar.to_word(a[j]);
+            for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(hi * 32 + j * 4 + lo)]);
+            inv8<0, 3, 2>(ar, a, ((N + x0) >> 5) + hi);          // stages 2, 3, 4
+#pragma unroll
+            for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = ar.to_word(a[j]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(j * 32 + lane)]);
+        inv8<0, 3, 5>(ar, a, (N + x0) >> 8);                      // stages 5, 6, 7
+        // values stay lazy; the strided phase finishes the transform
+#pragma unroll
+        for (int j = 0; j < 8; j++) gl[x0 + j * 32 + lane] = ar.to_word(a[j]);
     }
-    __syncwarp();
-#pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(j * 32 + lane)]);
-    inv8<0, 3, 5>(ar, a, (N + x0) >> 8);                      // stages 5, 6, 7
-    // values stay lazy; the strided phase finishes the transform
-#pragma unroll
-    for (int j = 0; j < 8; j++) g[j * 32 + lane] = ar.to_word(a[j]);
 }
 
 template <bool INV>
-__global__ void __launch_bounds__(kThreadsB, 2) ntt_contig(NttArgs P) {
-    __shared__ u64 S[kChunk * kChunksPerCta];
+__global__ void __launch_bounds__(kThreadsB, 2) ntt_contig(NttArgs P, int tiles) {
+    extern __shared__ __align__(16) u64 S[];       // 2 buffers x 16 chunks x 256 words
     const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
     if (q < kF64Bound) {
-        if (INV) inv_contig_body<F64Arith>(P, S); else fwd_contig_body<F64Arith>(P, S);
+        if (INV) inv_contig_body<F64Arith>(P, S, tiles); else fwd_contig_body<F64Arith>(P, S, tiles);
     } else if (q < kLazyBound) {
-        if (INV) inv_contig_body<IntArith<true>>(P, S); else fwd_contig_body<IntArith<true>>(P, S);
+        if (INV) inv_contig_body<IntArith<true>>(P, S, tiles); else fwd_contig_body<IntArith<true>>(P, S, tiles);
     } else {
-        if (INV) inv_contig_body<IntArith<false>>(P, S); else fwd_contig_body<IntArith<false>>(P, S);
+        if (INV) inv_contig_body<IntArith<false>>(P, S, tiles); else fwd_contig_body<IntArith<false>>(P, S, tiles);
     }
 }
 
@@ -518,11 +553,18 @@ int run_ntt(ckks_b200_context* c, u64* d_data, int start_limb_off, int start_mod
             case 8: launch_strided<8>(inverse, grid_c, P, st); break;
         }
     };
+    // the contiguous kernel walks over several tiles per CTA so that its prefetch has something to run ahead of
+    const int ntile = c->N / (kChunk * kChunksPerCta);
+    const int tiles = ntile >= 4 ? 4 : ntile;
+    const size_t smem_c = 2 * kChunk * kChunksPerCta * sizeof(u64);
+    dim3 grid_k(ntile / tiles, mod_num, poly_num);
     if (!inverse) {
         strided();
-        ntt_contig<false><<<grid_c, kThreadsB, 0, st>>>(P);
+        CKB_CUDA(cudaFuncSetAttribute(ntt_contig<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c));
+        ntt_contig<false><<<grid_k, kThreadsB, smem_c, st>>>(P, tiles);
     } else {
-        ntt_contig<true><<<grid_c, kThreadsB, 0, st>>>(P);
+        CKB_CUDA(cudaFuncSetAttribute(ntt_contig<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c));
+        ntt_contig<true><<<grid_k, kThreadsB, smem_c, st>>>(P, tiles);
         strided();
     }
     count_launch(2);
