@@ -86,14 +86,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 #define CKB_PROF_FLUSH(base)
 #endif
 
-// Bounded wait.  Returns false when the budget ran out (the flag is raised).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* flags, int where) {
+// Bounded wait.  Returns false when the budget ran out (the flag is raised) or when another
+// role of the CTA has given up (abort is the CTA's shared flag, looked at from the slow path only).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* flags, int where, const int* abort) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > WAIT_BUDGET) {
-            atomicExch(&flags[1], where);
-            return false;
+        if ((++spins & 63) == 0) {
+            if (*(const volatile int*)abort) return false;
+            if (clock64() - t0 > WAIT_BUDGET) {
+                atomicExch(&flags[1], where);
+                return false;
+            }
         }
     }
     return true;
@@ -136,9 +141,12 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 B,
 // 128 B from one K half to the next (leading offset), 256 B from one 8-row group to the
 // next (stride offset), descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(256 >> 4) << 32) |
-           ((uint64_t)1 << 46);
+// Shared-memory addresses are below 2^18, so the 14-bit address field is addr >> 4 and a byte
+// offset inside the stage is added to the low word as offset >> 4 without touching the rest.
+constexpr uint32_t DESC_LO = (uint32_t)(128 >> 4) << 16;                    // leading offset
+constexpr uint32_t DESC_HI = (uint32_t)(256 >> 4) | (1u << (46 - 32));      // stride offset, version
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr16) {            // addr16 = shared address >> 4
+    return ((uint64_t)DESC_HI << 32) | (uint64_t)(DESC_LO + addr16);
 }
 // Instruction descriptor: s32 accumulate, A signed or unsigned 8-bit, B unsigned 8-bit,
 // both K-major, M = 128, N = n.
@@ -285,36 +293,43 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            uint32_t it = 0;           // running stage counter
+            uint32_t s = 0, ph = 0, issued = 0;    // ring position, its phase parity, copies in flight at most NS
             bool ok = true;
             for (long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 const int mt = (int)(item % P.MT);
                 const long ct = item / P.MT;
+                const uint8_t* const asrc0 = P.wplanes + (size_t)mt * P.KBN * C_::A_STAGE;
                 for (int limb = limbs_n - 1; limb >= 0 && ok; limb--) {
-                    const uint8_t* asrc = P.wplanes + (size_t)mt * P.KBN * C_::A_STAGE;
+                    const uint8_t* asrc = asrc0;
                     const uint8_t* bsrc = P.xplanes + ((size_t)limb * P.CT + ct) * P.KBN * C_::B_STAGE;
-                    for (int kb = 0; kb < P.KBN; kb++, it++) {
-                        const int s = it % NS;
-                        const uint32_t ph = (it / NS) & 1;
-                        if (it >= (uint32_t)NS && !mbar_wait(empty_bar + 8 * s, ph ^ 1, P.flags, 1)) { ok = false; break; }
-                        if (*(volatile int*)&abort_flag) { ok = false; break; }
+                    for (int kb = 0; kb < P.KBN; kb++) {
+                        if (issued >= (uint32_t)NS && !mbar_wait(empty_bar + 8 * s, ph ^ 1, P.flags, 1, &abort_flag)) { ok = false; break; }
                         const uint32_t dst = smem_base + s * C_::STAGE;
                         mbar_arrive_expect_tx(full_bar + 8 * s, C_::STAGE);
-                        bulk_g2s(dst, asrc + (size_t)kb * C_::A_STAGE, C_::A_STAGE, full_bar + 8 * s);
-                        bulk_g2s(dst + C_::A_STAGE, bsrc + (size_t)kb * C_::B_STAGE, C_::B_STAGE, full_bar + 8 * s);
+                        bulk_g2s(dst, asrc, C_::A_STAGE, full_bar + 8 * s);
+                        bulk_g2s(dst + C_::A_STAGE, bsrc, C_::B_STAGE, full_bar + 8 * s);
+                        asrc += C_::A_STAGE;
+                        bsrc += C_::B_STAGE;
+                        issued++;
+                        if (++s == (uint32_t)NS) { s = 0; ph ^= 1; }
                     }
                 }
             }
             if (!ok) atomicExch(&abort_flag, 1);
-            // Drain: every copy this thread issued must have landed before the CTA exits.
-            const uint32_t issued = it;
-            for (uint32_t j = issued > (uint32_t)NS ? issued - NS : 0; j < issued; j++)
-                mbar_wait(full_bar + 8 * (j % NS), (j / NS) & 1, P.flags, 2);
+            // Drain: every copy this thread issued must have landed before the CTA exits.  The last
+            // min(issued, NS) copies sit in the ring positions before s, going backwards.
+            uint32_t n = issued < (uint32_t)NS ? issued : (uint32_t)NS;
+            uint32_t ds = s, dph = ph;
+            for (uint32_t j = 0; j < n; j++) {
+                if (ds == 0) { ds = NS; dph ^= 1; }
+                ds--;
+                mbar_wait(full_bar + 8 * ds, dph, P.flags, 2, &abort_flag);
+            }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            uint32_t it = 0, tile = 0;
+            uint32_t s = 0, ph = 0, tile = 0;
             bool ok = true;
             CKB_PROF_DECL
             const long long prof_start = clock64();
@@ -325,44 +340,49 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
             constexpr uint32_t idesc_head_s = instr_desc(TC * (SC - 1), true);
             constexpr uint32_t idesc_tail_u = instr_desc(TC, false);
             constexpr uint32_t idesc_tail_s = instr_desc(TC, true);
+            const uint32_t base16 = smem_base >> 4;
             for (long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 for (int limb = limbs_n - 1; limb >= 0 && ok; limb--, tile++) {
                     CKB_PROF_BEGIN();
-                    if (tile > 0 && !mbar_wait(tmem_empty_bar, (tile - 1) & 1, P.flags, 3)) { ok = false; break; }
+                    if (tile > 0 && !mbar_wait(tmem_empty_bar, (tile - 1) & 1, P.flags, 3, &abort_flag)) { ok = false; break; }
                     CKB_PROF_END(0);
                     tc_fence_after();
-                    for (int kb = 0; kb < P.KBN; kb++, it++) {
-                        const int s = it % NS;
+                    for (int kb = 0; kb < P.KBN; kb++) {
                         CKB_PROF_BEGIN();
-                        if (!mbar_wait(full_bar + 8 * s, (it / NS) & 1, P.flags, 4)) { ok = false; break; }
+                        if (!mbar_wait(full_bar + 8 * s, ph, P.flags, 4, &abort_flag)) { ok = false; break; }
                         CKB_PROF_END(1);
-                        if (*(volatile int*)&abort_flag) { ok = false; break; }
                         tc_fence_after();
-                        const uint32_t a_base = smem_base + s * C_::STAGE;
-                        const uint32_t b_base = a_base + C_::A_STAGE;
-#pragma unroll
-                        for (int ks = 0; ks < KS; ks++) {
-                            const uint64_t bdesc = smem_desc(b_base + ks * SC * B_PLANE_STEP);
-                            const bool first = (kb == 0 && ks == 0);
+                        const uint32_t a16 = base16 + s * (C_::STAGE >> 4);
+                        const uint32_t b16 = a16 + (C_::A_STAGE >> 4);
+                        if (kb == 0) {
+                            // First K step of the tile: plane 0 overwrites its columns; every later plane
+                            // accumulates into the columns it shares with earlier planes and overwrites
+                            // the new top diagonal (ciphertext plane SC-1) with a second instruction.
 #pragma unroll
                             for (int a = 0; a < SW; a++) {
-                                const uint64_t adesc = smem_desc(a_base + (a * KS + ks) * A_PLANE_STEP);
+                                const uint64_t adesc = smem_desc(a16 + ((a * KS) * A_PLANE_STEP >> 4));
                                 const bool sgn = (a == SW - 1);
                                 const uint32_t d = tmem_base + a * TC;
-                                if (!first) {
-                                    umma_i8(d, adesc, bdesc, sgn ? idesc_full_s : idesc_full_u, 1);
-                                } else if (a == 0) {
-                                    umma_i8(d, adesc, bdesc, idesc_full_u, 0);
+                                if (a == 0) {
+                                    umma_i8(d, adesc, smem_desc(b16), idesc_full_u, 0);
                                 } else {
-                                    // columns shared with earlier planes accumulate, the new
-                                    // top diagonal (ciphertext plane SC-1) is overwritten
-                                    umma_i8(d, adesc, bdesc, sgn ? idesc_head_s : idesc_head_u, 1);
-                                    const uint64_t btail = smem_desc(b_base + (ks * SC + SC - 1) * B_PLANE_STEP);
-                                    umma_i8(d + (SC - 1) * TC, adesc, btail, sgn ? idesc_tail_s : idesc_tail_u, 0);
+                                    umma_i8(d, adesc, smem_desc(b16), sgn ? idesc_head_s : idesc_head_u, 1);
+                                    umma_i8(d + (SC - 1) * TC, adesc, smem_desc(b16 + ((SC - 1) * B_PLANE_STEP >> 4)),
+                                            sgn ? idesc_tail_s : idesc_tail_u, 0);
                                 }
                             }
                         }
+#pragma unroll
+                        for (int ks = 0; ks < KS; ks++) {
+                            if (ks == 0 && kb == 0) continue;
+                            const uint64_t bdesc = smem_desc(b16 + (ks * SC * B_PLANE_STEP >> 4));
+#pragma unroll
+                            for (int a = 0; a < SW; a++)
+                                umma_i8(tmem_base + a * TC, smem_desc(a16 + ((a * KS + ks) * A_PLANE_STEP >> 4)), bdesc,
+                                        a == SW - 1 ? idesc_full_s : idesc_full_u, 1);
+                        }
                         umma_commit(empty_bar + 8 * s);
+                        if (++s == (uint32_t)NS) { s = 0; ph ^= 1; }
                     }
                     if (ok) umma_commit(tmem_full_bar);
                 }
@@ -391,7 +411,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
             const long c0 = P.col_begin + ct * TC + half * 16;
             for (int limb = limbs_n - 1; limb >= 0 && ok; limb--, tile++) {
                 CKB_PROF_BEGIN();
-                if (!mbar_wait(tmem_full_bar, tile & 1, P.flags, 5)) { ok = false; break; }
+                if (!mbar_wait(tmem_full_bar, tile & 1, P.flags, 5, &abort_flag)) { ok = false; break; }
                 CKB_PROF_END(0);
                 tc_fence_after();
                 CKB_PROF_BEGIN();
