@@ -295,21 +295,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
         if (lane == 0) {
             uint32_t s = 0, ph = 0, issued = 0;    // ring position, its phase parity, copies in flight at most NS
             bool ok = true;
+            const int krot = (int)((blockIdx.x / P.MT) % P.KBN);
             for (long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 const int mt = (int)(item % P.MT);
                 const long ct = item / P.MT;
                 const uint8_t* const asrc0 = P.wplanes + (size_t)mt * P.KBN * C_::A_STAGE;
                 for (int limb = limbs_n - 1; limb >= 0 && ok; limb--) {
-                    const uint8_t* asrc = asrc0;
-                    const uint8_t* bsrc = P.xplanes + ((size_t)limb * P.CT + ct) * P.KBN * C_::B_STAGE;
+                    const uint8_t* const bsrc0 = P.xplanes + ((size_t)limb * P.CT + ct) * P.KBN * C_::B_STAGE;
+                    // The sum over K is exact, so its order is free: every CTA starts at another
+                    // K block, which keeps the CTAs from asking L2 for the same weight block at once.
+                    int kbr = krot;
                     for (int kb = 0; kb < P.KBN; kb++) {
                         if (issued >= (uint32_t)NS && !mbar_wait(empty_bar + 8 * s, ph ^ 1, P.flags, 1, &abort_flag)) { ok = false; break; }
                         const uint32_t dst = smem_base + s * C_::STAGE;
                         mbar_arrive_expect_tx(full_bar + 8 * s, C_::STAGE);
-                        bulk_g2s(dst, asrc, C_::A_STAGE, full_bar + 8 * s);
-                        bulk_g2s(dst + C_::A_STAGE, bsrc, C_::B_STAGE, full_bar + 8 * s);
-                        asrc += C_::A_STAGE;
-                        bsrc += C_::B_STAGE;
+                        bulk_g2s(dst, asrc0 + (size_t)kbr * C_::A_STAGE, C_::A_STAGE, full_bar + 8 * s);
+                        bulk_g2s(dst + C_::A_STAGE, bsrc0 + (size_t)kbr * C_::B_STAGE, C_::B_STAGE, full_bar + 8 * s);
+                        if (++kbr == P.KBN) kbr = 0;
                         issued++;
                         if (++s == (uint32_t)NS) { s = 0; ph ^= 1; }
                     }
