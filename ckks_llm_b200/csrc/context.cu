@@ -226,6 +226,56 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
         t_mu[k] = make_ulonglong2(hi, lo);
     }
 
+    // Byte planes of the ModUp constants for the tensor-core kernel, in the order its MMA
+    // descriptors read them: per 32-deep K step a block of tc_npad rows x 32 bytes made of core
+    // matrices (8 rows x 16 bytes, 128 bytes from one K half to the other, 256 bytes from one
+    // 8-row group to the next).  A level qualifies when every target modulus lies in
+    // [2^40, 2^62) (the kernel reduces with an FP64 quotient estimate) and when
+    // sum_j rb_j*h_j (h_j = Qblk/q_j mod t_k) can never fall below v*F (F = Qblk mod t_k): the 128-bit
+    // difference the reference forms would wrap there, and only the CUDA-core kernel reproduces that wrap.
+    const int apad = (A + 3) / 4 * 4;
+    c->tc_kpad = apad * 8;
+    c->tc_npad = (T * 8 + 15) / 16 * 16;
+    const size_t tile_bytes = (size_t)c->tc_kpad * c->tc_npad;
+    std::vector<uint8_t> planes(T > 0 ? (size_t)q_num * B * tile_bytes : 0, 0);
+    std::vector<double> t_inv(T ? T : 1, 0.0);
+    c->mu_tc_ok.assign(q_num, 0);
+    bool t_range_ok = T > 0 && T * 8 <= 256 && A <= 16;
+    for (int k = 0; k < T; k++) {
+        t_inv[k] = 1.0 / (double)tv[k];
+        if (tv[k] < (1ull << 40) || tv[k] >= (1ull << 62)) t_range_ok = false;
+    }
+    for (int l = 0; l < q_num && T > 0; l++) {
+        int blocks = (l + 1 + A - 1) / A;
+        bool ok = t_range_ok;
+        for (int b = 0; b < blocks; b++) {
+            int cnt = std::min(A, l + 1 - b * A);
+            uint8_t* tile = planes.data() + ((size_t)l * B + b) * tile_bytes;
+            for (int k = 0; k < T; k++) {
+                const u64 tk = tv[k];
+                const u64 full = blk_mod_t[((size_t)l * B + b) * T + k];
+                for (int j = 0; j < cnt; j++) {
+                    u64 cst = hat_mod_t[(((size_t)l * B + b) * T + k) * A + j];
+                    // v <= (sum_j rb_j/q_j)(1 + 2^-45) even after rounding, so h_j*q_j >= F(1 + 2^-40) for every j
+                    // keeps sum_j rb_j*h_j >= v*F.  A one-limb digit has h = 1 and v = 0 as long as
+                    // (q-1)/q rounds below 1.0, which it does for q < 2^52.
+                    const u64 qj = qv[b * A + j];
+                    if (cnt == 1 ? qj >= (1ull << 52) : (u128)cst * qj < (u128)full + (full >> 40) + 1) ok = false;
+                    for (int bb = 0; bb < 8; bb++) {
+                        const int kk = j * 8 + bb, ks = kk / 32, kc = (kk % 32) / 16, kin = kk % 16;
+                        for (int a = 0; a < 8; a++) {
+                            const int n = k * 8 + a;
+                            tile[(size_t)ks * c->tc_npad * 32 + (size_t)(n / 8) * 256 + kc * 128 + (n % 8) * 16 + kin] =
+                                (uint8_t)(cst >> (8 * a));
+                        }
+                        cst = h_mulmod(cst, 256 % tk, tk);
+                    }
+                }
+            }
+        }
+        c->mu_tc_ok[l] = ok ? 1 : 0;
+    }
+
     int st = CKKS_B200_OK;
     std::vector<u64> mods(c->moduli.begin(), c->moduli.end());
     if (!st) st = upload(&c->tw_fwd, fwd);
@@ -241,6 +291,11 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
     if (!st) st = upload(&c->mu_hat_mod_t, hat_mod_t);
     if (!st) st = upload(&c->mu_blk_mod_t, blk_mod_t);
     if (!st) st = upload(&c->d_t_mu, t_mu);
+    if (!st) st = upload(&c->mu_planes, planes);
+    if (!st) st = upload(&c->d_t_inv, t_inv);
+    if (!st && cudaMalloc(&c->d_flags, 16 * sizeof(int)) != cudaSuccess) st = CKKS_B200_ERR_NOMEM;
+    if (!st && cudaMemset(c->d_flags, 0, 16 * sizeof(int)) != cudaSuccess) st = CKKS_B200_ERR_CUDA;
+    if (!st && cudaMallocHost(&c->h_flags, 16 * sizeof(int)) != cudaSuccess) st = CKKS_B200_ERR_NOMEM;
     if (st) { ckks_b200_context_destroy(c); return st; }
     *out = c;
     return CKKS_B200_OK;
@@ -251,6 +306,8 @@ extern "C" int ckks_b200_context_destroy(ckks_b200_context* c) {
     DeviceGuard guard(c->device);
     cudaFree(c->tw_fwd); cudaFree(c->tw_inv); cudaFree(c->tw_fwd_d); cudaFree(c->tw_inv_d); cudaFree(c->d_moduli); cudaFree(c->d_ninv); cudaFree(c->d_qinv64);
     cudaFree(c->mu_hat_inv); cudaFree(c->mu_hat_mod_t); cudaFree(c->mu_blk_mod_t);
+    cudaFree(c->mu_planes); cudaFree(c->d_t_inv); cudaFree(c->d_flags);
+    if (c->h_flags) cudaFreeHost(c->h_flags);
     cudaFree(c->d_t_mu); cudaFree(c->h2d_buf); cudaFree(c->h2d_buf2); cudaFree(c->ptr_buf); cudaFree(c->pack_buf);
     delete c;
     return CKKS_B200_OK;

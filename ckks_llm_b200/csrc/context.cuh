@@ -35,6 +35,20 @@ struct ckks_b200_context {
     u64* mu_blk_mod_t = nullptr;
     ulonglong2* d_t_mu = nullptr;            // [t_num] Barrett mu {hi, lo}
 
+    // Tensor-core ModUp (modup_umma.cu).  The contraction runs over the bytes of the rb_j:
+    // K index j*8+b stands for byte b of rb_j, and the constant it meets is
+    // ((Qblk/q_j) * 2^(8b)) mod t_k, itself cut into eight bytes (row k*8+a = byte a for target k).
+    //   mu_planes [l][blocks_max][tc_kpad/32][tc_npad rows][32 bytes]  in MMA core-matrix order
+    //   mu_tc_ok  [l]  1 when level l may take the tensor-core kernel
+    //   d_t_inv   [t_num] 1.0 / t_k
+    uint8_t* mu_planes = nullptr;
+    std::vector<uint8_t> mu_tc_ok;
+    double* d_t_inv = nullptr;
+    int tc_kpad = 0, tc_npad = 0;
+    int modup_algo = 0;                      // CKKS_B200_MODUP_AUTO / _TENSOR / _SIMT
+    int* d_flags = nullptr;                  // [16] [1] = site of a device-side wait that ran out
+    int* h_flags = nullptr;                  // pinned mirror
+
     // Scratch for the *_host entry points, grown on demand.
     u64* h2d_buf = nullptr;
     size_t h2d_cap = 0;
@@ -52,4 +66,7 @@ namespace ckb {
 u64 find_mth_root(u64 M, u64 q);
 void fill_psi_tables(u64 psi, u64 q, uint32_t n, std::vector<u64>& tab, std::vector<u64>& tabinv);
 int ensure_buf(u64** buf, size_t* cap, size_t words);
+// Tensor-core ModUp (modup_umma.cu): whether level l qualifies, and the launch.
+bool modup_tensor_ok(const ckks_b200_context* c, int l);
+int modup_tensor(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int batch, cudaStream_t st);
 }  // namespace ckb

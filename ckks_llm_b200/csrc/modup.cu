@@ -2,7 +2,9 @@
 // floating-point overflow count), the operation of Context_23::modUpQjtoT_23 in the
 // reference (src/ckks/include/BasisConv.cuh:84-179).
 //
-// One thread converts one coefficient of one digit: it reads the alpha residues of the
+// This file holds the CUDA-core kernel and the dispatch; levels whose tables qualify go to the
+// tensor-core kernel in modup_umma.cu.  In the CUDA-core kernel
+// one thread converts one coefficient of one digit: it reads the alpha residues of the
 // digit (coalesced across the warp, one limb at a time), forms rb_j = x_j * (Qblk/q_j)^-1
 // mod q_j and the overflow count v = trunc(sum_j rb_j / q_j) in IEEE double precision in
 // limb order, and for every target modulus t_k accumulates sum_j rb_j * (Qblk/q_j mod t_k)
@@ -81,6 +83,10 @@ int run_modup(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int batc
     if (batch == 0) return CKKS_B200_OK;
     DeviceGuard guard(c->device);
     CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", c->device);
+    CKB_REQUIRE(c->modup_algo != CKKS_B200_MODUP_TENSOR || modup_tensor_ok(c, l), CKKS_B200_ERR_UNSUPPORTED,
+                "level %d does not qualify for the tensor-core ModUp (moduli outside [2^40,2^62), more than 16 of them, "
+                "or tables on which the reference's 128-bit difference could wrap)", l);
+    if (c->modup_algo != CKKS_B200_MODUP_SIMT && modup_tensor_ok(c, l)) return modup_tensor(c, d_out, d_in, l, batch, st);
     const int A = c->alpha, B = c->blocks_max, T = c->t_num;
     ModUpArgs P;
     P.out = d_out;
@@ -109,6 +115,28 @@ int run_modup(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int batc
 
 }  // namespace
 
+extern "C" int ckks_b200_modup_set_algo(ckks_b200_context* c, int algo) {
+    CKB_REQUIRE(c != nullptr, CKKS_B200_ERR_ARG, "null argument");
+    CKB_REQUIRE(algo >= 0 && algo <= 2, CKKS_B200_ERR_ARG, "unknown algorithm %d", algo);
+    c->modup_algo = algo;
+    return CKKS_B200_OK;
+}
+
+// Synchronise `stream` and report whether a bounded device-side wait of a tensor-core
+// ModUp on this context ran out since the last check.
+extern "C" int ckks_b200_context_check(ckks_b200_context* c, void* stream) {
+    CKB_REQUIRE(c != nullptr, CKKS_B200_ERR_ARG, "null argument");
+    DeviceGuard guard(c->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", c->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    CKB_CUDA(cudaMemcpyAsync(c->h_flags, c->d_flags, 16 * sizeof(int), cudaMemcpyDeviceToHost, st));
+    CKB_CUDA(cudaMemsetAsync(c->d_flags, 0, 16 * sizeof(int), st));
+    CKB_CUDA(cudaStreamSynchronize(st));
+    CKB_REQUIRE(c->h_flags[1] == 0, CKKS_B200_ERR_TIMEOUT,
+                "a device-side wait ran out of its clock budget (site %d)", c->h_flags[1]);
+    return CKKS_B200_OK;
+}
+
 extern "C" int ckks_b200_modup_qj_to_t(ckks_b200_context* c, uint64_t* d_out, const uint64_t* d_in,
                                        int l, int batch, void* stream) {
     return run_modup(c, (u64*)d_out, (const u64*)d_in, l, batch, (cudaStream_t)stream);
@@ -132,6 +160,5 @@ extern "C" int ckks_b200_modup_qj_to_t_host(ckks_b200_context* c, uint64_t* h_ou
     st = run_modup(c, c->h2d_buf2, c->h2d_buf, l, batch, 0);
     if (st) return st;
     CKB_CUDA(cudaMemcpyAsync(h_out, c->h2d_buf2, out_words * 8, cudaMemcpyDeviceToHost, 0));
-    CKB_CUDA(cudaStreamSynchronize(0));
-    return CKKS_B200_OK;
+    return ckks_b200_context_check(c, 0);
 }

@@ -1,0 +1,287 @@
+// ModUp on the 5th-generation tensor cores (tcgen05, sm_100a): the operation of
+// Context_23::modUpQjtoT_23 in the reference (src/ckks/include/BasisConv.cuh:84-179) with the
+// alpha x t_num table product moved off the 64-bit integer multiplier.
+//
+// For one coefficient of one digit the conversion is
+//     out_k = ( sum_j rb_j * (Qblk/q_j mod t_k)  -  v * (Qblk mod t_k) )  mod t_k ,
+//     rb_j = x_j * (Qblk/q_j)^-1 mod q_j ,   v = trunc( sum_j rb_j / q_j )  in IEEE doubles.
+// Write rb_j in bytes, rb_j = sum_b rb_{j,b} 2^(8b).  Modulo t_k the sum equals
+//     sum_{j,b} rb_{j,b} * c_{k,j,b} ,   c_{k,j,b} = ((Qblk/q_j) * 2^(8b)) mod t_k ,
+// and with c_{k,j,b} cut into bytes too this is an unsigned 8-bit matrix product:
+//     D[x][k*8+a] = sum_{(j,b)} rb_{j,b}[x] * byte_a(c_{k,j,b}) ,   K = 8*alpha,  N = 8*t_num .
+// One UMMA (M = 128 coefficients) per 32 bytes of K does it; the s32 results stay below 2^23.
+// Each thread then recombines its row, sum_a D_a 2^(8a) < 2^80, reduces it modulo t_k with an
+// FP64 quotient estimate (t_k in [2^40, 2^62)), subtracts the overflow term from a small table and
+// stores.  What is left on the integer pipes is the alpha Shoup products that make rb_j.
+//
+// The result is the exact residue.  The reference (and the CUDA-core kernel in modup.cu) forms
+// the difference in 128 bits, which equals the exact residue unless the sum falls below
+// v*(Qblk mod t_k); context creation checks the tables for that and sends such levels to the
+// CUDA-core kernel.
+//
+// A CTA runs four independent groups of 128 threads.  A group owns one operand tile in shared
+// memory and 128 columns of tensor memory and walks over tiles of 128 coefficients: every
+// thread prepares its coefficient's row, one thread issues the instructions, all wait on the
+// group's mbarrier (bounded; a wait that runs out raises a flag and the group leaves), then
+// every thread finishes its own row.  The next tile's residues are loaded before that wait.
+#include "context.cuh"
+#include "umma.cuh"
+
+using namespace ckb;
+using namespace ckb::umma;
+
+namespace {
+
+constexpr int GROUPS = 4;
+constexpr int THREADS = 128 * GROUPS;
+constexpr int GROUP_COLS = 128;          // tensor-memory columns per group
+
+struct ModUpTcArgs {
+    u64* out;
+    const u64* in;
+    const u64* q;                 // q moduli [q_num]
+    const u64* t;                 // t moduli [t_num]
+    const double* t_inv;          // [t_num]
+    const ulonglong2* hat_inv;    // [blocks_max*alpha] for this level
+    const u64* blk_mod_t;         // [blocks_max][t_num] for this level
+    const uint8_t* planes;        // [blocks_max][kpad/32][npad][32] for this level
+    int* flags;
+    uint32_t N;
+    int q_num, t_num, alpha, l, blocks, batch, npad;
+};
+
+__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+// AND of a predicate over the 128 threads of a group (also a barrier).
+__device__ __forceinline__ bool group_all(bool p, int id) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %1, 0;\n\t"
+        "bar.red.and.pred q, %2, 128, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)p), "r"(id)
+        : "memory");
+    return r != 0;
+}
+
+template <int APAD>
+__global__ void __launch_bounds__(THREADS, 1) modup_umma_kernel(ModUpTcArgs P) {
+    constexpr int KSTEPS = APAD * 8 / 32;
+    constexpr int A_TILE = KSTEPS * TM * 32;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t bars[GROUPS];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int g = tid >> 7, r = tid & 127;
+    const int T = P.t_num;
+    const int b_tile = KSTEPS * P.npad * 32;
+    uint8_t* sA = smem + g * A_TILE;
+    uint8_t* sB = smem + GROUPS * A_TILE;                                   // [blocks][KSTEPS][npad*32]
+    u64* s_q = reinterpret_cast<u64*>(sB + P.blocks * b_tile);             // [blocks][APAD]
+    ulonglong2* s_hinv = reinterpret_cast<ulonglong2*>(s_q + P.blocks * APAD);   // [blocks][APAD]
+    u64* s_vt = reinterpret_cast<u64*>(s_hinv + P.blocks * APAD);          // [blocks][APAD+1][T]  v*(Qblk mod t_k) mod t_k
+    u64* s_t = s_vt + P.blocks * (APAD + 1) * T;                           // [T]
+    double* s_tinv = reinterpret_cast<double*>(s_t + T);                   // [T]
+
+    for (int i = tid; i < P.blocks * b_tile / 16; i += THREADS)
+        reinterpret_cast<uint4*>(sB)[i] = reinterpret_cast<const uint4*>(P.planes)[i];
+    for (int i = tid; i < P.blocks * APAD; i += THREADS) {
+        const int blk = i / APAD, j = i % APAD;
+        const bool live = j < P.alpha && blk * P.alpha + j <= P.l;
+        s_q[i] = live ? P.q[blk * P.alpha + j] : 1;
+        s_hinv[i] = live ? P.hat_inv[blk * P.alpha + j] : make_ulonglong2(0, 0);
+    }
+    for (int i = tid; i < P.blocks * T; i += THREADS) {
+        const int blk = i / T, k = i % T;
+        const u64 tk = P.t[k], bm = P.blk_mod_t[i];
+        u64 acc = 0;
+        for (int v = 0; v <= APAD; v++) {
+            s_vt[(blk * (APAD + 1) + v) * T + k] = acc;
+            acc += bm;                       // bm < t_k < 2^62: no overflow
+            if (acc >= tk) acc -= tk;
+        }
+    }
+    for (int i = tid; i < T; i += THREADS) {
+        s_t[i] = P.t[i];
+        s_tinv[i] = P.t_inv[i];
+    }
+    if (tid == 0) {
+        for (int i = 0; i < GROUPS; i++) mbar_init(smem_u32(&bars[i]), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&tmem_slot), GROUPS * GROUP_COLS);
+        tmem_relinquish();
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the constant tiles, for the MMA's reads
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_g = tmem_slot + g * GROUP_COLS;
+    const uint32_t bar = smem_u32(&bars[g]);
+    const uint32_t a16 = smem_u32(sA) >> 4, b16 = smem_u32(sB) >> 4;
+    const uint32_t idesc = instr_desc(P.npad, false);
+
+    const long tiles_x = P.N / TM;
+    const long total = (long)P.batch * P.blocks * tiles_x;
+    const long stride = (long)gridDim.x * GROUPS;
+    long tile = (long)blockIdx.x * GROUPS + g;
+
+    // residues of a tile's coefficient r, one per limb of its digit (zero beyond the digit)
+    auto load_tile = [&](long tl, u64 (&x)[APAD]) {
+        const long xt = tl % tiles_x;
+        const long rest = tl / tiles_x;
+        const int blk = (int)(rest % P.blocks);
+        const long bt = rest / P.blocks;
+        const int cnt = min(P.alpha, P.l + 1 - blk * P.alpha);
+        const u64* src = P.in + ((size_t)bt * P.q_num + (size_t)blk * P.alpha) * P.N + xt * TM + r;
+#pragma unroll
+        for (int j = 0; j < APAD; j++) x[j] = j < cnt ? src[(size_t)j * P.N] : 0;
+    };
+
+    u64 cur[APAD];
+    if (tile < total) load_tile(tile, cur);
+    uint32_t phase = 0;
+    bool ok = true;
+    // byte offset of this thread's row inside a K step: 8-row group, row in the group
+    const uint32_t row_off = (uint32_t)(r >> 3) * 256 + (uint32_t)(r & 7) * 16;
+    while (tile < total && ok) {
+        const long xt = tile % tiles_x;
+        const long rest = tile / tiles_x;
+        const int blk = (int)(rest % P.blocks);
+        const long bt = rest / P.blocks;
+
+        // ---- rb_j, the overflow count, and this coefficient's row of the byte matrix ----
+        double vv = 0.0;
+#pragma unroll
+        for (int j = 0; j < APAD; j++) {
+            const u64 qj = s_q[blk * APAD + j];
+            const ulonglong2 hi = s_hinv[blk * APAD + j];
+            const u64 rb = shoup_mul(cur[j], hi.x, hi.y, qj);      // zero beyond the digit (hi = 0)
+            vv += __ddiv_rn((double)rb, (double)qj);               // adds 0.0 there: the sum is unchanged
+            // K index j*8+b: step j/4, K half (j%4)/2, byte offset (j%2)*8 inside the 16-byte row
+            *reinterpret_cast<u64*>(sA + (j / 4) * (TM * 32) + ((j % 4) / 2) * 128 + row_off + (j % 2) * 8) = rb;
+        }
+        const int v = (int)vv;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        const long next = tile + stride;
+        if (next < total) load_tile(next, cur);
+        group_sync(1 + g);
+        if (r == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++)
+                umma_i8(tmem_g, smem_desc(a16 + (ks * TM * 32 >> 4)),
+                        smem_desc(b16 + ((blk * b_tile + ks * P.npad * 32) >> 4)), idesc, ks > 0);
+            umma_commit(bar);
+        }
+        bool mine = mbar_wait(bar, phase, P.flags, 10 + g, &abort_flag);
+        phase ^= 1;
+        ok = group_all(mine, 1 + g);
+        if (!ok) break;
+        tc_fence_after();
+
+        // ---- this coefficient's row: recombine, reduce, subtract the overflow term, store ----
+        const uint32_t taddr = tmem_g + ((uint32_t)((warp & 3) * 32) << 16);
+        u64* dst = P.out + (((size_t)bt * P.blocks + blk) * T) * P.N + xt * TM + r;
+        const u64* vt = s_vt + (blk * (APAD + 1) + v) * T;
+        for (int k0 = 0; k0 < T; k0 += 4) {
+            int32_t D[4][8];
+#pragma unroll
+            for (int u = 0; u < 4; u++) tmem_ld8(taddr + (k0 + u) * 8, D[u]);
+            tmem_ld_wait();
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int k = k0 + u;
+                if (k >= T) break;
+                const u64 g0 = (u64)(uint32_t)D[u][0] + ((u64)(uint32_t)D[u][1] << 8) + ((u64)(uint32_t)D[u][2] << 16) +
+                               ((u64)(uint32_t)D[u][3] << 24);
+                const u64 g1 = (u64)(uint32_t)D[u][4] + ((u64)(uint32_t)D[u][5] << 8) + ((u64)(uint32_t)D[u][6] << 16) +
+                               ((u64)(uint32_t)D[u][7] << 24);
+                const u64 lo = g0 + (g1 << 32);              // the row's value modulo 2^64
+                // g0, g1 < 2^48: exact as doubles through the 2^52 offset
+                const double d0 = __hiloint2double(0x43300000 + (int)(g0 >> 32), (int)(uint32_t)g0) - 4503599627370496.0;
+                const double d1 = __hiloint2double(0x43300000 + (int)(g1 >> 32), (int)(uint32_t)g1) - 4503599627370496.0;
+                const double val = fma(d1, 4294967296.0, d0);               // the value, to 53 bits
+                const double qd = val * s_tinv[k] + 4503599627370496.0;      // nearest integer quotient (< 2^40)
+                const u64 qh = (u64)__double_as_longlong(qd) & 0xFFFFFFFFFFFFFull;
+                const u64 tk = s_t[k];
+                u64 res = lo - qh * tk;                      // in (-t/2 - 1, t/2 + 1) modulo 2^64
+                if ((long long)res < 0) res += tk;
+                const u64 sub = vt[k];
+                res = res >= sub ? res - sub : res + tk - sub;
+                dst[(size_t)k * P.N] = res;
+            }
+        }
+        tc_fence_before();
+        tile = next;
+    }
+    if (!ok && r == 0) atomicExch(&abort_flag, 1);
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_slot, GROUPS * GROUP_COLS);
+    }
+}
+
+template <int APAD>
+int launch(ckks_b200_context* c, const ModUpTcArgs& P, cudaStream_t st) {
+    constexpr int KSTEPS = APAD * 8 / 32;
+    const size_t smem = (size_t)GROUPS * KSTEPS * TM * 32 + (size_t)P.blocks * KSTEPS * P.npad * 32 +
+                        (size_t)P.blocks * APAD * (8 + 16) + (size_t)P.blocks * (APAD + 1) * P.t_num * 8 +
+                        (size_t)P.t_num * 16;
+    CKB_REQUIRE(smem <= 200 * 1024, CKKS_B200_ERR_UNSUPPORTED, "ModUp tables of %zu bytes do not fit shared memory", smem);
+    CKB_CUDA(cudaFuncSetAttribute(modup_umma_kernel<APAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int sms = 0;
+    CKB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device));
+    const long total = (long)P.batch * P.blocks * (P.N / TM);
+    const long want = (total + GROUPS - 1) / GROUPS;
+    const int grid = (int)(want < sms ? want : sms);
+    modup_umma_kernel<APAD><<<grid, THREADS, smem, st>>>(P);
+    count_launch();
+    CKB_CUDA(cudaGetLastError());
+    return CKKS_B200_OK;
+}
+
+}  // namespace
+
+namespace ckb {
+
+bool modup_tensor_ok(const ckks_b200_context* c, int l) {
+    return c->mu_planes != nullptr && l >= 0 && l < (int)c->mu_tc_ok.size() && c->mu_tc_ok[l] != 0 &&
+           c->N % TM == 0 && c->tc_npad <= GROUP_COLS;
+}
+
+int modup_tensor(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int batch, cudaStream_t st) {
+    const int A = c->alpha, B = c->blocks_max, T = c->t_num;
+    ModUpTcArgs P;
+    P.out = d_out;
+    P.in = d_in;
+    P.q = c->d_moduli + c->p_num;
+    P.t = c->d_moduli + c->p_num + c->q_num;
+    P.t_inv = c->d_t_inv;
+    P.hat_inv = c->mu_hat_inv + (size_t)l * B * A;
+    P.blk_mod_t = c->mu_blk_mod_t + (size_t)l * B * T;
+    P.planes = c->mu_planes + (size_t)l * B * c->tc_kpad * c->tc_npad;
+    P.flags = c->d_flags;
+    P.N = c->N;
+    P.q_num = c->q_num;
+    P.t_num = T;
+    P.alpha = A;
+    P.l = l;
+    P.blocks = (l + 1 + A - 1) / A;
+    P.batch = batch;
+    P.npad = c->tc_npad;
+    if (c->tc_kpad == 32) return launch<4>(c, P, st);
+    if (c->tc_kpad == 64) return launch<8>(c, P, st);
+    if (c->tc_kpad == 96) return launch<12>(c, P, st);
+    return launch<16>(c, P, st);
+}
+
+}  // namespace ckb

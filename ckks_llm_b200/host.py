@@ -83,6 +83,16 @@ class Context_23:
         capi.check(self.lib.ckks_b200_modup_qj_to_t(
             self._h, output.data_ptr(), input.data_ptr(), l, batch_size, _stream_ptr(self.device)))
 
+    # Kernel choice for modUpQjtoT_23: "auto" (tensor cores where the level's tables qualify),
+    # "tensor" (insist) or "simt" (64-bit CUDA-core kernel).  The reference has one kernel.
+    def set_modup_algo(self, algo):
+        code = {"auto": 0, "tensor": 1, "simt": 2}[algo]
+        capi.check(self.lib.ckks_b200_modup_set_algo(self._h, code))
+
+    # Synchronise the current stream; raises on a device-side wait that ran out.
+    def check(self):
+        capi.check(self.lib.ckks_b200_context_check(self._h, _stream_ptr(self.device)))
+
     # host-buffer forms (numpy uint64 arrays, transformed in place / returned)
     def ToNTTInplace_host(self, host_a, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len):
         assert host_a.dtype == np.uint64 and host_a.flags.c_contiguous

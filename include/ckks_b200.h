@@ -85,6 +85,19 @@ int ckks_b200_modup_qj_to_t(ckks_b200_context* ctx, uint64_t* d_out, const uint6
                             int l, int batch, void* stream);
 int ckks_b200_modup_qj_to_t_host(ckks_b200_context* ctx, uint64_t* h_out, const uint64_t* h_in,
                                  int l, int batch);
+/* Kernel choice for ModUp on this context (no counterpart in the reference, which has one
+ * kernel).  AUTO takes the tensor-core kernel (the alpha x t_num table product as an 8-bit
+ * tcgen05 matrix product) on every level whose tables qualify and the 64-bit CUDA-core kernel
+ * elsewhere; TENSOR insists and returns CKKS_B200_ERR_UNSUPPORTED on a level that does not
+ * qualify; SIMT always takes the CUDA-core kernel.  Both give the reference's residues. */
+#define CKKS_B200_MODUP_AUTO 0
+#define CKKS_B200_MODUP_TENSOR 1
+#define CKKS_B200_MODUP_SIMT 2
+int ckks_b200_modup_set_algo(ckks_b200_context* ctx, int algo);
+/* Synchronises `stream` and returns CKKS_B200_ERR_TIMEOUT when a bounded device-side wait
+ * of a tensor-core ModUp on this context ran out since the last check (the *_host entry
+ * point checks by itself). */
+int ckks_b200_context_check(ckks_b200_context* ctx, void* stream);
 
 /* ---- ring packing, RLWE -> MLWE ---------------------------------------------
  * PCMM_Scheme::rlweCipherDecompose (pcmm/PCMM_Scheme.cuh:51-125): d_rlwe is the

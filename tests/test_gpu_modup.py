@@ -10,7 +10,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(oracle, logN, alpha, q_num, t_num, l, batch, seed, q_bits=50, t_bits=60):
+def _run(oracle, logN, alpha, q_num, t_num, l, batch, seed, q_bits=50, t_bits=60, algos=("tensor", "simt", "auto"),
+         edge=False):
+    """Both kernels (the tcgen05 byte-plane product and the 64-bit CUDA-core one) against the oracle."""
     N = 1 << logN
     p = params.ntt_primes(q_bits + 1, 2 * N, alpha)
     q = params.ntt_primes(q_bits, 2 * N, q_num)
@@ -18,14 +20,26 @@ def _run(oracle, logN, alpha, q_num, t_num, l, batch, seed, q_bits=50, t_bits=60
     ctx = Context_23(logN, p, q, t)
     rng = np.random.default_rng(seed)
     inp = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(batch)])
+    if edge:
+        # extreme residues: zeros, q-1 everywhere (overflow count at its maximum), single ones
+        qa = np.array(q, dtype=np.uint64)
+        inp[0, :, 0] = 0
+        inp[0, :, 1] = qa - np.uint64(1)
+        inp[0, :, 2] = 1
+        inp[0, :, 3] = 0
+        inp[0, 0, 3] = 1
+        inp[0, :, 4:132] = (qa - np.uint64(1))[:, None]
     blocks = (l + 1 + alpha - 1) // alpha
-    out = torch.full((batch * blocks * t_num * N,), -1, dtype=torch.int64, device=ctx.device)
-    ctx.modUpQjtoT_23(out, as_u64_tensor(inp, ctx.device), l, batch)
-    got = to_u64_numpy(out).reshape(batch, blocks, t_num, N)
     exp = oracle.modup(inp, N, q, t, alpha, l, batch)
-    assert np.array_equal(got, exp)
-    host = ctx.modUpQjtoT_23_host(inp, l, batch)
-    assert np.array_equal(host, exp)
+    for algo in algos:
+        ctx.set_modup_algo(algo)
+        out = torch.full((batch * blocks * t_num * N,), -1, dtype=torch.int64, device=ctx.device)
+        ctx.modUpQjtoT_23(out, as_u64_tensor(inp, ctx.device), l, batch)
+        ctx.check()
+        got = to_u64_numpy(out).reshape(batch, blocks, t_num, N)
+        assert np.array_equal(got, exp), algo
+        host = ctx.modUpQjtoT_23_host(inp, l, batch)
+        assert np.array_equal(host, exp), algo
     ctx.close()
 
 
@@ -43,3 +57,37 @@ def test_config3_shape(oracle, cuda_device):
     """Configuration 3: N=2^16, 24 Q-limbs (50-bit), alpha=8 -> 3 digits, 12 target limbs
     (60-bit); a reduced batch keeps the CPU oracle to seconds (full batch is timed in bench)."""
     _run(oracle, 16, 8, 24, 12, 23, 4, seed=0)
+
+
+def test_extreme_residues(oracle, cuda_device):
+    _run(oracle, 12, 8, 16, 12, 15, 2, seed=4, edge=True)
+    _run(oracle, 12, 4, 8, 5, 6, 1, seed=5, edge=True)         # ragged digit, odd target count
+
+
+def test_digit_sizes_off_the_mma_step(oracle, cuda_device):
+    """alpha that is not a multiple of four pads the contraction with zero rows."""
+    _run(oracle, 12, 5, 10, 4, 9, 2, seed=6)
+    _run(oracle, 12, 2, 6, 16, 5, 1, seed=7)                    # sixteen targets fill the accumulator columns
+    _run(oracle, 12, 11, 22, 3, 21, 1, seed=8)
+
+
+def test_wide_q_limbs(oracle, cuda_device):
+    _run(oracle, 12, 4, 8, 6, 7, 2, seed=9, q_bits=59, t_bits=61)
+
+
+def test_tensor_kernel_refuses_what_it_cannot_reduce(oracle, cuda_device):
+    """Targets outside [2^40, 2^62) go to the CUDA-core kernel; insisting on tensor cores is an error."""
+    from ckks_llm_b200.capi import CkksB200Error
+    N = 1 << 12
+    p = params.ntt_primes(31, 2 * N, 2)
+    q = params.ntt_primes(30, 2 * N, 4)
+    t = params.ntt_primes(36, 2 * N, 3)
+    ctx = Context_23(12, p, q, t)
+    rng = np.random.default_rng(10)
+    inp = np.stack([H.uniform_residues(rng, q, (N,))])
+    exp = oracle.modup(inp, N, q, t, 2, 3, 1)
+    assert np.array_equal(ctx.modUpQjtoT_23_host(inp, 3, 1), exp)         # auto -> CUDA cores
+    ctx.set_modup_algo("tensor")
+    with pytest.raises(CkksB200Error):
+        ctx.modUpQjtoT_23_host(inp, 3, 1)
+    ctx.close()
