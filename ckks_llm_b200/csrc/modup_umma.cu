@@ -65,7 +65,21 @@ __device__ __forceinline__ bool group_all(bool p, int id) {
     return r != 0;
 }
 
-template <int APAD>
+// u64 below 2^52 -> double, exactly: plant the value in the mantissa of 2^52 and subtract the offset.
+__device__ __forceinline__ double small_to_double(u64 x) {
+    return __hiloint2double(0x43300000 + (int)(x >> 32), (int)(uint32_t)x) - 4503599627370496.0;
+}
+__device__ __forceinline__ u64 mad_wide(uint32_t a, uint32_t b, u64 c) {
+    u64 d;
+    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(d) : "r"(a), "r"(b), "l"(c));
+    return d;
+}
+
+// F64Q: every q modulus is below 2^50, and rb_j = x_j * w_j mod q_j is then formed on the FP64 pipe
+// (exact: h + l = x*w with h = fl(x*w), l the FMA remainder; h - c*q is a small integer for
+// c = rint(h/q); w is kept centred, |w| <= q/2, so the result stays within (-0.7q, 0.7q)).
+// Otherwise rb_j is a 64-bit Shoup product.
+template <int APAD, bool F64Q>
 __global__ void __launch_bounds__(THREADS, 1) modup_umma_kernel(ModUpTcArgs P) {
     constexpr int KSTEPS = APAD * 8 / 32;
     constexpr int A_TILE = KSTEPS * TM * 32;
@@ -85,14 +99,22 @@ __global__ void __launch_bounds__(THREADS, 1) modup_umma_kernel(ModUpTcArgs P) {
     u64* s_vt = reinterpret_cast<u64*>(s_hinv + P.blocks * APAD);          // [blocks][APAD+1][T]  v*(Qblk mod t_k) mod t_k
     u64* s_t = s_vt + P.blocks * (APAD + 1) * T;                           // [T]
     double* s_tinv = reinterpret_cast<double*>(s_t + T);                   // [T]
+    double* s_qd = s_tinv + T;                                             // [blocks][APAD]  q_j as a double
+    double* s_qinv = s_qd + P.blocks * APAD;                               // [blocks][APAD]  1/q_j (0 beyond the digit)
+    double* s_wd = s_qinv + P.blocks * APAD;                               // [blocks][APAD]  (Qblk/q_j)^-1 mod q_j, centred
 
     for (int i = tid; i < P.blocks * b_tile / 16; i += THREADS)
         reinterpret_cast<uint4*>(sB)[i] = reinterpret_cast<const uint4*>(P.planes)[i];
     for (int i = tid; i < P.blocks * APAD; i += THREADS) {
         const int blk = i / APAD, j = i % APAD;
         const bool live = j < P.alpha && blk * P.alpha + j <= P.l;
-        s_q[i] = live ? P.q[blk * P.alpha + j] : 1;
+        const u64 qj = live ? P.q[blk * P.alpha + j] : 1;
+        s_q[i] = qj;
         s_hinv[i] = live ? P.hat_inv[blk * P.alpha + j] : make_ulonglong2(0, 0);
+        s_qd[i] = (double)qj;
+        s_qinv[i] = live ? 1.0 / (double)qj : 0.0;
+        const u64 w = live ? P.hat_inv[blk * P.alpha + j].x : 0;
+        s_wd[i] = w > qj / 2 ? -(double)(qj - w) : (double)w;
     }
     for (int i = tid; i < P.blocks * T; i += THREADS) {
         const int blk = i / T, k = i % T;
@@ -156,17 +178,45 @@ __global__ void __launch_bounds__(THREADS, 1) modup_umma_kernel(ModUpTcArgs P) {
         const long bt = rest / P.blocks;
 
         // ---- rb_j, the overflow count, and this coefficient's row of the byte matrix ----
-        double vv = 0.0;
+        // The reference's count is v = trunc(sum_j rb_j / q_j) with IEEE divisions added in limb
+        // order.  est = sum_j rb_j * (1/q_j) differs from that sum by less than 2^-46, so both
+        // truncate alike unless est sits within 2^-40 of an integer; only then are the divisions made.
+        double est = 0.0;
 #pragma unroll
         for (int j = 0; j < APAD; j++) {
-            const u64 qj = s_q[blk * APAD + j];
-            const ulonglong2 hi = s_hinv[blk * APAD + j];
-            const u64 rb = shoup_mul(cur[j], hi.x, hi.y, qj);      // zero beyond the digit (hi = 0)
-            vv += __ddiv_rn((double)rb, (double)qj);               // adds 0.0 there: the sum is unchanged
+            u64 rb;
+            double rbd;
+            if (F64Q) {
+                const double q = s_qd[blk * APAD + j], u = s_qinv[blk * APAD + j], w = s_wd[blk * APAD + j];
+                const double x = small_to_double(cur[j]);
+                const double h = __dmul_rn(x, w);
+                const double l = __fma_rn(x, w, -h);
+                const double c = __dadd_rn(__fma_rn(h, u, 6755399441055744.0), -6755399441055744.0);
+                rbd = __dadd_rn(__fma_rn(-c, q, h), l);
+                if (rbd < 0.0) rbd = __dadd_rn(rbd, q);
+                rb = (u64)__double_as_longlong(__dadd_rn(rbd, 4503599627370496.0)) & 0x000FFFFFFFFFFFFFull;
+            } else {
+                const ulonglong2 hi = s_hinv[blk * APAD + j];
+                rb = shoup_mul(cur[j], hi.x, hi.y, s_q[blk * APAD + j]);
+                rbd = (double)rb;
+            }
+            // beyond the digit w = 0 and 1/q = 0: rb = 0 and est is unchanged
+            est = fma(rbd, s_qinv[blk * APAD + j], est);
             // K index j*8+b: step j/4, K half (j%4)/2, byte offset (j%2)*8 inside the 16-byte row
             *reinterpret_cast<u64*>(sA + (j / 4) * (TM * 32) + ((j % 4) / 2) * 128 + row_off + (j % 2) * 8) = rb;
         }
-        const int v = (int)vv;
+        int v = (int)est;
+        {
+            const double frac = est - (double)v;
+            if (frac < 0x1p-40 || frac > 1.0 - 0x1p-40) {
+                double vv = 0.0;
+                for (int j = 0; j < APAD; j++) {
+                    const u64 rb = *reinterpret_cast<const u64*>(sA + (j / 4) * (TM * 32) + ((j % 4) / 2) * 128 + row_off + (j % 2) * 8);
+                    vv += __ddiv_rn((double)rb, s_qd[blk * APAD + j]);      // rb = 0 beyond the digit: adds 0.0
+                }
+                v = (int)vv;
+            }
+        }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         const long next = tile + stride;
         if (next < total) load_tile(next, cur);
@@ -198,15 +248,13 @@ __global__ void __launch_bounds__(THREADS, 1) modup_umma_kernel(ModUpTcArgs P) {
             for (int u = 0; u < 4; u++) {
                 const int k = k0 + u;
                 if (k >= T) break;
-                const u64 g0 = (u64)(uint32_t)D[u][0] + ((u64)(uint32_t)D[u][1] << 8) + ((u64)(uint32_t)D[u][2] << 16) +
-                               ((u64)(uint32_t)D[u][3] << 24);
-                const u64 g1 = (u64)(uint32_t)D[u][4] + ((u64)(uint32_t)D[u][5] << 8) + ((u64)(uint32_t)D[u][6] << 16) +
-                               ((u64)(uint32_t)D[u][7] << 24);
+                // sum_a D_a 2^(8a) in two halves of four (each below 2^48)
+                const u64 g0 = mad_wide((uint32_t)D[u][3], 1u << 24, mad_wide((uint32_t)D[u][2], 1u << 16,
+                               mad_wide((uint32_t)D[u][1], 1u << 8, (u64)(uint32_t)D[u][0])));
+                const u64 g1 = mad_wide((uint32_t)D[u][7], 1u << 24, mad_wide((uint32_t)D[u][6], 1u << 16,
+                               mad_wide((uint32_t)D[u][5], 1u << 8, (u64)(uint32_t)D[u][4])));
                 const u64 lo = g0 + (g1 << 32);              // the row's value modulo 2^64
-                // g0, g1 < 2^48: exact as doubles through the 2^52 offset
-                const double d0 = __hiloint2double(0x43300000 + (int)(g0 >> 32), (int)(uint32_t)g0) - 4503599627370496.0;
-                const double d1 = __hiloint2double(0x43300000 + (int)(g1 >> 32), (int)(uint32_t)g1) - 4503599627370496.0;
-                const double val = fma(d1, 4294967296.0, d0);               // the value, to 53 bits
+                const double val = fma(small_to_double(g1), 4294967296.0, small_to_double(g0));   // the value, to 53 bits
                 const double qd = val * s_tinv[k] + 4503599627370496.0;      // nearest integer quotient (< 2^40)
                 const u64 qh = (u64)__double_as_longlong(qd) & 0xFFFFFFFFFFFFFull;
                 const u64 tk = s_t[k];
@@ -230,20 +278,20 @@ __global__ void __launch_bounds__(THREADS, 1) modup_umma_kernel(ModUpTcArgs P) {
     }
 }
 
-template <int APAD>
+template <int APAD, bool F64Q>
 int launch(ckks_b200_context* c, const ModUpTcArgs& P, cudaStream_t st) {
     constexpr int KSTEPS = APAD * 8 / 32;
     const size_t smem = (size_t)GROUPS * KSTEPS * TM * 32 + (size_t)P.blocks * KSTEPS * P.npad * 32 +
                         (size_t)P.blocks * APAD * (8 + 16) + (size_t)P.blocks * (APAD + 1) * P.t_num * 8 +
-                        (size_t)P.t_num * 16;
+                        (size_t)P.t_num * 16 + (size_t)P.blocks * APAD * 24;
     CKB_REQUIRE(smem <= 200 * 1024, CKKS_B200_ERR_UNSUPPORTED, "ModUp tables of %zu bytes do not fit shared memory", smem);
-    CKB_CUDA(cudaFuncSetAttribute(modup_umma_kernel<APAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CKB_CUDA(cudaFuncSetAttribute(modup_umma_kernel<APAD, F64Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int sms = 0;
     CKB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device));
     const long total = (long)P.batch * P.blocks * (P.N / TM);
     const long want = (total + GROUPS - 1) / GROUPS;
     const int grid = (int)(want < sms ? want : sms);
-    modup_umma_kernel<APAD><<<grid, THREADS, smem, st>>>(P);
+    modup_umma_kernel<APAD, F64Q><<<grid, THREADS, smem, st>>>(P);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
@@ -278,10 +326,18 @@ int modup_tensor(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int b
     P.blocks = (l + 1 + A - 1) / A;
     P.batch = batch;
     P.npad = c->tc_npad;
-    if (c->tc_kpad == 32) return launch<4>(c, P, st);
-    if (c->tc_kpad == 64) return launch<8>(c, P, st);
-    if (c->tc_kpad == 96) return launch<12>(c, P, st);
-    return launch<16>(c, P, st);
+    bool q_small = true;
+    for (int i = 0; i < c->q_num; i++) q_small = q_small && c->moduli[c->p_num + i] < (1ull << 50);
+    if (q_small) {
+        if (c->tc_kpad == 32) return launch<4, true>(c, P, st);
+        if (c->tc_kpad == 64) return launch<8, true>(c, P, st);
+        if (c->tc_kpad == 96) return launch<12, true>(c, P, st);
+        return launch<16, true>(c, P, st);
+    }
+    if (c->tc_kpad == 32) return launch<4, false>(c, P, st);
+    if (c->tc_kpad == 64) return launch<8, false>(c, P, st);
+    if (c->tc_kpad == 96) return launch<12, false>(c, P, st);
+    return launch<16, false>(c, P, st);
 }
 
 }  // namespace ckb
