@@ -30,10 +30,10 @@ NTT_CFG = dict(logN=16, limbs=40, q_bits=50, polys=32)
 MODUP_CFG = dict(logN=16, q_num=24, q_bits=50, t_num=12, t_bits=60, alpha=8, batch=32)
 SW, SC = 5, 7          # byte planes the PCMM workload needs: 40-bit signed weights, 50-bit residues
 # DRAM traffic (bytes) from the ncu captures summarised under profiles/, per unit of work
-PCMM_TRAFFIC_PER_LIMB = (709.55e6 + 770.68e6) / 2                    # pcmm_umma_kernel<5,7>, 768x768, per limb
-NTT_TRAFFIC_PER_XFORM = {"forward": (167.90e6 + 111.49e6 + 194.98e6 + 112.24e6) / 320,
-                         "inverse": (197.69e6 + 116.77e6 + 167.91e6 + 109.20e6) / 320}
-MODUP_TRAFFIC_PER_POLY = (100.74e6 + 99.14e6) / 8
+PCMM_TRAFFIC_PER_LIMB = (709.07e6 + 767.26e6) / 2                    # pcmm_umma_kernel<5,7>, 768x768, per limb
+NTT_TRAFFIC_PER_XFORM = {"forward": (167.90e6 + 113.26e6 + 196.91e6 + 112.88e6) / 320,
+                         "inverse": (202.12e6 + 113.41e6 + 167.91e6 + 108.10e6) / 320}
+MODUP_TRAFFIC_PER_POLY = (100.73e6 + 95.66e6) / 8
 
 
 def measured_peaks():
