@@ -250,6 +250,52 @@ def bench_modup(torch, device, steps, warmup, peaks):
                        "l2_policy": "input+output (1 GB) larger than L2"}}
 
 
+def bench_levels(torch, device, steps, warmup, peaks):
+    """Scheme_23::rescaleAndEqual and Bootstrapper::modUpQ0toQL on 16 ciphertexts of the BERT chain
+    (N=2^16, 20 x 50-bit limbs): device time per ciphertext, with the bytes each must move."""
+    from ckks_llm_b200 import capi, params
+    from ckks_llm_b200.host import Context_23, _stream_ptr
+    logN, limbs, cts = 16, 20, 16
+    N = 1 << logN
+    p = params.ntt_primes(51, 2 * N, 1)
+    q = params.ntt_primes(50, 2 * N, limbs)
+    ctx = Context_23(logN, p, q, [], device=device.index)
+    g = torch.Generator(device=device).manual_seed(3)
+    data = torch.empty((cts, 2, limbs, N), dtype=torch.int64, device=device)
+    for i, qi in enumerate(q):
+        data[:, :, i, :] = torch.randint(0, qi, (cts, 2, N), generator=g, device=device, dtype=torch.int64)
+    L, st = limbs - 1, _stream_ptr(device)
+    calls = {
+        "rescale": (lambda c: capi.check(ctx.lib.ckks_b200_rescale(ctx._h, data[c].data_ptr(), L, L, st)),
+                    (1 + 1 + 3 * L) * 2 * 8 * N, "INTT of the last limb, 19 reductions, 19 NTTs, combine"),
+        "modup_q0_to_ql": (lambda c: capi.check(ctx.lib.ckks_b200_modup_q0_to_ql(ctx._h, data[c].data_ptr(), L, L, 1 << 10, st)),
+                           (1 + 1 + L + 2 * (L + 1)) * 2 * 8 * N, "INTT of limb 0, 19 lifts, 20 NTTs"),
+    }
+    res = {}
+    for name, (fn, bytes_per_ct, what) in calls.items():
+        for _ in range(warmup):
+            for c in range(cts):
+                fn(c)
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            for c in range(cts):
+                fn(c)
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms = e0.elapsed_time(e1) / (steps * cts)
+        gbs = bytes_per_ct / (ms * 1e-3) / 1e9
+        res[name] = {"ciphertexts_per_sec": 1e3 / ms, "ms_per_ciphertext": ms, "steps": what,
+                     "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                  "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                                  "note": "algorithmic bytes: every limb touched is read once and written once per step of the sandwich"}}
+    ctx.close()
+    res["config"] = {"workload": "level changes on 16 ciphertexts, N=2^16, 20x50-bit limbs, level 19",
+                     "l2_policy": "16 ciphertexts (336 MB) larger than L2, visited round-robin"}
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -406,6 +452,7 @@ def main():
             try:
                 extra["ntt"] = bench_ntt(torch, device, max(args.steps, 10), args.warmup, peaks)
                 extra["modup"] = bench_modup(torch, device, max(args.steps, 10), args.warmup, peaks)
+                extra["levels"] = bench_levels(torch, device, max(args.steps, 10), args.warmup, peaks)
             except Exception as ex:           # the headline stays valid without the side measurements
                 extra["side_error"] = repr(ex)
     else:

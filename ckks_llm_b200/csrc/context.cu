@@ -287,6 +287,14 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
     std::vector<u64> qinv64(c->mod_num);
     for (int i = 0; i < c->mod_num; i++) qinv64[i] = (u64)((((u128)1) << 64) / c->moduli[i]);
     if (!st) st = upload(&c->d_qinv64, qinv64);
+    // q_l^-1 mod q_i for i < l (the reference's qiInvVecModql, Context_23.cuh:424-434)
+    std::vector<ulonglong2> qlinv((size_t)q_num * q_num, make_ulonglong2(0, 0));
+    for (int l = 1; l < q_num; l++)
+        for (int i = 0; i < l; i++) {
+            u64 inv = h_invmod(qv[l] % qv[i], qv[i]);
+            qlinv[(size_t)l * q_num + i] = make_ulonglong2(inv, h_shoup(inv, qv[i]));
+        }
+    if (!st) st = upload(&c->d_qlinv, qlinv);
     if (!st) st = upload(&c->mu_hat_inv, hat_inv);
     if (!st) st = upload(&c->mu_hat_mod_t, hat_mod_t);
     if (!st) st = upload(&c->mu_blk_mod_t, blk_mod_t);
@@ -306,7 +314,7 @@ extern "C" int ckks_b200_context_destroy(ckks_b200_context* c) {
     DeviceGuard guard(c->device);
     cudaFree(c->tw_fwd); cudaFree(c->tw_inv); cudaFree(c->tw_fwd_d); cudaFree(c->tw_inv_d); cudaFree(c->d_moduli); cudaFree(c->d_ninv); cudaFree(c->d_qinv64);
     cudaFree(c->mu_hat_inv); cudaFree(c->mu_hat_mod_t); cudaFree(c->mu_blk_mod_t);
-    cudaFree(c->mu_planes); cudaFree(c->d_t_inv); cudaFree(c->d_flags);
+    cudaFree(c->mu_planes); cudaFree(c->d_t_inv); cudaFree(c->d_flags); cudaFree(c->d_qlinv); cudaFree(c->resc_buf);
     if (c->h_flags) cudaFreeHost(c->h_flags);
     cudaFree(c->d_t_mu); cudaFree(c->h2d_buf); cudaFree(c->h2d_buf2); cudaFree(c->ptr_buf); cudaFree(c->pack_buf);
     delete c;

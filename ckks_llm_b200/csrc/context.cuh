@@ -25,6 +25,7 @@ struct ckks_b200_context {
     u64* d_moduli = nullptr;                 // [mod_num]
     ulonglong2* d_ninv = nullptr;            // [mod_num] {N^-1, shoup}
     u64* d_qinv64 = nullptr;                 // [mod_num] floor(2^64 / q)
+    ulonglong2* d_qlinv = nullptr;           // [q_num][q_num] row l, entry i < l: {q_l^-1 mod q_i, shoup} (rescale)
 
     // ModUp tables, one group per level l in [0, q_num):
     //   hat_inv   [l][blocks_max*alpha]           {inv, shoup} of (Qblk/q_j)^-1 mod q_j
@@ -58,6 +59,8 @@ struct ckks_b200_context {
     size_t ptr_cap = 0;
     u64* pack_buf = nullptr;                 // embedded MLWE polynomials and key products of the packing
     size_t pack_cap = 0;
+    u64* resc_buf = nullptr;                 // the last limb spread over the lower limbs (rescale)
+    size_t resc_cap = 0;
 };
 
 namespace ckb {

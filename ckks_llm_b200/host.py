@@ -124,6 +124,41 @@ class Ciphertext:
         self.cipher_device = cipher
 
 
+class Scheme_23:
+    """The level-lowering step of the reference's evaluator that the PCMM pipeline uses
+    (src/ckks/include/Scheme_23.cuh:368-385)."""
+
+    def __init__(self, context):
+        self.context = context
+
+    # Scheme_23::rescaleAndEqual(Ciphertext&), src/ckks/include/Scheme_23.cuh:368-385
+    def rescaleAndEqual(self, cipher):
+        ctx = self.context
+        capi.check(ctx.lib.ckks_b200_rescale(ctx._h, cipher.cipher_device.data_ptr(), cipher.L, cipher.l,
+                                             _stream_ptr(ctx.device)))
+        cipher.scale = cipher.scale / ctx.qVec[cipher.l]
+        cipher.l -= 1
+
+
+class Bootstrapper:
+    """The level-raising step in front of the bootstrapping pipeline
+    (src/ckks/include/bootstrapping/Bootstrapper.cuh:192-209)."""
+
+    def __init__(self, context, precision):
+        self.context = context
+        self.precision = int(precision)
+
+    # Bootstrapper::modUpQ0toQL(Ciphertext&, int target_level): a no-op unless the ciphertext is at level 0 (:194)
+    def modUpQ0toQL(self, cipher, target_level):
+        if cipher.l != 0:
+            return
+        ctx = self.context
+        scale_up = C.c_int(ctx.qVec[0] // self.precision).value      # the kernel's parameter is an int (:6)
+        capi.check(ctx.lib.ckks_b200_modup_q0_to_ql(ctx._h, cipher.cipher_device.data_ptr(), cipher.L, target_level,
+                                                    scale_up, _stream_ptr(ctx.device)))
+        cipher.l = target_level
+
+
 class MLWECiphertext:
     """Device buffer [L+1][k+1][N1] words (src/ckks/include/pcmm/MLWECiphertext.cuh:6-78)."""
 

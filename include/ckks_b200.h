@@ -99,6 +99,23 @@ int ckks_b200_modup_set_algo(ckks_b200_context* ctx, int algo);
  * point checks by itself). */
 int ckks_b200_context_check(ckks_b200_context* ctx, void* stream);
 
+/* ---- level changes around the PCMM ------------------------------------------
+ * d_cipher is the reference's Ciphertext buffer, a limbs then b limbs, each [L+1][N], NTT
+ * domain, limb i modulo q_i of the context.
+ *
+ * Scheme_23::rescaleAndEqual (Scheme_23.cuh:339-385): divides a level-l ciphertext by q_l:
+ * limbs i < l become (x_i - NTT_i(INTT_l(x_l) mod q_i)) * q_l^-1 mod q_i.  As in the reference
+ * limb l is left holding its coefficients; the caller lowers the level and divides the scale by
+ * q_l (:380-381).  1 <= l <= L. */
+int ckks_b200_rescale(ckks_b200_context* ctx, uint64_t* d_cipher, int L, int l, void* stream);
+/* Bootstrapper::modUpQ0toQL (bootstrapping/Bootstrapper.cuh:192-209, kernel Bootstrapping.cuh:6-23):
+ * raises a level-0 ciphertext to target_level: the coefficients of limb 0 are lifted centred
+ * (values above q_0/2 become x - q_0 + q_i*scale_up, in 64-bit unsigned arithmetic like the
+ * reference) and reduced modulo q_1..q_target, then limbs 0..target_level go back to the NTT
+ * domain.  scale_up is the reference's qVec[0] / precision (:203). */
+int ckks_b200_modup_q0_to_ql(ckks_b200_context* ctx, uint64_t* d_cipher, int L, int target_level,
+                             long long scale_up, void* stream);
+
 /* ---- ring packing, RLWE -> MLWE ---------------------------------------------
  * PCMM_Scheme::rlweCipherDecompose (pcmm/PCMM_Scheme.cuh:51-125): d_rlwe is the
  * reference's Ciphertext buffer, a limbs then b limbs, each [L+1][N]; limbs 0..l are

@@ -65,6 +65,41 @@ public:
     }
 };
 
+// RLWE ciphertext carrier with the members the path reads (Ciphertext.cuh:5-100): cipher_device holds the a
+// limbs then the b limbs, each [L+1][N], and is owned by the caller.
+struct Ciphertext {
+    uint64_tt* cipher_device = nullptr;
+    long N = 0;
+    int L = 0, l = 0, slots = 0;
+    long double scale = 1.0L;
+};
+
+// Scheme_23::rescaleAndEqual(Ciphertext&) (Scheme_23.cuh:368-385).
+class Scheme_23 {
+public:
+    Context_23& context;
+    explicit Scheme_23(Context_23& context_) : context(context_) {}
+    void rescaleAndEqual(Ciphertext& cipher, cudaStream_t stream = 0) {
+        check(ckks_b200_rescale(context.b200, (uint64_t*)cipher.cipher_device, cipher.L, cipher.l, stream));
+        cipher.scale = cipher.scale / (long double)context.qVec[cipher.l];
+        cipher.l -= 1;
+    }
+};
+
+// Bootstrapper::modUpQ0toQL(Ciphertext&, int) (bootstrapping/Bootstrapper.cuh:192-209).
+class Bootstrapper {
+public:
+    Context_23& context;
+    uint64_tt precision;
+    Bootstrapper(Context_23& context_, uint64_tt precision_) : context(context_), precision(precision_) {}
+    void modUpQ0toQL(Ciphertext& cipher, int target_level, cudaStream_t stream = 0) {
+        if (cipher.l != 0) return;
+        const int scale_up = (int)(context.qVec[0] / precision);       // the reference kernel's parameter is an int
+        check(ckks_b200_modup_q0_to_ql(context.b200, (uint64_t*)cipher.cipher_device, cipher.L, target_level, scale_up, stream));
+        cipher.l = target_level;
+    }
+};
+
 // One cudaMalloc per object, freed in the destructor, deep copy on copy: the reference's
 // ownership rules (MLWECiphertext.cuh:26-77).
 class MLWECiphertext {

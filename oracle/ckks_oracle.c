@@ -601,3 +601,68 @@ ORC_API void orc_pack_moddown(const u64 *O, u64 *out_a, u64 *out_b, long N, u64 
         }
     }
 }
+
+
+/* ---------------------------------------------------------------------------
+ * Level changes around the PCMM: the elementwise kernels of Scheme_23::rescaleAndEqual and
+ * Bootstrapper::modUpQ0toQL.  Cipher buffers are [2][stride][n]; q points at the q moduli.
+ * ------------------------------------------------------------------------- */
+
+/* mod_to_qi: src/ckks/include/Scheme_23.cuh:356-366 with barrett_reduce_uint64_uint64
+ * (uint128.cuh:214-225): s = hi64(mu_hi * x), a = x - s*q, one conditional subtraction;
+ * mu_hi = high word of floor(2^128/q).  The value may stay in [q, 2q) like the reference's. */
+ORC_API void orc_mod_to_qi(u64 *buf, const u64 *cipher, uint32_t n, int stride, int l, const u64 *q)
+{
+#pragma omp parallel for collapse(2)
+    for (int c = 0; c < 2; c++)
+        for (int i = 0; i < l; i++) {
+            u64 qi = q[i];
+            u64 mu_hi = (u64)((~(u128)0 / qi) >> 64);
+            for (uint32_t x = 0; x < n; x++) {
+                u64 rb = cipher[((size_t)c * stride + l) * n + x];
+                u64 s = (u64)(((u128)mu_hi * rb) >> 64);
+                u64 a = rb - s * qi;
+                buf[((size_t)c * stride + i) * n + x] = csub_q(a, qi);
+            }
+        }
+}
+
+/* rescaleAndEqual_new_kernel: src/ckks/include/Scheme_23.cuh:339-354.
+ * qinv[i] = q_l^-1 mod q_i with its Shoup companion. */
+ORC_API void orc_rescale_combine(u64 *cipher, const u64 *buf, uint32_t n, int stride, int l, const u64 *q,
+                                 const u64 *qinv, const u64 *qinv_shoup)
+{
+#pragma omp parallel for collapse(2)
+    for (int c = 0; c < 2; c++)
+        for (int i = 0; i < l; i++) {
+            u64 qi = q[i];
+            for (uint32_t x = 0; x < n; x++) {
+                size_t idx = ((size_t)c * stride + i) * n + x;
+                u64 ra = cipher[idx] + 2 * qi - buf[idx];
+                ra = csub_q(ra, qi);
+                cipher[idx] = mulmod_shoup(ra, qinv[i], qinv_shoup[i], qi);
+            }
+        }
+}
+
+/* modUpQ0toQL_kernel: src/ckks/include/bootstrapping/Bootstrapping.cuh:6-23.  The C expression
+ * int64_t(ra) - q0 + (qi * scale_up) mixes int64, uint64 and int operands and is therefore
+ * evaluated in uint64; temp %= qi likewise. */
+ORC_API void orc_modup_q0_to_ql(u64 *cipher, uint32_t n, int stride, int target_level, const u64 *q, int scale_up)
+{
+#pragma omp parallel for collapse(2)
+    for (int c = 0; c < 2; c++)
+        for (int i = 0; i < target_level; i++) {
+            u64 qi = q[i + 1], q0 = q[0];
+            for (uint32_t x = 0; x < n; x++) {
+                u64 ra = cipher[(size_t)c * stride * n + x];
+                int64_t temp;
+                if (ra > q0 / 2)
+                    temp = (int64_t)((u64)(int64_t)ra - q0 + (qi * (u64)(int64_t)scale_up));
+                else
+                    temp = (int64_t)ra;
+                temp = (int64_t)((u64)temp % qi);
+                cipher[((size_t)c * stride + i + 1) * n + x] = (u64)temp;
+            }
+        }
+}

@@ -54,6 +54,9 @@ def lib():
                                      C.c_uint64, C.c_uint64]
         L.orc_pack_keymac.argtypes = [_U64P, _U64P, _U64P, C.c_long, C.c_int, _U64P]
         L.orc_pack_moddown.argtypes = [_U64P, _U64P, _U64P, C.c_long, C.c_uint64, C.c_uint64]
+        L.orc_mod_to_qi.argtypes = [_U64P, _U64P, C.c_uint32, C.c_int, C.c_int, _U64P]
+        L.orc_rescale_combine.argtypes = [_U64P, _U64P, C.c_uint32, C.c_int, C.c_int, _U64P, _U64P, _U64P]
+        L.orc_modup_q0_to_ql.argtypes = [_U64P, C.c_uint32, C.c_int, C.c_int, _U64P, C.c_int]
         _lib = L
     return _lib
 
@@ -217,3 +220,33 @@ def mlwe_packing(mlwe, keys, N1, k, p, q0, tables):
     sub.psi_shoup, sub.psiinv_shoup = tables.psi_shoup[1:2].copy(), tables.psiinv_shoup[1:2].copy()
     ntt_batch(res, sub, 0, 0, 2, 1, 1)                       # :428
     return res[:, 0, :], stages
+
+
+def rescale(cipher, tables, p_num, L, l):
+    """Scheme_23::rescaleAndEqual (Scheme_23.cuh:368-385) on a cipher buffer [2][L+1][n] (modified in
+    place and returned); tables cover the moduli [p | q | ...]."""
+    n = tables.n
+    cipher = np.ascontiguousarray(cipher, dtype=np.uint64)
+    flat = cipher.reshape(-1)
+    q = np.ascontiguousarray(tables.moduli[p_num:p_num + L + 1])
+    ntt_batch(flat, tables, l, p_num + l, 2, 1, L + 1, inverse=True)
+    buf = np.zeros_like(flat)
+    lib().orc_mod_to_qi(buf, flat, n, L + 1, l, q)
+    ntt_batch(buf, tables, 0, p_num, 2, l, L + 1)
+    qinv = np.array([pow(int(q[l]), -1, int(q[i])) for i in range(l)], dtype=np.uint64)
+    qinv_s = np.array([(int(qinv[i]) << 64) // int(q[i]) for i in range(l)], dtype=np.uint64)
+    lib().orc_rescale_combine(flat, buf, n, L + 1, l, q, qinv, qinv_s)
+    return cipher
+
+
+def modup_q0_to_ql(cipher, tables, p_num, L, target_level, scale_up):
+    """Bootstrapper::modUpQ0toQL (bootstrapping/Bootstrapper.cuh:192-209) on a level-0 cipher buffer
+    [2][L+1][n] (modified in place and returned)."""
+    n = tables.n
+    cipher = np.ascontiguousarray(cipher, dtype=np.uint64)
+    flat = cipher.reshape(-1)
+    q = np.ascontiguousarray(tables.moduli[p_num:p_num + L + 1])
+    ntt_batch(flat, tables, 0, p_num, 2, 1, L + 1, inverse=True)
+    lib().orc_modup_q0_to_ql(flat, n, L + 1, target_level, q, int(scale_up))
+    ntt_batch(flat, tables, 0, p_num, 2, target_level + 1, L + 1)
+    return cipher

@@ -30,6 +30,8 @@ def lib():
                                 _U64P, _U64P, _U64P, _U64P]
         L.ref_ppmm.argtypes = [_F32P, _U64P, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _U64P,
                                C.c_double, _U64P, _U64P]
+        L.ref_rescale_stage.argtypes = [_U64P, _U64P, C.c_int, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, _U64P, _U64P]
+        L.ref_modup_q0_to_ql.argtypes = [_U64P, C.c_int, _U64P, C.c_int, C.c_int, C.c_int, C.c_int]
         L.ref_decompose.argtypes = [_U64P, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _U64P]
         _lib = L
     return _lib
@@ -132,3 +134,32 @@ def pack_moddown(O, logN, p, q0):
     if rc:
         raise RuntimeError(f"ref_pack_moddown failed with {rc}")
     return out
+
+
+def rescale(cipher, logN, pq, p_num, L, l):
+    """Scheme_23::rescaleAndEqual's sequence (Scheme_23.cuh:368-385) with the reference's own kernels and
+    transform launchers on a cipher buffer [2][L+1][N]; returns the buffer afterwards."""
+    pq = np.ascontiguousarray(pq, dtype=np.uint64)
+    q = [int(v) for v in pq[p_num:]]
+    c = ntt(np.ascontiguousarray(cipher, dtype=np.uint64).reshape(2, L + 1, -1), logN, pq, l, p_num + l, 2, 1, L + 1,
+            inverse=True).reshape(-1)
+    buf = np.zeros_like(c)
+    qinv = np.array([pow(q[l], -1, q[i]) for i in range(l)], dtype=np.uint64)
+    qinv_s = np.array([(int(qinv[i]) << 64) // q[i] for i in range(l)], dtype=np.uint64)
+    rc = lib().ref_rescale_stage(c, buf, logN, pq, p_num, L + 1, l, 0, qinv, qinv_s)
+    assert rc == 0, rc
+    buf = ntt(buf.reshape(2, L + 1, -1), logN, pq, 0, p_num, 2, l, L + 1).reshape(-1)
+    rc = lib().ref_rescale_stage(c, buf, logN, pq, p_num, L + 1, l, 1, qinv, qinv_s)
+    assert rc == 0, rc
+    return c.reshape(2, L + 1, -1)
+
+
+def modup_q0_to_ql(cipher, logN, pq, p_num, L, target_level, scale_up):
+    """Bootstrapper::modUpQ0toQL's sequence (bootstrapping/Bootstrapper.cuh:192-209) with the reference's kernel
+    and transform launchers."""
+    pq = np.ascontiguousarray(pq, dtype=np.uint64)
+    c = ntt(np.ascontiguousarray(cipher, dtype=np.uint64).reshape(2, L + 1, -1), logN, pq, 0, p_num, 2, 1, L + 1,
+            inverse=True).reshape(-1)
+    rc = lib().ref_modup_q0_to_ql(c, logN, pq, p_num, L + 1, target_level, int(scale_up))
+    assert rc == 0, rc
+    return ntt(c.reshape(2, L + 1, -1), logN, pq, 0, p_num, 2, target_level + 1, L + 1)

@@ -26,6 +26,7 @@ using namespace std;
 #include "TimeUtils.cuh"
 #include "pcmm/PCMM_Context.cuh"
 #include "pcmm/PCMM_Scheme.cuh"
+#include "bootstrapping/Bootstrapping.cuh"
 
 #define RD_CUDA(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { fprintf(stderr, "ref_driver: %s -> %s\n", #x, cudaGetErrorString(e_)); return 100 + (int)e_; } } while (0)
 
@@ -329,5 +330,60 @@ extern "C" int ref_pack_moddown(const unsigned long long* h_O, unsigned long lon
     RD_CUDA(cudaDeviceSynchronize());
     RD_CUDA(cudaMemcpy(h_out, d_out, 8 * 2 * N, cudaMemcpyDeviceToHost));
     cudaFree(d_O); cudaFree(d_out); cudaFree(d_pinv); cudaFree(d_pinvs);
+    return 0;
+}
+
+// The elementwise kernels of Scheme_23::rescaleAndEqual (Scheme_23.cuh:339-385) on a cipher buffer
+// [2][q_stride][N]: stage 0 = mod_to_qi (h_cipher -> h_buf), stage 1 = rescaleAndEqual_new_kernel
+// (h_cipher, h_buf -> h_cipher).  The transforms between them are ref_ntt's.  pqt = [p | q].
+extern "C" int ref_rescale_stage(unsigned long long* h_cipher, unsigned long long* h_buf, int logN,
+                                 const unsigned long long* pqt, int p_num, int q_stride, int l, int stage,
+                                 const unsigned long long* qinv, const unsigned long long* qinv_shoup) {
+    const int n_mod = p_num + q_stride;
+    if (n_mod > max_pqt_num || l < 1) return 1;
+    const long N = 1L << logN;
+    int rc = upload_pqt(pqt, n_mod);
+    if (rc) return rc;
+    const size_t bytes = 8 * (size_t)2 * q_stride * N;
+    uint64_tt *dc = nullptr, *db = nullptr, *dq = nullptr, *dqs = nullptr;
+    RD_CUDA(cudaMalloc(&dc, bytes));
+    RD_CUDA(cudaMalloc(&db, bytes));
+    RD_CUDA(cudaMalloc(&dq, 8 * l));
+    RD_CUDA(cudaMalloc(&dqs, 8 * l));
+    RD_CUDA(cudaMemcpy(dc, h_cipher, bytes, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(db, h_buf, bytes, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(dq, qinv, 8 * l, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(dqs, qinv_shoup, 8 * l, cudaMemcpyHostToDevice));
+    dim3 resc_dim(N / rescale_block, l, 2);
+    if (stage == 0) mod_to_qi<<<resc_dim, rescale_block>>>(db, dc, N, p_num, q_stride, l);
+    else rescaleAndEqual_new_kernel<<<resc_dim, rescale_block>>>(dc, db, N, p_num, q_stride, l, dq, dqs);
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    RD_CUDA(cudaMemcpy(h_cipher, dc, bytes, cudaMemcpyDeviceToHost));
+    RD_CUDA(cudaMemcpy(h_buf, db, bytes, cudaMemcpyDeviceToHost));
+    cudaFree(dc); cudaFree(db); cudaFree(dq); cudaFree(dqs);
+    return 0;
+}
+
+// modUpQ0toQL_kernel (bootstrapping/Bootstrapping.cuh:6-23) on a cipher buffer [2][q_stride][N]
+// whose limb 0 holds coefficients; fills limbs 1..target_level.
+extern "C" int ref_modup_q0_to_ql(unsigned long long* h_cipher, int logN, const unsigned long long* pqt, int p_num,
+                                  int q_stride, int target_level, int scale_up) {
+    const int n_mod = p_num + q_stride;
+    if (n_mod > max_pqt_num || target_level < 1 || target_level >= q_stride) return 1;
+    const long N = 1L << logN;
+    if (N < modUpQ0toQL_block) return 1;
+    int rc = upload_pqt(pqt, n_mod);
+    if (rc) return rc;
+    const size_t bytes = 8 * (size_t)2 * q_stride * N;
+    uint64_tt* dc = nullptr;
+    RD_CUDA(cudaMalloc(&dc, bytes));
+    RD_CUDA(cudaMemcpy(dc, h_cipher, bytes, cudaMemcpyHostToDevice));
+    dim3 dim(N / modUpQ0toQL_block, target_level, 2);
+    modUpQ0toQL_kernel<<<dim, modUpQ0toQL_block>>>(dc, N, p_num, q_stride, scale_up);
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    RD_CUDA(cudaMemcpy(h_cipher, dc, bytes, cudaMemcpyDeviceToHost));
+    cudaFree(dc);
     return 0;
 }

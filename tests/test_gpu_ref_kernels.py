@@ -98,3 +98,47 @@ def test_reference_ppmm_kernel(oracle, cuda_device, limbs):
         got = PCMM_Scheme(pc, algo=algo).PPMM_host(W, X, M, K, N1, K, scaler)
         assert np.array_equal(got, ref_out), algo
     pc.close()
+
+
+def test_reference_rescale_kernels(oracle, cuda_device):
+    """mod_to_qi + rescaleAndEqual_new_kernel with the reference's transform launchers
+    (Scheme_23.cuh:339-385) == oracle == library."""
+    from ckks_llm_b200.host import Ciphertext, Scheme_23
+    logN, N = 14, 1 << 14
+    p = params.ntt_primes(51, 2 * N, 2)
+    q = params.ntt_primes(50, 2 * N, 3) + params.ntt_primes(60, 2 * N, 2)     # mixed widths, the last limb is 60-bit
+    L, l = len(q) - 1, len(q) - 1
+    rng = np.random.default_rng(21)
+    cipher = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)])
+    ref = R.rescale(cipher, logN, p + q, len(p), L, l)
+    T = oracle.NttTables(N, p + q)
+    orc = oracle.rescale(cipher.copy(), T, len(p), L, l)
+    assert np.array_equal(orc, ref)
+    ctx = Context_23(logN, p, q, [])
+    ct = Ciphertext(N, L, l, N // 2, 1.0, cipher=as_u64_tensor(cipher.reshape(-1), ctx.device))
+    Scheme_23(ctx).rescaleAndEqual(ct)
+    assert np.array_equal(to_u64_numpy(ct.cipher_device).reshape(2, L + 1, N), ref)
+    ctx.close()
+
+
+def test_reference_modup_q0_to_ql_kernel(oracle, cuda_device):
+    """modUpQ0toQL_kernel with the reference's transform launchers (bootstrapping/Bootstrapper.cuh:192-209)
+    == oracle == library."""
+    from ckks_llm_b200.host import Bootstrapper, Ciphertext
+    logN, N = 14, 1 << 14
+    p = params.ntt_primes(51, 2 * N, 1)
+    q = params.ntt_primes(60, 2 * N, 1) + params.ntt_primes(50, 2 * N, 4)     # a wide q0 and narrower upper limbs
+    L, target = len(q) - 1, 3
+    precision = 1 << 50
+    scale_up = q[0] // precision
+    rng = np.random.default_rng(22)
+    cipher = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)])
+    ref = R.modup_q0_to_ql(cipher, logN, p + q, len(p), L, target, scale_up)
+    T = oracle.NttTables(N, p + q)
+    orc = oracle.modup_q0_to_ql(cipher.copy(), T, len(p), L, target, scale_up)
+    assert np.array_equal(orc, ref)
+    ctx = Context_23(logN, p, q, [])
+    ct = Ciphertext(N, L, 0, N // 2, 1.0, cipher=as_u64_tensor(cipher.reshape(-1), ctx.device))
+    Bootstrapper(ctx, precision).modUpQ0toQL(ct, target)
+    assert np.array_equal(to_u64_numpy(ct.cipher_device).reshape(2, L + 1, N), ref)
+    ctx.close()
