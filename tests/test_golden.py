@@ -66,3 +66,17 @@ def test_ppmm_matches_reference_kernel(oracle):
     out = oracle.ppmm(W, X, q, scaler)
     assert [int(v) for v in out[0, 0, :4]] == g["ppmm"]["head"]
     assert _digest(out) == g["ppmm"]["out"]
+
+
+def test_level_changes_match_reference_kernels(oracle):
+    g, gg = _load("ref_kernels_b200.json"), _cases()
+    logN, p, q, l, cipher = gg.rescale_case()
+    T = oracle.NttTables(1 << logN, p + q)
+    out = oracle.rescale(cipher.copy(), T, len(p), len(q) - 1, l)
+    assert [int(v) for v in out[0, 0, :4]] == g["rescale"]["head"]
+    assert _digest(out) == g["rescale"]["out"]
+    logN, p, q, target, scale_up, cipher = gg.modup_q0_case()
+    T = oracle.NttTables(1 << logN, p + q)
+    out = oracle.modup_q0_to_ql(cipher.copy(), T, len(p), len(q) - 1, target, scale_up)
+    assert [int(v) for v in out[0, 1, :4]] == g["modup_q0_to_ql"]["head"]
+    assert _digest(out) == g["modup_q0_to_ql"]["out"]
