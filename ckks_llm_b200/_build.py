@@ -7,7 +7,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 LIB = os.path.join(PKG, "libckks_b200.so")
-SOURCES = ["context.cu", "ntt.cu", "modup.cu", "modup_umma.cu", "pcmm.cu", "pcmm_umma.cu", "pcmm_static.cu", "ringpack.cu", "rescale.cu"]
+SOURCES = ["context.cu", "ntt.cu", "modup.cu", "modup_umma.cu", "pcmm.cu", "pcmm_umma.cu", "pcmm_static.cu", "ringpack.cu", "rescale.cu", "keyswitch.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--threads", "2"]
 

@@ -295,6 +295,74 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
             qlinv[(size_t)l * q_num + i] = make_ulonglong2(inv, h_shoup(inv, qv[i]));
         }
     if (!st) st = upload(&c->d_qlinv, qlinv);
+
+    // Key-switch chain constants (Context_23.cuh:60-192, 286-351).  T = prod t_i, P = prod p_j.
+    {
+        const int PQ = p_num + q_num;
+        const u64* mv = c->moduli.data();
+        std::vector<ulonglong2> pq_mu(PQ ? PQ : 1), t_hat_inv(T ? T : 1), p_hat_inv(p_num ? p_num : 1), p_inv_mod_q(q_num);
+        std::vector<u64> t_hat_mod_r((size_t)PQ * (T ? T : 1), 0), half_t(c->mod_num, 0), t_mod_pq(PQ ? PQ : 1, 0),
+            p_hat_mod_q((size_t)q_num * (p_num ? p_num : 1), 0);
+        for (int i = 0; i < PQ; i++) {
+            u64 hi, lo;
+            h_barrett_mu(mv[i], &hi, &lo);
+            pq_mu[i] = make_ulonglong2(hi, lo);
+        }
+        for (int i = 0; i < T; i++) {
+            u64 prod = 1;
+            for (int ii = 0; ii < T; ii++)
+                if (ii != i) prod = h_mulmod(prod, tv[ii] % tv[i], tv[i]);
+            u64 inv = h_invmod(prod, tv[i]);
+            t_hat_inv[i] = make_ulonglong2(inv, h_shoup(inv, tv[i]));
+        }
+        for (int r = 0; r < PQ && T > 0; r++) {
+            u64 full = 1;
+            for (int j = 0; j < T; j++) {
+                u64 prod = 1;
+                for (int jj = 0; jj < T; jj++)
+                    if (jj != j) prod = h_mulmod(prod, tv[jj] % mv[r], mv[r]);
+                t_hat_mod_r[(size_t)r * T + j] = prod;
+                full = h_mulmod(full, tv[j] % mv[r], mv[r]);
+            }
+            t_mod_pq[r] = full;
+        }
+        // floor(T/2) = (T-1)/2 for odd T; modulo m it is ((T mod 2m) - 1) / 2
+        c->chain_ok = true;
+        for (int i = 0; i < c->mod_num; i++) c->chain_ok = c->chain_ok && mv[i] < (1ull << 62);
+        for (int i = 0; i < c->mod_num && T > 0 && c->chain_ok; i++) {
+            const u128 m2 = (u128)2 * mv[i];                                  // below 2^63: products stay below 2^126
+            u128 acc = 1;
+            for (int j = 0; j < T; j++) acc = (acc * (tv[j] % m2)) % m2;
+            half_t[i] = (u64)((acc - 1) / 2);
+        }
+        for (int j = 0; j < p_num; j++) {
+            u64 prod = 1;
+            for (int jj = 0; jj < p_num; jj++)
+                if (jj != j) prod = h_mulmod(prod, mv[jj] % mv[j], mv[j]);
+            u64 inv = h_invmod(prod, mv[j]);
+            p_hat_inv[j] = make_ulonglong2(inv, h_shoup(inv, mv[j]));
+        }
+        for (int i = 0; i < q_num; i++) {
+            u64 full = 1;
+            for (int j = 0; j < p_num; j++) {
+                u64 prod = 1;
+                for (int jj = 0; jj < p_num; jj++)
+                    if (jj != j) prod = h_mulmod(prod, mv[jj] % qv[i], qv[i]);
+                p_hat_mod_q[(size_t)i * p_num + j] = prod;
+                full = h_mulmod(full, mv[j] % qv[i], qv[i]);
+            }
+            u64 inv = p_num ? h_invmod(full, qv[i]) : 1;
+            p_inv_mod_q[i] = make_ulonglong2(inv, h_shoup(inv, qv[i]));
+        }
+        if (!st) st = upload(&c->d_pq_mu, pq_mu);
+        if (!st) st = upload(&c->d_t_hat_inv, t_hat_inv);
+        if (!st) st = upload(&c->d_t_hat_mod_r, t_hat_mod_r);
+        if (!st) st = upload(&c->d_half_t, half_t);
+        if (!st) st = upload(&c->d_t_mod_pq, t_mod_pq);
+        if (!st) st = upload(&c->d_p_hat_inv, p_hat_inv);
+        if (!st) st = upload(&c->d_p_hat_mod_q, p_hat_mod_q);
+        if (!st) st = upload(&c->d_p_inv_mod_q, p_inv_mod_q);
+    }
     if (!st) st = upload(&c->mu_hat_inv, hat_inv);
     if (!st) st = upload(&c->mu_hat_mod_t, hat_mod_t);
     if (!st) st = upload(&c->mu_blk_mod_t, blk_mod_t);
@@ -314,6 +382,8 @@ extern "C" int ckks_b200_context_destroy(ckks_b200_context* c) {
     DeviceGuard guard(c->device);
     cudaFree(c->tw_fwd); cudaFree(c->tw_inv); cudaFree(c->tw_fwd_d); cudaFree(c->tw_inv_d); cudaFree(c->d_moduli); cudaFree(c->d_ninv); cudaFree(c->d_qinv64);
     cudaFree(c->mu_hat_inv); cudaFree(c->mu_hat_mod_t); cudaFree(c->mu_blk_mod_t);
+    cudaFree(c->d_pq_mu); cudaFree(c->d_t_hat_inv); cudaFree(c->d_t_hat_mod_r); cudaFree(c->d_half_t); cudaFree(c->d_t_mod_pq);
+    cudaFree(c->d_p_hat_inv); cudaFree(c->d_p_hat_mod_q); cudaFree(c->d_p_inv_mod_q); cudaFree(c->ks_buf);
     cudaFree(c->mu_planes); cudaFree(c->d_t_inv); cudaFree(c->d_flags); cudaFree(c->d_qlinv); cudaFree(c->resc_buf);
     if (c->h_flags) cudaFreeHost(c->h_flags);
     cudaFree(c->d_t_mu); cudaFree(c->h2d_buf); cudaFree(c->h2d_buf2); cudaFree(c->ptr_buf); cudaFree(c->pack_buf);

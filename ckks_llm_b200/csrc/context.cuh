@@ -50,6 +50,19 @@ struct ckks_b200_context {
     int* d_flags = nullptr;                  // [16] [1] = site of a device-side wait that ran out
     int* h_flags = nullptr;                  // pinned mirror
 
+    // Key-switch chain (keyswitch.cu), the reference's tables of Context_23.cuh:60-192 and :286-351:
+    ulonglong2* d_pq_mu = nullptr;           // [p_num+q_num] Barrett mu {hi, lo} of [p | q]
+    ulonglong2* d_t_hat_inv = nullptr;       // [t_num] {(T/t_i)^-1 mod t_i, shoup}
+    u64* d_t_hat_mod_r = nullptr;            // [p_num+q_num][t_num] (T/t_i) mod r, r over [p | q]
+    u64* d_half_t = nullptr;                 // [mod_num] floor(T/2) mod each of [p | q | t]
+    u64* d_t_mod_pq = nullptr;               // [p_num+q_num] T mod r
+    ulonglong2* d_p_hat_inv = nullptr;       // [p_num] {(P/p_j)^-1 mod p_j, shoup}
+    u64* d_p_hat_mod_q = nullptr;            // [q_num][p_num] (P/p_j) mod q_i
+    ulonglong2* d_p_inv_mod_q = nullptr;     // [q_num] {P^-1 mod q_i, shoup}
+    bool chain_ok = false;                   // every modulus below 2^62 (the tables above are built only then)
+    u64* ks_buf = nullptr;                   // workspace of ckks_b200_keyswitch
+    size_t ks_cap = 0;
+
     // Scratch for the *_host entry points, grown on demand.
     u64* h2d_buf = nullptr;
     size_t h2d_cap = 0;

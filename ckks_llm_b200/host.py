@@ -33,8 +33,9 @@ class Context_23:
     (src/ckks/include/Context_23.h:19-279): moduli [p | q | t], ToNTTInplace,
     FromNTTInplace, modUpQjtoT_23."""
 
-    def __init__(self, logN, pVec, qVec, tVec=(), device=0):
+    def __init__(self, logN, pVec, qVec, tVec=(), device=0, gamma=3):
         self.lib = capi.load()
+        self.gamma = int(gamma)             # moduli of [p | q] per block of the key-switch chain (Params.cuh:28)
         self.logN, self.N = int(logN), 1 << int(logN)
         self.pVec, self.qVec, self.tVec = list(pVec), list(qVec), list(tVec)
         self.p_num, self.q_num, self.t_num = len(self.pVec), len(self.qVec), len(self.tVec)
@@ -82,6 +83,34 @@ class Context_23:
     def modUpQjtoT_23(self, output, input, l, batch_size):
         capi.check(self.lib.ckks_b200_modup_qj_to_t(
             self._h, output.data_ptr(), input.data_ptr(), l, batch_size, _stream_ptr(self.device)))
+
+    # ---- key-switch chain (KeySwitch_23.cuh:192-236); gamma is the reference's Context_23::gamma ----
+    # Context_23::external_product_T, src/ckks/include/ExternalProduct.cuh:83-97
+    def external_product_T(self, output, cipher_modUp_QjtoT, swk_modUp_RitoT, l):
+        capi.check(self.lib.ckks_b200_external_product_t(
+            self._h, output.data_ptr(), cipher_modUp_QjtoT.data_ptr(), swk_modUp_RitoT.data_ptr(), l, self.gamma,
+            _stream_ptr(self.device)))
+
+    # Context_23::FromNTTInplace_for_externalProduct, src/ckks/include/Context_23.cuh:909-930 (as mult_23 calls it)
+    def FromNTTInplace_for_externalProduct(self, device_a, l):
+        capi.check(self.lib.ckks_b200_ntt_inverse_ext(self._h, device_a.data_ptr(), l, self.gamma, _stream_ptr(self.device)))
+
+    # Context_23::modUpTtoPQl_23, src/ckks/include/BasisConv.cuh:237-248
+    def modUpTtoPQl_23(self, modUp_TtoQj_buffer, exProduct_T_temp, l, batch_size):
+        capi.check(self.lib.ckks_b200_modup_t_to_pql(
+            self._h, modUp_TtoQj_buffer.data_ptr(), exProduct_T_temp.data_ptr(), l, self.gamma, batch_size,
+            _stream_ptr(self.device)))
+
+    # Context_23::modDownPQltoQl_23, src/ckks/include/BasisConv.cuh:327-347
+    def modDownPQltoQl_23(self, output, modUp_TtoQj_buffer, l, batch_size):
+        capi.check(self.lib.ckks_b200_moddown_pql_to_ql(
+            self._h, output.data_ptr(), modUp_TtoQj_buffer.data_ptr(), l, self.gamma, batch_size,
+            _stream_ptr(self.device)))
+
+    # the chain of Scheme_23::mult_23 between the tensor product and the final addition (:219-232)
+    def keyswitch(self, output, input, swk, l):
+        capi.check(self.lib.ckks_b200_keyswitch(self._h, output.data_ptr(), input.data_ptr(), swk.data_ptr(), l, self.gamma,
+                                                _stream_ptr(self.device)))
 
     # Kernel choice for modUpQjtoT_23: "auto" (tensor cores where the level's tables qualify),
     # "tensor" (insist) or "simt" (64-bit CUDA-core kernel).  The reference has one kernel.

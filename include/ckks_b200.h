@@ -116,6 +116,34 @@ int ckks_b200_rescale(ckks_b200_context* ctx, uint64_t* d_cipher, int L, int l, 
 int ckks_b200_modup_q0_to_ql(ckks_b200_context* ctx, uint64_t* d_cipher, int L, int target_level,
                              long long scale_up, void* stream);
 
+/* ---- key-switch chain -------------------------------------------------------
+ * The steps of Scheme_23::mult_23 / rotate / conjugate between the tensor product and the final
+ * addition (KeySwitch_23.cuh:192-236), after modUpQjtoT_23 and the NTT over T.  gamma is the
+ * reference's Context_23::gamma (moduli of [p | q] per output block); R = ceil((p_num+q_num)/gamma)
+ * is its Ri_blockNum and dnum = q_num / p_num.  Every modulus must be below 2^62.
+ *
+ * Context_23::external_product_T (ExternalProduct.cuh:7-97): d_cipher_t [ceil((l+1)/p_num)][t_num][N]
+ * (digits over T, NTT domain); d_swk the key, [2][dnum][R][t_num][N]; d_out [2][R][t_num][N], of which
+ * blocks 0..ceil((p_num+l+1)/gamma)-1 are written. */
+int ckks_b200_external_product_t(ckks_b200_context* ctx, uint64_t* d_out, const uint64_t* d_cipher_t,
+                                 const uint64_t* d_swk, int l, int gamma, void* stream);
+/* Context_23::FromNTTInplace_for_externalProduct (Context_23.cuh:909-930) as the chain calls it: the
+ * inverse transform over T of the written blocks of both halves of a [2][R][t_num][N] buffer. */
+int ckks_b200_ntt_inverse_ext(ckks_b200_context* ctx, uint64_t* d_data, int l, int gamma, void* stream);
+/* Context_23::modUpTtoPQl_23 (BasisConv.cuh:183-248): d_in [batch][R][t_num][N] (coefficients over T)
+ * -> d_out, same half stride R*t_num*N, limb i of [p | q_0..q_l] at offset i*N of its half. */
+int ckks_b200_modup_t_to_pql(ckks_b200_context* ctx, uint64_t* d_out, const uint64_t* d_in, int l, int gamma,
+                             int batch, void* stream);
+/* Context_23::modDownPQltoQl_23 (BasisConv.cuh:251-347): d_in as written by ckks_b200_modup_t_to_pql ->
+ * d_out [batch][q_num][N], limbs 0..l (coefficients). */
+int ckks_b200_moddown_pql_to_ql(ckks_b200_context* ctx, uint64_t* d_out, const uint64_t* d_in, int l, int gamma,
+                                int batch, void* stream);
+/* The whole chain for one polynomial, as mult_23 runs it (KeySwitch_23.cuh:219-232): d_in [l+1][N]
+ * (NTT domain) -> INTT -> modUpQjtoT_23 -> NTT over T -> external product with d_swk -> INTT -> modUp to
+ * [p | q] -> modDown -> NTT; d_out [2][q_num][N], limbs 0..l.  Workspaces belong to the context. */
+int ckks_b200_keyswitch(ckks_b200_context* ctx, uint64_t* d_out, const uint64_t* d_in, const uint64_t* d_swk,
+                        int l, int gamma, void* stream);
+
 /* ---- ring packing, RLWE -> MLWE ---------------------------------------------
  * PCMM_Scheme::rlweCipherDecompose (pcmm/PCMM_Scheme.cuh:51-125): d_rlwe is the
  * reference's Ciphertext buffer, a limbs then b limbs, each [L+1][N]; limbs 0..l are

@@ -63,6 +63,26 @@ public:
     void modUpQjtoT_23(uint64_tt* output, uint64_tt* input, int l, int batch_size, cudaStream_t stream = 0) {
         check(ckks_b200_modup_qj_to_t(b200, (uint64_t*)output, (const uint64_t*)input, l, batch_size, stream));
     }
+
+    // Key-switch chain of Scheme_23::mult_23 (KeySwitch_23.cuh:219-232); gamma as in Params.cuh:28.
+    int gamma = 3;
+    void external_product_T(uint64_tt* output, uint64_tt* cipher_modUp_QjtoT, uint64_tt* swk_modUp_RitoT, int l,
+                            cudaStream_t stream = 0) {
+        check(ckks_b200_external_product_t(b200, (uint64_t*)output, (const uint64_t*)cipher_modUp_QjtoT,
+                                           (const uint64_t*)swk_modUp_RitoT, l, gamma, stream));
+    }
+    void FromNTTInplace_for_externalProduct(uint64_tt* device_a, int l, cudaStream_t stream = 0) {
+        check(ckks_b200_ntt_inverse_ext(b200, (uint64_t*)device_a, l, gamma, stream));
+    }
+    void modUpTtoPQl_23(uint64_tt* modUp_TtoQj_buffer, uint64_tt* exProduct_T_temp, int l, int batch_size,
+                        cudaStream_t stream = 0) {
+        check(ckks_b200_modup_t_to_pql(b200, (uint64_t*)modUp_TtoQj_buffer, (const uint64_t*)exProduct_T_temp, l, gamma,
+                                       batch_size, stream));
+    }
+    void modDownPQltoQl_23(uint64_tt* output, uint64_tt* modUp_TtoQj_buffer, int l, int batch_size, cudaStream_t stream = 0) {
+        check(ckks_b200_moddown_pql_to_ql(b200, (uint64_t*)output, (const uint64_t*)modUp_TtoQj_buffer, l, gamma, batch_size,
+                                          stream));
+    }
 };
 
 // RLWE ciphertext carrier with the members the path reads (Ciphertext.cuh:5-100): cipher_device holds the a

@@ -666,3 +666,98 @@ ORC_API void orc_modup_q0_to_ql(u64 *cipher, uint32_t n, int stride, int target_
             }
         }
 }
+
+/* ---------------------------------------------------------------------------
+ * Key-switch chain of the CKKS-23 evaluator (Scheme_23::mult_23, KeySwitch_23.cuh:192-236).
+ * R = Ri_blockNum = ceil((p_num+q_num)/gamma); tables are passed in by the caller.
+ * ------------------------------------------------------------------------- */
+
+/* external_product_T_kernel: src/ckks/include/ExternalProduct.cuh:7-48 */
+ORC_API void orc_external_product_t(u64 *out, const u64 *cipher, const u64 *swk, uint32_t n, int t_num, int R,
+                                    int cipher_blocks, int blocks, int dnum, const u64 *t)
+{
+#pragma omp parallel for collapse(2)
+    for (int blk = 0; blk < blocks; blk++)
+        for (int k = 0; k < t_num; k++) {
+            u64 tk = t[k], mu_hi, mu_lo;
+            orc_barrett_mu(tk, &mu_hi, &mu_lo);
+            for (uint32_t x = 0; x < n; x++)
+                for (int h = 0; h < 2; h++) {
+                    u128 acc = 0;
+                    for (int i = 0; i < cipher_blocks; i++) {
+                        u64 ra = cipher[((size_t)i * t_num + k) * n + x];
+                        u64 rb = swk[(size_t)h * R * t_num * dnum * n +
+                                     ((size_t)i * t_num * R + (size_t)blk * t_num + k) * n + x];
+                        acc += (u128)ra * rb;
+                    }
+                    out[(size_t)h * R * t_num * n + ((size_t)blk * t_num + k) * n + x] = barrett128(acc, tk, mu_hi, mu_lo);
+                }
+        }
+}
+
+/* modUpTtoPQl_23_kernel: src/ckks/include/BasisConv.cuh:183-235.
+ * pq = [p | q] moduli; t_hat_inv(+shoup)[t_num]; t_hat_mod_r[(p_num+q_num)][t_num]; half_t over [p | q | t];
+ * t_mod_pq[p_num+q_num]. */
+ORC_API void orc_modup_t_to_pql(u64 *out, const u64 *in, uint32_t n, int p_num, int q_num, int t_num, int l, int gamma,
+                                int batch, const u64 *pq, const u64 *t, const u64 *t_hat_inv, const u64 *t_hat_inv_shoup,
+                                const u64 *t_hat_mod_r, const u64 *half_t, const u64 *t_mod_pq)
+{
+    int R = (p_num + q_num + gamma - 1) / gamma;
+    int blocks = (p_num + l + 1 + gamma - 1) / gamma;
+#pragma omp parallel for collapse(2)
+    for (int c = 0; c < batch; c++)
+        for (int blk = 0; blk < blocks; blk++)
+            for (uint32_t x = 0; x < n; x++) {
+                u64 rb[64];
+                double vv = 0;
+                for (int i = 0; i < t_num; i++) {
+                    u64 ra = in[(size_t)c * R * t_num * n + ((size_t)blk * t_num + i) * n + x];
+                    ra = ra + half_t[p_num + q_num + i];
+                    rb[i] = mulmod_shoup(ra, t_hat_inv[i], t_hat_inv_shoup[i], t[i]);
+                    double rr = (double)rb[i];
+                    vv += rr / (double)t[i];
+                }
+                int vv_floor = (int)vv;
+                for (int j = 0; j < gamma && j + blk * gamma < p_num + l + 1; j++) {
+                    int r = j + blk * gamma;
+                    u64 ri = pq[r], mu_hi, mu_lo;
+                    orc_barrett_mu(ri, &mu_hi, &mu_lo);
+                    u128 acc = 0;
+                    for (int i = 0; i < t_num; i++) acc += (u128)rb[i] * t_hat_mod_r[(size_t)r * t_num + i];
+                    acc -= (u128)((u64)vv_floor * t_mod_pq[r]);          /* sub_uint128_uint64: wraps like the kernel */
+                    u64 lo = barrett128(acc, ri, mu_hi, mu_lo);
+                    lo = lo + ri - half_t[r];
+                    out[(size_t)c * R * t_num * n + (size_t)r * n + x] = csub_q(lo, ri);
+                }
+            }
+}
+
+/* modDownPQltoQl_23_multi_kernel and _alpha1_multi_kernel: src/ckks/include/BasisConv.cuh:251-325 */
+ORC_API void orc_moddown_pql_to_ql(u64 *out, const u64 *in, uint32_t n, int p_num, int q_num, int t_num, int l, int gamma,
+                                   int batch, const u64 *pq, const u64 *p_hat_inv, const u64 *p_hat_inv_shoup,
+                                   const u64 *p_hat_mod_q, const u64 *p_inv_mod_q, const u64 *p_inv_mod_q_shoup)
+{
+    int R = (p_num + q_num + gamma - 1) / gamma;
+#pragma omp parallel for collapse(2)
+    for (int c = 0; c < batch; c++)
+        for (int i = 0; i <= l; i++) {
+            u64 qi = pq[p_num + i], mu_hi, mu_lo;
+            orc_barrett_mu(qi, &mu_hi, &mu_lo);
+            const u64 *src = in + (size_t)c * R * t_num * n;
+            for (uint32_t x = 0; x < n; x++) {
+                u64 part;
+                if (p_num == 1) {
+                    part = src[x] % qi;
+                } else {
+                    u128 acc = 0;
+                    for (int j = 0; j < p_num; j++) {
+                        u64 rb = mulmod_shoup(src[(size_t)j * n + x], p_hat_inv[j], p_hat_inv_shoup[j], pq[j]);
+                        acc += (u128)rb * p_hat_mod_q[(size_t)i * p_num + j];
+                    }
+                    part = barrett128(acc, qi, mu_hi, mu_lo);
+                }
+                u64 d = qi - part + src[(size_t)(p_num + i) * n + x];
+                out[((size_t)c * q_num + i) * n + x] = mulmod_shoup(d, p_inv_mod_q[i], p_inv_mod_q_shoup[i], qi);
+            }
+        }
+}

@@ -54,6 +54,10 @@ def lib():
                                      C.c_uint64, C.c_uint64]
         L.orc_pack_keymac.argtypes = [_U64P, _U64P, _U64P, C.c_long, C.c_int, _U64P]
         L.orc_pack_moddown.argtypes = [_U64P, _U64P, _U64P, C.c_long, C.c_uint64, C.c_uint64]
+        L.orc_external_product_t.argtypes = [_U64P, _U64P, _U64P, C.c_uint32, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                             _U64P]
+        L.orc_modup_t_to_pql.argtypes = [_U64P, _U64P, C.c_uint32] + [C.c_int] * 6 + [_U64P] * 7
+        L.orc_moddown_pql_to_ql.argtypes = [_U64P, _U64P, C.c_uint32] + [C.c_int] * 6 + [_U64P] * 6
         L.orc_mod_to_qi.argtypes = [_U64P, _U64P, C.c_uint32, C.c_int, C.c_int, _U64P]
         L.orc_rescale_combine.argtypes = [_U64P, _U64P, C.c_uint32, C.c_int, C.c_int, _U64P, _U64P, _U64P]
         L.orc_modup_q0_to_ql.argtypes = [_U64P, C.c_uint32, C.c_int, C.c_int, _U64P, C.c_int]
@@ -250,3 +254,93 @@ def modup_q0_to_ql(cipher, tables, p_num, L, target_level, scale_up):
     lib().orc_modup_q0_to_ql(flat, n, L + 1, target_level, q, int(scale_up))
     ntt_batch(flat, tables, 0, p_num, 2, target_level + 1, L + 1)
     return cipher
+
+
+class KeySwitchTables:
+    """Constants of the key-switch chain computed with Python integers (definitions of
+    Context_23::preComputeOnCPU, Context_23.cuh:60-192 and :286-351)."""
+
+    def __init__(self, p, q, t):
+        p, q, t = [int(v) for v in p], [int(v) for v in q], [int(v) for v in t]
+        self.p, self.q, self.t = p, q, t
+        pq = p + q
+        T = 1
+        for v in t:
+            T *= v
+        P = 1
+        for v in p:
+            P *= v
+        u = lambda xs: np.array(xs, dtype=np.uint64)
+        shoup = lambda x, m: (x << 64) // m
+        self.pq = u(pq)
+        self.tv = u(t)
+        inv = [pow(T // ti, -1, ti) for ti in t]
+        self.t_hat_inv, self.t_hat_inv_shoup = u(inv), u([shoup(a, m) for a, m in zip(inv, t)])
+        self.t_hat_mod_r = u([[(T // ti) % r for ti in t] for r in pq]).reshape(-1)
+        self.half_t = u([(T // 2) % m for m in pq + t])
+        self.t_mod_pq = u([T % r for r in pq])
+        inv = [pow(P // pj, -1, pj) for pj in p]
+        self.p_hat_inv, self.p_hat_inv_shoup = u(inv), u([shoup(a, m) for a, m in zip(inv, p)])
+        self.p_hat_mod_q = u([[(P // pj) % qi for pj in p] for qi in q]).reshape(-1)
+        inv = [pow(P, -1, qi) for qi in q]
+        self.p_inv_mod_q, self.p_inv_mod_q_shoup = u(inv), u([shoup(a, m) for a, m in zip(inv, q)])
+
+
+def external_product_t(cipher_t, swk, n, KT, l, gamma):
+    """Context_23::external_product_T (ExternalProduct.cuh:7-97): cipher_t [cipher_blocks][t_num][n], swk
+    [2][dnum][R][t_num][n] -> out [2][R][t_num][n] (blocks beyond the level stay zero)."""
+    p_num, q_num, t_num = len(KT.p), len(KT.q), len(KT.t)
+    R = (p_num + q_num + gamma - 1) // gamma
+    cb = (l + 1 + p_num - 1) // p_num
+    blocks = (p_num + l + 1 + gamma - 1) // gamma
+    out = np.zeros((2, R, t_num, n), dtype=np.uint64)
+    lib().orc_external_product_t(out.reshape(-1), np.ascontiguousarray(cipher_t, dtype=np.uint64).reshape(-1),
+                                 np.ascontiguousarray(swk, dtype=np.uint64).reshape(-1), n, t_num, R, cb, blocks,
+                                 q_num // p_num, KT.tv)
+    return out
+
+
+def modup_t_to_pql(inp, n, KT, l, gamma, batch):
+    """Context_23::modUpTtoPQl_23 (BasisConv.cuh:183-248): in [batch][R][t_num][n] -> out of the same shape with
+    limb i of [p | q_0..q_l] at flat limb offset i of its half."""
+    p_num, q_num, t_num = len(KT.p), len(KT.q), len(KT.t)
+    R = (p_num + q_num + gamma - 1) // gamma
+    out = np.zeros((batch, R * t_num, n), dtype=np.uint64)
+    lib().orc_modup_t_to_pql(out.reshape(-1), np.ascontiguousarray(inp, dtype=np.uint64).reshape(-1), n, p_num, q_num,
+                             t_num, l, gamma, batch, KT.pq, KT.tv, KT.t_hat_inv, KT.t_hat_inv_shoup, KT.t_hat_mod_r,
+                             KT.half_t, KT.t_mod_pq)
+    return out
+
+
+def moddown_pql_to_ql(inp, n, KT, l, gamma, batch):
+    """Context_23::modDownPQltoQl_23 (BasisConv.cuh:251-347): in as written by modup_t_to_pql -> out
+    [batch][q_num][n], limbs 0..l."""
+    p_num, q_num, t_num = len(KT.p), len(KT.q), len(KT.t)
+    out = np.zeros((batch, q_num, n), dtype=np.uint64)
+    lib().orc_moddown_pql_to_ql(out.reshape(-1), np.ascontiguousarray(inp, dtype=np.uint64).reshape(-1), n, p_num, q_num,
+                                t_num, l, gamma, batch, KT.pq, KT.p_hat_inv, KT.p_hat_inv_shoup, KT.p_hat_mod_q,
+                                KT.p_inv_mod_q, KT.p_inv_mod_q_shoup)
+    return out
+
+
+def keyswitch(inp, swk, tables, KT, l, gamma):
+    """The chain of Scheme_23::mult_23 between the tensor product and the final addition
+    (KeySwitch_23.cuh:219-232): inp [l+1][n] (NTT domain) -> out [2][q_num][n] (NTT domain, limbs 0..l).
+    tables: NttTables over [p | q | t]."""
+    n = tables.n
+    p_num, q_num, t_num = len(KT.p), len(KT.q), len(KT.t)
+    R = (p_num + q_num + gamma - 1) // gamma
+    cb = (l + 1 + p_num - 1) // p_num
+    blocks = (p_num + l + 1 + gamma - 1) // gamma
+    coef = np.zeros((q_num, n), dtype=np.uint64)
+    coef[:l + 1] = inp
+    ntt_batch(coef.reshape(-1), tables, 0, p_num, 1, l + 1, q_num, inverse=True)
+    dig = modup(coef[None], n, KT.q, KT.t, p_num, l, 1)[0]                     # [cb][t_num][n]
+    ntt_batch(dig.reshape(-1), tables, 0, p_num + q_num, cb, t_num, t_num)
+    ext = external_product_t(dig, swk, n, KT, l, gamma)
+    for h in range(2):
+        ntt_batch(ext[h].reshape(-1), tables, 0, p_num + q_num, blocks, t_num, t_num, inverse=True)
+    pq = modup_t_to_pql(ext, n, KT, l, gamma, 2)
+    out = moddown_pql_to_ql(pq, n, KT, l, gamma, 2)
+    ntt_batch(out.reshape(-1), tables, 0, p_num, 2, l + 1, q_num)
+    return out

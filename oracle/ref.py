@@ -32,6 +32,7 @@ def lib():
                                C.c_double, _U64P, _U64P]
         L.ref_rescale_stage.argtypes = [_U64P, _U64P, C.c_int, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, _U64P, _U64P]
         L.ref_modup_q0_to_ql.argtypes = [_U64P, C.c_int, _U64P, C.c_int, C.c_int, C.c_int, C.c_int]
+        L.ref_keyswitch_stage.argtypes = [_U64P, _U64P, _U64P, C.c_int, _U64P] + [C.c_int] * 6 + [_U64P] * 10
         L.ref_decompose.argtypes = [_U64P, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _U64P]
         _lib = L
     return _lib
@@ -163,3 +164,21 @@ def modup_q0_to_ql(cipher, logN, pq, p_num, L, target_level, scale_up):
     rc = lib().ref_modup_q0_to_ql(c, logN, pq, p_num, L + 1, target_level, int(scale_up))
     assert rc == 0, rc
     return ntt(c.reshape(2, L + 1, -1), logN, pq, 0, p_num, 2, target_level + 1, L + 1)
+
+
+def keyswitch_stage(stage, inp, aux, logN, KT, l, gamma):
+    """One kernel of the key-switch chain through the reference's launcher: stage 0 external_product_T
+    (inp = digits over T, aux = key), 1 modUpTtoPQl_23, 2 modDownPQltoQl_23.  KT: oracle.KeySwitchTables."""
+    p_num, q_num, t_num = len(KT.p), len(KT.q), len(KT.t)
+    n = 1 << logN
+    R = (p_num + q_num + gamma - 1) // gamma
+    out = np.zeros((2, q_num, n) if stage == 2 else (2, R, t_num, n), dtype=np.uint64)
+    pqt = np.array(KT.p + KT.q + KT.t, dtype=np.uint64)
+    aux = np.zeros(1, dtype=np.uint64) if aux is None else np.ascontiguousarray(aux, dtype=np.uint64).reshape(-1)
+    rc = lib().ref_keyswitch_stage(out.reshape(-1), np.ascontiguousarray(inp, dtype=np.uint64).reshape(-1), aux, logN, pqt,
+                                   p_num, q_num, t_num, l, gamma, stage, KT.t_hat_inv, KT.t_hat_inv_shoup, KT.t_hat_mod_r,
+                                   KT.half_t, KT.t_mod_pq, KT.p_hat_inv, KT.p_hat_inv_shoup, KT.p_hat_mod_q,
+                                   KT.p_inv_mod_q, KT.p_inv_mod_q_shoup)
+    if rc:
+        raise RuntimeError(f"ref_keyswitch_stage failed with {rc}")
+    return out

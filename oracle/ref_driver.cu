@@ -387,3 +387,69 @@ extern "C" int ref_modup_q0_to_ql(unsigned long long* h_cipher, int logN, const 
     cudaFree(dc);
     return 0;
 }
+
+// The three kernels of the key-switch chain through the reference's own launchers
+// (Context_23::external_product_T, modUpTtoPQl_23, modDownPQltoQl_23) on a zero-initialised context
+// whose integer members and table pointers are filled here.  pqt = [p | q | t]; tables come from the
+// caller in the reference's layouts.  stage 0: external product (h_in = digits over T, h_aux = key);
+// stage 1: T -> [p | q]; stage 2: ModDown.  Buffers are [2][R*t_num][N] except the ModDown output [2][q_num][N].
+extern "C" int ref_keyswitch_stage(unsigned long long* h_out, const unsigned long long* h_in, const unsigned long long* h_aux,
+                                   int logN, const unsigned long long* pqt, int p_num, int q_num, int t_num, int l, int gamma,
+                                   int stage, const unsigned long long* t_hat_inv, const unsigned long long* t_hat_inv_shoup,
+                                   const unsigned long long* t_hat_mod_r, const unsigned long long* half_t,
+                                   const unsigned long long* t_mod_pq, const unsigned long long* p_hat_inv,
+                                   const unsigned long long* p_hat_inv_shoup, const unsigned long long* p_hat_mod_q,
+                                   const unsigned long long* p_inv_mod_q, const unsigned long long* p_inv_mod_q_shoup) {
+    const int n_mod = p_num + q_num + t_num;
+    if (n_mod > max_pqt_num || p_num > max_p_num || t_num > max_tnum) return 1;
+    const long N = 1L << logN;
+    int rc = upload_pqt(pqt, n_mod);
+    if (rc) return rc;
+    RD_CUDA(cudaMemcpyToSymbol(halfTmodpqti_cons, half_t, 8 * n_mod));
+    RD_CUDA(cudaMemcpyToSymbol(Tmodpqi_cons, t_mod_pq, 8 * (p_num + q_num)));
+    RD_CUDA(cudaMemcpyToSymbol(Pinvmodqi_cons, p_inv_mod_q, 8 * q_num));
+    RD_CUDA(cudaMemcpyToSymbol(Pinvmodqi_shoup_cons, p_inv_mod_q_shoup, 8 * q_num));
+    RD_CUDA(cudaMemcpyToSymbol(pHatInvVecModp_cons, p_hat_inv, 8 * p_num));
+    RD_CUDA(cudaMemcpyToSymbol(pHatInvVecModp_shoup_cons, p_hat_inv_shoup, 8 * p_num));
+    Context_23* c = fake_context();
+    c->N = N;
+    c->logN = logN;
+    c->p_num = p_num; c->q_num = q_num; c->t_num = t_num;
+    c->K = p_num; c->L = q_num - 1;
+    c->gamma = gamma;
+    c->dnum = q_num / p_num;
+    c->Ri_blockNum = (p_num + q_num + gamma - 1) / gamma;
+    const int R = c->Ri_blockNum;
+    if (R > max_Riblock_num) { free(c); return 1; }
+    const size_t tb = (size_t)2 * R * t_num * N;
+    RD_CUDA(cudaMalloc(&c->THatInvVecModti_23_device, 8 * t_num));
+    RD_CUDA(cudaMalloc(&c->THatInvVecModti_23_shoup_device, 8 * t_num));
+    RD_CUDA(cudaMalloc(&c->THatVecModRi_23_device, 8 * (size_t)(p_num + q_num) * t_num));
+    RD_CUDA(cudaMalloc(&c->pHatVecModq_23_device, 8 * (size_t)q_num * p_num));
+    RD_CUDA(cudaMemcpy(c->THatInvVecModti_23_device, t_hat_inv, 8 * t_num, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(c->THatInvVecModti_23_shoup_device, t_hat_inv_shoup, 8 * t_num, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(c->THatVecModRi_23_device, t_hat_mod_r, 8 * (size_t)(p_num + q_num) * t_num, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(c->pHatVecModq_23_device, p_hat_mod_q, 8 * (size_t)q_num * p_num, cudaMemcpyHostToDevice));
+    uint64_tt *din = nullptr, *daux = nullptr, *dout = nullptr;
+    const int cipher_blocks = (l + 1 + p_num - 1) / p_num;
+    const size_t in_words = stage == 0 ? (size_t)cipher_blocks * t_num * N : tb;
+    const size_t aux_words = stage == 0 ? (size_t)2 * c->dnum * R * t_num * N : 1;
+    const size_t out_words = stage == 2 ? (size_t)2 * q_num * N : tb;
+    RD_CUDA(cudaMalloc(&din, 8 * in_words));
+    RD_CUDA(cudaMalloc(&daux, 8 * aux_words));
+    RD_CUDA(cudaMalloc(&dout, 8 * out_words));
+    RD_CUDA(cudaMemcpy(din, h_in, 8 * in_words, cudaMemcpyHostToDevice));
+    if (stage == 0) RD_CUDA(cudaMemcpy(daux, h_aux, 8 * aux_words, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(dout, h_out, 8 * out_words, cudaMemcpyHostToDevice));
+    if (stage == 0) c->external_product_T(dout, din, daux, l);
+    else if (stage == 1) c->modUpTtoPQl_23(dout, din, l, 2);
+    else c->modDownPQltoQl_23(dout, din, l, 2);
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    RD_CUDA(cudaMemcpy(h_out, dout, 8 * out_words, cudaMemcpyDeviceToHost));
+    cudaFree(din); cudaFree(daux); cudaFree(dout);
+    cudaFree(c->THatInvVecModti_23_device); cudaFree(c->THatInvVecModti_23_shoup_device);
+    cudaFree(c->THatVecModRi_23_device); cudaFree(c->pHatVecModq_23_device);
+    free(c);
+    return 0;
+}

@@ -1,0 +1,77 @@
+"""GPU parity of the key-switch chain (external product over T, T -> [p | q] conversion, ModDown and the
+whole chain of Scheme_23::mult_23) against the CPU oracle, through the reference-shaped mirrors."""
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+from ckks_llm_b200 import params
+from ckks_llm_b200.host import Context_23, as_u64_tensor, to_u64_numpy
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(oracle, logN, p_num, q_num, t_num, gamma, q_bits=50, t_bits=60):
+    N = 1 << logN
+    p = params.ntt_primes(q_bits + 1, 2 * N, p_num)
+    q = params.ntt_primes(q_bits, 2 * N, q_num)
+    t = params.ntt_primes(t_bits, 2 * N, t_num)
+    ctx = Context_23(logN, p, q, t, gamma=gamma)
+    return N, p, q, t, ctx, oracle.KeySwitchTables(p, q, t)
+
+
+def _shapes(p, q, t, l, gamma):
+    R = (len(p) + len(q) + gamma - 1) // gamma
+    return R, (l + 1 + len(p) - 1) // len(p), len(q) // len(p), (len(p) + l + 1 + gamma - 1) // gamma
+
+
+CASES = [(12, 2, 6, 4, 3, 5), (12, 3, 9, 5, 4, 8), (13, 1, 5, 3, 3, 2), (12, 2, 6, 4, 3, 0), (12, 4, 8, 8, 5, 6)]
+
+
+@pytest.mark.parametrize("logN,p_num,q_num,t_num,gamma,l", CASES)
+def test_chain_stages(oracle, cuda_device, logN, p_num, q_num, t_num, gamma, l):
+    N, p, q, t, ctx, KT = _setup(oracle, logN, p_num, q_num, t_num, gamma)
+    R, cb, dnum, blocks = _shapes(p, q, t, l, gamma)
+    rng = np.random.default_rng(logN * 100 + l)
+    dev = ctx.device
+    # external product
+    cipher = np.stack([H.uniform_residues(rng, t, (N,)) for _ in range(cb)])
+    swk = np.stack([H.uniform_residues(rng, t, (N,)) for _ in range(2 * dnum * R)]).reshape(2, dnum, R, t_num, N)
+    exp = oracle.external_product_t(cipher, swk, N, KT, l, gamma)
+    out = torch.zeros(2 * R * t_num * N, dtype=torch.int64, device=dev)
+    ctx.external_product_T(out, as_u64_tensor(cipher, dev), as_u64_tensor(swk, dev), l)
+    assert np.array_equal(to_u64_numpy(out).reshape(2, R, t_num, N), exp)
+    # T -> [p | q]: any residues, and values at the centring boundaries
+    inp = np.stack([H.uniform_residues(rng, t, (N,)) for _ in range(2 * R)]).reshape(2, R, t_num, N)
+    inp[0, 0, :, 0] = 0
+    inp[0, 0, :, 1] = np.array(t, dtype=np.uint64) - np.uint64(1)
+    inp[0, 0, :, 2] = KT.half_t[len(p) + len(q):]
+    exp = oracle.modup_t_to_pql(inp, N, KT, l, gamma, 2)
+    out = torch.zeros(2 * R * t_num * N, dtype=torch.int64, device=dev)
+    ctx.modUpTtoPQl_23(out, as_u64_tensor(inp, dev), l, 2)
+    assert np.array_equal(to_u64_numpy(out).reshape(2, R * t_num, N), exp)
+    # ModDown
+    pqin = np.zeros((2, R * t_num, N), dtype=np.uint64)
+    for c in range(2):
+        pqin[c, :len(p) + len(q)] = H.uniform_residues(rng, p + q, (N,))
+    exp = oracle.moddown_pql_to_ql(pqin, N, KT, l, gamma, 2)
+    out = torch.zeros(2 * len(q) * N, dtype=torch.int64, device=dev)
+    ctx.modDownPQltoQl_23(out, as_u64_tensor(pqin, dev), l, 2)
+    assert np.array_equal(to_u64_numpy(out).reshape(2, len(q), N), exp)
+    ctx.close()
+
+
+@pytest.mark.parametrize("logN,p_num,q_num,t_num,gamma,l", [(12, 2, 6, 4, 3, 5), (13, 3, 9, 5, 4, 6), (14, 1, 4, 3, 3, 3)])
+def test_whole_chain(oracle, cuda_device, logN, p_num, q_num, t_num, gamma, l):
+    N, p, q, t, ctx, KT = _setup(oracle, logN, p_num, q_num, t_num, gamma)
+    R, cb, dnum, blocks = _shapes(p, q, t, l, gamma)
+    rng = np.random.default_rng(7 + logN)
+    T = oracle.NttTables(N, p + q + t)
+    inp = H.uniform_residues(rng, q[:l + 1], (N,))
+    swk = np.stack([H.uniform_residues(rng, t, (N,)) for _ in range(2 * dnum * R)]).reshape(2, dnum, R, t_num, N)
+    exp = oracle.keyswitch(inp, swk, T, KT, l, gamma)
+    out = torch.zeros(2 * len(q) * N, dtype=torch.int64, device=ctx.device)
+    ctx.keyswitch(out, as_u64_tensor(inp, ctx.device), as_u64_tensor(swk, ctx.device), l)
+    got = to_u64_numpy(out).reshape(2, len(q), N)
+    assert np.array_equal(got[:, :l + 1], exp[:, :l + 1])
+    ctx.close()

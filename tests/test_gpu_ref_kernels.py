@@ -14,6 +14,8 @@ from ckks_llm_b200 import capi, params
 from ckks_llm_b200.host import Context_23, PCMM_Context, PCMM_Scheme, as_u64_tensor, to_u64_numpy
 from oracle import ref as R
 
+R_ = R        # the key-switch test uses R for the block count
+
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not R.available(), reason="reference driver library not built")]
 
 
@@ -141,4 +143,44 @@ def test_reference_modup_q0_to_ql_kernel(oracle, cuda_device):
     ct = Ciphertext(N, L, 0, N // 2, 1.0, cipher=as_u64_tensor(cipher.reshape(-1), ctx.device))
     Bootstrapper(ctx, precision).modUpQ0toQL(ct, target)
     assert np.array_equal(to_u64_numpy(ct.cipher_device).reshape(2, L + 1, N), ref)
+    ctx.close()
+
+
+@pytest.mark.parametrize("p_num,q_num,t_num,gamma,l", [(2, 6, 4, 3, 5), (1, 5, 3, 3, 3), (3, 9, 5, 4, 7)])
+def test_reference_keyswitch_kernels(oracle, cuda_device, p_num, q_num, t_num, gamma, l):
+    """external_product_T, modUpTtoPQl_23 and modDownPQltoQl_23 through the reference's own launchers
+    (ExternalProduct.cuh:83-97, BasisConv.cuh:237-248, :327-347) == oracle == library."""
+    logN, N = 12, 1 << 12
+    p = params.ntt_primes(51, 2 * N, p_num)
+    q = params.ntt_primes(50, 2 * N, q_num)
+    t = params.ntt_primes(60, 2 * N, t_num)
+    KT = oracle.KeySwitchTables(p, q, t)
+    ctx = Context_23(logN, p, q, t, gamma=gamma)
+    dev = ctx.device
+    R = (p_num + q_num + gamma - 1) // gamma
+    cb, dnum = (l + 1 + p_num - 1) // p_num, q_num // p_num
+    rng = np.random.default_rng(31 + p_num)
+    cipher = np.stack([H.uniform_residues(rng, t, (N,)) for _ in range(cb)])
+    swk = np.stack([H.uniform_residues(rng, t, (N,)) for _ in range(2 * dnum * R)]).reshape(2, dnum, R, t_num, N)
+    ref = R_.keyswitch_stage(0, cipher, swk, logN, KT, l, gamma)
+    assert np.array_equal(oracle.external_product_t(cipher, swk, N, KT, l, gamma), ref)
+    out = torch.zeros(2 * R * t_num * N, dtype=torch.int64, device=dev)
+    ctx.external_product_T(out, as_u64_tensor(cipher, dev), as_u64_tensor(swk, dev), l)
+    assert np.array_equal(to_u64_numpy(out).reshape(2, R, t_num, N), ref)
+
+    inp = np.stack([H.uniform_residues(rng, t, (N,)) for _ in range(2 * R)]).reshape(2, R, t_num, N)
+    ref = R_.keyswitch_stage(1, inp, None, logN, KT, l, gamma)
+    assert np.array_equal(oracle.modup_t_to_pql(inp, N, KT, l, gamma, 2).reshape(ref.shape), ref)
+    out = torch.zeros(2 * R * t_num * N, dtype=torch.int64, device=dev)
+    ctx.modUpTtoPQl_23(out, as_u64_tensor(inp, dev), l, 2)
+    assert np.array_equal(to_u64_numpy(out).reshape(ref.shape), ref)
+
+    pqin = np.zeros((2, R * t_num, N), dtype=np.uint64)
+    for c in range(2):
+        pqin[c, :p_num + q_num] = H.uniform_residues(rng, p + q, (N,))
+    ref = R_.keyswitch_stage(2, pqin, None, logN, KT, l, gamma)
+    assert np.array_equal(oracle.moddown_pql_to_ql(pqin, N, KT, l, gamma, 2)[:, :l + 1], ref[:, :l + 1])
+    out = torch.zeros(2 * q_num * N, dtype=torch.int64, device=dev)
+    ctx.modDownPQltoQl_23(out, as_u64_tensor(pqin, dev), l, 2)
+    assert np.array_equal(to_u64_numpy(out).reshape(2, q_num, N)[:, :l + 1], ref[:, :l + 1])
     ctx.close()
