@@ -296,12 +296,61 @@ def bench_levels(torch, device, steps, warmup, peaks):
     return res
 
 
+def bench_keyswitch(torch, device, steps, warmup, peaks):
+    """The key-switch chain (ckks_b200_keyswitch) on the ModUp configuration's moduli: N=2^16, 24 x 50-bit q,
+    8 special primes (dnum 3), 12 x 60-bit t, gamma 6, top level: device time per switched polynomial."""
+    from ckks_llm_b200 import params
+    from ckks_llm_b200.host import Context_23
+    logN, K, qn, T, gamma = 16, 8, 24, 12, 6
+    N, l = 1 << logN, qn - 1
+    p = params.ntt_primes(51, 2 * N, K)
+    q = params.ntt_primes(50, 2 * N, qn)
+    t = params.ntt_primes(60, 2 * N, T)
+    ctx = Context_23(logN, p, q, t, device=device.index, gamma=gamma)
+    R = (K + qn + gamma - 1) // gamma
+    cb, blocks, dnum = (l + 1 + K - 1) // K, (K + l + 1 + gamma - 1) // gamma, qn // K
+    g = torch.Generator(device=device).manual_seed(4)
+    inp = torch.empty((qn, N), dtype=torch.int64, device=device)
+    for i, qi in enumerate(q):
+        inp[i] = torch.randint(0, qi, (N,), generator=g, device=device, dtype=torch.int64)
+    swk = torch.empty((2 * dnum * R, T, N), dtype=torch.int64, device=device)
+    for k, tk in enumerate(t):
+        swk[:, k, :] = torch.randint(0, tk, (2 * dnum * R, N), generator=g, device=device, dtype=torch.int64)
+    out = torch.empty((2, qn, N), dtype=torch.int64, device=device)
+    for _ in range(warmup):
+        ctx.keyswitch(out, inp, swk, l)
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        ctx.keyswitch(out, inp, swk, l)
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1) / steps
+    limb_polys = (2 * (l + 1)                                   # copy of the input
+                  + 2 * (l + 1) + (l + 1) + cb * T + 2 * cb * T  # INTT, ModUp to T, NTT over T
+                  + cb * T + 2 * cb * blocks * T + 2 * blocks * T  # external product: digits, key, output
+                  + 4 * blocks * T                               # INTT over T
+                  + 2 * blocks * T + 2 * (K + l + 1)             # T -> [p | q]
+                  + 2 * (K + l + 1) + 2 * (l + 1)                # ModDown
+                  + 4 * (l + 1))                                 # NTT
+    gbs = limb_polys * 8 * N / (ms * 1e-3) / 1e9
+    ctx.close()
+    return {"switches_per_sec": 1e3 / ms, "ms_per_switch": ms,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                         "note": "algorithmic bytes: every stage reads its inputs and writes its outputs once; the key is %d MB"
+                                 % (2 * dnum * R * T * N * 8 // 2**20)},
+            "config": {"workload": "key-switch chain N=2^16, 24x50-bit q, 8 p, 12x60-bit t, gamma 6, level 23",
+                       "l2_policy": "the key alone (216 MB) is larger than L2"}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", choices=["pcmm", "ntt", "modup"], default="pcmm")
+    ap.add_argument("--workload", choices=["pcmm", "ntt", "modup", "keyswitch"], default="pcmm")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -453,6 +502,7 @@ def main():
                 extra["ntt"] = bench_ntt(torch, device, max(args.steps, 10), args.warmup, peaks)
                 extra["modup"] = bench_modup(torch, device, max(args.steps, 10), args.warmup, peaks)
                 extra["levels"] = bench_levels(torch, device, max(args.steps, 10), args.warmup, peaks)
+                extra["keyswitch"] = bench_keyswitch(torch, device, max(args.steps, 10), args.warmup, peaks)
             except Exception as ex:           # the headline stays valid without the side measurements
                 extra["side_error"] = repr(ex)
     else:
@@ -467,6 +517,12 @@ def main():
             roof = r["forward"]["roofline"]
             extra["ntt"] = r
             metric, unit, cfg = "ntt_limb_xforms_per_sec", "limb-xforms/s", r["config"]
+        elif args.workload == "keyswitch":
+            r = bench_keyswitch(torch, device, args.steps, args.warmup, peaks)
+            ms = r["ms_per_switch"]
+            value = world * r["switches_per_sec"]
+            roof = r["roofline"]
+            metric, unit, cfg = "keyswitch_per_sec", "switches/s", r["config"]
         else:
             r = bench_modup(torch, device, args.steps, args.warmup, peaks)
             ms = r["ms_per_step"]

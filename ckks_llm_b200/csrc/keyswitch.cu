@@ -109,31 +109,45 @@ struct ModDownArgs {
 
 // modDownPQltoQl_23_multi_kernel / _alpha1_multi_kernel: out[c][i][x] = (x_{q_i} - [x_P]_{q_i}) * P^-1 mod q_i,
 // where [x_P]_{q_i} is the fast-basis-conversion value of the p part (no overflow correction, as in the reference).
-__global__ void __launch_bounds__(kThreads) moddown_kernel(ModDownArgs P) {
+// One thread per coefficient: the p_num products rb_j are formed once and serve every output limb.
+template <int PMAX>
+__global__ void __launch_bounds__(kThreads) moddown_kernel(ModDownArgs P, int l) {
     const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
-    const int i = blockIdx.y, c = blockIdx.z;
+    const int c = blockIdx.y;
     if (x >= P.N) return;
     const u64* src = P.in + (size_t)c * P.R * P.t_num * P.N + x;
-    const u64 qi = P.pq[P.p_num + i];
-    u64 part;
-    if (P.p_num == 1) {
-        const u64 ra = src[0];
-        u64 r = ra - __umul64hi(ra, P.qinv64[P.p_num + i]) * qi;      // ra % qi
-        r = csub(r, qi);
-        part = csub(r, qi);
-    } else {
-        u64 lo = 0, hi = 0;
-        for (int j = 0; j < P.p_num; j++) {
-            const ulonglong2 w = P.p_hat_inv[j];
-            const u64 rb = shoup_mul(src[(size_t)j * P.N], w.x, w.y, P.pq[j]);
-            mac128(lo, hi, rb, P.p_hat_mod_q[(size_t)i * P.p_num + j]);
+    u64 rb[PMAX];
+#pragma unroll
+    for (int j = 0; j < PMAX; j++) {
+        rb[j] = 0;
+        if (j < P.p_num) {
+            if (P.p_num == 1) {
+                rb[j] = src[0];
+            } else {
+                const ulonglong2 w = P.p_hat_inv[j];
+                rb[j] = shoup_mul(src[(size_t)j * P.N], w.x, w.y, P.pq[j]);
+            }
         }
-        const ulonglong2 mu = P.pq_mu[P.p_num + i];
-        part = barrett128(lo, hi, qi, mu.x, mu.y);
     }
-    const u64 d = qi - part + src[(size_t)(P.p_num + i) * P.N];       // in (0, 2q)
-    const ulonglong2 w = P.p_inv_mod_q[i];
-    P.out[((size_t)c * P.q_num + i) * P.N + x] = shoup_mul(d, w.x, w.y, qi);
+    for (int i = 0; i <= l; i++) {
+        const u64 qi = P.pq[P.p_num + i];
+        u64 part;
+        if (P.p_num == 1) {
+            u64 r = rb[0] - __umul64hi(rb[0], P.qinv64[P.p_num + i]) * qi;      // x_p % q_i
+            r = csub(r, qi);
+            part = csub(r, qi);
+        } else {
+            u64 lo = 0, hi = 0;
+#pragma unroll
+            for (int j = 0; j < PMAX; j++)
+                if (j < P.p_num) mac128(lo, hi, rb[j], P.p_hat_mod_q[(size_t)i * P.p_num + j]);
+            const ulonglong2 mu = P.pq_mu[P.p_num + i];
+            part = barrett128(lo, hi, qi, mu.x, mu.y);
+        }
+        const u64 d = qi - part + src[(size_t)(P.p_num + i) * P.N];       // in (0, 2q)
+        const ulonglong2 w = P.p_inv_mod_q[i];
+        P.out[((size_t)c * P.q_num + i) * P.N + x] = shoup_mul(d, w.x, w.y, qi);
+    }
 }
 
 int check_chain(ckks_b200_context* c, int l, int gamma) {
@@ -236,8 +250,10 @@ extern "C" int ckks_b200_moddown_pql_to_ql(ckks_b200_context* c, uint64_t* d_out
     P.q_num = c->q_num;
     P.t_num = c->t_num;
     P.R = (c->p_num + c->q_num + gamma - 1) / gamma;
-    dim3 grid((c->N + kThreads - 1) / kThreads, l + 1, batch);
-    moddown_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(P);
+    dim3 grid((c->N + kThreads - 1) / kThreads, batch);
+    if (c->p_num <= 4) moddown_kernel<4><<<grid, kThreads, 0, (cudaStream_t)stream>>>(P, l);
+    else if (c->p_num <= 8) moddown_kernel<8><<<grid, kThreads, 0, (cudaStream_t)stream>>>(P, l);
+    else moddown_kernel<16><<<grid, kThreads, 0, (cudaStream_t)stream>>>(P, l);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
