@@ -19,8 +19,9 @@
 // v*(Qblk mod t_k); context creation checks the tables for that and sends such levels to the
 // CUDA-core kernel.
 //
-// A CTA runs four independent groups of 128 threads.  A group owns one operand tile in shared
-// memory and 128 columns of tensor memory and walks over tiles of 128 coefficients: every
+// A CTA runs NG independent groups of 128 threads: five when the 8*t_num accumulator columns of a group
+// fit 96 tensor-memory columns (t_num <= 12), four with 128 columns each otherwise.  A group owns one
+// operand tile in shared memory and its columns of tensor memory and walks over tiles of 128 coefficients: every
 // thread prepares its coefficient's row, one thread issues the instructions, all wait on the
 // group's mbarrier (bounded; a wait that runs out raises a flag and the group leaves), then
 // every thread finishes its own row.  The next tile's residues are loaded before that wait.
@@ -32,9 +33,7 @@ using namespace ckb::umma;
 
 namespace {
 
-constexpr int GROUPS = 4;
-constexpr int THREADS = 128 * GROUPS;
-constexpr int GROUP_COLS = 128;          // tensor-memory columns per group
+constexpr int TMEM_COLS = 512;           // the whole tensor memory of the SM, split evenly over the groups
 
 struct ModUpTcArgs {
     u64* out;
@@ -79,8 +78,9 @@ __device__ __forceinline__ u64 mad_wide(uint32_t a, uint32_t b, u64 c) {
 // (exact: h + l = x*w with h = fl(x*w), l the FMA remainder; h - c*q is a small integer for
 // c = rint(h/q); w is kept centred, |w| <= q/2, so the result stays within (-0.7q, 0.7q)).
 // Otherwise rb_j is a 64-bit Shoup product.
-template <int APAD, bool F64Q>
-__global__ void __launch_bounds__(THREADS, 1) modup_umma_kernel(ModUpTcArgs P) {
+template <int APAD, bool F64Q, int NG>
+__global__ void __launch_bounds__(128 * NG, 1) modup_umma_kernel(ModUpTcArgs P) {
+    constexpr int GROUPS = NG, THREADS = 128 * NG, GROUP_COLS = NG == 5 ? 96 : 128;
     constexpr int KSTEPS = APAD * 8 / 32;
     constexpr int A_TILE = KSTEPS * TM * 32;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(THREADS, 1) modup_umma_kernel(ModUpTcArgs P) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
-        tmem_alloc(smem_u32(&tmem_slot), GROUPS * GROUP_COLS);
+        tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
         tmem_relinquish();
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the constant tiles, for the MMA's reads
@@ -274,27 +274,35 @@ __global__ void __launch_bounds__(THREADS, 1) modup_umma_kernel(ModUpTcArgs P) {
     __syncthreads();
     if (warp == 0) {
         tc_fence_after();
-        tmem_dealloc(tmem_slot, GROUPS * GROUP_COLS);
+        tmem_dealloc(tmem_slot, TMEM_COLS);
     }
 }
 
-template <int APAD, bool F64Q>
-int launch(ckks_b200_context* c, const ModUpTcArgs& P, cudaStream_t st) {
+template <int APAD, bool F64Q, int NG>
+int launch_groups(ckks_b200_context* c, const ModUpTcArgs& P, cudaStream_t st) {
+    constexpr int GROUPS = NG, THREADS = 128 * NG;
     constexpr int KSTEPS = APAD * 8 / 32;
     const size_t smem = (size_t)GROUPS * KSTEPS * TM * 32 + (size_t)P.blocks * KSTEPS * P.npad * 32 +
                         (size_t)P.blocks * APAD * (8 + 16) + (size_t)P.blocks * (APAD + 1) * P.t_num * 8 +
                         (size_t)P.t_num * 16 + (size_t)P.blocks * APAD * 24;
     CKB_REQUIRE(smem <= 200 * 1024, CKKS_B200_ERR_UNSUPPORTED, "ModUp tables of %zu bytes do not fit shared memory", smem);
-    CKB_CUDA(cudaFuncSetAttribute(modup_umma_kernel<APAD, F64Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CKB_CUDA(cudaFuncSetAttribute(modup_umma_kernel<APAD, F64Q, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int sms = 0;
     CKB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device));
     const long total = (long)P.batch * P.blocks * (P.N / TM);
     const long want = (total + GROUPS - 1) / GROUPS;
     const int grid = (int)(want < sms ? want : sms);
-    modup_umma_kernel<APAD, F64Q><<<grid, THREADS, smem, st>>>(P);
+    modup_umma_kernel<APAD, F64Q, NG><<<grid, THREADS, smem, st>>>(P);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
+}
+
+template <int APAD, bool F64Q>
+int launch(ckks_b200_context* c, const ModUpTcArgs& P, cudaStream_t st) {
+    // the accumulator loads run in groups of four targets, so five groups need 8*ceil4(t_num) <= 96
+    if ((P.t_num + 3) / 4 * 32 <= 96) return launch_groups<APAD, F64Q, 5>(c, P, st);
+    return launch_groups<APAD, F64Q, 4>(c, P, st);
 }
 
 }  // namespace
@@ -303,7 +311,7 @@ namespace ckb {
 
 bool modup_tensor_ok(const ckks_b200_context* c, int l) {
     return c->mu_planes != nullptr && l >= 0 && l < (int)c->mu_tc_ok.size() && c->mu_tc_ok[l] != 0 &&
-           c->N % TM == 0 && c->tc_npad <= GROUP_COLS;
+           c->N % TM == 0 && c->tc_npad <= 128;
 }
 
 int modup_tensor(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int batch, cudaStream_t st) {
