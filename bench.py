@@ -296,6 +296,62 @@ def bench_levels(torch, device, steps, warmup, peaks):
     return res
 
 
+def bench_ringpack(torch, device, steps, warmup, peaks):
+    """rlweCipherDecompose and mlweCipherPacking at the BERT geometry the reference runs (N=2^16, N1=128, rank 512,
+    two ring-pack limbs, one special prime): device time per call with the bytes each must move."""
+    from ckks_llm_b200 import params
+    from ckks_llm_b200.host import Ciphertext, Context_23, MLWECiphertext, PCMM_Context, PCMM_Scheme
+    logN, N1, L = 16, 128, 1
+    N, k = 1 << logN, (1 << logN) // N1
+    q = params.ntt_primes(50, 2 * N, L + 1)
+    p = [params.ntt_primes(51, 2 * N, 1)[0]]
+    ctx = Context_23(logN, p, q, [], device=device.index)
+    pc = PCMM_Context(N1, k, p, q, device=device.index)
+    sch = PCMM_Scheme(pc, context=ctx)
+    g = torch.Generator(device=device).manual_seed(5)
+    rl = torch.empty((2, L + 1, N), dtype=torch.int64, device=device)
+    for i, qi in enumerate(q):
+        rl[:, i, :] = torch.randint(0, qi, (2, N), generator=g, device=device, dtype=torch.int64)
+    ct = Ciphertext(N, L, L, N // 2, 1.0, device=device.index, cipher=rl.reshape(-1))
+    mlwe = [MLWECiphertext(N1, L, L, k, 1.0, device=device.index) for _ in range(k)]
+    keys = torch.empty((k, 2, 2, N), dtype=torch.int64, device=device)           # [k][a,b][p,q0][N]
+    for i, m in enumerate([p[0], q[0]]):
+        keys[:, :, i, :] = torch.randint(0, m, (k, 2, N), generator=g, device=device, dtype=torch.int64)
+    sch.addRepakcingKey(keys.reshape(-1))
+    out_ct = Ciphertext(N, L, 0, N // 2, 1.0, device=device.index)
+    C = (k + 1) * N1
+    calls = {
+        # INTT and NTT of 2(L+1) limb-polynomials around the gather, k MLWE ciphertexts of (L+1)*C words written
+        "rlwe_decompose": (lambda: sch.rlweCipherDecompose(ct, mlwe, k, 0),
+                           (4 * 2 * (L + 1) * N + 2 * (L + 1) * N + k * (L + 1) * C) * 8),
+        # embed k+1 polynomials over (p, q0); 2k forward transforms; keys 4kN words; 4 inverse; ModDown; 2 forward
+        "mlwe_packing": (lambda: sch.mlweCipherPacking(out_ct, mlwe, k, 0),
+                         (k * C + 2 * (k + 1) * N + 2 * 2 * k * N + 2 * k * N + 4 * k * N + 4 * 2 * N + 4 * N + 2 * 2 * N) * 8),
+    }
+    res = {}
+    for name, (fn, nbytes) in calls.items():
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms = e0.elapsed_time(e1) / steps
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        res[name] = {"calls_per_sec": 1e3 / ms, "ms_per_call": ms,
+                     "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                  "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                                  "note": "algorithmic bytes: every stage reads its inputs and writes its outputs once"}}
+    pc.close()
+    ctx.close()
+    res["config"] = {"workload": "ring packing N=2^16, N1=128, rank 512, 2 limbs + 1 special prime, 512 MLWE ciphertexts",
+                     "l2_policy": "MLWE set 538 MB and keys 1.07 GB, larger than L2"}
+    return res
+
+
 def bench_keyswitch(torch, device, steps, warmup, peaks):
     """The key-switch chain (ckks_b200_keyswitch) on the ModUp configuration's moduli: N=2^16, 24 x 50-bit q,
     8 special primes (dnum 3), 12 x 60-bit t, gamma 6, top level: device time per switched polynomial."""
@@ -503,6 +559,7 @@ def main():
                 extra["modup"] = bench_modup(torch, device, max(args.steps, 10), args.warmup, peaks)
                 extra["levels"] = bench_levels(torch, device, max(args.steps, 10), args.warmup, peaks)
                 extra["keyswitch"] = bench_keyswitch(torch, device, max(args.steps, 10), args.warmup, peaks)
+                extra["ringpack"] = bench_ringpack(torch, device, max(args.steps, 10), args.warmup, peaks)
             except Exception as ex:           # the headline stays valid without the side measurements
                 extra["side_error"] = repr(ex)
     else:

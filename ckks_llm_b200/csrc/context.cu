@@ -383,7 +383,7 @@ extern "C" int ckks_b200_context_destroy(ckks_b200_context* c) {
     cudaFree(c->tw_fwd); cudaFree(c->tw_inv); cudaFree(c->tw_fwd_d); cudaFree(c->tw_inv_d); cudaFree(c->d_moduli); cudaFree(c->d_ninv); cudaFree(c->d_qinv64);
     cudaFree(c->mu_hat_inv); cudaFree(c->mu_hat_mod_t); cudaFree(c->mu_blk_mod_t);
     cudaFree(c->d_pq_mu); cudaFree(c->d_t_hat_inv); cudaFree(c->d_t_hat_mod_r); cudaFree(c->d_half_t); cudaFree(c->d_t_mod_pq);
-    cudaFree(c->d_p_hat_inv); cudaFree(c->d_p_hat_mod_q); cudaFree(c->d_p_inv_mod_q); cudaFree(c->ks_buf);
+    cudaFree(c->d_p_hat_inv); cudaFree(c->d_p_hat_mod_q); cudaFree(c->d_p_inv_mod_q); cudaFree(c->ks_buf); cudaFree(c->mul_buf);
     cudaFree(c->mu_planes); cudaFree(c->d_t_inv); cudaFree(c->d_flags); cudaFree(c->d_qlinv); cudaFree(c->resc_buf);
     if (c->h_flags) cudaFreeHost(c->h_flags);
     cudaFree(c->d_t_mu); cudaFree(c->h2d_buf); cudaFree(c->h2d_buf2); cudaFree(c->ptr_buf); cudaFree(c->pack_buf);

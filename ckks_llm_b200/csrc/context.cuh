@@ -62,6 +62,8 @@ struct ckks_b200_context {
     bool chain_ok = false;                   // every modulus below 2^62 (the tables above are built only then)
     u64* ks_buf = nullptr;                   // workspace of ckks_b200_keyswitch
     size_t ks_cap = 0;
+    u64* mul_buf = nullptr;                  // the three products and the switched pair of ckks_b200_mult
+    size_t mul_cap = 0;
 
     // Scratch for the *_host entry points, grown on demand.
     u64* h2d_buf = nullptr;

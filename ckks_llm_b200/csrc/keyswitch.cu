@@ -150,6 +150,45 @@ __global__ void __launch_bounds__(kThreads) moddown_kernel(ModDownArgs P, int l)
     }
 }
 
+// compute_c0c1c2_kernel (src/ckks/include/poly_arithmetic.cuh:787-818): the three products of a ciphertext
+// multiplication per limb, a1*a2, b1*b2 and a1*b2 + a2*b1 (as (a1+b1)(a2+b2) minus the other two), modulo q_i.
+__global__ void __launch_bounds__(kThreads) tensor_product_kernel(u64* __restrict__ axbx, u64* __restrict__ axax,
+                                                                  u64* __restrict__ bxbx, const u64* __restrict__ c1,
+                                                                  const u64* __restrict__ c2, uint32_t N, int stride,
+                                                                  const u64* __restrict__ q, const ulonglong2* __restrict__ mu) {
+    const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
+    const int i = blockIdx.y;
+    if (x >= N) return;
+    const size_t a = (size_t)i * N + x, b = ((size_t)stride + i) * N + x;
+    const u64 a1 = c1[a], b1 = c1[b], a2 = c2[a], b2 = c2[b];
+    const u64 qi = q[i];
+    const ulonglong2 m = mu[i];
+    u64 l1 = 0, h1 = 0, l2 = 0, h2 = 0, l3 = 0, h3 = 0;
+    mac128(l1, h1, a1, a2);
+    mac128(l2, h2, b1, b2);
+    mac128(l3, h3, a1 + b1, a2 + b2);
+    h3 -= h1 + (l3 < l1);
+    l3 -= l1;
+    h3 -= h2 + (l3 < l2);
+    l3 -= l2;
+    axax[a] = barrett128(l1, h1, qi, m.x, m.y);
+    bxbx[a] = barrett128(l2, h2, qi, m.x, m.y);
+    axbx[a] = barrett128(l3, h3, qi, m.x, m.y);
+}
+
+// cipher_add_axbx_batch_device_kernel (poly_arithmetic.cuh:155-172): a += ax, b += bx per limb.
+__global__ void __launch_bounds__(kThreads) add_switched_kernel(u64* __restrict__ cipher, const u64* __restrict__ ax,
+                                                                const u64* __restrict__ bx, uint32_t N, int stride,
+                                                                const u64* __restrict__ q) {
+    const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
+    const int i = blockIdx.y;
+    if (x >= N) return;
+    const size_t a = (size_t)i * N + x, b = ((size_t)stride + i) * N + x;
+    const u64 qi = q[i];
+    cipher[a] = csub(cipher[a] + ax[a], qi);
+    cipher[b] = csub(cipher[b] + bx[a], qi);
+}
+
 int check_chain(ckks_b200_context* c, int l, int gamma) {
     CKB_REQUIRE(c != nullptr, CKKS_B200_ERR_ARG, "null argument");
     CKB_REQUIRE(c->t_num > 0 && c->p_num > 0, CKKS_B200_ERR_ARG, "the context has no T basis or no special primes");
@@ -291,4 +330,35 @@ extern "C" int ckks_b200_keyswitch(ckks_b200_context* c, uint64_t* d_out, const 
     if (!rc) rc = ckks_b200_moddown_pql_to_ql(c, d_out, (const uint64_t*)pqbuf, l, gamma, 2, stream);
     if (!rc) rc = ckks_b200_ntt_forward(c, d_out, 0, K, 2, l + 1, c->q_num, stream);
     return rc;
+}
+
+// Scheme_23::mult_23 (src/ckks/include/KeySwitch_23.cuh:192-236): d_res = d_c1 * d_c2 relinearised with the key
+// d_rlk.  All three are Ciphertext buffers, a limbs then b limbs, each [q_num][N], NTT domain, level l >= 1 as in the
+// reference (its level-0 and missing-key cases are the caller's, :194-201).  d_res may be one of the operands.
+extern "C" int ckks_b200_mult(ckks_b200_context* c, uint64_t* d_res, const uint64_t* d_c1, const uint64_t* d_c2,
+                              const uint64_t* d_rlk, int l, int gamma, void* stream) {
+    int rc = check_chain(c, l, gamma);
+    if (rc) return rc;
+    CKB_REQUIRE(d_res && d_c1 && d_c2 && d_rlk, CKKS_B200_ERR_ARG, "null argument");
+    DeviceGuard guard(c->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", c->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t n = c->N, limb_words = (size_t)c->q_num * n;
+    rc = ensure_buf(&c->mul_buf, &c->mul_cap, 5 * limb_words);
+    if (rc) return rc;
+    u64 *axbx = c->mul_buf, *axax = axbx + limb_words, *bxbx = axax + limb_words, *sw = bxbx + limb_words;
+    const u64* q = c->d_moduli + c->p_num;
+    dim3 grid((c->N + kThreads - 1) / kThreads, l + 1);
+    tensor_product_kernel<<<grid, kThreads, 0, st>>>(axbx, axax, bxbx, (const u64*)d_c1, (const u64*)d_c2, c->N, c->q_num, q,
+                                                     c->d_pq_mu + c->p_num);
+    count_launch();
+    CKB_CUDA(cudaGetLastError());
+    rc = ckks_b200_keyswitch(c, (uint64_t*)sw, (const uint64_t*)axax, d_rlk, l, gamma, stream);
+    if (rc) return rc;
+    add_switched_kernel<<<grid, kThreads, 0, st>>>(sw, axbx, bxbx, c->N, c->q_num, q);
+    count_launch();
+    CKB_CUDA(cudaGetLastError());
+    // the switched pair lives in the workspace so that d_res may alias an operand; only limbs 0..l are copied
+    CKB_CUDA(cudaMemcpy2DAsync(d_res, limb_words * 8, sw, limb_words * 8, (size_t)(l + 1) * n * 8, 2, cudaMemcpyDeviceToDevice, st));
+    return CKKS_B200_OK;
 }

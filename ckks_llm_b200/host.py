@@ -160,6 +160,23 @@ class Scheme_23:
     def __init__(self, context):
         self.context = context
 
+    # Scheme_23::mult_23(cipher_res, cipher1, cipher2), src/ckks/include/KeySwitch_23.cuh:192-236.  rlk_23 is the
+    # relinearisation key block [2][dnum][R][t_num][N] (key generation is the caller's).
+    rlk_23 = None
+
+    def mult_23(self, cipher_res, cipher1, cipher2):
+        if cipher1.l == 0 or cipher2.l == 0:
+            raise ValueError("Ciphertexts are on level 0")                 # invalid_argument at :194-197
+        if self.rlk_23 is None:
+            raise ValueError("rotKey_23 not exists")                       # :198-201
+        ctx = self.context
+        l = min(cipher1.l, cipher2.l)
+        capi.check(ctx.lib.ckks_b200_mult(ctx._h, cipher_res.cipher_device.data_ptr(), cipher1.cipher_device.data_ptr(),
+                                          cipher2.cipher_device.data_ptr(), self.rlk_23.data_ptr(), l, ctx.gamma,
+                                          _stream_ptr(ctx.device)))
+        cipher_res.l = l
+        cipher_res.scale = cipher1.scale * cipher2.scale
+
     # Scheme_23::rescaleAndEqual(Ciphertext&), src/ckks/include/Scheme_23.cuh:368-385
     def rescaleAndEqual(self, cipher):
         ctx = self.context

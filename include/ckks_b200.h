@@ -143,6 +143,13 @@ int ckks_b200_moddown_pql_to_ql(ckks_b200_context* ctx, uint64_t* d_out, const u
  * [p | q] -> modDown -> NTT; d_out [2][q_num][N], limbs 0..l.  Workspaces belong to the context. */
 int ckks_b200_keyswitch(ckks_b200_context* ctx, uint64_t* d_out, const uint64_t* d_in, const uint64_t* d_swk,
                         int l, int gamma, void* stream);
+/* Scheme_23::mult_23 (KeySwitch_23.cuh:192-236): ciphertext times ciphertext with relinearisation: the three
+ * products per limb (compute_c0c1c2, poly_arithmetic.cuh:787-824), the key-switch chain on a1*a2 with the
+ * relinearisation key d_rlk, and the final addition (cipher_add_axbx_batch_device, poly_arithmetic.cuh:155-172,
+ * :416-420).  d_res, d_c1, d_c2: Ciphertext buffers [2][q_num][N], NTT domain, both operands at level l >= 1;
+ * d_res may be one of the operands.  The caller multiplies the scales and sets the level (:211-212). */
+int ckks_b200_mult(ckks_b200_context* ctx, uint64_t* d_res, const uint64_t* d_c1, const uint64_t* d_c2,
+                   const uint64_t* d_rlk, int l, int gamma, void* stream);
 
 /* ---- ring packing, RLWE -> MLWE ---------------------------------------------
  * PCMM_Scheme::rlweCipherDecompose (pcmm/PCMM_Scheme.cuh:51-125): d_rlwe is the

@@ -761,3 +761,37 @@ ORC_API void orc_moddown_pql_to_ql(u64 *out, const u64 *in, uint32_t n, int p_nu
             }
         }
 }
+
+/* compute_c0c1c2_kernel: src/ckks/include/poly_arithmetic.cuh:787-818.  c1, c2: [2][stride][n]. */
+ORC_API void orc_tensor_product(u64 *axbx, u64 *axax, u64 *bxbx, const u64 *c1, const u64 *c2, uint32_t n, int stride,
+                                int limbs, const u64 *q)
+{
+#pragma omp parallel for
+    for (int i = 0; i < limbs; i++) {
+        u64 qi = q[i], mu_hi, mu_lo;
+        orc_barrett_mu(qi, &mu_hi, &mu_lo);
+        for (uint32_t x = 0; x < n; x++) {
+            size_t a = (size_t)i * n + x, b = ((size_t)stride + i) * n + x;
+            u64 ra1 = c1[a], rb1 = c1[b], ra2 = c2[a], rb2 = c2[b];
+            u128 t1 = (u128)ra1 * ra2, t2 = (u128)rb1 * rb2;
+            u128 t3 = (u128)(ra1 + rb1) * (ra2 + rb2);
+            t3 -= t1;
+            t3 -= t2;
+            axax[a] = barrett128(t1, qi, mu_hi, mu_lo);
+            bxbx[a] = barrett128(t2, qi, mu_hi, mu_lo);
+            axbx[a] = barrett128(t3, qi, mu_hi, mu_lo);
+        }
+    }
+}
+
+/* cipher_add_axbx_batch_device_kernel: src/ckks/include/poly_arithmetic.cuh:155-172 */
+ORC_API void orc_add_switched(u64 *cipher, const u64 *ax, const u64 *bx, uint32_t n, int stride, int limbs, const u64 *q)
+{
+#pragma omp parallel for
+    for (int i = 0; i < limbs; i++)
+        for (uint32_t x = 0; x < n; x++) {
+            size_t a = (size_t)i * n + x, b = ((size_t)stride + i) * n + x;
+            cipher[a] = csub_q(cipher[a] + ax[a], q[i]);
+            cipher[b] = csub_q(cipher[b] + bx[a], q[i]);
+        }
+}

@@ -58,6 +58,8 @@ def lib():
                                              _U64P]
         L.orc_modup_t_to_pql.argtypes = [_U64P, _U64P, C.c_uint32] + [C.c_int] * 6 + [_U64P] * 7
         L.orc_moddown_pql_to_ql.argtypes = [_U64P, _U64P, C.c_uint32] + [C.c_int] * 6 + [_U64P] * 6
+        L.orc_tensor_product.argtypes = [_U64P, _U64P, _U64P, _U64P, _U64P, C.c_uint32, C.c_int, C.c_int, _U64P]
+        L.orc_add_switched.argtypes = [_U64P, _U64P, _U64P, C.c_uint32, C.c_int, C.c_int, _U64P]
         L.orc_mod_to_qi.argtypes = [_U64P, _U64P, C.c_uint32, C.c_int, C.c_int, _U64P]
         L.orc_rescale_combine.argtypes = [_U64P, _U64P, C.c_uint32, C.c_int, C.c_int, _U64P, _U64P, _U64P]
         L.orc_modup_q0_to_ql.argtypes = [_U64P, C.c_uint32, C.c_int, C.c_int, _U64P, C.c_int]
@@ -344,3 +346,25 @@ def keyswitch(inp, swk, tables, KT, l, gamma):
     out = moddown_pql_to_ql(pq, n, KT, l, gamma, 2)
     ntt_batch(out.reshape(-1), tables, 0, p_num, 2, l + 1, q_num)
     return out
+
+
+def tensor_product(c1, c2, n, q, l):
+    """compute_c0c1c2 (poly_arithmetic.cuh:787-824): c1, c2 [2][q_num][n] -> (a1b2+a2b1, a1a2, b1b2), each [q_num][n]."""
+    q_num = len(q)
+    outs = [np.zeros((q_num, n), dtype=np.uint64) for _ in range(3)]
+    lib().orc_tensor_product(outs[0].reshape(-1), outs[1].reshape(-1), outs[2].reshape(-1),
+                             np.ascontiguousarray(c1, dtype=np.uint64).reshape(-1),
+                             np.ascontiguousarray(c2, dtype=np.uint64).reshape(-1), n, q_num, l + 1,
+                             np.ascontiguousarray(q, dtype=np.uint64))
+    return outs
+
+
+def mult(c1, c2, rlk, tables, KT, l, gamma):
+    """Scheme_23::mult_23 (KeySwitch_23.cuh:192-236): c1, c2 [2][q_num][n] in the NTT domain -> result
+    [2][q_num][n], limbs 0..l."""
+    n = tables.n
+    axbx, axax, bxbx = tensor_product(c1, c2, n, KT.q, l)
+    res = keyswitch(axax[:l + 1], rlk, tables, KT, l, gamma)
+    lib().orc_add_switched(res.reshape(-1), axbx.reshape(-1), bxbx.reshape(-1), n, len(KT.q), l + 1,
+                           np.array(KT.q, dtype=np.uint64))
+    return res

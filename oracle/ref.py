@@ -33,6 +33,8 @@ def lib():
         L.ref_rescale_stage.argtypes = [_U64P, _U64P, C.c_int, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, _U64P, _U64P]
         L.ref_modup_q0_to_ql.argtypes = [_U64P, C.c_int, _U64P, C.c_int, C.c_int, C.c_int, C.c_int]
         L.ref_keyswitch_stage.argtypes = [_U64P, _U64P, _U64P, C.c_int, _U64P] + [C.c_int] * 6 + [_U64P] * 10
+        if hasattr(L, "ref_tensor_product"):
+            L.ref_tensor_product.argtypes = [_U64P, _U64P, _U64P, C.c_int, _U64P, C.c_int, C.c_int, C.c_int, C.c_int]
         L.ref_decompose.argtypes = [_U64P, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _U64P]
         _lib = L
     return _lib
@@ -182,3 +184,25 @@ def keyswitch_stage(stage, inp, aux, logN, KT, l, gamma):
     if rc:
         raise RuntimeError(f"ref_keyswitch_stage failed with {rc}")
     return out
+
+
+def tensor_product(c1, c2, logN, pq, p_num, l):
+    """compute_c0c1c2 as mult_23 calls it: returns [3][q_num][N] = (a1b2+a2b1, a1a2, b1b2)."""
+    c1 = np.ascontiguousarray(c1, dtype=np.uint64)
+    q_num, n = c1.shape[1], c1.shape[2]
+    out = np.zeros((3, q_num, n), dtype=np.uint64)
+    rc = lib().ref_tensor_product(out.reshape(-1), c1.copy().reshape(-1), np.ascontiguousarray(c2, dtype=np.uint64).reshape(-1),
+                                  logN, np.ascontiguousarray(pq, dtype=np.uint64), p_num, q_num, l, 0)
+    assert rc == 0, rc
+    return out
+
+
+def add_switched(cipher, axbx, logN, pq, p_num, l):
+    """cipher_add_axbx_batch_device as mult_23 calls it: cipher [2][q_num][N] += axbx [2][q_num][N] (ax then bx)."""
+    c = np.ascontiguousarray(cipher, dtype=np.uint64).copy()
+    q_num = c.shape[1]
+    dummy = np.zeros(1, dtype=np.uint64)
+    rc = lib().ref_tensor_product(dummy, c.reshape(-1), np.ascontiguousarray(axbx, dtype=np.uint64).reshape(-1), logN,
+                                  np.ascontiguousarray(pq, dtype=np.uint64), p_num, q_num, l, 1)
+    assert rc == 0, rc
+    return c

@@ -453,3 +453,34 @@ extern "C" int ref_keyswitch_stage(unsigned long long* h_out, const unsigned lon
     free(c);
     return 0;
 }
+
+// compute_c0c1c2 and cipher_add_axbx_batch_device (poly_arithmetic.cuh:787-824, :155-172, :416-420) as
+// Scheme_23::mult_23 calls them, on Ciphertext buffers [2][q_num][N]; pq = [p | q].  mode 0: h_out = the three
+// products [3][q_num][N] (a1b2+a2b1, a1a2, b1b2) of h_c1 and h_c2; mode 1: h_c1 += (h_c2 viewed as [ax | bx]).
+extern "C" int ref_tensor_product(unsigned long long* h_out, unsigned long long* h_c1, const unsigned long long* h_c2,
+                                  int logN, const unsigned long long* pq, int p_num, int q_num, int l, int mode) {
+    const int n_mod = p_num + q_num;
+    if (n_mod > max_pqt_num) return 1;
+    const long N = 1L << logN;
+    int rc = upload_pqt(pq, n_mod);
+    if (rc) return rc;
+    const size_t half = (size_t)q_num * N, bytes = 8 * 2 * half;
+    uint64_tt *d1 = nullptr, *d2 = nullptr, *d3 = nullptr;
+    RD_CUDA(cudaMalloc(&d1, bytes));
+    RD_CUDA(cudaMalloc(&d2, bytes));
+    RD_CUDA(cudaMalloc(&d3, 8 * 3 * half));
+    RD_CUDA(cudaMemcpy(d1, h_c1, bytes, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(d2, h_c2, bytes, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemset(d3, 0, 8 * 3 * half));
+    if (mode == 0) {
+        compute_c0c1c2(d3, d3 + half, d3 + 2 * half, d1, d2, d1 + half, d2 + half, N, 0, p_num, l + 1);
+    } else {
+        cipher_add_axbx_batch_device(d1, d2, d2 + half, N, p_num, l + 1, q_num);
+    }
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    if (mode == 0) RD_CUDA(cudaMemcpy(h_out, d3, 8 * 3 * half, cudaMemcpyDeviceToHost));
+    else RD_CUDA(cudaMemcpy(h_c1, d1, bytes, cudaMemcpyDeviceToHost));
+    cudaFree(d1); cudaFree(d2); cudaFree(d3);
+    return 0;
+}

@@ -75,3 +75,35 @@ def test_whole_chain(oracle, cuda_device, logN, p_num, q_num, t_num, gamma, l):
     got = to_u64_numpy(out).reshape(2, len(q), N)
     assert np.array_equal(got[:, :l + 1], exp[:, :l + 1])
     ctx.close()
+
+
+@pytest.mark.parametrize("logN,p_num,q_num,t_num,gamma,l", [(12, 2, 6, 4, 3, 5), (13, 1, 4, 3, 3, 2)])
+def test_mult_23(oracle, cuda_device, logN, p_num, q_num, t_num, gamma, l):
+    """Ciphertext x ciphertext with relinearisation through the Scheme_23 mirror, the result aliasing an operand."""
+    from ckks_llm_b200.host import Ciphertext, Scheme_23
+    N, p, q, t, ctx, KT = _setup(oracle, logN, p_num, q_num, t_num, gamma)
+    R, cb, dnum, blocks = _shapes(p, q, t, l, gamma)
+    rng = np.random.default_rng(11 + logN)
+    T = oracle.NttTables(N, p + q + t)
+    c1 = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)])
+    c2 = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)])
+    c1[0, :, :2] = (np.array(q, dtype=np.uint64) - np.uint64(1))[:, None]           # largest residues in every product
+    c1[1, :, :2] = c2[0, :, :2] = c2[1, :, :2] = c1[0, :, :2]
+    rlk = np.stack([H.uniform_residues(rng, t, (N,)) for _ in range(2 * dnum * R)]).reshape(2, dnum, R, t_num, N)
+    exp = oracle.mult(c1, c2, rlk, T, KT, l, gamma)
+    L = len(q) - 1
+    sch = Scheme_23(ctx)
+    a = Ciphertext(N, L, l, N // 2, 2.0 ** 40, cipher=as_u64_tensor(c1.reshape(-1), ctx.device))
+    b = Ciphertext(N, L, l + 0, N // 2, 2.0 ** 30, cipher=as_u64_tensor(c2.reshape(-1), ctx.device))
+    with pytest.raises(ValueError):
+        sch.mult_23(a, a, b)                                                          # no key yet
+    sch.rlk_23 = as_u64_tensor(rlk.reshape(-1), ctx.device)
+    sch.mult_23(a, a, b)                                                              # result over the first operand
+    got = to_u64_numpy(a.cipher_device).reshape(2, len(q), N)
+    assert np.array_equal(got[:, :l + 1], exp[:, :l + 1])
+    assert np.array_equal(got[:, l + 1:], c1[:, l + 1:])                              # limbs above the level untouched
+    assert a.l == l and a.scale == 2.0 ** 70
+    zero = Ciphertext(N, L, 0, N // 2, 1.0, cipher=as_u64_tensor(c2.reshape(-1), ctx.device))
+    with pytest.raises(ValueError):
+        sch.mult_23(a, a, zero)
+    ctx.close()

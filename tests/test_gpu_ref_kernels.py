@@ -184,3 +184,25 @@ def test_reference_keyswitch_kernels(oracle, cuda_device, p_num, q_num, t_num, g
     ctx.modDownPQltoQl_23(out, as_u64_tensor(pqin, dev), l, 2)
     assert np.array_equal(to_u64_numpy(out).reshape(2, q_num, N)[:, :l + 1], ref[:, :l + 1])
     ctx.close()
+
+
+def test_reference_tensor_product_and_addition(oracle, cuda_device):
+    """compute_c0c1c2 and cipher_add_axbx_batch_device (poly_arithmetic.cuh:787-824, :155-172) == oracle."""
+    if not hasattr(R_.lib(), "ref_tensor_product"):
+        pytest.skip("reference driver built without the tensor-product entry")
+    logN, N, l = 12, 1 << 12, 3
+    p = params.ntt_primes(51, 2 * N, 2)
+    q = params.ntt_primes(50, 2 * N, 3) + params.ntt_primes(60, 2 * N, 2)
+    rng = np.random.default_rng(41)
+    c1 = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)])
+    c2 = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)])
+    c1[:, :, 0] = c2[:, :, 0] = np.array(q, dtype=np.uint64) - np.uint64(1)
+    ref = R_.tensor_product(c1, c2, logN, p + q, len(p), l)
+    orc = oracle.tensor_product(c1, c2, N, q, l)
+    for i in range(3):
+        assert np.array_equal(orc[i][:l + 1], ref[i][:l + 1])
+    summed = R_.add_switched(c1, np.stack([ref[0], ref[2]]), logN, p + q, len(p), l)
+    exp = c1.copy()
+    oracle.lib().orc_add_switched(exp.reshape(-1), np.ascontiguousarray(ref[0]).reshape(-1), np.ascontiguousarray(ref[2]).reshape(-1),
+                                  N, len(q), l + 1, np.array(q, dtype=np.uint64))
+    assert np.array_equal(exp, summed)
