@@ -25,8 +25,6 @@
 // thread prepares its coefficient's row, one thread issues the instructions, all wait on the
 // group's mbarrier (bounded; a wait that runs out raises a flag and the group leaves), then
 // every thread finishes its own row.  The next tile's residues are loaded before that wait.
-#include <cstdlib>
-
 #include "context.cuh"
 #include "umma.cuh"
 
@@ -51,17 +49,17 @@ struct ModUpTcArgs {
     int q_num, t_num, alpha, l, blocks, batch, npad;
 };
 
-__device__ __forceinline__ void group_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
-// AND of a predicate over the n threads of a group (also a barrier).
-__device__ __forceinline__ bool group_all(bool p, int id, int n) {
+__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+// AND of a predicate over the 128 threads of a group (also a barrier).
+__device__ __forceinline__ bool group_all(bool p, int id) {
     uint32_t r;
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %1, 0;\n\t"
-        "bar.red.and.pred q, %2, %3, p;\n\t"
+        "bar.red.and.pred q, %2, 128, p;\n\t"
         "selp.u32 %0, 1, 0, q;\n\t}"
         : "=r"(r)
-        : "r"((uint32_t)p), "r"(id), "r"(n)
+        : "r"((uint32_t)p), "r"(id)
         : "memory");
     return r != 0;
 }
@@ -80,11 +78,9 @@ __device__ __forceinline__ u64 mad_wide(uint32_t a, uint32_t b, u64 c) {
 // (exact: h + l = x*w with h = fl(x*w), l the FMA remainder; h - c*q is a small integer for
 // c = rint(h/q); w is kept centred, |w| <= q/2, so the result stays within (-0.7q, 0.7q)).
 // Otherwise rb_j is a 64-bit Shoup product.
-// NH threads share a row (coefficient): each makes 1/NH of the row's rb_j and finishes 1/NH of its targets.
-template <int APAD, bool F64Q, int NG, int NH>
-__global__ void __launch_bounds__(128 * NG * NH, 1) modup_umma_kernel(ModUpTcArgs P) {
-    constexpr int GROUPS = NG, GSIZE = 128 * NH, THREADS = GSIZE * NG, GROUP_COLS = NG == 5 ? 96 : 128;
-    constexpr int JN = APAD / NH;            // limbs per thread
+template <int APAD, bool F64Q, int NG>
+__global__ void __launch_bounds__(128 * NG, 1) modup_umma_kernel(ModUpTcArgs P) {
+    constexpr int GROUPS = NG, THREADS = 128 * NG, GROUP_COLS = NG == 5 ? 96 : 128;
     constexpr int KSTEPS = APAD * 8 / 32;
     constexpr int A_TILE = KSTEPS * TM * 32;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -93,8 +89,7 @@ __global__ void __launch_bounds__(128 * NG * NH, 1) modup_umma_kernel(ModUpTcArg
     __shared__ int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    const int g = tid / GSIZE, r = tid & 127, h = (tid % GSIZE) >> 7;
-    const int j0 = h * JN;                   // this thread's limbs are j0 .. j0+JN-1
+    const int g = tid >> 7, r = tid & 127;
     const int T = P.t_num;
     const int b_tile = KSTEPS * P.npad * 32;
     uint8_t* sA = smem + g * A_TILE;
@@ -107,7 +102,6 @@ __global__ void __launch_bounds__(128 * NG * NH, 1) modup_umma_kernel(ModUpTcArg
     double* s_qd = s_tinv + T;                                             // [blocks][APAD]  q_j as a double
     double* s_qinv = s_qd + P.blocks * APAD;                               // [blocks][APAD]  1/q_j (0 beyond the digit)
     double* s_wd = s_qinv + P.blocks * APAD;                               // [blocks][APAD]  (Qblk/q_j)^-1 mod q_j, centred
-    double* s_est = s_wd + P.blocks * APAD + g * (2 * NH * 128);           // [tile parity][NH][128] partial overflow sums
 
     for (int i = tid; i < P.blocks * b_tile / 16; i += THREADS)
         reinterpret_cast<uint4*>(sB)[i] = reinterpret_cast<const uint4*>(P.planes)[i];
@@ -160,7 +154,7 @@ __global__ void __launch_bounds__(128 * NG * NH, 1) modup_umma_kernel(ModUpTcArg
     long tile = (long)blockIdx.x * GROUPS + g;
 
     // residues of a tile's coefficient r, one per limb of its digit (zero beyond the digit)
-    auto load_tile = [&](long tl, u64 (&x)[JN]) {
+    auto load_tile = [&](long tl, u64 (&x)[APAD]) {
         const long xt = tl % tiles_x;
         const long rest = tl / tiles_x;
         const int blk = (int)(rest % P.blocks);
@@ -168,12 +162,12 @@ __global__ void __launch_bounds__(128 * NG * NH, 1) modup_umma_kernel(ModUpTcArg
         const int cnt = min(P.alpha, P.l + 1 - blk * P.alpha);
         const u64* src = P.in + ((size_t)bt * P.q_num + (size_t)blk * P.alpha) * P.N + xt * TM + r;
 #pragma unroll
-        for (int j = 0; j < JN; j++) x[j] = j0 + j < cnt ? src[(size_t)(j0 + j) * P.N] : 0;
+        for (int j = 0; j < APAD; j++) x[j] = j < cnt ? src[(size_t)j * P.N] : 0;
     };
 
-    u64 cur[JN];
+    u64 cur[APAD];
     if (tile < total) load_tile(tile, cur);
-    uint32_t phase = 0, parity = 0;
+    uint32_t phase = 0;
     bool ok = true;
     // byte offset of this thread's row inside a K step: 8-row group, row in the group
     const uint32_t row_off = (uint32_t)(r >> 3) * 256 + (uint32_t)(r & 7) * 16;
@@ -189,52 +183,27 @@ __global__ void __launch_bounds__(128 * NG * NH, 1) modup_umma_kernel(ModUpTcArg
         // truncate alike unless est sits within 2^-40 of an integer; only then are the divisions made.
         double est = 0.0;
 #pragma unroll
-        for (int jj = 0; jj < JN; jj++) {
-            const int j = j0 + jj;
+        for (int j = 0; j < APAD; j++) {
             u64 rb;
             double rbd;
             if (F64Q) {
                 const double q = s_qd[blk * APAD + j], u = s_qinv[blk * APAD + j], w = s_wd[blk * APAD + j];
-                const double x = small_to_double(cur[jj]);
-                const double hh = __dmul_rn(x, w);
-                const double l = __fma_rn(x, w, -hh);
-                const double c = __dadd_rn(__fma_rn(hh, u, 6755399441055744.0), -6755399441055744.0);
-                rbd = __dadd_rn(__fma_rn(-c, q, hh), l);
+                const double x = small_to_double(cur[j]);
+                const double h = __dmul_rn(x, w);
+                const double l = __fma_rn(x, w, -h);
+                const double c = __dadd_rn(__fma_rn(h, u, 6755399441055744.0), -6755399441055744.0);
+                rbd = __dadd_rn(__fma_rn(-c, q, h), l);
                 if (rbd < 0.0) rbd = __dadd_rn(rbd, q);
                 rb = (u64)__double_as_longlong(__dadd_rn(rbd, 4503599627370496.0)) & 0x000FFFFFFFFFFFFFull;
             } else {
                 const ulonglong2 hi = s_hinv[blk * APAD + j];
-                rb = shoup_mul(cur[jj], hi.x, hi.y, s_q[blk * APAD + j]);
+                rb = shoup_mul(cur[j], hi.x, hi.y, s_q[blk * APAD + j]);
                 rbd = (double)rb;
             }
             // beyond the digit w = 0 and 1/q = 0: rb = 0 and est is unchanged
             est = fma(rbd, s_qinv[blk * APAD + j], est);
             // K index j*8+b: step j/4, K half (j%4)/2, byte offset (j%2)*8 inside the 16-byte row
             *reinterpret_cast<u64*>(sA + (j / 4) * (TM * 32) + ((j % 4) / 2) * 128 + row_off + (j % 2) * 8) = rb;
-        }
-        if (NH > 1) s_est[(parity * NH + h) * 128 + r] = est;          // read back after the group barrier below
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        const long next = tile + stride;
-        if (next < total) load_tile(next, cur);
-        group_sync(1 + g, GSIZE);
-        if (r == 0 && h == 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ks++)
-                umma_i8(tmem_g, smem_desc(a16 + (ks * TM * 32 >> 4)),
-                        smem_desc(b16 + ((blk * b_tile + ks * P.npad * 32) >> 4)), idesc, ks > 0);
-            umma_commit(bar);
-        }
-        bool mine = mbar_wait(bar, phase, P.flags, 10 + g, &abort_flag);
-        phase ^= 1;
-        ok = group_all(mine, 1 + g, GSIZE);
-        if (!ok) break;
-        tc_fence_after();
-        if (NH > 1) {
-            est = 0.0;
-#pragma unroll
-            for (int hh = 0; hh < NH; hh++) est += s_est[(parity * NH + hh) * 128 + r];     // same order in every thread of the row
-            parity ^= 1;
         }
         int v = (int)est;
         {
@@ -248,23 +217,37 @@ __global__ void __launch_bounds__(128 * NG * NH, 1) modup_umma_kernel(ModUpTcArg
                 v = (int)vv;
             }
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        const long next = tile + stride;
+        if (next < total) load_tile(next, cur);
+        group_sync(1 + g);
+        if (r == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++)
+                umma_i8(tmem_g, smem_desc(a16 + (ks * TM * 32 >> 4)),
+                        smem_desc(b16 + ((blk * b_tile + ks * P.npad * 32) >> 4)), idesc, ks > 0);
+            umma_commit(bar);
+        }
+        bool mine = mbar_wait(bar, phase, P.flags, 10 + g, &abort_flag);
+        phase ^= 1;
+        ok = group_all(mine, 1 + g);
+        if (!ok) break;
+        tc_fence_after();
 
         // ---- this coefficient's row: recombine, reduce, subtract the overflow term, store ----
         const uint32_t taddr = tmem_g + ((uint32_t)((warp & 3) * 32) << 16);
         u64* dst = P.out + (((size_t)bt * P.blocks + blk) * T) * P.N + xt * TM + r;
         const u64* vt = s_vt + (blk * (APAD + 1) + v) * T;
-        constexpr int KU = NH > 1 ? 2 : 4;               // targets per batch of accumulator loads
-        const int th = (T + NH - 1) / NH;                // targets per thread of a row
-        const int k_end = min(T, (h + 1) * th);
-        for (int k0 = h * th; k0 < k_end; k0 += KU) {
-            int32_t D[KU][8];
+        for (int k0 = 0; k0 < T; k0 += 4) {
+            int32_t D[4][8];
 #pragma unroll
-            for (int u = 0; u < KU; u++) tmem_ld8(taddr + min(k0 + u, T - 1) * 8, D[u]);
+            for (int u = 0; u < 4; u++) tmem_ld8(taddr + (k0 + u) * 8, D[u]);
             tmem_ld_wait();
 #pragma unroll
-            for (int u = 0; u < KU; u++) {
+            for (int u = 0; u < 4; u++) {
                 const int k = k0 + u;
-                if (k >= k_end) break;
+                if (k >= T) break;
                 // sum_a D_a 2^(8a) in two halves of four (each below 2^48)
                 const u64 g0 = mad_wide((uint32_t)D[u][3], 1u << 24, mad_wide((uint32_t)D[u][2], 1u << 16,
                                mad_wide((uint32_t)D[u][1], 1u << 8, (u64)(uint32_t)D[u][0])));
@@ -295,21 +278,21 @@ __global__ void __launch_bounds__(128 * NG * NH, 1) modup_umma_kernel(ModUpTcArg
     }
 }
 
-template <int APAD, bool F64Q, int NG, int NH>
+template <int APAD, bool F64Q, int NG>
 int launch_groups(ckks_b200_context* c, const ModUpTcArgs& P, cudaStream_t st) {
-    constexpr int GROUPS = NG, THREADS = 128 * NG * NH;
+    constexpr int GROUPS = NG, THREADS = 128 * NG;
     constexpr int KSTEPS = APAD * 8 / 32;
     const size_t smem = (size_t)GROUPS * KSTEPS * TM * 32 + (size_t)P.blocks * KSTEPS * P.npad * 32 +
                         (size_t)P.blocks * APAD * (8 + 16) + (size_t)P.blocks * (APAD + 1) * P.t_num * 8 +
-                        (size_t)P.t_num * 16 + (size_t)P.blocks * APAD * 24 + (size_t)GROUPS * 2 * NH * 128 * 8;
+                        (size_t)P.t_num * 16 + (size_t)P.blocks * APAD * 24;
     CKB_REQUIRE(smem <= 200 * 1024, CKKS_B200_ERR_UNSUPPORTED, "ModUp tables of %zu bytes do not fit shared memory", smem);
-    CKB_CUDA(cudaFuncSetAttribute(modup_umma_kernel<APAD, F64Q, NG, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CKB_CUDA(cudaFuncSetAttribute(modup_umma_kernel<APAD, F64Q, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int sms = 0;
     CKB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device));
     const long total = (long)P.batch * P.blocks * (P.N / TM);
     const long want = (total + GROUPS - 1) / GROUPS;
     const int grid = (int)(want < sms ? want : sms);
-    modup_umma_kernel<APAD, F64Q, NG, NH><<<grid, THREADS, smem, st>>>(P);
+    modup_umma_kernel<APAD, F64Q, NG><<<grid, THREADS, smem, st>>>(P);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
@@ -317,16 +300,9 @@ int launch_groups(ckks_b200_context* c, const ModUpTcArgs& P, cudaStream_t st) {
 
 template <int APAD, bool F64Q>
 int launch(ckks_b200_context* c, const ModUpTcArgs& P, cudaStream_t st) {
-    static const int nh = getenv("CKKS_B200_MODUP_NH") ? atoi(getenv("CKKS_B200_MODUP_NH")) : 1;      // development switch
-    static const int ng = getenv("CKKS_B200_MODUP_NG") ? atoi(getenv("CKKS_B200_MODUP_NG")) : 5;
     // the accumulator loads run in groups of four targets, so five groups need 8*ceil4(t_num) <= 96
-    const bool five = ng == 5 && (P.t_num + 3) / 4 * 32 <= 96;
-    if (nh == 2) {
-        if (five) return launch_groups<APAD, F64Q, 5, 2>(c, P, st);
-        return launch_groups<APAD, F64Q, 4, 2>(c, P, st);
-    }
-    if (five) return launch_groups<APAD, F64Q, 5, 1>(c, P, st);
-    return launch_groups<APAD, F64Q, 4, 1>(c, P, st);
+    if ((P.t_num + 3) / 4 * 32 <= 96) return launch_groups<APAD, F64Q, 5>(c, P, st);
+    return launch_groups<APAD, F64Q, 4>(c, P, st);
 }
 
 }  // namespace
