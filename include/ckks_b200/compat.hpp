@@ -99,6 +99,17 @@ class Scheme_23 {
 public:
     Context_23& context;
     explicit Scheme_23(Context_23& context_) : context(context_) {}
+    // Scheme_23::mult_23 (KeySwitch_23.cuh:192-236); rlk_23 is the relinearisation key block on the device.
+    uint64_tt* rlk_23 = nullptr;
+    void mult_23(Ciphertext& cipher_res, Ciphertext& cipher1, Ciphertext& cipher2, cudaStream_t stream = 0) {
+        if (cipher1.l == 0 || cipher2.l == 0) throw std::invalid_argument("Ciphertexts are on level 0");
+        if (rlk_23 == nullptr) throw std::invalid_argument("rotKey_23 not exists");
+        const int l = cipher1.l < cipher2.l ? cipher1.l : cipher2.l;
+        check(ckks_b200_mult(context.b200, (uint64_t*)cipher_res.cipher_device, (const uint64_t*)cipher1.cipher_device,
+                             (const uint64_t*)cipher2.cipher_device, (const uint64_t*)rlk_23, l, context.gamma, stream));
+        cipher_res.l = l;
+        cipher_res.scale = cipher1.scale * cipher2.scale;
+    }
     void rescaleAndEqual(Ciphertext& cipher, cudaStream_t stream = 0) {
         check(ckks_b200_rescale(context.b200, (uint64_t*)cipher.cipher_device, cipher.L, cipher.l, stream));
         cipher.scale = cipher.scale / (long double)context.qVec[cipher.l];
