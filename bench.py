@@ -406,7 +406,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", choices=["pcmm", "ntt", "modup", "keyswitch"], default="pcmm")
+    ap.add_argument("--workload", choices=["pcmm", "ntt", "modup", "keyswitch", "ringpack"], default="pcmm")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -574,6 +574,13 @@ def main():
             roof = r["forward"]["roofline"]
             extra["ntt"] = r
             metric, unit, cfg = "ntt_limb_xforms_per_sec", "limb-xforms/s", r["config"]
+        elif args.workload == "ringpack":
+            r = bench_ringpack(torch, device, args.steps, args.warmup, peaks)
+            ms = r["mlwe_packing"]["ms_per_call"]
+            value = world * r["mlwe_packing"]["calls_per_sec"]
+            roof = r["mlwe_packing"]["roofline"]
+            extra["ringpack"] = r
+            metric, unit, cfg = "mlwe_packings_per_sec", "packings/s", r["config"]
         elif args.workload == "keyswitch":
             r = bench_keyswitch(torch, device, args.steps, args.warmup, peaks)
             ms = r["ms_per_switch"]

@@ -8,52 +8,62 @@
 // with gap = k / mlwe_num, in the coefficient domain; the reference runs an inverse NTT on
 // the RLWE ciphertext first and a forward NTT afterwards, and so does this entry point.
 //
-// One thread writes one output word; consecutive threads write consecutive words of an
-// MLWE polynomial (coalesced), and read the RLWE limb with stride k.  The limb (512 KiB at
-// N = 2^16) is read k times over and stays in L2, so HBM sees the output stream only:
-// (k+1)*N1 words per MLWE ciphertext per limb.
+// For 1 <= r < k the source index falls by one as r rises by one, while the output is contiguous in g.
+// A thread block therefore moves a 32 x 32 tile of (r, g) through shared memory: it reads with lanes
+// along r (consecutive RLWE words) and writes with lanes along g (consecutive MLWE words), so both
+// sides are coalesced.  HBM sees the output stream, (k+1)*N1 words per MLWE ciphertext per limb; the
+// RLWE limb (512 KiB at N = 2^16) is re-read from L2.
 #include "context.cuh"
 
 using namespace ckb;
 
 namespace {
 
-__global__ void __launch_bounds__(256) rlwe_decompose_kernel(const u64* __restrict__ rlwe, u64* const* __restrict__ mlwe,
-                                                             const u64* __restrict__ q_moduli, long N, int N1, int k,
-                                                             int mlwe_num, int L) {
-    const long C = (long)(k + 1) * N1;
-    const long w = (long)blockIdx.x * blockDim.x + threadIdx.x;     // word inside one limb of one MLWE ciphertext
-    if (w >= C) return;
-    const int limb = blockIdx.y, i = blockIdx.z;
-    const u64 q = q_moduli[limb];
-    const int gap = k / mlwe_num;
-    const int r = (int)(w / N1), g = (int)(w % N1);
-    const u64* A = rlwe + N * limb;
-    const u64* B = rlwe + N * (L + 1 + limb);
+// word g of polynomial r of MLWE ciphertext i, one limb (the index maps at the top of the file)
+__device__ __forceinline__ u64 decompose_word(const u64* __restrict__ A, const u64* __restrict__ B, u64 q, long N, int N1, int k,
+                                              int gap, int i, int r, int g) {
     long addr;
-    bool negate;
-    const u64* src;
+    bool negate = false;
+    const u64* src = A;
     if (r == k) {                 // b polynomial
         addr = (long)i * gap + (long)g * k;
         src = B;
-        negate = false;
     } else if (r == 0) {
         addr = (long)i * gap + (long)g * k;
-        src = A;
-        negate = false;
     } else if (g == 0) {
         addr = (long)(N1 - 1) * k + (k - r) + (long)i * gap;
-        src = A;
         negate = true;
     } else {
         addr = (long)(g - 1) * k + (k - r) + (long)i * gap;
-        src = A;
-        negate = false;
     }
     if (addr >= N) { addr -= N; negate = !negate; }
-    u64 v = src[addr];
-    if (negate) v = v == 0 ? 0 : q - v;
-    mlwe[i][(size_t)limb * C + w] = v;
+    const u64 v = src[addr];
+    return negate ? (v == 0 ? 0 : q - v) : v;
+}
+
+__global__ void __launch_bounds__(256) rlwe_decompose_kernel(const u64* __restrict__ rlwe, u64* const* __restrict__ mlwe,
+                                                             const u64* __restrict__ q_moduli, long N, int N1, int k,
+                                                             int mlwe_num, int L, int g_tiles) {
+    __shared__ u64 tile[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;               // 32 x 8
+    const int r0 = (blockIdx.x / g_tiles) * 32, g0 = (blockIdx.x % g_tiles) * 32;
+    const int limb = blockIdx.y, i = blockIdx.z;
+    const u64 q = q_moduli[limb];
+    const int gap = k / mlwe_num;
+    const u64* A = rlwe + N * limb;
+    const u64* B = rlwe + N * (L + 1 + limb);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int g = g0 + ty + 8 * j, r = r0 + tx;             // lanes along r
+        if (g < N1 && r <= k) tile[ty + 8 * j][tx] = decompose_word(A, B, q, N, N1, k, gap, i, r, g);
+    }
+    __syncthreads();
+    const long C = (long)(k + 1) * N1;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int r = r0 + ty + 8 * j, g = g0 + tx;             // lanes along g
+        if (g < N1 && r <= k) mlwe[i][(size_t)limb * C + (size_t)r * N1 + g] = tile[tx][ty + 8 * j];
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -65,19 +75,32 @@ __global__ void __launch_bounds__(256) rlwe_decompose_kernel(const u64* __restri
 // mlweCipherEmbedding_new_kernel (:312-359): coefficient g of polynomial r of ciphertext i
 // goes to position g*k + i*gap of embedded polynomial r; the p limb gets the centred lift.
 // E: (k+1) polynomials of [2][N], zeroed beforehand.
+// The source is contiguous in g, the destination in i: a 32 x 32 tile of (i, g) goes through shared memory so that
+// both the reads (lanes along g) and the writes (lanes along i) are coalesced.
 __global__ void __launch_bounds__(256) pack_embed_kernel(const u64* const* __restrict__ mlwe, u64* __restrict__ E, long N,
-                                                         int N1, int k, int mlwe_num, u64 p, u64 q0) {
-    const long C = (long)(k + 1) * N1;
-    const long w = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (w >= C) return;
-    const int i = blockIdx.y;
-    const int r = (int)(w / N1), g = (int)(w % N1);
+                                                         int N1, int k, int mlwe_num, u64 p, u64 q0, int g_tiles) {
+    __shared__ u64 tile[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;               // 32 x 8
+    const int i0 = (blockIdx.x / g_tiles) * 32, g0 = (blockIdx.x % g_tiles) * 32;
+    const int r = blockIdx.y;
     const int gap = k / mlwe_num;
-    const u64 v = mlwe[i][w];                                   // limb 0 of ciphertext i
-    const long pos = (long)g * k + (long)i * gap;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int i = i0 + ty + 8 * j, g = g0 + tx;             // lanes along g
+        if (i < mlwe_num && g < N1) tile[ty + 8 * j][tx] = mlwe[i][(size_t)r * N1 + g];      // limb 0 of ciphertext i
+    }
+    __syncthreads();
     u64* poly = E + (size_t)r * 2 * N;
-    poly[N + pos] = v;
-    poly[pos] = v > (q0 >> 1) ? (p - (q0 - v)) % p : v;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int g = g0 + ty + 8 * j, i = i0 + tx;             // lanes along i
+        if (i < mlwe_num && g < N1) {
+            const u64 v = tile[tx][ty + 8 * j];
+            const long pos = (long)g * k + (long)i * gap;
+            poly[N + pos] = v;
+            poly[pos] = v > (q0 >> 1) ? (p - (q0 - v)) % p : v;
+        }
+    }
 }
 
 // mlweCipherMultRepackingKey_kernel (:261-289): (A, B) = sum_i E_i * key_i in the NTT domain.
@@ -146,10 +169,11 @@ extern "C" int ckks_b200_mlwe_packing(ckks_b200_context* c, uint64_t* d_rlwe, in
     u64* E = c->pack_buf;
     u64* O = E + (size_t)(k + 1) * 2 * N;
     CKB_CUDA(cudaMemcpyAsync(c->ptr_buf, h_mlwe_ptrs, sizeof(u64*) * mlwe_num, cudaMemcpyHostToDevice, st));
-    CKB_CUDA(cudaMemsetAsync(E, 0, sizeof(u64) * (size_t)(k + 1) * 2 * N, st));                       // :397
-    const long C = (long)(k + 1) * N1;
-    pack_embed_kernel<<<dim3((unsigned)((C + 255) / 256), mlwe_num), 256, 0, st>>>((const u64* const*)c->ptr_buf, E, N, N1,
-                                                                                  k, mlwe_num, p, q0);
+    // the reference clears the buffer (:397); with as many ciphertexts as the rank every position is written below
+    if (mlwe_num != k) CKB_CUDA(cudaMemsetAsync(E, 0, sizeof(u64) * (size_t)(k + 1) * 2 * N, st));
+    const int g_tiles = (N1 + 31) / 32;
+    pack_embed_kernel<<<dim3((unsigned)(((mlwe_num + 31) / 32) * g_tiles), k + 1), dim3(32, 8), 0, st>>>(
+        (const u64* const*)c->ptr_buf, E, N, N1, k, mlwe_num, p, q0, g_tiles);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     // the k a-polynomials to the NTT domain over [p, q0] (:401)
@@ -197,10 +221,10 @@ extern "C" int ckks_b200_rlwe_decompose(ckks_b200_context* c, uint64_t* d_rlwe, 
         rc = ckks_b200_ntt_inverse(c, d_rlwe, 0, c->p_num, 2, l + 1, L + 1, stream);     // :107
         if (rc) return rc;
     }
-    const long C = (long)(mlwe_rank + 1) * N1;
-    dim3 grid((unsigned)((C + 255) / 256), l + 1, mlwe_num);
-    rlwe_decompose_kernel<<<grid, 256, 0, st>>>((const u64*)d_rlwe, (u64* const*)c->ptr_buf, c->d_moduli + c->p_num,
-                                                (long)c->N, N1, mlwe_rank, mlwe_num, L);
+    const int g_tiles = (N1 + 31) / 32;
+    dim3 grid((unsigned)((mlwe_rank / 32 + 1) * g_tiles), l + 1, mlwe_num);
+    rlwe_decompose_kernel<<<grid, dim3(32, 8), 0, st>>>((const u64*)d_rlwe, (u64* const*)c->ptr_buf, c->d_moduli + c->p_num,
+                                                        (long)c->N, N1, mlwe_rank, mlwe_num, L, g_tiles);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     if (ntt_domain) {
