@@ -368,6 +368,23 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
     if (!st) st = upload(&c->mu_blk_mod_t, blk_mod_t);
     if (!st) st = upload(&c->d_t_mu, t_mu);
     if (!st) st = upload(&c->mu_planes, planes);
+    {
+        std::vector<u64> src_mod((size_t)q_num * B * apad, 1), tgt_mod((size_t)B * (T ? T : 1), 0);
+        std::vector<ulonglong2> src_hinv((size_t)q_num * B * apad, make_ulonglong2(0, 0));
+        for (int l = 0; l < q_num && T > 0; l++)
+            for (int b = 0; b < (l + 1 + A - 1) / A; b++)
+                for (int j = 0; j < std::min(A, l + 1 - b * A); j++) {
+                    src_mod[((size_t)l * B + b) * apad + j] = qv[b * A + j];
+                    src_hinv[((size_t)l * B + b) * apad + j] = hat_inv[((size_t)l * B + b) * A + j];
+                }
+        for (int b = 0; b < B; b++)
+            for (int k = 0; k < T; k++) tgt_mod[(size_t)b * T + k] = tv[k];
+        std::vector<u64> zeros((size_t)B * std::max(apad, T ? T : 1), 0);
+        if (!st) st = upload(&c->mu_src_mod, src_mod);
+        if (!st) st = upload(&c->mu_src_hinv, src_hinv);
+        if (!st) st = upload(&c->mu_src_pre, zeros);
+        if (!st) st = upload(&c->mu_tgt_mod, tgt_mod);
+    }
     if (!st) st = upload(&c->d_t_inv, t_inv);
     if (!st && cudaMalloc(&c->d_flags, 16 * sizeof(int)) != cudaSuccess) st = CKKS_B200_ERR_NOMEM;
     if (!st && cudaMemset(c->d_flags, 0, 16 * sizeof(int)) != cudaSuccess) st = CKKS_B200_ERR_CUDA;
@@ -377,9 +394,89 @@ extern "C" int ckks_b200_context_create(ckks_b200_context** out, int device, int
     return CKKS_B200_OK;
 }
 
+namespace ckb {
+int build_tpq_tables(ckks_b200_context* c, int gamma) {
+    if (c->tpq.count(gamma)) return CKKS_B200_OK;
+    TpqTables tb;
+    const int PQ = c->p_num + c->q_num, T = c->t_num;
+    const u64* mv = c->moduli.data();
+    const u64* tv = mv + PQ;
+    const int R = (PQ + gamma - 1) / gamma, apad = (T + 3) / 4 * 4;
+    tb.kpad = apad * 8;
+    tb.npad = (gamma * 8 + 15) / 16 * 16;
+    bool ok = c->chain_ok && T >= 2 && T <= 16 && tb.npad <= 128;
+    std::vector<u64> src_mod((size_t)R * apad, 1), src_pre((size_t)R * apad, 0), tgt_mod((size_t)R * gamma, 0),
+        tgt_f((size_t)R * gamma, 0), tgt_post((size_t)R * gamma, 0);
+    std::vector<ulonglong2> src_hinv((size_t)R * apad, make_ulonglong2(0, 0));
+    std::vector<uint8_t> planes(ok ? (size_t)R * tb.kpad * tb.npad : 0, 0);
+    for (int blk = 0; blk < R && ok; blk++) {
+        for (int j = 0; j < T; j++) {
+            u64 prod = 1;
+            for (int jj = 0; jj < T; jj++)
+                if (jj != j) prod = h_mulmod(prod, tv[jj] % tv[j], tv[j]);
+            const u64 inv = h_invmod(prod, tv[j]);
+            src_mod[(size_t)blk * apad + j] = tv[j];
+            src_hinv[(size_t)blk * apad + j] = make_ulonglong2(inv, h_shoup(inv, tv[j]));
+            const u128 m2 = (u128)2 * tv[j];
+            u128 acc = 1;
+            for (int jj = 0; jj < T; jj++) acc = (acc * (tv[jj] % m2)) % m2;
+            src_pre[(size_t)blk * apad + j] = (u64)((acc - 1) / 2);         // floor(T/2) mod t_j
+        }
+        uint8_t* tile = planes.data() + (size_t)blk * tb.kpad * tb.npad;
+        for (int k = 0; k < gamma && blk * gamma + k < PQ; k++) {
+            const u64 r = mv[blk * gamma + k];
+            if (r < (1ull << 40)) ok = false;
+            u64 full = 1;
+            for (int j = 0; j < T; j++) full = h_mulmod(full, tv[j] % r, r);
+            const u128 m2 = (u128)2 * r;
+            u128 acc = 1;
+            for (int j = 0; j < T; j++) acc = (acc * (tv[j] % m2)) % m2;
+            tgt_mod[(size_t)blk * gamma + k] = r;
+            tgt_f[(size_t)blk * gamma + k] = full;
+            tgt_post[(size_t)blk * gamma + k] = (u64)((acc - 1) / 2);
+            for (int j = 0; j < T; j++) {
+                u64 cst = 1;
+                for (int jj = 0; jj < T; jj++)
+                    if (jj != j) cst = h_mulmod(cst, tv[jj] % r, r);
+                // sum_j rb_j*h_j >= v*F needs h_j*t_j >= F(1 + 2^-40) for every j (see the Q -> T tables above)
+                if ((u128)cst * tv[j] < (u128)full + (full >> 40) + 1) ok = false;
+                for (int bb = 0; bb < 8; bb++) {
+                    const int kk = j * 8 + bb, ks = kk / 32, kc = (kk % 32) / 16, kin = kk % 16;
+                    for (int a = 0; a < 8; a++) {
+                        const int n = k * 8 + a;
+                        tile[(size_t)ks * tb.npad * 32 + (size_t)(n / 8) * 256 + kc * 128 + (n % 8) * 16 + kin] = (uint8_t)(cst >> (8 * a));
+                    }
+                    cst = h_mulmod(cst, 256 % r, r);
+                }
+            }
+        }
+    }
+    tb.ok = ok;
+    int st = CKKS_B200_OK;
+    if (ok) {
+        DeviceGuard guard(c->device);
+        if (!st) st = upload(&tb.src_mod, src_mod);
+        if (!st) st = upload(&tb.src_hinv, src_hinv);
+        if (!st) st = upload(&tb.src_pre, src_pre);
+        if (!st) st = upload(&tb.tgt_mod, tgt_mod);
+        if (!st) st = upload(&tb.tgt_f, tgt_f);
+        if (!st) st = upload(&tb.tgt_post, tgt_post);
+        if (!st) st = upload(&tb.planes, planes);
+    }
+    c->tpq[gamma] = tb;
+    return st;
+}
+}  // namespace ckb
+
 extern "C" int ckks_b200_context_destroy(ckks_b200_context* c) {
     if (!c) return CKKS_B200_OK;
     DeviceGuard guard(c->device);
+    for (auto& kv : c->tpq) {
+        TpqTables& tb = kv.second;
+        cudaFree(tb.src_mod); cudaFree(tb.src_hinv); cudaFree(tb.src_pre); cudaFree(tb.tgt_mod); cudaFree(tb.tgt_f);
+        cudaFree(tb.tgt_post); cudaFree(tb.planes);
+    }
+    cudaFree(c->mu_src_mod); cudaFree(c->mu_src_hinv); cudaFree(c->mu_src_pre); cudaFree(c->mu_tgt_mod);
     cudaFree(c->tw_fwd); cudaFree(c->tw_inv); cudaFree(c->tw_fwd_d); cudaFree(c->tw_inv_d); cudaFree(c->d_moduli); cudaFree(c->d_ninv); cudaFree(c->d_qinv64);
     cudaFree(c->mu_hat_inv); cudaFree(c->mu_hat_mod_t); cudaFree(c->mu_blk_mod_t);
     cudaFree(c->d_pq_mu); cudaFree(c->d_t_hat_inv); cudaFree(c->d_t_hat_mod_r); cudaFree(c->d_half_t); cudaFree(c->d_t_mod_pq);

@@ -1,8 +1,24 @@
 // Context handle: moduli, NTT twiddle tables and ModUp tables resident in HBM.
 #pragma once
+#include <map>
 #include <vector>
 
 #include "common.cuh"
+
+// Tables of the tensor-core T -> [p | q] conversion for one gamma (modup_umma.cu), all on the device:
+// per block of gamma targets the source columns (the t moduli, the same for every block), the targets and
+// the byte planes of ((T/t_j) * 2^(8b)) mod r.
+struct TpqTables {
+    bool ok = false;              // every target in [2^40, 2^62), the reference's 128-bit difference cannot wrap
+    int kpad = 0, npad = 0;
+    u64* src_mod = nullptr;       // [R][apad]
+    ulonglong2* src_hinv = nullptr;
+    u64* src_pre = nullptr;       // floor(T/2) mod t_j
+    u64* tgt_mod = nullptr;       // [R][gamma]
+    u64* tgt_f = nullptr;         // T mod r
+    u64* tgt_post = nullptr;      // floor(T/2) mod r
+    uint8_t* planes = nullptr;    // [R][kpad/32][npad][32]
+};
 
 struct ckks_b200_context {
     int device = 0;
@@ -46,6 +62,12 @@ struct ckks_b200_context {
     std::vector<uint8_t> mu_tc_ok;
     double* d_t_inv = nullptr;
     int tc_kpad = 0, tc_npad = 0;
+    // the same conversion's per-block tables in the generic form the kernel reads:
+    u64* mu_src_mod = nullptr;               // [l][blocks_max][tc_kpad/8]  q_j of the digit (1 beyond it)
+    ulonglong2* mu_src_hinv = nullptr;       // [l][blocks_max][tc_kpad/8]
+    u64* mu_src_pre = nullptr;               // zeros (nothing is pre-added or post-subtracted in this conversion)
+    u64* mu_tgt_mod = nullptr;               // [blocks_max][t_num]  the t moduli for every block
+    std::map<int, TpqTables> tpq;            // tables of the T -> [p | q] conversion, by gamma, built on first use
     int modup_algo = 0;                      // CKKS_B200_MODUP_AUTO / _TENSOR / _SIMT
     int* d_flags = nullptr;                  // [16] [1] = site of a device-side wait that ran out
     int* h_flags = nullptr;                  // pinned mirror
@@ -84,6 +106,10 @@ namespace ckb {
 u64 find_mth_root(u64 M, u64 q);
 void fill_psi_tables(u64 psi, u64 q, uint32_t n, std::vector<u64>& tab, std::vector<u64>& tabinv);
 int ensure_buf(u64** buf, size_t* cap, size_t words);
+// Builds (once per gamma) the tables of the tensor-core T -> [p | q] conversion.
+int build_tpq_tables(ckks_b200_context* c, int gamma);
+bool modup_t_tensor_ok(const ckks_b200_context* c, int gamma);
+int modup_t_tensor(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int gamma, int batch, cudaStream_t st);
 // Tensor-core ModUp (modup_umma.cu): whether level l qualifies, and the launch.
 bool modup_tensor_ok(const ckks_b200_context* c, int l);
 int modup_tensor(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int batch, cudaStream_t st);

@@ -240,6 +240,13 @@ extern "C" int ckks_b200_modup_t_to_pql(ckks_b200_context* c, uint64_t* d_out, c
     if (batch == 0) return CKKS_B200_OK;
     DeviceGuard guard(c->device);
     CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", c->device);
+    // the tensor-core contraction where this gamma's tables qualify (the kernel choice follows ModUp's), else CUDA cores
+    rc = build_tpq_tables(c, gamma);
+    if (rc) return rc;
+    CKB_REQUIRE(c->modup_algo != CKKS_B200_MODUP_TENSOR || modup_t_tensor_ok(c, gamma), CKKS_B200_ERR_UNSUPPORTED,
+                "the T -> [p | q] tables of gamma=%d do not qualify for the tensor-core conversion", gamma);
+    if (c->modup_algo != CKKS_B200_MODUP_SIMT && modup_t_tensor_ok(c, gamma))
+        return modup_t_tensor(c, (u64*)d_out, (const u64*)d_in, l, gamma, batch, (cudaStream_t)stream);
     ModUpTArgs P;
     P.out = (u64*)d_out;
     P.in = (const u64*)d_in;

@@ -19,6 +19,14 @@
 // v*(Qblk mod t_k); context creation checks the tables for that and sends such levels to the
 // CUDA-core kernel.
 //
+// The same kernel serves the second conversion of the key-switch chain, Context_23::modUpTtoPQl_23
+// (BasisConv.cuh:183-248): there the sources are the t moduli (60-bit, so rb_j is a Shoup product of
+// x_j + floor(T/2)), the targets of a block are gamma moduli of [p | q], and floor(T/2) mod r is
+// subtracted at the end, which the overflow table absorbs.  Everything that differs between the two
+// conversions sits in per-block tables: source moduli, inverse hat constants and pre-added constants;
+// target moduli, the multiple subtracted per unit of the overflow count and the constant subtracted
+// at the end; the byte planes; and four strides.
+//
 // A CTA runs NG independent groups of 128 threads: five when the 8*t_num accumulator columns of a group
 // fit 96 tensor-memory columns (t_num <= 12), four with 128 columns each otherwise.  A group owns one
 // operand tile in shared memory and its columns of tensor memory and walks over tiles of 128 coefficients: every
@@ -35,18 +43,21 @@ namespace {
 
 constexpr int TMEM_COLS = 512;           // the whole tensor memory of the SM, split evenly over the groups
 
-struct ModUpTcArgs {
+struct BconvArgs {
     u64* out;
     const u64* in;
-    const u64* q;                 // q moduli [q_num]
-    const u64* t;                 // t moduli [t_num]
-    const double* t_inv;          // [t_num]
-    const ulonglong2* hat_inv;    // [blocks_max*alpha] for this level
-    const u64* blk_mod_t;         // [blocks_max][t_num] for this level
-    const uint8_t* planes;        // [blocks_max][kpad/32][npad][32] for this level
+    const u64* src_mod;           // [blocks][APAD]  modulus of source limb j of block blk (1: no such limb)
+    const ulonglong2* src_hinv;   // [blocks][APAD]  {hat_j^-1 mod m_j, shoup}
+    const u64* src_pre;           // [blocks][APAD]  added to the residue before the product
+    const u64* tgt_mod;           // [blocks][tg]    target moduli
+    const u64* tgt_f;             // [blocks][tg]    (product of the block's source moduli) mod r
+    const u64* tgt_post;          // [blocks][tg]    subtracted at the end, below r
+    const uint8_t* planes;        // [blocks][kpad/32][npad][32]
     int* flags;
     uint32_t N;
-    int q_num, t_num, alpha, l, blocks, batch, npad;
+    int blocks, batch, tg, npad;
+    int tgt_limit;                // target k of block blk exists iff blk*tg + k < tgt_limit
+    size_t in_batch, in_blk, out_batch, out_blk;      // strides in words; limb j / target k sits j*N / k*N further
 };
 
 __device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
@@ -74,12 +85,12 @@ __device__ __forceinline__ u64 mad_wide(uint32_t a, uint32_t b, u64 c) {
     return d;
 }
 
-// F64Q: every q modulus is below 2^50, and rb_j = x_j * w_j mod q_j is then formed on the FP64 pipe
+// F64Q: every source modulus is below 2^50 and nothing is pre-added, and rb_j = x_j * w_j mod m_j is then formed on the FP64 pipe
 // (exact: h + l = x*w with h = fl(x*w), l the FMA remainder; h - c*q is a small integer for
 // c = rint(h/q); w is kept centred, |w| <= q/2, so the result stays within (-0.7q, 0.7q)).
 // Otherwise rb_j is a 64-bit Shoup product.
 template <int APAD, bool F64Q, int NG>
-__global__ void __launch_bounds__(128 * NG, 1) modup_umma_kernel(ModUpTcArgs P) {
+__global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
     constexpr int GROUPS = NG, THREADS = 128 * NG, GROUP_COLS = NG == 5 ? 96 : 128;
     constexpr int KSTEPS = APAD * 8 / 32;
     constexpr int A_TILE = KSTEPS * TM * 32;
@@ -90,45 +101,46 @@ __global__ void __launch_bounds__(128 * NG, 1) modup_umma_kernel(ModUpTcArgs P) 
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int g = tid >> 7, r = tid & 127;
-    const int T = P.t_num;
+    const int T = P.tg;
     const int b_tile = KSTEPS * P.npad * 32;
     uint8_t* sA = smem + g * A_TILE;
     uint8_t* sB = smem + GROUPS * A_TILE;                                   // [blocks][KSTEPS][npad*32]
-    u64* s_q = reinterpret_cast<u64*>(sB + P.blocks * b_tile);             // [blocks][APAD]
+    u64* s_q = reinterpret_cast<u64*>(sB + P.blocks * b_tile);             // [blocks][APAD]  source moduli
     ulonglong2* s_hinv = reinterpret_cast<ulonglong2*>(s_q + P.blocks * APAD);   // [blocks][APAD]
-    u64* s_vt = reinterpret_cast<u64*>(s_hinv + P.blocks * APAD);          // [blocks][APAD+1][T]  v*(Qblk mod t_k) mod t_k
-    u64* s_t = s_vt + P.blocks * (APAD + 1) * T;                           // [T]
-    double* s_tinv = reinterpret_cast<double*>(s_t + T);                   // [T]
-    double* s_qd = s_tinv + T;                                             // [blocks][APAD]  q_j as a double
-    double* s_qinv = s_qd + P.blocks * APAD;                               // [blocks][APAD]  1/q_j (0 beyond the digit)
-    double* s_wd = s_qinv + P.blocks * APAD;                               // [blocks][APAD]  (Qblk/q_j)^-1 mod q_j, centred
+    u64* s_vt = reinterpret_cast<u64*>(s_hinv + P.blocks * APAD);          // [blocks][APAD+1][T]  (v*F + post) mod r
+    u64* s_t = s_vt + P.blocks * (APAD + 1) * T;                           // [blocks][T]  target moduli (0: none)
+    double* s_tinv = reinterpret_cast<double*>(s_t + P.blocks * T);        // [blocks][T]
+    double* s_qd = s_tinv + P.blocks * T;                                  // [blocks][APAD]  m_j as a double
+    double* s_qinv = s_qd + P.blocks * APAD;                               // [blocks][APAD]  1/m_j (0 where there is no limb)
+    double* s_wd = s_qinv + P.blocks * APAD;                               // [blocks][APAD]  hat_j^-1 mod m_j, centred
+    u64* s_pre = reinterpret_cast<u64*>(s_wd + P.blocks * APAD);           // [blocks][APAD]
 
     for (int i = tid; i < P.blocks * b_tile / 16; i += THREADS)
         reinterpret_cast<uint4*>(sB)[i] = reinterpret_cast<const uint4*>(P.planes)[i];
     for (int i = tid; i < P.blocks * APAD; i += THREADS) {
-        const int blk = i / APAD, j = i % APAD;
-        const bool live = j < P.alpha && blk * P.alpha + j <= P.l;
-        const u64 qj = live ? P.q[blk * P.alpha + j] : 1;
-        s_q[i] = qj;
-        s_hinv[i] = live ? P.hat_inv[blk * P.alpha + j] : make_ulonglong2(0, 0);
-        s_qd[i] = (double)qj;
-        s_qinv[i] = live ? 1.0 / (double)qj : 0.0;
-        const u64 w = live ? P.hat_inv[blk * P.alpha + j].x : 0;
-        s_wd[i] = w > qj / 2 ? -(double)(qj - w) : (double)w;
+        const u64 mj = P.src_mod[i];
+        const bool live = mj != 1;
+        s_q[i] = mj;
+        s_hinv[i] = live ? P.src_hinv[i] : make_ulonglong2(0, 0);
+        s_pre[i] = live ? P.src_pre[i] : 0;
+        s_qd[i] = (double)mj;
+        s_qinv[i] = live ? 1.0 / (double)mj : 0.0;
+        const u64 w = live ? P.src_hinv[i].x : 0;
+        s_wd[i] = w > mj / 2 ? -(double)(mj - w) : (double)w;
     }
     for (int i = tid; i < P.blocks * T; i += THREADS) {
         const int blk = i / T, k = i % T;
-        const u64 tk = P.t[k], bm = P.blk_mod_t[i];
-        u64 acc = 0;
+        const bool live = blk * T + k < P.tgt_limit && P.tgt_mod[i] != 0;
+        const u64 rk = live ? P.tgt_mod[i] : 0;
+        s_t[i] = rk;
+        s_tinv[i] = live ? 1.0 / (double)rk : 0.0;
+        u64 acc = live ? P.tgt_post[i] : 0;
+        const u64 f = live ? P.tgt_f[i] : 0;
         for (int v = 0; v <= APAD; v++) {
             s_vt[(blk * (APAD + 1) + v) * T + k] = acc;
-            acc += bm;                       // bm < t_k < 2^62: no overflow
-            if (acc >= tk) acc -= tk;
+            acc += f;                        // f, acc < r < 2^62: no overflow
+            if (acc >= rk) acc -= rk;
         }
-    }
-    for (int i = tid; i < T; i += THREADS) {
-        s_t[i] = P.t[i];
-        s_tinv[i] = P.t_inv[i];
     }
     if (tid == 0) {
         for (int i = 0; i < GROUPS; i++) mbar_init(smem_u32(&bars[i]), 1);
@@ -159,10 +171,9 @@ __global__ void __launch_bounds__(128 * NG, 1) modup_umma_kernel(ModUpTcArgs P) 
         const long rest = tl / tiles_x;
         const int blk = (int)(rest % P.blocks);
         const long bt = rest / P.blocks;
-        const int cnt = min(P.alpha, P.l + 1 - blk * P.alpha);
-        const u64* src = P.in + ((size_t)bt * P.q_num + (size_t)blk * P.alpha) * P.N + xt * TM + r;
+        const u64* src = P.in + (size_t)bt * P.in_batch + (size_t)blk * P.in_blk + xt * TM + r;
 #pragma unroll
-        for (int j = 0; j < APAD; j++) x[j] = j < cnt ? src[(size_t)j * P.N] : 0;
+        for (int j = 0; j < APAD; j++) x[j] = s_q[blk * APAD + j] != 1 ? src[(size_t)j * P.N] : 0;
     };
 
     u64 cur[APAD];
@@ -197,7 +208,7 @@ __global__ void __launch_bounds__(128 * NG, 1) modup_umma_kernel(ModUpTcArgs P) 
                 rb = (u64)__double_as_longlong(__dadd_rn(rbd, 4503599627370496.0)) & 0x000FFFFFFFFFFFFFull;
             } else {
                 const ulonglong2 hi = s_hinv[blk * APAD + j];
-                rb = shoup_mul(cur[j], hi.x, hi.y, s_q[blk * APAD + j]);
+                rb = shoup_mul(cur[j] + s_pre[blk * APAD + j], hi.x, hi.y, s_q[blk * APAD + j]);   // exact for any 64-bit operand
                 rbd = (double)rb;
             }
             // beyond the digit w = 0 and 1/q = 0: rb = 0 and est is unchanged
@@ -237,8 +248,10 @@ __global__ void __launch_bounds__(128 * NG, 1) modup_umma_kernel(ModUpTcArgs P) 
 
         // ---- this coefficient's row: recombine, reduce, subtract the overflow term, store ----
         const uint32_t taddr = tmem_g + ((uint32_t)((warp & 3) * 32) << 16);
-        u64* dst = P.out + (((size_t)bt * P.blocks + blk) * T) * P.N + xt * TM + r;
+        u64* dst = P.out + (size_t)bt * P.out_batch + (size_t)blk * P.out_blk + xt * TM + r;
         const u64* vt = s_vt + (blk * (APAD + 1) + v) * T;
+        const u64* tmod = s_t + blk * T;
+        const double* tinv = s_tinv + blk * T;
         for (int k0 = 0; k0 < T; k0 += 4) {
             int32_t D[4][8];
 #pragma unroll
@@ -255,9 +268,10 @@ __global__ void __launch_bounds__(128 * NG, 1) modup_umma_kernel(ModUpTcArgs P) 
                                mad_wide((uint32_t)D[u][5], 1u << 8, (u64)(uint32_t)D[u][4])));
                 const u64 lo = g0 + (g1 << 32);              // the row's value modulo 2^64
                 const double val = fma(small_to_double(g1), 4294967296.0, small_to_double(g0));   // the value, to 53 bits
-                const double qd = val * s_tinv[k] + 4503599627370496.0;      // nearest integer quotient (< 2^40)
+                const u64 tk = tmod[k];
+                if (tk == 0) continue;                       // no such target in this block
+                const double qd = val * tinv[k] + 4503599627370496.0;        // nearest integer quotient (< 2^40)
                 const u64 qh = (u64)__double_as_longlong(qd) & 0xFFFFFFFFFFFFFull;
-                const u64 tk = s_t[k];
                 u64 res = lo - qh * tk;                      // in (-t/2 - 1, t/2 + 1) modulo 2^64
                 if ((long long)res < 0) res += tk;
                 const u64 sub = vt[k];
@@ -279,30 +293,38 @@ __global__ void __launch_bounds__(128 * NG, 1) modup_umma_kernel(ModUpTcArgs P) 
 }
 
 template <int APAD, bool F64Q, int NG>
-int launch_groups(ckks_b200_context* c, const ModUpTcArgs& P, cudaStream_t st) {
+int launch_groups(ckks_b200_context* c, const BconvArgs& P, cudaStream_t st) {
     constexpr int GROUPS = NG, THREADS = 128 * NG;
     constexpr int KSTEPS = APAD * 8 / 32;
     const size_t smem = (size_t)GROUPS * KSTEPS * TM * 32 + (size_t)P.blocks * KSTEPS * P.npad * 32 +
-                        (size_t)P.blocks * APAD * (8 + 16) + (size_t)P.blocks * (APAD + 1) * P.t_num * 8 +
-                        (size_t)P.t_num * 16 + (size_t)P.blocks * APAD * 24;
+                        (size_t)P.blocks * APAD * (8 + 16) + (size_t)P.blocks * (APAD + 1) * P.tg * 8 +
+                        (size_t)P.blocks * P.tg * 16 + (size_t)P.blocks * APAD * 32;
     CKB_REQUIRE(smem <= 200 * 1024, CKKS_B200_ERR_UNSUPPORTED, "ModUp tables of %zu bytes do not fit shared memory", smem);
-    CKB_CUDA(cudaFuncSetAttribute(modup_umma_kernel<APAD, F64Q, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CKB_CUDA(cudaFuncSetAttribute(bconv_umma_kernel<APAD, F64Q, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int sms = 0;
     CKB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device));
     const long total = (long)P.batch * P.blocks * (P.N / TM);
     const long want = (total + GROUPS - 1) / GROUPS;
     const int grid = (int)(want < sms ? want : sms);
-    modup_umma_kernel<APAD, F64Q, NG><<<grid, THREADS, smem, st>>>(P);
+    bconv_umma_kernel<APAD, F64Q, NG><<<grid, THREADS, smem, st>>>(P);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
 }
 
 template <int APAD, bool F64Q>
-int launch(ckks_b200_context* c, const ModUpTcArgs& P, cudaStream_t st) {
+int launch(ckks_b200_context* c, const BconvArgs& P, cudaStream_t st) {
     // the accumulator loads run in groups of four targets, so five groups need 8*ceil4(t_num) <= 96
-    if ((P.t_num + 3) / 4 * 32 <= 96) return launch_groups<APAD, F64Q, 5>(c, P, st);
+    if ((P.tg + 3) / 4 * 32 <= 96) return launch_groups<APAD, F64Q, 5>(c, P, st);
     return launch_groups<APAD, F64Q, 4>(c, P, st);
+}
+
+template <bool F64Q>
+int launch_apad(ckks_b200_context* c, const BconvArgs& P, int kpad, cudaStream_t st) {
+    if (kpad == 32) return launch<4, F64Q>(c, P, st);
+    if (kpad == 64) return launch<8, F64Q>(c, P, st);
+    if (kpad == 96) return launch<12, F64Q>(c, P, st);
+    return launch<16, F64Q>(c, P, st);
 }
 
 }  // namespace
@@ -315,37 +337,64 @@ bool modup_tensor_ok(const ckks_b200_context* c, int l) {
 }
 
 int modup_tensor(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int batch, cudaStream_t st) {
-    const int A = c->alpha, B = c->blocks_max, T = c->t_num;
-    ModUpTcArgs P;
+    const int A = c->alpha, B = c->blocks_max, T = c->t_num, AP = c->tc_kpad / 8;
+    BconvArgs P;
     P.out = d_out;
     P.in = d_in;
-    P.q = c->d_moduli + c->p_num;
-    P.t = c->d_moduli + c->p_num + c->q_num;
-    P.t_inv = c->d_t_inv;
-    P.hat_inv = c->mu_hat_inv + (size_t)l * B * A;
-    P.blk_mod_t = c->mu_blk_mod_t + (size_t)l * B * T;
+    P.src_mod = c->mu_src_mod + (size_t)l * B * AP;
+    P.src_hinv = c->mu_src_hinv + (size_t)l * B * AP;
+    P.src_pre = c->mu_src_pre;                          // zeros
+    P.tgt_mod = c->mu_tgt_mod;                          // the t moduli for every block
+    P.tgt_f = c->mu_blk_mod_t + (size_t)l * B * T;
+    P.tgt_post = c->mu_src_pre;                         // zeros
     P.planes = c->mu_planes + (size_t)l * B * c->tc_kpad * c->tc_npad;
     P.flags = c->d_flags;
     P.N = c->N;
-    P.q_num = c->q_num;
-    P.t_num = T;
-    P.alpha = A;
-    P.l = l;
     P.blocks = (l + 1 + A - 1) / A;
     P.batch = batch;
+    P.tg = T;
     P.npad = c->tc_npad;
+    P.tgt_limit = 1 << 30;
+    P.in_batch = (size_t)c->q_num * c->N;
+    P.in_blk = (size_t)A * c->N;
+    P.out_batch = (size_t)P.blocks * T * c->N;
+    P.out_blk = (size_t)T * c->N;
     bool q_small = true;
     for (int i = 0; i < c->q_num; i++) q_small = q_small && c->moduli[c->p_num + i] < (1ull << 50);
-    if (q_small) {
-        if (c->tc_kpad == 32) return launch<4, true>(c, P, st);
-        if (c->tc_kpad == 64) return launch<8, true>(c, P, st);
-        if (c->tc_kpad == 96) return launch<12, true>(c, P, st);
-        return launch<16, true>(c, P, st);
-    }
-    if (c->tc_kpad == 32) return launch<4, false>(c, P, st);
-    if (c->tc_kpad == 64) return launch<8, false>(c, P, st);
-    if (c->tc_kpad == 96) return launch<12, false>(c, P, st);
-    return launch<16, false>(c, P, st);
+    return q_small ? launch_apad<true>(c, P, c->tc_kpad, st) : launch_apad<false>(c, P, c->tc_kpad, st);
+}
+
+bool modup_t_tensor_ok(const ckks_b200_context* c, int gamma) {
+    auto it = c->tpq.find(gamma);
+    return it != c->tpq.end() && it->second.ok && c->N % TM == 0;
+}
+
+// Context_23::modUpTtoPQl_23 on the tensor cores; the tables of this gamma were built by the caller (keyswitch.cu).
+int modup_t_tensor(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int gamma, int batch, cudaStream_t st) {
+    const TpqTables& tb = c->tpq.at(gamma);
+    const int R = (c->p_num + c->q_num + gamma - 1) / gamma;
+    BconvArgs P;
+    P.out = d_out;
+    P.in = d_in;
+    P.src_mod = tb.src_mod;
+    P.src_hinv = tb.src_hinv;
+    P.src_pre = tb.src_pre;
+    P.tgt_mod = tb.tgt_mod;
+    P.tgt_f = tb.tgt_f;
+    P.tgt_post = tb.tgt_post;
+    P.planes = tb.planes;
+    P.flags = c->d_flags;
+    P.N = c->N;
+    P.blocks = (c->p_num + l + 1 + gamma - 1) / gamma;
+    P.batch = batch;
+    P.tg = gamma;
+    P.npad = tb.npad;
+    P.tgt_limit = c->p_num + l + 1;
+    P.in_batch = (size_t)R * c->t_num * c->N;
+    P.in_blk = (size_t)c->t_num * c->N;
+    P.out_batch = P.in_batch;
+    P.out_blk = (size_t)gamma * c->N;
+    return launch_apad<false>(c, P, tb.kpad, st);
 }
 
 }  // namespace ckb

@@ -47,9 +47,12 @@ def test_chain_stages(oracle, cuda_device, logN, p_num, q_num, t_num, gamma, l):
     inp[0, 0, :, 1] = np.array(t, dtype=np.uint64) - np.uint64(1)
     inp[0, 0, :, 2] = KT.half_t[len(p) + len(q):]
     exp = oracle.modup_t_to_pql(inp, N, KT, l, gamma, 2)
-    out = torch.zeros(2 * R * t_num * N, dtype=torch.int64, device=dev)
-    ctx.modUpTtoPQl_23(out, as_u64_tensor(inp, dev), l, 2)
-    assert np.array_equal(to_u64_numpy(out).reshape(2, R * t_num, N), exp)
+    for algo in ("tensor", "simt", "auto"):          # the tcgen05 byte-plane contraction and the 64-bit CUDA-core kernel
+        ctx.set_modup_algo(algo)
+        out = torch.zeros(2 * R * t_num * N, dtype=torch.int64, device=dev)
+        ctx.modUpTtoPQl_23(out, as_u64_tensor(inp, dev), l, 2)
+        ctx.check()
+        assert np.array_equal(to_u64_numpy(out).reshape(2, R * t_num, N), exp), algo
     # ModDown
     pqin = np.zeros((2, R * t_num, N), dtype=np.uint64)
     for c in range(2):

@@ -171,9 +171,12 @@ def test_reference_keyswitch_kernels(oracle, cuda_device, p_num, q_num, t_num, g
     inp = np.stack([H.uniform_residues(rng, t, (N,)) for _ in range(2 * R)]).reshape(2, R, t_num, N)
     ref = R_.keyswitch_stage(1, inp, None, logN, KT, l, gamma)
     assert np.array_equal(oracle.modup_t_to_pql(inp, N, KT, l, gamma, 2).reshape(ref.shape), ref)
-    out = torch.zeros(2 * R * t_num * N, dtype=torch.int64, device=dev)
-    ctx.modUpTtoPQl_23(out, as_u64_tensor(inp, dev), l, 2)
-    assert np.array_equal(to_u64_numpy(out).reshape(ref.shape), ref)
+    for algo in ("tensor", "simt"):
+        ctx.set_modup_algo(algo)
+        out = torch.zeros(2 * R * t_num * N, dtype=torch.int64, device=dev)
+        ctx.modUpTtoPQl_23(out, as_u64_tensor(inp, dev), l, 2)
+        assert np.array_equal(to_u64_numpy(out).reshape(ref.shape), ref), algo
+    ctx.set_modup_algo("auto")
 
     pqin = np.zeros((2, R * t_num, N), dtype=np.uint64)
     for c in range(2):
