@@ -296,6 +296,67 @@ def bench_levels(torch, device, steps, warmup, peaks):
     return res
 
 
+PCMM_SHAPES = {
+    # BASELINE.json configs[3], second weight: 768 features in, 3072 out, same ciphertext set as the headline
+    "pcmm-bert3072": dict(logN=16, N1=128, rank=512, M=3072, K=768, limbs=20, shard=1,
+                          what="bert-base PCMM 3072x768 (W~N(0,0.02) at 2^40), 768 ciphertexts x 20 limbs x 65664 words"),
+    # BASELINE.json configs[4]: one GPU's share (an eighth of the columns, all limbs) of the LLaMA-7B-shaped PCMM
+    "pcmm-llama-shard": dict(logN=16, N1=2048, rank=32, M=4096, K=4096, limbs=24, shard=8,
+                             what="LLaMA-7B PCMM 4096x4096 (W~N(0,0.02) at 2^40), 4096 ciphertexts x 24 limbs x 67584 words, "
+                                  "columns [0, C/8) of every ciphertext: the share of one of 8 GPUs"),
+}
+
+
+def bench_pcmm_shape(torch, device, steps, warmup, peaks, name):
+    """Other PCMM shapes of the named configurations, through the same entry point as the headline."""
+    from ckks_llm_b200 import capi, params
+    from ckks_llm_b200.host import MLWECiphertext, PCMM_Context, PCMM_Scheme
+    c = PCMM_SHAPES[name]
+    N = 1 << c["logN"]
+    q = params.ntt_primes(50, 2 * N, c["limbs"])
+    Cw = (c["rank"] + 1) * c["N1"]
+    g = torch.Generator(device=device).manual_seed(6)
+    X = torch.empty((c["K"], c["limbs"], Cw), dtype=torch.int64, device=device)
+    for i, qi in enumerate(q):
+        X[:, i, :] = torch.randint(0, qi, (c["K"], Cw), generator=g, device=device, dtype=torch.int64)
+    W = torch.randn((c["M"], c["K"]), generator=g, device=device, dtype=torch.float32) * 0.02
+    pc = PCMM_Context(c["N1"], c["rank"], [], q, device=device.index)
+    sch = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR)
+    cts = [MLWECiphertext(c["N1"], c["limbs"] - 1, c["limbs"] - 1, c["rank"], 1.0, cipher=X[n].reshape(-1))
+           for n in range(c["K"])]
+    col_end = (Cw // c["shard"]) // 32 * 32
+
+    def step():
+        return sch.PPMM(W, cts, c["M"], c["K"], c["N1"], c["K"], scaler=float(1 << 40), col_begin=0, col_end=col_end,
+                        copy_back=False)
+
+    for _ in range(warmup):
+        step()
+    sch.check()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    mains, pres = [], []
+    e0.record()
+    for _ in range(steps):
+        step()
+        p_ms, m_ms = sch.last_timing()
+        pres.append(p_ms)
+        mains.append(m_ms)
+    e1.record()
+    torch.cuda.synchronize(device)
+    sch.check()
+    ms = e0.elapsed_time(e1) / steps
+    ops = 2.0 * SW * SC * c["M"] * c["K"] * col_end * c["limbs"]
+    main = float(np.mean(mains))
+    achieved = ops / (main * 1e-3) / 1e12
+    peak = 2.0 * peaks["bf16_tflops"]
+    pc.close()
+    return {"ct_rows_per_sec": c["M"] / (ms * 1e-3), "ms_per_step": ms,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s (int8)", "frac": achieved / peak,
+                         "traffic": None, "kernel": "pcmm_umma_kernel<5,7>", "kernel_ms": main, "prepass_ms": float(np.mean(pres))},
+            "config": {"workload": c["what"], "columns": col_end,
+                       "l2_policy": "ciphertext and output sets of tens of GB, far larger than L2"}}
+
+
 def bench_ringpack(torch, device, steps, warmup, peaks):
     """rlweCipherDecompose and mlweCipherPacking at the BERT geometry the reference runs (N=2^16, N1=128, rank 512,
     two ring-pack limbs, one special prime): device time per call with the bytes each must move."""
@@ -406,7 +467,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", choices=["pcmm", "ntt", "modup", "keyswitch", "ringpack"], default="pcmm")
+    ap.add_argument("--workload", choices=["pcmm", "ntt", "modup", "keyswitch", "ringpack", "pcmm-bert3072", "pcmm-llama-shard"], default="pcmm")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -574,6 +635,12 @@ def main():
             roof = r["forward"]["roofline"]
             extra["ntt"] = r
             metric, unit, cfg = "ntt_limb_xforms_per_sec", "limb-xforms/s", r["config"]
+        elif args.workload in PCMM_SHAPES:
+            r = bench_pcmm_shape(torch, device, args.steps, args.warmup, peaks, args.workload)
+            ms = r["ms_per_step"]
+            value = world * r["ct_rows_per_sec"]
+            roof = r["roofline"]
+            metric, unit, cfg = "pcmm_ct_rows_per_sec", "ct-rows/s", r["config"]
         elif args.workload == "ringpack":
             r = bench_ringpack(torch, device, args.steps, args.warmup, peaks)
             ms = r["mlwe_packing"]["ms_per_call"]
