@@ -304,11 +304,16 @@ PCMM_SHAPES = {
     "pcmm-llama-shard": dict(logN=16, N1=2048, rank=32, M=4096, K=4096, limbs=24, shard=8,
                              what="LLaMA-7B PCMM 4096x4096 (W~N(0,0.02) at 2^40), 4096 ciphertexts x 24 limbs x 67584 words, "
                                   "columns [0, C/8) of every ciphertext: the share of one of 8 GPUs"),
+    # the same column-sharded layout at a size that runs in seconds (512 x 512, four limbs): checks of the N > 1 path
+    "pcmm-shard-mini": dict(logN=16, N1=2048, rank=32, M=512, K=512, limbs=4, shard=8,
+                            what="column-sharded PCMM 512x512, 512 ciphertexts x 4 limbs x 67584 words"),
 }
 
 
-def bench_pcmm_shape(torch, device, steps, warmup, peaks, name):
-    """Other PCMM shapes of the named configurations, through the same entry point as the headline."""
+def bench_pcmm_shape(torch, device, steps, warmup, peaks, name, rank=0, world=1, dist=None):
+    """Other PCMM shapes of the named configurations, through the same entry point as the headline.  A shape with
+    shard > 1 is one PCMM split by column range: on one GPU it runs the share of one of `shard` GPUs, on N > 1 GPUs
+    every rank runs its own range (strong scaling) and the NCCL gather of the output is timed beside it."""
     from ckks_llm_b200 import capi, params
     from ckks_llm_b200.host import MLWECiphertext, PCMM_Context, PCMM_Scheme
     c = PCMM_SHAPES[name]
@@ -324,10 +329,13 @@ def bench_pcmm_shape(torch, device, steps, warmup, peaks, name):
     sch = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR)
     cts = [MLWECiphertext(c["N1"], c["limbs"] - 1, c["limbs"] - 1, c["rank"], 1.0, cipher=X[n].reshape(-1))
            for n in range(c["K"])]
-    col_end = (Cw // c["shard"]) // 32 * 32
+    from ckks_llm_b200 import shard as sharding
+    split = world if (world > 1 and c["shard"] > 1) else c["shard"]
+    ranges = sharding.column_ranges(Cw, split)
+    col_begin, col_end = ranges[rank if world > 1 and c["shard"] > 1 else 0]
 
     def step():
-        return sch.PPMM(W, cts, c["M"], c["K"], c["N1"], c["K"], scaler=float(1 << 40), col_begin=0, col_end=col_end,
+        return sch.PPMM(W, cts, c["M"], c["K"], c["N1"], c["K"], scaler=float(1 << 40), col_begin=col_begin, col_end=col_end,
                         copy_back=False)
 
     for _ in range(warmup):
@@ -345,16 +353,38 @@ def bench_pcmm_shape(torch, device, steps, warmup, peaks, name):
     torch.cuda.synchronize(device)
     sch.check()
     ms = e0.elapsed_time(e1) / steps
-    ops = 2.0 * SW * SC * c["M"] * c["K"] * col_end * c["limbs"]
+    gather_ms = None
+    if world > 1 and c["shard"] > 1:
+        tt = torch.tensor([ms], device=device)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+        out_full = sch.ppmm_output[:c["M"] * c["limbs"] * Cw].view(c["M"], c["limbs"], Cw)
+        sharding.gather_output(out_full, ranges, rows_per_step=256)            # warm-up of the collective
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        sharding.gather_output(out_full, ranges, rows_per_step=256)
+        g1.record()
+        torch.cuda.synchronize(device)
+        tt = torch.tensor([g0.elapsed_time(g1)], device=device)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        gather_ms = float(tt.item())
+    ops = 2.0 * SW * SC * c["M"] * c["K"] * (col_end - col_begin) * c["limbs"]
     main = float(np.mean(mains))
     achieved = ops / (main * 1e-3) / 1e12
     peak = 2.0 * peaks["bf16_tflops"]
     pc.close()
-    return {"ct_rows_per_sec": c["M"] / (ms * 1e-3), "ms_per_step": ms,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s (int8)", "frac": achieved / peak,
-                         "traffic": None, "kernel": "pcmm_umma_kernel<5,7>", "kernel_ms": main, "prepass_ms": float(np.mean(pres))},
-            "config": {"workload": c["what"], "columns": col_end,
-                       "l2_policy": "ciphertext and output sets of tens of GB, far larger than L2"}}
+    res = {"ct_rows_per_sec": c["M"] / (ms * 1e-3), "ms_per_step": ms, "sharded": c["shard"] > 1,
+           "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s (int8)", "frac": achieved / peak,
+                        "traffic": None, "kernel": "pcmm_umma_kernel<5,7>", "kernel_ms": main, "prepass_ms": float(np.mean(pres))},
+           "config": {"workload": c["what"], "columns": [int(col_begin), int(col_end)], "column_split": split,
+                      "l2_policy": "ciphertext and output sets of tens of GB, far larger than L2"}}
+    if gather_ms is not None:
+        res["gather"] = {"ms": gather_ms, "bytes_received_per_rank": int(c["M"] * c["limbs"] * (Cw - (col_end - col_begin)) * 8),
+                         "ct_rows_per_sec_with_gather": c["M"] / ((ms + gather_ms) * 1e-3),
+                         "note": "NCCL all-gather of the output column ranges, after the multiply, not overlapped"}
+    return res
 
 
 def bench_ringpack(torch, device, steps, warmup, peaks):
@@ -467,7 +497,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", choices=["pcmm", "ntt", "modup", "keyswitch", "ringpack", "pcmm-bert3072", "pcmm-llama-shard"], default="pcmm")
+    ap.add_argument("--workload", choices=["pcmm", "ntt", "modup", "keyswitch", "ringpack", "pcmm-bert3072", "pcmm-llama-shard", "pcmm-shard-mini"], default="pcmm")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -636,10 +666,14 @@ def main():
             extra["ntt"] = r
             metric, unit, cfg = "ntt_limb_xforms_per_sec", "limb-xforms/s", r["config"]
         elif args.workload in PCMM_SHAPES:
-            r = bench_pcmm_shape(torch, device, args.steps, args.warmup, peaks, args.workload)
+            r = bench_pcmm_shape(torch, device, args.steps, args.warmup, peaks, args.workload, rank, world,
+                                 dist if world > 1 else None)
             ms = r["ms_per_step"]
-            value = world * r["ct_rows_per_sec"]
+            # a column-sharded multiply is one job split over the ranks; independent replicas otherwise
+            value = r["ct_rows_per_sec"] if r["sharded"] else world * r["ct_rows_per_sec"]
             roof = r["roofline"]
+            if "gather" in r:
+                extra["gather"] = r["gather"]
             metric, unit, cfg = "pcmm_ct_rows_per_sec", "ct-rows/s", r["config"]
         elif args.workload == "ringpack":
             r = bench_ringpack(torch, device, args.steps, args.warmup, peaks)
@@ -667,7 +701,8 @@ def main():
 
     if rank == 0:
         line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "strong" if (args.workload in PCMM_SHAPES and PCMM_SHAPES[args.workload]["shard"] > 1 and world > 1) else "weak",
                 "vs_baseline": None, "dtype": "u64 (int8 planes on tensor cores, s32 accumulate)" if args.workload == "pcmm" else "u64",
                 "data": "synthetic", "config": dict(cfg, small=True) if args.small else cfg, "roofline": roof, "clocks": clocks,
                 "gpu_launches": launches_timed if launches_timed is not None else int(capi.load().ckks_b200_kernel_launches() - launches0),

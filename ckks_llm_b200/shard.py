@@ -36,22 +36,27 @@ def unit_ranges(count, world):
     return out
 
 
-def gather_output(out_full, ranges, group=None):
+def gather_output(out_full, ranges, group=None, rows_per_step=None):
     """All-gather the column ranges of a PCMM output.
 
     out_full: [M][limbs][C] tensor on every rank in which only this rank's columns
     (ranges[rank]) are valid.  On return every rank holds all columns.  Ranges may be ragged:
-    slices are padded to the widest one for the collective."""
+    slices are padded to the widest one for the collective.  rows_per_step bounds the staging
+    memory: the rows are gathered that many at a time (default: all at once)."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     wmax = max(c1 - c0 for c0, c1 in ranges)
     M, limbs, _ = out_full.shape
-    mine = torch.zeros((M, limbs, wmax), dtype=out_full.dtype, device=out_full.device)
+    step = M if not rows_per_step else max(1, min(M, int(rows_per_step)))
     c0, c1 = ranges[rank]
-    mine[:, :, :c1 - c0] = out_full[:, :, c0:c1]
-    parts = [torch.empty_like(mine) for _ in range(world)]
-    dist.all_gather(parts, mine, group=group)
-    for r, (a, b) in enumerate(ranges):
-        if r != rank and b > a:
-            out_full[:, :, a:b] = parts[r][:, :, :b - a]
+    mine = torch.zeros((step, limbs, wmax), dtype=out_full.dtype, device=out_full.device)
+    parts = torch.empty((world * step, limbs, wmax), dtype=out_full.dtype, device=out_full.device)   # rank r at rows r*step..
+    for m0 in range(0, M, step):
+        m1 = min(M, m0 + step)
+        n = m1 - m0
+        mine[:n, :, :c1 - c0] = out_full[m0:m1, :, c0:c1]
+        dist.all_gather_into_tensor(parts, mine, group=group)
+        for r, (a, b) in enumerate(ranges):
+            if r != rank and b > a:
+                out_full[m0:m1, :, a:b] = parts[r * step:r * step + n, :, :b - a]
     return out_full
