@@ -370,6 +370,41 @@ def bench_pcmm_shape(torch, device, steps, warmup, peaks, name, rank=0, world=1,
         tt = torch.tensor([g0.elapsed_time(g1)], device=device)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         gather_ms = float(tt.item())
+    fused = None
+    if world > 1 and c["shard"] > 1:
+        # Fused form: the multiply's epilogue stores every output word into the peers' buffers as well (plain peer
+        # stores over NVLink), so after one launch per rank and a host barrier every rank holds the whole output.
+        def checksums(t):
+            flat = t.view(-1)
+            return int(flat.sum().item()), int(flat[::4099].sum().item())
+        want = checksums(out_full)                       # the NCCL-gathered output
+        peers, bases = sharding.open_peer_buffers(sch.ppmm_output)
+        pc.set_peer_outputs([peers[r] for r in sorted(peers)])
+        out_full.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        for _ in range(2):
+            step()
+        sch.check()
+        dist.barrier()
+        got = checksums(out_full)
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(steps):
+            step()
+        f1.record()
+        torch.cuda.synchronize(device)
+        sch.check()
+        tt = torch.tensor([f0.elapsed_time(f1) / steps], device=device)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        okt = torch.tensor([1 if got == want else 0], device=device)
+        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+        fused = {"ms": float(tt.item()), "ct_rows_per_sec": c["M"] / (float(tt.item()) * 1e-3),
+                 "matches_nccl_gather": bool(okt.item()),
+                 "note": "one launch per rank: every output word is stored locally and into the 7 peers' buffers by the epilogue"}
+        pc.set_peer_outputs([])
+        dist.barrier()
+        sharding.close_peer_buffers(device.index, bases)
     ops = 2.0 * SW * SC * c["M"] * c["K"] * (col_end - col_begin) * c["limbs"]
     main = float(np.mean(mains))
     achieved = ops / (main * 1e-3) / 1e12
@@ -384,6 +419,7 @@ def bench_pcmm_shape(torch, device, steps, warmup, peaks, name, rank=0, world=1,
         res["gather"] = {"ms": gather_ms, "bytes_received_per_rank": int(c["M"] * c["limbs"] * (Cw - (col_end - col_begin)) * 8),
                          "ct_rows_per_sec_with_gather": c["M"] / ((ms + gather_ms) * 1e-3),
                          "note": "NCCL all-gather of the output column ranges, after the multiply, not overlapped"}
+        res["gather"]["fused_peer_stores"] = fused
     return res
 
 

@@ -2,6 +2,8 @@
 // multiply, and the host-buffer wrapper.  The tensor-core multiply lives in
 // pcmm_umma.cu.  Semantics follow PCMM_Scheme::PPMM and pcmm_cuda_core_kernel of the
 // reference (src/ckks/include/pcmm/PPMM_kernel.cuh:93-349).
+#include <cstring>
+
 #include "pcmm.cuh"
 
 using namespace ckb;
@@ -200,6 +202,36 @@ extern "C" int ckks_b200_pcmm_destroy(ckks_b200_pcmm* pc) {
     return CKKS_B200_OK;
 }
 
+// Opens a CUDA IPC memory handle exported by another process (another rank's cudaIpcGetMemHandle) for use from
+// `device`: the mapping is made with that device current and with lazy peer access, which is what lets kernels
+// running on it store into the other GPU's memory.
+extern "C" int ckks_b200_ipc_open(int device, const void* handle, void** d_base) {
+    CKB_REQUIRE(handle != nullptr && d_base != nullptr, CKKS_B200_ERR_ARG, "null argument");
+    DeviceGuard guard(device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    CKB_CUDA(cudaIpcOpenMemHandle(d_base, h, cudaIpcMemLazyEnablePeerAccess));
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_ipc_close(int device, void* d_base) {
+    CKB_REQUIRE(d_base != nullptr, CKKS_B200_ERR_ARG, "null argument");
+    DeviceGuard guard(device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", device);
+    CKB_CUDA(cudaIpcCloseMemHandle(d_base));
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_pcmm_set_peer_outputs(ckks_b200_pcmm* pc, uint64_t* const* d_peer_out, int count) {
+    CKB_REQUIRE(pc != nullptr && count >= 0 && count <= 7, CKKS_B200_ERR_ARG, "null handle or peer count outside [0,7]");
+    CKB_REQUIRE(count == 0 || d_peer_out != nullptr, CKKS_B200_ERR_ARG, "null pointer table");
+    for (int i = 0; i < count; i++) CKB_REQUIRE(d_peer_out[i] != nullptr, CKKS_B200_ERR_ARG, "peer pointer %d is null", i);
+    for (int i = 0; i < 7; i++) pc->peer_out[i] = i < count ? (u64*)d_peer_out[i] : nullptr;
+    pc->n_peers = count;
+    return CKKS_B200_OK;
+}
+
 extern "C" int ckks_b200_pcmm_ppmm(ckks_b200_pcmm* pc, const float* d_W,
                                    const uint64_t* const* h_X_ptrs, uint64_t* d_out, int mat_M,
                                    int mat_N, int mat_K, int mlwe_num, double scaler,
@@ -224,6 +256,7 @@ extern "C" int ckks_b200_pcmm_ppmm(ckks_b200_pcmm* pc, const float* d_W,
     int rc = prepare(pc, d_W, (const u64* const*)h_X_ptrs, mat_M, mat_N, scaler, st, &w_bits);
     if (rc) return rc;
     if (algo == CKKS_B200_PCMM_SIMT) {
+        CKB_REQUIRE(pc->n_peers == 0, CKKS_B200_ERR_UNSUPPORTED, "peer outputs are written by the tensor-core kernel only");
         dim3 grid((unsigned)((col_end - col_begin + TS - 1) / TS), (mat_M + TS - 1) / TS);
         pcmm_simt_kernel<<<grid, 256, 0, st>>>(pc->d_w, pc->d_xptrs, (u64*)d_out, pc->d_limbs, mat_M,
                                                mat_N, pc->C, pc->q_count, col_begin, col_end);

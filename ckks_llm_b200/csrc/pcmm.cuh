@@ -24,6 +24,8 @@ struct ckks_b200_pcmm {
     size_t w_cap = 0;
     const u64** d_xptrs = nullptr;    // device copy of the ciphertext pointer table
     size_t xptrs_cap = 0;
+    u64* peer_out[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // see ckks_b200_pcmm_set_peer_outputs
+    int n_peers = 0;
     int* d_flags = nullptr;           // [0] max |w| bits seen, [1] device-side wait timeout, ...
     int* h_flags = nullptr;           // pinned mirror
 

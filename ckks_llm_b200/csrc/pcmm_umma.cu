@@ -64,6 +64,8 @@ struct UmmaArgs {
     const uint8_t* wplanes;    // [mt][kb][a][ks][4096]
     const uint8_t* xplanes;    // [limb][ct][kb][ks][b][1024]
     u64* out;                  // [M][limbs][C]
+    u64* peers[7];             // output buffers of the same shape on other GPUs that also receive every word written
+    int n_peers;
     const PcmmLimb* limbs;
     int* flags;
     int M, limbs_n;
@@ -309,7 +311,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
         const int half = ew >> 2;              // which 16 of the 32 columns
         uint8_t* stg = smem + (size_t)NS * C_::STAGE + (size_t)ew * STG_WARP;
         u64 last[16];
-        const bool vec_ok = (P.C & 1) == 0 && (reinterpret_cast<uintptr_t>(P.out) & 15) == 0;   // 16-byte stores stay aligned
+        bool vec_ok = (P.C & 1) == 0 && (reinterpret_cast<uintptr_t>(P.out) & 15) == 0;   // 16-byte stores stay aligned
+        for (int dest = 0; dest < P.n_peers; dest++) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(P.peers[dest]) & 15) == 0;
         uint32_t tile = 0;
         bool ok = true;
         CKB_PROF_DECL
@@ -387,12 +390,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                     const int mm = mt * TM + quarter * 32 + r;
                     const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(stg + r * STG_ROW + pair * 16);
                     if (mm < P.M) {
-                        u64* dst = P.out + ((size_t)mm * limbs_n + limb) * P.C + c;
-                        if (vec_ok && c + 1 < P.col_end) {
-                            *reinterpret_cast<ulonglong2*>(dst) = v;
-                        } else {
-                            if (c < P.col_end) dst[0] = v.x;
-                            if (c + 1 < P.col_end) dst[1] = v.y;
+                        const size_t off = ((size_t)mm * limbs_n + limb) * P.C + c;
+                        // the local output, then the same words into every peer's output buffer (plain
+                        // peer stores over NVLink): the gather of a column-sharded multiply rides on the epilogue
+                        for (int dest = -1; dest < P.n_peers; dest++) {
+                            u64* dst = (dest < 0 ? P.out : P.peers[dest]) + off;
+                            if (vec_ok && c + 1 < P.col_end) {
+                                *reinterpret_cast<ulonglong2*>(dst) = v;
+                            } else {
+                                if (c < P.col_end) dst[0] = v.x;
+                                if (c + 1 < P.col_end) dst[1] = v.y;
+                            }
                         }
                     }
                 }
@@ -444,6 +452,8 @@ int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, 
     P.wplanes = pc->d_wplanes;
     P.xplanes = pc->d_xplanes;
     P.out = d_out;
+    P.n_peers = pc->n_peers;
+    for (int i = 0; i < 7; i++) P.peers[i] = i < pc->n_peers ? pc->peer_out[i] : nullptr;
     P.limbs = pc->d_limbs;
     P.flags = pc->d_flags;
     P.M = M;

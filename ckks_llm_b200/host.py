@@ -231,6 +231,12 @@ class PCMM_Context:
             C.byref(self._h), device, self.N1, self.mlwe_rank, capi.u64_array(self.q_ringpack),
             self.ringpack_q_count))
 
+    def set_peer_outputs(self, peer_pointers):
+        """Device addresses, valid on this GPU, of the other GPUs' output buffers (same layout as the local output)
+        that every tensor-core multiply from now on also writes; an empty list switches it off."""
+        ptrs = (C.c_void_p * max(len(peer_pointers), 1))(*[int(p) for p in peer_pointers])
+        capi.check(self.lib.ckks_b200_pcmm_set_peer_outputs(self._h, ptrs, len(peer_pointers)))
+
     def close(self):
         if self._h:
             self.lib.ckks_b200_pcmm_destroy(self._h)

@@ -60,3 +60,45 @@ def gather_output(out_full, ranges, group=None, rows_per_step=None):
             if r != rank and b > a:
                 out_full[m0:m1, :, a:b] = parts[r * step:r * step + n, :, :b - a]
     return out_full
+
+
+def open_peer_buffers(t, group=None):
+    """Maps the other ranks' copies of a CUDA tensor into this process for kernels on this rank's GPU.
+
+    Every rank passes its own tensor `t` (same shape everywhere).  The ranks exchange the CUDA IPC handles of the
+    allocations behind their tensors and each opens the others' with its own GPU current.  Returns
+    ({rank: device address of that rank's tensor}, [base addresses to hand to close_peer_buffers]).  The owners must
+    keep their tensors alive for as long as anybody uses the mappings."""
+    import ctypes as C
+    from . import capi
+    lib = capi.load()
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    info = t.untyped_storage()._share_cuda_()          # (device, handle bytes, size, offset of the storage in its allocation, ...)
+    handle = bytes(info[1])
+    if len(handle) == 66:                              # torch prefixes the 64-byte handle with a version and a kind byte
+        if handle[1:2] == b"e":
+            raise RuntimeError("the tensor's memory is an expandable segment, not a cudaMalloc block: no IPC memory handle")
+        handle = handle[2:]
+    if len(handle) != 64:
+        raise RuntimeError(f"unexpected CUDA IPC handle length {len(handle)}")
+    meta = (handle, int(info[3]) + t.storage_offset() * t.element_size())
+    metas = [None] * world
+    dist.all_gather_object(metas, meta, group=group)
+    addrs, bases = {}, []
+    for r in range(world):
+        if r == rank:
+            continue
+        handle, offset = metas[r]
+        base = C.c_void_p()
+        capi.check(lib.ckks_b200_ipc_open(t.device.index, handle, C.byref(base)))
+        bases.append(base.value)
+        addrs[r] = base.value + offset
+    return addrs, bases
+
+
+def close_peer_buffers(device_index, bases):
+    from . import capi
+    lib = capi.load()
+    for b in bases:
+        capi.check(lib.ckks_b200_ipc_close(device_index, b))

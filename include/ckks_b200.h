@@ -219,6 +219,20 @@ int ckks_b200_pcmm_copy_back(ckks_b200_pcmm* pc, const uint64_t* d_out,
  * of a tensor-core multiply on this handle gave up since the last check (no reference
  * counterpart: the reference never checks a CUDA status). */
 int ckks_b200_pcmm_check(ckks_b200_pcmm* pc, void* stream);
+/* No counterpart in the reference (which runs on one GPU).  For a multiply split by column range over several
+ * GPUs whose consumer wants the whole output on every GPU: d_peer_out holds up to 7 device pointers, valid on
+ * this GPU, to the OTHER GPUs' output buffers (same [M][limbs][C] layout; peer mappings, e.g. opened CUDA IPC
+ * handles).  From the next tensor-core multiply on, every word the kernel stores to d_out it also stores, at the
+ * same offset, into each of them (plain peer stores over NVLink from the epilogue), so the gather costs no
+ * separate pass.  The words are in place on the peers once this GPU's stream has been synchronised; the ranks
+ * then meet on the host.  count = 0 switches it off.  The CUDA-core algorithm does not support it. */
+int ckks_b200_pcmm_set_peer_outputs(ckks_b200_pcmm* pc, uint64_t* const* d_peer_out, int count);
+/* Helpers for the pointers above when the other GPUs belong to other processes: ckks_b200_ipc_open maps the
+ * allocation behind a 64-byte CUDA IPC memory handle (cudaIpcGetMemHandle in the owning process) for use by
+ * kernels on `device` (cudaIpcOpenMemHandle with lazy peer access, `device` current) and returns its base
+ * address; ckks_b200_ipc_close unmaps it. */
+int ckks_b200_ipc_open(int device, const void* handle, void** d_base);
+int ckks_b200_ipc_close(int device, void* d_base);
 /* Device time in milliseconds of the latest tensor-core multiply on this handle, split
  * into its slicing pre-pass and its main kernel; waits for them.  Stands in for the
  * CUDATimer the reference wraps around its kernel (PPMM_kernel.cuh:301-343). */
