@@ -160,7 +160,8 @@ __global__ void slice_cipher_kernel(const u64* const* __restrict__ X, uint8_t* _
 // ---------------------------------------------------------------------------
 // Main kernel
 // ---------------------------------------------------------------------------
-template <int SW, int SC>
+// PEERS: every stored word also goes into the other GPUs' output buffers listed in P.peers.
+template <int SW, int SC, bool PEERS>
 __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
     using C_ = Cfg<SW, SC>;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -312,7 +313,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
         uint8_t* stg = smem + (size_t)NS * C_::STAGE + (size_t)ew * STG_WARP;
         u64 last[16];
         bool vec_ok = (P.C & 1) == 0 && (reinterpret_cast<uintptr_t>(P.out) & 15) == 0;   // 16-byte stores stay aligned
-        for (int dest = 0; dest < P.n_peers; dest++) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(P.peers[dest]) & 15) == 0;
+        if (PEERS)
+            for (int dest = 0; dest < P.n_peers; dest++) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(P.peers[dest]) & 15) == 0;
         uint32_t tile = 0;
         bool ok = true;
         CKB_PROF_DECL
@@ -393,7 +395,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                         const size_t off = ((size_t)mm * limbs_n + limb) * P.C + c;
                         // the local output, then the same words into every peer's output buffer (plain
                         // peer stores over NVLink): the gather of a column-sharded multiply rides on the epilogue
-                        for (int dest = -1; dest < P.n_peers; dest++) {
+                        for (int dest = -1; dest < (PEERS ? P.n_peers : 0); dest++) {
                             u64* dst = (dest < 0 ? P.out : P.peers[dest]) + off;
                             if (vec_ok && c + 1 < P.col_end) {
                                 *reinterpret_cast<ulonglong2*>(dst) = v;
@@ -466,11 +468,13 @@ int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, 
     P.KBN = KBN;
     P.num_stages = C_::MAX_STAGES;
     const size_t smem = (size_t)C_::MAX_STAGES * C_::STAGE + STG_BYTES;
-    CKB_CUDA(cudaFuncSetAttribute(pcmm_umma_kernel<SW, SC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CKB_CUDA(cudaFuncSetAttribute(pcmm_umma_kernel<SW, SC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CKB_CUDA(cudaFuncSetAttribute(pcmm_umma_kernel<SW, SC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     long items = (long)MT * CT;
     int grid = (int)(items < sms ? items : sms);
     CKB_CUDA(cudaEventRecord(pc->ev[1], st));
-    pcmm_umma_kernel<SW, SC><<<grid, NUM_THREADS, smem, st>>>(P);
+    if (pc->n_peers > 0) pcmm_umma_kernel<SW, SC, true><<<grid, NUM_THREADS, smem, st>>>(P);
+    else pcmm_umma_kernel<SW, SC, false><<<grid, NUM_THREADS, smem, st>>>(P);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     CKB_CUDA(cudaEventRecord(pc->ev[2], st));

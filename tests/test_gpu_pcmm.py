@@ -167,6 +167,37 @@ def test_column_range(oracle, cuda_device):
         pc.close()
 
 
+def test_peer_output_buffers_receive_the_same_words(oracle, cuda_device):
+    """The epilogue's extra stores into other GPUs' output buffers, exercised with two more buffers on this GPU:
+    each must end up with exactly the words of the local output, inside the column range only."""
+    q = params.ntt_primes(50, 1 << 13, 3)
+    N1, rank, M, K = 64, 3, 160, 96              # M spans two 128-row tiles, the second one ragged
+    Cw = (rank + 1) * N1
+    rng = np.random.default_rng(12)
+    W = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    pc = PCMM_Context(N1, rank, [], q)
+    sch = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR)
+    X, cts = _ciphers(np.random.default_rng(12), q, K, N1, rank, pc.device)
+    peers = [torch.full((M * len(q) * Cw,), -1, dtype=torch.int64, device=pc.device) for _ in range(2)]
+    pc.set_peer_outputs([t.data_ptr() for t in peers])
+    sch.ppmm_output = torch.full((M * len(q) * Cw,), -1, dtype=torch.int64, device=pc.device)
+    out = sch.PPMM(torch.from_numpy(W).to(pc.device), cts, M, K, N1, K, scaler=float(1 << 30), col_begin=32, col_end=224,
+                   copy_back=False)
+    sch.check()
+    got = to_u64_numpy(out)
+    exp = oracle.ppmm(W, X, q, float(1 << 30))
+    assert np.array_equal(got[:, :, 32:224], exp[:, :, 32:224])
+    for t in peers:
+        assert torch.equal(t, sch.ppmm_output)
+    # the CUDA-core algorithm does not write peers and says so
+    sch.algo = capi.PCMM_SIMT
+    with pytest.raises(capi.CkksB200Error):
+        sch.PPMM(torch.from_numpy(W).to(pc.device), cts, M, K, N1, K, scaler=float(1 << 30), copy_back=False)
+    pc.set_peer_outputs([])
+    sch.PPMM(torch.from_numpy(W).to(pc.device), cts, M, K, N1, K, scaler=float(1 << 30), copy_back=False)
+    pc.close()
+
+
 def test_shape_rules_and_errors(cuda_device, capsys):
     q = params.ntt_primes(50, 1 << 13, 2)
     pc = PCMM_Context(64, 3, [], q)
