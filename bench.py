@@ -30,10 +30,10 @@ NTT_CFG = dict(logN=16, limbs=40, q_bits=50, polys=32)
 MODUP_CFG = dict(logN=16, q_num=24, q_bits=50, t_num=12, t_bits=60, alpha=8, batch=32)
 SW, SC = 5, 7          # byte planes the PCMM workload needs: 40-bit signed weights, 50-bit residues
 # DRAM traffic (bytes) from the ncu captures summarised under profiles/, per unit of work
-PCMM_TRAFFIC_PER_LIMB = (709.07e6 + 767.26e6) / 2                    # pcmm_umma_kernel<5,7>, 768x768, per limb
+PCMM_TRAFFIC_PER_LIMB = (709.12e6 + 766.83e6) / 2                    # pcmm_umma_kernel<5,7,false>, 768x768, per limb
 NTT_TRAFFIC_PER_XFORM = {"forward": (167.90e6 + 113.26e6 + 196.91e6 + 112.88e6) / 320,
                          "inverse": (202.12e6 + 113.41e6 + 167.91e6 + 108.10e6) / 320}
-MODUP_TRAFFIC_PER_POLY = (100.73e6 + 95.66e6) / 8
+MODUP_TRAFFIC_PER_POLY = (100.74e6 + 96.33e6) / 8
 
 
 def measured_peaks():
