@@ -537,6 +537,7 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--host-chunks", type=int, default=0, help="column chunks of the host-buffer call (0 = the library's choice)")
     ap.add_argument("--no-side", action="store_true", help="skip the NTT / ModUp side measurements")
     ap.add_argument("--small", action="store_true",
                     help="profiling-sized case: PCMM with 2 limbs, NTT with 8 polys, ModUp batch 8 (not a bench value)")
@@ -656,6 +657,8 @@ def main():
             sch.ppmm_output = None
             torch.cuda.empty_cache()
             L = capi.load()
+            if args.host_chunks:
+                pc.set_host_chunks(args.host_chunks)
 
             def host_step():
                 capi.check(L.ckks_b200_pcmm_ppmm_host(pc._h, Wh.data_ptr(), Xh.data_ptr(), outh.data_ptr(), c["M"], c["K"],

@@ -24,7 +24,7 @@ SYMBOLS = [
     "ckks_b200_moddown_pql_to_ql", "ckks_b200_keyswitch", "ckks_b200_mult",
     "ckks_b200_rlwe_decompose", "ckks_b200_mlwe_packing",
     "ckks_b200_pcmm_create", "ckks_b200_pcmm_destroy", "ckks_b200_pcmm_ppmm",
-    "ckks_b200_pcmm_ppmm_host", "ckks_b200_pcmm_copy_back", "ckks_b200_pcmm_check", "ckks_b200_pcmm_set_peer_outputs", "ckks_b200_ipc_open", "ckks_b200_ipc_close", "ckks_b200_pcmm_last_timing", "ckks_b200_pcmm_ppmm_static",
+    "ckks_b200_pcmm_ppmm_host", "ckks_b200_pcmm_copy_back", "ckks_b200_pcmm_check", "ckks_b200_pcmm_set_peer_outputs", "ckks_b200_pcmm_set_host_chunks", "ckks_b200_ipc_open", "ckks_b200_ipc_close", "ckks_b200_pcmm_last_timing", "ckks_b200_pcmm_ppmm_static",
     "ckks_b200_kernel_launches",
 ]
 
@@ -73,6 +73,7 @@ def load():
     L.ckks_b200_modup_t_to_pql.argtypes = [vp, vp, vp, i, i, i, vp]
     L.ckks_b200_moddown_pql_to_ql.argtypes = [vp, vp, vp, i, i, i, vp]
     L.ckks_b200_pcmm_set_peer_outputs.argtypes = [vp, vp, i]
+    L.ckks_b200_pcmm_set_host_chunks.argtypes = [vp, i]
     L.ckks_b200_ipc_open.argtypes = [i, C.c_char_p, C.POINTER(C.c_void_p)]
     L.ckks_b200_ipc_close.argtypes = [i, vp]
     L.ckks_b200_keyswitch.argtypes = [vp, vp, vp, vp, i, i, vp]

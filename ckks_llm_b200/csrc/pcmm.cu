@@ -268,6 +268,13 @@ extern "C" int ckks_b200_pcmm_ppmm(ckks_b200_pcmm* pc, const float* d_W,
                        w_bits, st);
 }
 
+extern "C" int ckks_b200_pcmm_set_host_chunks(ckks_b200_pcmm* pc, int chunks) {
+    CKB_REQUIRE(pc, CKKS_B200_ERR_ARG, "null handle");
+    CKB_REQUIRE(chunks >= 0 && chunks <= 256, CKKS_B200_ERR_ARG, "chunk count %d outside [0,256]", chunks);
+    pc->host_chunks = chunks;
+    return CKKS_B200_OK;
+}
+
 extern "C" int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, const uint64_t* h_X,
                                         uint64_t* h_out, int mat_M, int mat_N, int mat_K,
                                         int mlwe_num, double scaler, int algo) {
@@ -289,7 +296,7 @@ extern "C" int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, co
     cudaStream_t s_in = pc->hs[0], s_mm = pc->hs[1], s_out = pc->hs[2];
     const long tiles = (pc->C + 31) / 32;
     const size_t total_bytes = 8 * ct_words * ((size_t)mlwe_num + mat_M);
-    int nchunk = total_bytes > ((size_t)256 << 20) ? 8 : 1;
+    int nchunk = pc->host_chunks > 0 ? pc->host_chunks : total_bytes > ((size_t)256 << 20) ? 16 : 1;
     if (nchunk > tiles) nchunk = (int)tiles;
     while ((int)pc->hev.size() < 2 * nchunk) {
         cudaEvent_t e;

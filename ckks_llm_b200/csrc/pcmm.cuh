@@ -42,6 +42,7 @@ struct ckks_b200_pcmm {
     // streams and events of the pipelined *_host entry point
     cudaStream_t hs[3] = {nullptr, nullptr, nullptr};
     std::vector<cudaEvent_t> hev;
+    int host_chunks = 0;   // column chunks of the host-buffer call; 0 = chosen from the size
 
     // staging for the *_host entry point
     float* d_W_host = nullptr;

@@ -237,6 +237,10 @@ class PCMM_Context:
         ptrs = (C.c_void_p * max(len(peer_pointers), 1))(*[int(p) for p in peer_pointers])
         capi.check(self.lib.ckks_b200_pcmm_set_peer_outputs(self._h, ptrs, len(peer_pointers)))
 
+    def set_host_chunks(self, chunks):
+        """Number of column chunks the host-buffer multiply pipelines through its copy and compute streams (0 = automatic)."""
+        capi.check(self.lib.ckks_b200_pcmm_set_host_chunks(self._h, int(chunks)))
+
     def close(self):
         if self._h:
             self.lib.ckks_b200_pcmm_destroy(self._h)

@@ -207,7 +207,11 @@ int ckks_b200_pcmm_ppmm(ckks_b200_pcmm* pc, const float* d_W, const uint64_t* co
                         uint64_t* d_out, int mat_M, int mat_N, int mat_K, int mlwe_num,
                         double scaler, long col_begin, long col_end, int algo, void* stream);
 /* Host-buffer form: h_W fp32 [M][N], h_X contiguous [mlwe_num][q_count][(k+1)*N1],
- * h_out [M][q_count][(k+1)*N1]; copies in, multiplies, copies out, synchronises. */
+ * h_out [M][q_count][(k+1)*N1]; copies in, multiplies, copies out, synchronises.
+ * The columns are cut into chunks that move through copy-in, multiply and copy-out
+ * streams as a pipeline; ckks_b200_pcmm_set_host_chunks fixes their number (0 = chosen
+ * from the size of the call). */
+int ckks_b200_pcmm_set_host_chunks(ckks_b200_pcmm* pc, int chunks);
 int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, const uint64_t* h_X,
                              uint64_t* h_out, int mat_M, int mat_N, int mat_K, int mlwe_num,
                              double scaler, int algo);
