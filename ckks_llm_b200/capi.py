@@ -24,9 +24,14 @@ SYMBOLS = [
     "ckks_b200_moddown_pql_to_ql", "ckks_b200_keyswitch", "ckks_b200_mult",
     "ckks_b200_rlwe_decompose", "ckks_b200_mlwe_packing",
     "ckks_b200_pcmm_create", "ckks_b200_pcmm_destroy", "ckks_b200_pcmm_ppmm",
-    "ckks_b200_pcmm_ppmm_host", "ckks_b200_pcmm_copy_back", "ckks_b200_pcmm_check", "ckks_b200_pcmm_set_peer_outputs", "ckks_b200_pcmm_set_host_chunks", "ckks_b200_ipc_open", "ckks_b200_ipc_close", "ckks_b200_pcmm_last_timing", "ckks_b200_pcmm_ppmm_static",
+    "ckks_b200_pcmm_ppmm_host", "ckks_b200_pcmm_ppmm_rlwe", "ckks_b200_pcmm_copy_back", "ckks_b200_pcmm_check", "ckks_b200_pcmm_set_peer_outputs", "ckks_b200_pcmm_set_host_chunks", "ckks_b200_ipc_open", "ckks_b200_ipc_close", "ckks_b200_pcmm_last_timing", "ckks_b200_pcmm_ppmm_static",
     "ckks_b200_kernel_launches",
 ]
+
+
+class RlweSource(C.Structure):
+    """ckks_b200_rlwe_source of include/ckks_b200.h."""
+    _fields_ = [("d_rlwe", C.c_void_p), ("L", C.c_int), ("mlwe_num", C.c_int), ("offset", C.c_int)]
 
 
 class CkksB200Error(RuntimeError):
@@ -84,6 +89,7 @@ def load():
     L.ckks_b200_pcmm_create.argtypes = [C.POINTER(vp), i, i, i, u64p, i]
     L.ckks_b200_pcmm_destroy.argtypes = [vp]
     L.ckks_b200_pcmm_ppmm.argtypes = [vp, vp, C.POINTER(vp), vp, i, i, i, i, dbl, lng, lng, i, vp]
+    L.ckks_b200_pcmm_ppmm_rlwe.argtypes = [vp, vp, C.POINTER(RlweSource), i, vp, i, i, i, i, dbl, lng, lng, vp]
     L.ckks_b200_pcmm_ppmm_host.argtypes = [vp, vp, vp, vp, i, i, i, i, dbl, i]
     L.ckks_b200_pcmm_copy_back.argtypes = [vp, vp, C.POINTER(vp), i, i, vp]
     L.ckks_b200_pcmm_check.argtypes = [vp, vp]

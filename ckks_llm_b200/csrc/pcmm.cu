@@ -109,9 +109,11 @@ int prepare(ckks_b200_pcmm* pc, const float* d_W, const u64* const* h_X_ptrs, in
             double scaler, cudaStream_t st, int* w_bits) {
     int rc = ensure_dev(&pc->d_w, &pc->w_cap, (size_t)M * K);
     if (rc) return rc;
-    rc = ensure_dev(&pc->d_xptrs, &pc->xptrs_cap, (size_t)K);
-    if (rc) return rc;
-    CKB_CUDA(cudaMemcpyAsync((void*)pc->d_xptrs, h_X_ptrs, sizeof(u64*) * K, cudaMemcpyHostToDevice, st));
+    if (h_X_ptrs) {
+        rc = ensure_dev(&pc->d_xptrs, &pc->xptrs_cap, (size_t)K);
+        if (rc) return rc;
+        CKB_CUDA(cudaMemcpyAsync((void*)pc->d_xptrs, h_X_ptrs, sizeof(u64*) * K, cudaMemcpyHostToDevice, st));
+    }
     CKB_CUDA(cudaMemsetAsync(pc->d_flags, 0, 16 * sizeof(int), st));
     size_t count = (size_t)M * K;
     scale_weights_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(d_W, pc->d_w, count, scaler, pc->d_flags);
@@ -191,7 +193,7 @@ extern "C" int ckks_b200_pcmm_create(ckks_b200_pcmm** out, int device, int N1, i
 extern "C" int ckks_b200_pcmm_destroy(ckks_b200_pcmm* pc) {
     if (!pc) return CKKS_B200_OK;
     DeviceGuard guard(pc->device);
-    cudaFree(pc->d_limbs); cudaFree(pc->d_w); cudaFree((void*)pc->d_xptrs); cudaFree(pc->d_flags);
+    cudaFree(pc->d_limbs); cudaFree(pc->d_w); cudaFree((void*)pc->d_xptrs); cudaFree(pc->d_slots); cudaFree(pc->d_flags);
     if (pc->h_flags) cudaFreeHost(pc->h_flags);
     cudaFree(pc->d_wplanes); cudaFree(pc->d_xplanes);
     for (int i = 0; i < 3; i++) if (pc->ev[i]) cudaEventDestroy(pc->ev[i]);
@@ -264,8 +266,60 @@ extern "C" int ckks_b200_pcmm_ppmm(ckks_b200_pcmm* pc, const float* d_W,
         CKB_CUDA(cudaGetLastError());
         return CKKS_B200_OK;
     }
-    return pcmm_tensor(pc, pc->d_w, pc->d_xptrs, (u64*)d_out, mat_M, mat_N, col_begin, col_end,
+    return pcmm_tensor(pc, pc->d_w, pc->d_xptrs, nullptr, (u64*)d_out, mat_M, mat_N, col_begin, col_end,
                        w_bits, st);
+}
+
+// PCMM_Scheme::rlweCipherDecompose (PCMM_Scheme.cuh:51-125) followed by PCMM_Scheme::PPMM
+// (PPMM_kernel.cuh:254-349) as one call: the multiply's slicing pre-pass reads the RLWE
+// ciphertexts through the decomposition's index map, so the K MLWE ciphertexts (K times the
+// size of what they are made from) are never written to or read from HBM.
+extern "C" int ckks_b200_pcmm_ppmm_rlwe(ckks_b200_pcmm* pc, const float* d_W, const ckks_b200_rlwe_source* sources,
+                                        int n_sources, uint64_t* d_out, int mat_M, int mat_N, int mat_K,
+                                        int mlwe_num, double scaler, long col_begin, long col_end, void* stream) {
+    CKB_REQUIRE(pc && d_W && sources && d_out, CKKS_B200_ERR_ARG, "null argument");
+    CKB_REQUIRE(mat_K == pc->N1, CKKS_B200_ERR_SHAPE, "matrix K should be equal to N1!");
+    CKB_REQUIRE(mat_N == mlwe_num, CKKS_B200_ERR_SHAPE, "matrix N should be equal to mlwe number!");
+    CKB_REQUIRE(mat_M >= 1 && mat_N >= 1, CKKS_B200_ERR_ARG, "M and N must be positive");
+    CKB_REQUIRE(mat_N <= (1 << 20), CKKS_B200_ERR_UNSUPPORTED, "contraction length above 2^20");
+    CKB_REQUIRE(col_begin >= 0 && col_begin < col_end && col_end <= pc->C, CKKS_B200_ERR_ARG,
+                "column range [%ld,%ld) outside [0,%ld)", col_begin, col_end, pc->C);
+    CKB_REQUIRE(col_begin % 32 == 0 && (col_end % 32 == 0 || col_end == pc->C), CKKS_B200_ERR_ARG,
+                "column range must start and end on multiples of 32");
+    CKB_REQUIRE(n_sources >= 1, CKKS_B200_ERR_ARG, "no source ciphertext");
+    // every MLWE index must be produced by exactly one source
+    std::vector<RlweSlot> slots(mlwe_num, RlweSlot{nullptr, 0, 0, 0, 0});
+    for (int s = 0; s < n_sources; s++) {
+        const ckks_b200_rlwe_source& S = sources[s];
+        CKB_REQUIRE(S.d_rlwe != nullptr, CKKS_B200_ERR_ARG, "source %d is null", s);
+        CKB_REQUIRE(S.L + 1 >= pc->q_count, CKKS_B200_ERR_ARG, "source %d holds %d limbs, the multiply runs %d", s, S.L + 1,
+                    pc->q_count);
+        // the reference's check (PCMM_Scheme.cuh:103-106)
+        CKB_REQUIRE(S.mlwe_num >= 1 && S.mlwe_num <= pc->rank, CKKS_B200_ERR_SHAPE,
+                    "rlweCipherDecompose extract number muse <= mlwe_rank");
+        CKB_REQUIRE(S.offset >= 0 && S.offset + S.mlwe_num <= mlwe_num, CKKS_B200_ERR_ARG,
+                    "source %d fills ciphertexts [%d,%d) of %d", s, S.offset, S.offset + S.mlwe_num, mlwe_num);
+        for (int i = 0; i < S.mlwe_num; i++) {
+            RlweSlot& d = slots[S.offset + i];
+            CKB_REQUIRE(d.rlwe == nullptr, CKKS_B200_ERR_ARG, "ciphertext %d is filled by two sources", S.offset + i);
+            d.rlwe = (const u64*)S.d_rlwe;
+            d.L = S.L;
+            d.i = i;
+            d.gap = pc->rank / S.mlwe_num;
+        }
+    }
+    for (int n = 0; n < mlwe_num; n++)
+        CKB_REQUIRE(slots[n].rlwe != nullptr, CKKS_B200_ERR_ARG, "ciphertext %d is filled by no source", n);
+    DeviceGuard guard(pc->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc = ensure_dev(&pc->d_slots, &pc->slots_cap, (size_t)mlwe_num);
+    if (rc) return rc;
+    CKB_CUDA(cudaMemcpyAsync(pc->d_slots, slots.data(), sizeof(RlweSlot) * mlwe_num, cudaMemcpyHostToDevice, st));
+    int w_bits = 0;
+    rc = prepare(pc, d_W, nullptr, mat_M, mat_N, scaler, st, &w_bits);      // synchronises: `slots` may go out of scope
+    if (rc) return rc;
+    return pcmm_tensor(pc, pc->d_w, nullptr, pc->d_slots, (u64*)d_out, mat_M, mat_N, col_begin, col_end, w_bits, st);
 }
 
 extern "C" int ckks_b200_pcmm_set_host_chunks(ckks_b200_pcmm* pc, int chunks) {

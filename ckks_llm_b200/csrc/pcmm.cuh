@@ -13,6 +13,13 @@ struct PcmmLimb {
     u64 pad;
 };
 
+// Where MLWE ciphertext n of a multiply comes from when the PCMM reads RLWE ciphertexts directly:
+// ciphertext i of the decomposition of `rlwe` ([2][L+1][N] words, coefficient domain) with the given gap.
+struct RlweSlot {
+    const u64* rlwe;
+    int L, i, gap, pad;
+};
+
 struct ckks_b200_pcmm {
     int device = 0;
     int N1 = 0, rank = 0, q_count = 0;
@@ -24,6 +31,8 @@ struct ckks_b200_pcmm {
     size_t w_cap = 0;
     const u64** d_xptrs = nullptr;    // device copy of the ciphertext pointer table
     size_t xptrs_cap = 0;
+    RlweSlot* d_slots = nullptr;      // per-ciphertext sources of the multiply that decomposes on the fly
+    size_t slots_cap = 0;
     u64* peer_out[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // see ckks_b200_pcmm_set_peer_outputs
     int n_peers = 0;
     int* d_flags = nullptr;           // [0] max |w| bits seen, [1] device-side wait timeout, ...
@@ -69,7 +78,9 @@ int ensure_dev(T** buf, size_t* cap, size_t count) {
     return CKKS_B200_OK;
 }
 
-// Tensor-core path (pcmm_umma.cu).  w_bits = bit length of the largest |w|.
-int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, u64* d_out,
+// Tensor-core path (pcmm_umma.cu).  w_bits = bit length of the largest |w|.  The ciphertext words come from
+// the pointer table d_xptrs, or, when d_slots is given, straight from RLWE ciphertexts through the
+// decomposition's index map.
+int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots, u64* d_out,
                 int M, int K, long col_begin, long col_end, int w_bits, cudaStream_t st);
 }  // namespace ckb

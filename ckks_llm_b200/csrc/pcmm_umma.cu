@@ -25,6 +25,7 @@
 // bounded by a clock budget; a wait that runs out raises a flag the host turns into
 // CKKS_B200_ERR_TIMEOUT, and the CTA drains and exits.
 #include "pcmm.cuh"
+#include "ringpack.cuh"
 #include "umma.cuh"
 
 using namespace ckb;
@@ -143,6 +144,58 @@ __global__ void slice_cipher_kernel(const u64* const* __restrict__ X, uint8_t* _
     }
     const int ct = (int)(col / TC), cc = (int)(col % TC);
     for (int b = 0; b < SC; b++) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int wd = 0; wd < 4; wd++) {
+            uint32_t x = 0;
+#pragma unroll
+            for (int e = 0; e < 4; e++) x |= (uint32_t)((v[wd * 4 + e] >> (8 * b)) & 0xff) << (8 * e);
+            pk[wd] = x;
+        }
+        size_t off = (((((size_t)limb * CT + ct) * KBN + kb) * KS + ks) * SC + b) * B_PLANE_STEP +
+                     (size_t)(cc / 8) * 256 + kc * 128 + (cc % 8) * 16;
+        *reinterpret_cast<uint4*>(planes + off) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+}
+
+// Pre-pass 2 when the multiply reads RLWE ciphertexts directly: the same planes, with word
+// (n, limb, c) taken through the decomposition's index map instead of from a stored MLWE
+// ciphertext, so the MLWE ciphertexts never exist in HBM (the RLWE ciphertexts stay in L2:
+// 16*N bytes per limb against (rank+1)*N1*8 bytes per limb for EACH of the K ciphertexts made
+// from them).  One block per (column tile, K block, limb): the source is contiguous in n (for a
+// gap of one), the plane blob wants 16 n per 16-byte store, so a 32-column x 64-n tile goes
+// through shared memory, read with lanes along n and sliced with lanes along the columns.
+__global__ void __launch_bounds__(256) slice_rlwe_kernel(const RlweSlot* __restrict__ slots, uint8_t* __restrict__ planes,
+                                                         const PcmmLimb* __restrict__ limbs, int K, long N, int N1,
+                                                         int rank, long col_begin, long col_end, int CT, int KBN, int SC) {
+    static_assert(KB == 64 && TC == 32, "the thread mapping below is written for 64 x 32 tiles");
+    __shared__ u64 tile[TC][KB + 1];
+    const int ct = blockIdx.x, kb = blockIdx.y, limb = blockIdx.z;
+    const int t = threadIdx.x;
+    const u64 q = limbs[limb].q;
+    {
+        const int nl = t & (KB - 1), n = kb * KB + nl;
+        RlweSlot s = {nullptr, 0, 0, 0, 0};
+        if (n < K) s = slots[n];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int cl = (t >> 6) + 4 * j;
+            const long c = col_begin + (long)ct * TC + cl;
+            u64 v = 0;
+            if (n < K && c < col_end) {
+                const int r = (int)(c / N1), g = (int)(c % N1);
+                v = decompose_word(s.rlwe + N * limb, s.rlwe + N * (s.L + 1 + limb), q, N, N1, rank, s.gap, s.i, r, g);
+            }
+            tile[cl][nl] = v;
+        }
+    }
+    __syncthreads();
+    const int cc = t & 31, k16 = (t >> 5) & 3, half = t >> 7;
+    const int ks = k16 / 2, kc = k16 % 2;
+    u64 v[16];
+#pragma unroll
+    for (int e = 0; e < 16; e++) v[e] = tile[cc][k16 * 16 + e];
+    for (int b = half; b < SC; b += 2) {
         uint32_t pk[4];
 #pragma unroll
         for (int wd = 0; wd < 4; wd++) {
@@ -424,8 +477,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
 }
 
 template <int SW, int SC>
-int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, u64* d_out, int M, int K,
-           long col_begin, long col_end, cudaStream_t st) {
+int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots, u64* d_out, int M,
+           int K, long col_begin, long col_end, cudaStream_t st) {
     using C_ = Cfg<SW, SC>;
     const int MT = (M + TM - 1) / TM;
     const long ncol = col_end - col_begin;
@@ -441,9 +494,15 @@ int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, 
     {
         long total = (long)MT * TM * KBN * (KB / 16);
         slice_weights_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d_w, pc->d_wplanes, M, K, MT, KBN, SW);
-        dim3 grid((unsigned)(((long)CT * TC + 127) / 128), KBN * (KB / 16), pc->q_count);
-        slice_cipher_kernel<<<grid, 128, 0, st>>>(d_xptrs, pc->d_xplanes, K, pc->C, pc->q_count, col_begin, col_end,
-                                                  CT, KBN, SC);
+        if (d_slots) {
+            dim3 grid((unsigned)CT, KBN, pc->q_count);
+            slice_rlwe_kernel<<<grid, 256, 0, st>>>(d_slots, pc->d_xplanes, pc->d_limbs, K, (long)pc->rank * pc->N1, pc->N1,
+                                                    pc->rank, col_begin, col_end, CT, KBN, SC);
+        } else {
+            dim3 grid((unsigned)(((long)CT * TC + 127) / 128), KBN * (KB / 16), pc->q_count);
+            slice_cipher_kernel<<<grid, 128, 0, st>>>(d_xptrs, pc->d_xplanes, K, pc->C, pc->q_count, col_begin, col_end,
+                                                      CT, KBN, SC);
+        }
         count_launch(2);
         CKB_CUDA(cudaGetLastError());
     }
@@ -486,8 +545,8 @@ int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, 
 
 namespace ckb {
 
-int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, u64* d_out, int M, int K,
-                long col_begin, long col_end, int w_bits, cudaStream_t st) {
+int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots, u64* d_out,
+                int M, int K, long col_begin, long col_end, int w_bits, cudaStream_t st) {
     int q_bits = 0;
     for (u64 q : pc->q) {
         int b = 64 - __builtin_clzll(q);
@@ -507,10 +566,10 @@ int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xp
         const int pairs = in.sw < in.sc ? in.sw : in.sc;
         // |sum| per accumulator <= pairs * K * 255 * 255 must stay below 2^31
         if ((long long)pairs * ((K + KB - 1) / KB * KB) * 65025ll >= (1ll << 31)) continue;
-        if (in.sw == 4) return launch<4, 5>(pc, d_w, d_xptrs, d_out, M, K, col_begin, col_end, st);
-        if (in.sw == 5) return launch<5, 7>(pc, d_w, d_xptrs, d_out, M, K, col_begin, col_end, st);
-        if (in.sw == 6) return launch<6, 7>(pc, d_w, d_xptrs, d_out, M, K, col_begin, col_end, st);
-        return launch<8, 8>(pc, d_w, d_xptrs, d_out, M, K, col_begin, col_end, st);
+        if (in.sw == 4) return launch<4, 5>(pc, d_w, d_xptrs, d_slots, d_out, M, K, col_begin, col_end, st);
+        if (in.sw == 5) return launch<5, 7>(pc, d_w, d_xptrs, d_slots, d_out, M, K, col_begin, col_end, st);
+        if (in.sw == 6) return launch<6, 7>(pc, d_w, d_xptrs, d_slots, d_out, M, K, col_begin, col_end, st);
+        return launch<8, 8>(pc, d_w, d_xptrs, d_slots, d_out, M, K, col_begin, col_end, st);
     }
     set_error("no tensor-core configuration fits %d weight planes, %d residue planes and K=%d within s32 accumulators",
               sw, sc, K);

@@ -14,32 +14,11 @@
 // sides are coalesced.  HBM sees the output stream, (k+1)*N1 words per MLWE ciphertext per limb; the
 // RLWE limb (512 KiB at N = 2^16) is re-read from L2.
 #include "context.cuh"
+#include "ringpack.cuh"
 
 using namespace ckb;
 
 namespace {
-
-// word g of polynomial r of MLWE ciphertext i, one limb (the index maps at the top of the file)
-__device__ __forceinline__ u64 decompose_word(const u64* __restrict__ A, const u64* __restrict__ B, u64 q, long N, int N1, int k,
-                                              int gap, int i, int r, int g) {
-    long addr;
-    bool negate = false;
-    const u64* src = A;
-    if (r == k) {                 // b polynomial
-        addr = (long)i * gap + (long)g * k;
-        src = B;
-    } else if (r == 0) {
-        addr = (long)i * gap + (long)g * k;
-    } else if (g == 0) {
-        addr = (long)(N1 - 1) * k + (k - r) + (long)i * gap;
-        negate = true;
-    } else {
-        addr = (long)(g - 1) * k + (k - r) + (long)i * gap;
-    }
-    if (addr >= N) { addr -= N; negate = !negate; }
-    const u64 v = src[addr];
-    return negate ? (v == 0 ? 0 : q - v) : v;
-}
 
 __global__ void __launch_bounds__(256) rlwe_decompose_kernel(const u64* __restrict__ rlwe, u64* const* __restrict__ mlwe,
                                                              const u64* __restrict__ q_moduli, long N, int N1, int k,

@@ -317,6 +317,48 @@ class PCMM_Scheme:
             return
         capi.check(st)
 
+    def decomposeAndPPMM(self, plain_mat, sources, mlwe_cipher_decomposed, mat_M, mat_N, mat_K, mlwe_num, scaler=None,
+                         col_begin=0, col_end=None, ntt_domain=True, copy_back=True):
+        """rlweCipherDecompose of every (rlwe_cipher, mlwe_num, offset) in `sources` followed by PPMM, as one call
+        that never writes the decomposed ciphertexts (PCMM_Scheme.cuh:90-125 feeding PPMM_kernel.cuh:254-349; the
+        pairing of calls is Bert.cuh:249-254).  The result is that of the two separate calls, word for word.
+        mlwe_cipher_decomposed only receives the copy-back of the result rows, as after PPMM."""
+        pc, ctx = self.pcmm_context, self.context
+        if scaler is None:
+            scaler = self.scaler_for(sources[0][0].scale)
+        C_ = (pc.mlwe_rank + 1) * pc.N1
+        if col_end is None:
+            col_end = C_
+        need = mat_M * pc.ringpack_q_count * C_
+        if self.ppmm_output is None or self.ppmm_output.numel() < need:
+            self.ppmm_output = torch.empty(need, dtype=torch.int64, device=pc.device)
+        st_ptr = _stream_ptr(pc.device)
+        arr = (capi.RlweSource * max(len(sources), 1))()
+        for k, (ct, num, off) in enumerate(sources):
+            arr[k].d_rlwe, arr[k].L, arr[k].mlwe_num, arr[k].offset = ct.cipher_device.data_ptr(), ct.L, num, off
+        if ntt_domain:
+            for ct, _, _ in sources:
+                capi.check(self.lib.ckks_b200_ntt_inverse(ctx._h, ct.cipher_device.data_ptr(), 0, ctx.p_num, 2, ct.l + 1,
+                                                          ct.L + 1, st_ptr))
+        st = self.lib.ckks_b200_pcmm_ppmm_rlwe(pc._h, plain_mat.data_ptr(), arr, len(sources), self.ppmm_output.data_ptr(),
+                                               mat_M, mat_N, mat_K, mlwe_num, float(scaler), col_begin, col_end, st_ptr)
+        if ntt_domain:
+            for ct, _, _ in sources:
+                capi.check(self.lib.ckks_b200_ntt_forward(ctx._h, ct.cipher_device.data_ptr(), 0, ctx.p_num, 2, ct.l + 1,
+                                                          ct.L + 1, st_ptr))
+        if st == capi.ERR_SHAPE:
+            print(self.lib.ckks_b200_last_error().decode())
+            return None
+        capi.check(st)
+        out = self.ppmm_output[:need].view(mat_M, pc.ringpack_q_count, C_)
+        if copy_back:
+            ptrs = (C.c_void_p * max(mlwe_num, 1))(*[c.cipher_device.data_ptr() for c in mlwe_cipher_decomposed[:mlwe_num]])
+            capi.check(self.lib.ckks_b200_pcmm_copy_back(pc._h, self.ppmm_output.data_ptr(), ptrs, min(mlwe_num, mat_M), 1, st_ptr))
+            q_last = pc.q_ringpack[-1]
+            for c in mlwe_cipher_decomposed[:mlwe_num]:
+                c.scale = sources[0][0].scale * scaler / q_last
+        return out
+
     def addRepakcingKey(self, keys_device):
         """The reference generates the keys itself (PCMM_Scheme.cuh:152-223); key generation is
         out of scope here, so the caller hands over the finished block [k][2][2][N]."""

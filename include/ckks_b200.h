@@ -206,6 +206,25 @@ int ckks_b200_pcmm_destroy(ckks_b200_pcmm* pc);
 int ckks_b200_pcmm_ppmm(ckks_b200_pcmm* pc, const float* d_W, const uint64_t* const* h_X_ptrs,
                         uint64_t* d_out, int mat_M, int mat_N, int mat_K, int mlwe_num,
                         double scaler, long col_begin, long col_end, int algo, void* stream);
+/* Decompose and multiply in one call: PCMM_Scheme::rlweCipherDecompose
+ * (pcmm/PCMM_Scheme.cuh:51-125) feeding PCMM_Scheme::PPMM (pcmm/PPMM_kernel.cuh:254-349)
+ * without the MLWE ciphertexts in between.  Source s stands for the call
+ * rlweCipherDecompose(cipher_s, buffer, mlwe_num_s, offset_s): d_rlwe is that ciphertext,
+ * [2][L+1][N] words in the COEFFICIENT domain (the state between the decomposition's
+ * inverse and forward transforms; run ckks_b200_ntt_inverse first on a ciphertext in the
+ * NTT domain), limb i reduced modulo ring-pack modulus i.  Every MLWE index in
+ * [0, mlwe_num) must be filled by exactly one source.  The result is word for word that
+ * of ckks_b200_rlwe_decompose on every source followed by ckks_b200_pcmm_ppmm (tensor-core
+ * path).  Asynchronous on `stream`. */
+typedef struct {
+    const uint64_t* d_rlwe;
+    int L;        /* the ciphertext holds L+1 limbs per polynomial */
+    int mlwe_num; /* ciphertexts taken from it (gap = rank / mlwe_num) */
+    int offset;   /* index of its first ciphertext among the multiply's inputs */
+} ckks_b200_rlwe_source;
+int ckks_b200_pcmm_ppmm_rlwe(ckks_b200_pcmm* pc, const float* d_W, const ckks_b200_rlwe_source* sources,
+                             int n_sources, uint64_t* d_out, int mat_M, int mat_N, int mat_K, int mlwe_num,
+                             double scaler, long col_begin, long col_end, void* stream);
 /* Host-buffer form: h_W fp32 [M][N], h_X contiguous [mlwe_num][q_count][(k+1)*N1],
  * h_out [M][q_count][(k+1)*N1]; copies in, multiplies, copies out, synchronises.
  * The columns are cut into chunks that move through copy-in, multiply and copy-out

@@ -171,3 +171,100 @@ def test_packing_stages_match_reference_kernels(oracle, cuda_device):
     sch.mlweCipherPacking(out, cts, mlwe_num, 0)
     assert np.array_equal(to_u64_numpy(out.cipher_device).reshape(2, 2, N)[:, 0], exp)
     pc.close(); ctx.close()
+
+
+@pytest.mark.parametrize("logN,N1,parts,M", [
+    (12, 64, [(64, 0)], 40),                     # one source, every ciphertext of it (gap 1)
+    (12, 64, [(32, 0), (16, 32), (5, 48)], 70),  # three sources with gaps 2, 4 and 12; 53 ciphertexts, ragged K block
+    (13, 32, [(128, 0), (256, 128)], 130),       # the pipeline's pattern: one source half taken, one whole
+])
+def test_decompose_and_ppmm_in_one_call(oracle, cuda_device, logN, N1, parts, M):
+    """The multiply that reads RLWE ciphertexts through the decomposition's index map gives, word for word,
+    what rlweCipherDecompose followed by PPMM gives (and what the oracle gives for the two steps)."""
+    L = l = 2
+    N = 1 << logN
+    k = N // N1
+    q = params.ntt_primes(50, 2 * N, L + 1)
+    ctx = Context_23(logN, params.ntt_primes(51, 2 * N, 1), q, [])
+    rng = np.random.default_rng(logN * 100 + len(parts))
+    K = sum(n for n, _ in parts)
+    W = rng.uniform(-0.1, 0.1, (M, K)).astype(np.float32)
+    scaler = float(1 << 30)
+    pc = PCMM_Context(N1, k, [], q)
+    sch = PCMM_Scheme(pc, context=ctx)
+    rlwes, cts, exp_X = [], [], [None] * K
+    for num, off in parts:
+        rl = np.stack([H.uniform_residues(rng, q, (N,)), H.uniform_residues(rng, q, (N,))])
+        rlwes.append(rl)
+        cts.append(Ciphertext(N, L, l, N // 2, 1.0, cipher=as_u64_tensor(rl, ctx.device).reshape(-1)))
+        dec = oracle.rlwe_decompose(rl[0], rl[1], N1, k, num, q)
+        for i in range(num):
+            exp_X[off + i] = dec[i].reshape(L + 1, -1)
+    Wd = torch.from_numpy(W).to(ctx.device)
+    sources = [(ct, num, off) for ct, (num, off) in zip(cts, parts)]
+    mlwe = [MLWECiphertext(N1, L, l, k, 1.0) for _ in range(K)]
+    fused = to_u64_numpy(sch.decomposeAndPPMM(Wd, sources, mlwe, M, K, N1, K, scaler=scaler, ntt_domain=False,
+                                              copy_back=False)).copy()
+    sch.check()
+    for ct, rl in zip(cts, rlwes):
+        assert np.array_equal(to_u64_numpy(ct.cipher_device).reshape(rl.shape), rl)       # sources untouched
+    for ct, (num, off) in zip(cts, parts):
+        sch.rlweCipherDecompose(ct, mlwe, num, off, ntt_domain=False)
+    two_step = to_u64_numpy(sch.PPMM(Wd, mlwe, M, K, N1, K, scaler=scaler, copy_back=False))
+    assert np.array_equal(fused, two_step)
+    exp = oracle.ppmm(W, np.stack(exp_X), q, scaler)
+    assert np.array_equal(fused, exp)
+    pc.close(); ctx.close()
+
+
+def test_decompose_and_ppmm_from_ntt_domain_with_copy_back(oracle, cuda_device):
+    """Sources at rest in the NTT domain: transformed back for the multiply and forward again afterwards, and the
+    first limb of result row i lands in ciphertext i as after PPMM."""
+    logN, N1, L = 12, 64, 1
+    N, l = 1 << logN, 1
+    k = N // N1
+    q = params.ntt_primes(50, 2 * N, L + 1)
+    ctx = Context_23(logN, params.ntt_primes(51, 2 * N, 1), q, [])
+    rng = np.random.default_rng(77)
+    rl = np.stack([H.uniform_residues(rng, q, (N,)), H.uniform_residues(rng, q, (N,))])
+    T = oracle.NttTables(N, ctx.pVec + ctx.qVec)
+    ntt = rl.copy()
+    oracle.ntt_batch(ntt, T, 0, ctx.p_num, 2, l + 1, L + 1)
+    K = M = 64
+    W = rng.uniform(-0.1, 0.1, (M, K)).astype(np.float32)
+    pc = PCMM_Context(N1, k, [], q)
+    sch = PCMM_Scheme(pc, context=ctx)
+    ct = Ciphertext(N, L, l, N // 2, 1.0, cipher=as_u64_tensor(ntt, ctx.device).reshape(-1))
+    mlwe = [MLWECiphertext(N1, L, l, k, 1.0) for _ in range(K)]
+    out = to_u64_numpy(sch.decomposeAndPPMM(torch.from_numpy(W).to(ctx.device), [(ct, K, 0)], mlwe, M, K, N1, K,
+                                            scaler=float(1 << 30)))
+    sch.check()
+    X = oracle.rlwe_decompose(rl[0], rl[1], N1, k, K, q).reshape(K, L + 1, -1)
+    exp = oracle.ppmm(W, X, q, float(1 << 30))
+    assert np.array_equal(out, exp)
+    assert np.array_equal(to_u64_numpy(ct.cipher_device).reshape(ntt.shape), ntt)          # back in the NTT domain
+    for i in range(K):
+        assert np.array_equal(to_u64_numpy(mlwe[i].cipher_device).reshape(L + 1, -1)[0], exp[i, 0])
+    pc.close(); ctx.close()
+
+
+def test_decompose_and_ppmm_rejects_gaps_and_overlaps(cuda_device):
+    N, q, ctx, rlwe = _setup(12, 64, 1, seed=5)
+    pc = PCMM_Context(64, 64, [], q)
+    L_ = capi.load()
+    ct = as_u64_tensor(rlwe, ctx.device).reshape(-1)
+    W = torch.zeros((8, 64), dtype=torch.float32, device=ctx.device)
+    out = torch.empty(8 * 2 * 65 * 64, dtype=torch.int64, device=ctx.device)
+
+    def call(parts, K=64):
+        arr = (capi.RlweSource * len(parts))()
+        for j, (num, off) in enumerate(parts):
+            arr[j].d_rlwe, arr[j].L, arr[j].mlwe_num, arr[j].offset = ct.data_ptr(), 1, num, off
+        return L_.ckks_b200_pcmm_ppmm_rlwe(pc._h, W.data_ptr(), arr, len(parts), out.data_ptr(), 8, K, 64, K, 1.0, 0, 65 * 64, None)
+
+    assert call([(32, 0)]) == capi.ERR_ARG                      # ciphertexts 32..63 filled by no source
+    assert call([(64, 0), (8, 8)]) == capi.ERR_ARG              # filled twice
+    assert call([(65, 0)], K=65) == capi.ERR_SHAPE              # more than the rank from one source
+    assert call([(64, 0)]) == capi.OK
+    torch.cuda.synchronize()
+    pc.close(); ctx.close()
