@@ -423,6 +423,62 @@ def bench_pcmm_shape(torch, device, steps, warmup, peaks, name, rank=0, world=1,
     return res
 
 
+def bench_pcmm_from_rlwe(torch, device, steps, warmup, sch, pc, cts, W, q, ppmm_ms):
+    """The pipeline's pair of calls (Bert.cuh:249-254: rlweCipherDecompose of two ciphertexts into 512 + 256 MLWE
+    ciphertexts, then PPMM) at the headline shape, as two steps and as the one call whose slicing pre-pass reads the
+    RLWE ciphertexts through the decomposition's index map.  Coefficient-domain sources (the transforms around the
+    decomposition are the same in both forms and are left out).  The two outputs are compared word for word."""
+    from ckks_llm_b200.host import Ciphertext, Context_23
+    from ckks_llm_b200 import params
+    c = PCMM_CFG
+    N, L = 1 << c["logN"], c["limbs"] - 1
+    ctx = Context_23(c["logN"], [params.ntt_primes(51, 2 * N, 1)[0]], list(q), [], device=device.index)
+    sch.context = ctx
+    g = torch.Generator(device=device).manual_seed(11)
+    srcs = []
+    for _ in range(2):
+        rl = torch.empty((2, L + 1, N), dtype=torch.int64, device=device)
+        for i, qi in enumerate(q):
+            rl[:, i, :] = torch.randint(0, qi, (2, N), generator=g, device=device, dtype=torch.int64)
+        srcs.append(Ciphertext(N, L, L, N // 2, 1.0, device=device.index, cipher=rl.reshape(-1)))
+    sources = [(srcs[0], 512, 0), (srcs[1], 256, 512)]
+
+    def timed(fn):
+        for _ in range(max(warmup, 1)):
+            fn()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        return e0.elapsed_time(e1) / steps
+
+    def one_call():
+        return sch.decomposeAndPPMM(W, sources, cts, c["M"], c["K"], c["N1"], c["K"], scaler=c["scaler"], ntt_domain=False,
+                                    copy_back=False)
+
+    def decompose():
+        for ct, num, off in sources:
+            sch.rlweCipherDecompose(ct, cts, num, off, ntt_domain=False)
+
+    one_ms = timed(one_call)
+    pre_ms, main_ms = sch.last_timing()
+    got = one_call().clone()
+    dec_ms = timed(decompose)
+    two = sch.PPMM(W, cts, c["M"], c["K"], c["N1"], c["K"], scaler=c["scaler"], copy_back=False)
+    sch.check()
+    same = bool(torch.equal(got, two))
+    del got
+    ctx.close()
+    sch.context = None
+    return {"one_call_ms": one_ms, "one_call_ct_rows_per_sec": c["M"] / (one_ms * 1e-3), "one_call_prepass_ms": pre_ms,
+            "one_call_main_ms": main_ms, "decompose_ms": dec_ms, "ppmm_ms": ppmm_ms, "two_calls_ms": dec_ms + ppmm_ms,
+            "outputs_identical": same,
+            "note": "decompose writes and PPMM re-reads 8.07 GB of MLWE ciphertexts made from 42 MB; the one call does neither"}
+
+
 def bench_ringpack(torch, device, steps, warmup, peaks):
     """rlweCipherDecompose and mlweCipherPacking at the BERT geometry the reference runs (N=2^16, N1=128, rank 512,
     two ring-pack limbs, one special prime): device time per call with the bytes each must move."""
@@ -626,6 +682,8 @@ def main():
                 "kernel": "pcmm_umma_kernel<5,7>", "kernel_ms": main, "prepass_ms": float(np.mean(pre_ms)),
                 "peak_source": f"2 x bf16 dense {peaks['bf16_tflops']} TFLOP/s ({peaks['source']}); int8 dense is nominally 2x bf16",
                 "algorithmic_ops": "2*5*7 int8 ops per modular MAC x M*K*(N+N1)*limbs"}
+        if rank == 0 and world == 1 and not args.no_side:
+            extra["pcmm_from_rlwe"] = bench_pcmm_from_rlwe(torch, device, args.steps, args.warmup, sch, pc, cts, W, q, ms)
         metric, unit = "pcmm_ct_rows_per_sec", "ct-rows/s"
         workload = ("bert-base PCMM 768x768 (W~N(0,0.02) at 2^40), 768 ciphertexts x 20 limbs x 65664 words, "
                     "N=2^16, N1=128, rank 512, 50-bit limbs")

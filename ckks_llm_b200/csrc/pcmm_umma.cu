@@ -177,15 +177,18 @@ __global__ void __launch_bounds__(256) slice_rlwe_kernel(const RlweSlot* __restr
         const int nl = t & (KB - 1), n = kb * KB + nl;
         RlweSlot s = {nullptr, 0, 0, 0, 0};
         if (n < K) s = slots[n];
+        const u64* A = s.rlwe + N * limb;
+        const u64* B = s.rlwe + N * (s.L + 1 + limb);
+        // column c = r*N1 + g: one division for the tile's first column, steps from there
+        const long c0 = col_begin + (long)ct * TC;
+        const int r0 = (int)(c0 / N1), g0 = (int)(c0 - (long)r0 * N1);
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             const int cl = (t >> 6) + 4 * j;
-            const long c = col_begin + (long)ct * TC + cl;
+            int r = r0, g = g0 + cl;
+            while (g >= N1) { g -= N1; r++; }
             u64 v = 0;
-            if (n < K && c < col_end) {
-                const int r = (int)(c / N1), g = (int)(c % N1);
-                v = decompose_word(s.rlwe + N * limb, s.rlwe + N * (s.L + 1 + limb), q, N, N1, rank, s.gap, s.i, r, g);
-            }
+            if (n < K && c0 + cl < col_end) v = decompose_word(A, B, q, N, N1, rank, s.gap, s.i, r, g);
             tile[cl][nl] = v;
         }
     }
@@ -207,6 +210,91 @@ __global__ void __launch_bounds__(256) slice_rlwe_kernel(const RlweSlot* __restr
         size_t off = (((((size_t)limb * CT + ct) * KBN + kb) * KS + ks) * SC + b) * B_PLANE_STEP +
                      (size_t)(cc / 8) * 256 + kc * 128 + (cc % 8) * 16;
         *reinterpret_cast<uint4*>(planes + off) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+}
+
+// The same pre-pass for the usual case (N1 a multiple of 32, every 64-ciphertext K block
+// inside one source, gaps of at most 2), using the structure of the decomposition: with
+// the negacyclic convention A[x +- N] = -A[x], word g of polynomial r < k of ciphertext i is
+//   a_i,r[g] = A[g*k + i*gap - r]          (b_i[g] = B[g*k + i*gap])
+// so ciphertexts i and polynomials r see the same RLWE words shifted against one another.
+// A block takes 32 values of g, one K block of 64 ciphertexts and RB polynomials: it loads
+// the 32 runs of 63*gap + RB words those share (7 % of the words it emits, at a gap of one)
+// into shared memory and cuts the planes of its RB column tiles from them.  The last
+// "row block" is the b polynomial alone.
+constexpr int RB = 16;
+constexpr int SEG_MAX_GAP = 2;
+constexpr int SEG = 63 * SEG_MAX_GAP + RB + 1;     // odd: lanes along g fall into distinct banks (32-bit words)
+
+__global__ void __launch_bounds__(256) slice_rlwe_rows_kernel(const RlweSlot* __restrict__ slots, uint8_t* __restrict__ planes,
+                                                              const PcmmLimb* __restrict__ limbs, int K, long N, int N1,
+                                                              int rank, long col_begin, long col_end, int CT, int KBN,
+                                                              int SC) {
+    static_assert(KB == 64 && TC == 32, "the thread mapping below is written for 64 x 32 tiles");
+    // low and high words apart: a thread cuts either planes 0-3 or planes 4-7 and reads only the words it needs
+    __shared__ uint32_t seg[2][TC][SEG];
+    const int g_tiles = N1 / TC, rbn = (rank + RB - 1) / RB;
+    const int gt = blockIdx.x % g_tiles, rb = blockIdx.x / g_tiles;
+    const int kb = blockIdx.y, limb = blockIdx.z;
+    const bool bpoly = rb == rbn;
+    const int r0 = bpoly ? 0 : rb * RB;                                   // first polynomial, as it enters the index
+    const int rows = bpoly ? 1 : (rank - r0 < RB ? rank - r0 : RB);
+    const int crow0 = bpoly ? rank : r0;                                  // its row among the (k+1) rows of columns
+    const int g0 = gt * TC;
+    {
+        const long c_first = (long)crow0 * N1 + g0, c_last = (long)(crow0 + rows - 1) * N1 + g0;
+        if (c_last < col_begin || c_first >= col_end) return;             // block-uniform
+    }
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int n0 = kb * KB;
+    const RlweSlot s = slots[n0];
+    const int gap = s.gap;
+    const int span = 63 * gap + RB;
+    const u64* src = s.rlwe + N * ((bpoly ? s.L + 1 : 0) + limb);
+    const u64 q = limbs[limb].q;
+    // seg[.][g][x] = A[(g0+g)*k + i0*gap - (r0 + RB - 1) + x], sign folded in
+    for (int g = warp; g < TC; g += 8) {
+        const long base = (long)(g0 + g) * rank + (long)s.i * gap - (r0 + RB - 1);
+        for (int x = lane; x < span; x += 32) {
+            long idx = base + x;
+            bool neg = false;
+            if (idx < 0) { idx += N; neg = true; }
+            else if (idx >= N) { idx -= N; neg = true; }
+            u64 v = src[idx];
+            if (neg) v = v == 0 ? 0 : q - v;
+            seg[0][g][x] = (uint32_t)v;
+            seg[1][g][x] = (uint32_t)(v >> 32);
+        }
+    }
+    __syncthreads();
+    const int cc = t & 31, k16 = (t >> 5) & 3, half = t >> 7;
+    const int ks = k16 / 2, kc = k16 % 2;
+    const uint32_t* row = seg[half][cc];
+    const int valid = K - n0 - k16 * 16;                                   // ciphertexts of this 16-chunk that exist
+    for (int rr = 0; rr < rows; rr++) {
+        const long c = (long)(crow0 + rr) * N1 + g0;
+        if (c < col_begin || c >= col_end) continue;                       // block-uniform
+        const int ct = (int)((c - col_begin) / TC);
+        uint32_t w[16];
+        int x = k16 * 16 * gap - rr + (RB - 1);
+#pragma unroll
+        for (int e = 0; e < 16; e++, x += gap) w[e] = e < valid ? row[x] : 0u;
+        uint8_t* dst = planes + ((((size_t)limb * CT + ct) * KBN + kb) * KS + ks) * SC * B_PLANE_STEP +
+                       (size_t)(cc / 8) * 256 + kc * 128 + (cc % 8) * 16;
+#pragma unroll
+        for (int bb = 0; bb < 4; bb++) {
+            const int b = half * 4 + bb;
+            if (b < SC) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int wd = 0; wd < 4; wd++) {
+                    const uint32_t lo = __byte_perm(w[wd * 4 + 0], w[wd * 4 + 1], bb | ((4 + bb) << 4));
+                    const uint32_t hi = __byte_perm(w[wd * 4 + 2], w[wd * 4 + 3], bb | ((4 + bb) << 4));
+                    pk[wd] = __byte_perm(lo, hi, 0x5410);
+                }
+                *reinterpret_cast<uint4*>(dst + (size_t)b * B_PLANE_STEP) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+        }
     }
 }
 
@@ -477,8 +565,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
 }
 
 template <int SW, int SC>
-int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots, u64* d_out, int M,
-           int K, long col_begin, long col_end, cudaStream_t st) {
+int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots, bool slots_regular,
+           u64* d_out, int M, int K, long col_begin, long col_end, cudaStream_t st) {
     using C_ = Cfg<SW, SC>;
     const int MT = (M + TM - 1) / TM;
     const long ncol = col_end - col_begin;
@@ -494,7 +582,11 @@ int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, 
     {
         long total = (long)MT * TM * KBN * (KB / 16);
         slice_weights_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d_w, pc->d_wplanes, M, K, MT, KBN, SW);
-        if (d_slots) {
+        if (d_slots && slots_regular) {
+            dim3 grid((unsigned)((pc->N1 / TC) * ((pc->rank + RB - 1) / RB + 1)), KBN, pc->q_count);
+            slice_rlwe_rows_kernel<<<grid, 256, 0, st>>>(d_slots, pc->d_xplanes, pc->d_limbs, K, (long)pc->rank * pc->N1,
+                                                         pc->N1, pc->rank, col_begin, col_end, CT, KBN, SC);
+        } else if (d_slots) {
             dim3 grid((unsigned)CT, KBN, pc->q_count);
             slice_rlwe_kernel<<<grid, 256, 0, st>>>(d_slots, pc->d_xplanes, pc->d_limbs, K, (long)pc->rank * pc->N1, pc->N1,
                                                     pc->rank, col_begin, col_end, CT, KBN, SC);
@@ -545,8 +637,10 @@ int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, 
 
 namespace ckb {
 
-int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots, u64* d_out,
-                int M, int K, long col_begin, long col_end, int w_bits, cudaStream_t st) {
+int pcmm_slots_max_gap() { return SEG_MAX_GAP; }
+
+int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots,
+                bool slots_regular, u64* d_out, int M, int K, long col_begin, long col_end, int w_bits, cudaStream_t st) {
     int q_bits = 0;
     for (u64 q : pc->q) {
         int b = 64 - __builtin_clzll(q);
@@ -566,10 +660,10 @@ int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xp
         const int pairs = in.sw < in.sc ? in.sw : in.sc;
         // |sum| per accumulator <= pairs * K * 255 * 255 must stay below 2^31
         if ((long long)pairs * ((K + KB - 1) / KB * KB) * 65025ll >= (1ll << 31)) continue;
-        if (in.sw == 4) return launch<4, 5>(pc, d_w, d_xptrs, d_slots, d_out, M, K, col_begin, col_end, st);
-        if (in.sw == 5) return launch<5, 7>(pc, d_w, d_xptrs, d_slots, d_out, M, K, col_begin, col_end, st);
-        if (in.sw == 6) return launch<6, 7>(pc, d_w, d_xptrs, d_slots, d_out, M, K, col_begin, col_end, st);
-        return launch<8, 8>(pc, d_w, d_xptrs, d_slots, d_out, M, K, col_begin, col_end, st);
+        if (in.sw == 4) return launch<4, 5>(pc, d_w, d_xptrs, d_slots, slots_regular, d_out, M, K, col_begin, col_end, st);
+        if (in.sw == 5) return launch<5, 7>(pc, d_w, d_xptrs, d_slots, slots_regular, d_out, M, K, col_begin, col_end, st);
+        if (in.sw == 6) return launch<6, 7>(pc, d_w, d_xptrs, d_slots, slots_regular, d_out, M, K, col_begin, col_end, st);
+        return launch<8, 8>(pc, d_w, d_xptrs, d_slots, slots_regular, d_out, M, K, col_begin, col_end, st);
     }
     set_error("no tensor-core configuration fits %d weight planes, %d residue planes and K=%d within s32 accumulators",
               sw, sc, K);

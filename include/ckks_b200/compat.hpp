@@ -219,6 +219,33 @@ public:
         for (int i = 0; i < mlwe_num; i++)
             mlwe_cipher_decomposed[i]->scale = mlwe_cipher_decomposed[i]->scale * scaler / q_div;
     }
+
+    // rlweCipherDecompose of every source (PCMM_Scheme.cuh:90-125) feeding PPMM, as the one call that never
+    // writes the decomposed ciphertexts.  The sources are in the coefficient domain (the state between the
+    // decomposition's inverse and forward transforms); `scale` is theirs.  mlwe_cipher_decomposed only
+    // receives what PPMM leaves in it: the first limb of result row i in ciphertext i, and the new scale.
+    void decomposeAndPPMM(float* plain_mat, const std::vector<ckks_b200_rlwe_source>& sources, double scale,
+                          std::vector<MLWECiphertext*> mlwe_cipher_decomposed, int mat_M, int mat_N, int mat_K,
+                          int mlwe_num, cudaStream_t stream = 0) {
+        if (mat_K != pcmm_context.N1) { std::cout << "matrix K should be equal to N1!" << std::endl; return; }
+        if (mat_N != mlwe_num) { std::cout << "matrix N should be equal to mlwe number!" << std::endl; return; }
+        const long C = (long)(pcmm_context.mlwe_rank + 1) * pcmm_context.N1;
+        if (ppmm_output_rows < (size_t)mat_M) {
+            if (ppmm_output) cudaFree(ppmm_output);
+            if (cudaMalloc(&ppmm_output, sizeof(uint64_tt) * C * pcmm_context.ringpack_q_count * mat_M) != cudaSuccess)
+                throw std::runtime_error("cudaMalloc failed");
+            ppmm_output_rows = mat_M;
+        }
+        const long double q_div = (long double)pcmm_context.q_ringpack[pcmm_context.ringpack_q_count > 1 ? 1 : 0];
+        const long scaler = (long)(q_div * (long double)(1LL << 49) / scale);
+        check(ckks_b200_pcmm_ppmm_rlwe(pcmm_context.b200, plain_mat, sources.data(), (int)sources.size(),
+                                       (uint64_t*)ppmm_output, mat_M, mat_N, mat_K, mlwe_num, (double)scaler, 0, C, stream));
+        std::vector<uint64_t*> wptrs(mlwe_num);
+        for (int i = 0; i < mlwe_num; i++) wptrs[i] = (uint64_t*)mlwe_cipher_decomposed[i]->cipher_device;
+        const int rows_back = mlwe_num < mat_M ? mlwe_num : mat_M;
+        check(ckks_b200_pcmm_copy_back(pcmm_context.b200, (const uint64_t*)ppmm_output, wptrs.data(), rows_back, 1, stream));
+        for (int i = 0; i < mlwe_num; i++) mlwe_cipher_decomposed[i]->scale = scale * scaler / q_div;
+    }
 };
 
 }  // namespace ckks_b200

@@ -177,6 +177,8 @@ def test_packing_stages_match_reference_kernels(oracle, cuda_device):
     (12, 64, [(64, 0)], 40),                     # one source, every ciphertext of it (gap 1)
     (12, 64, [(32, 0), (16, 32), (5, 48)], 70),  # three sources with gaps 2, 4 and 12; 53 ciphertexts, ragged K block
     (13, 32, [(128, 0), (256, 128)], 130),       # the pipeline's pattern: one source half taken, one whole
+    (12, 64, [(64, 0), (36, 64)], 33),           # whole K blocks per source, the last one ragged
+    (12, 32, [(128, 0)], 16),                    # rank 128: eight row blocks of polynomials per tile column
 ])
 def test_decompose_and_ppmm_in_one_call(oracle, cuda_device, logN, N1, parts, M):
     """The multiply that reads RLWE ciphertexts through the decomposition's index map gives, word for word,
@@ -214,6 +216,15 @@ def test_decompose_and_ppmm_in_one_call(oracle, cuda_device, logN, N1, parts, M)
     assert np.array_equal(fused, two_step)
     exp = oracle.ppmm(W, np.stack(exp_X), q, scaler)
     assert np.array_equal(fused, exp)
+    # the same in three column ranges (a shard's view): the middle one starts and ends inside rows of polynomials
+    C_ = (k + 1) * N1
+    sch.ppmm_output.zero_()
+    cuts = [0, 32 * 3, 32 * ((C_ // 32) - 2), C_]
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        sch.decomposeAndPPMM(Wd, sources, mlwe, M, K, N1, K, scaler=scaler, col_begin=a, col_end=b, ntt_domain=False,
+                             copy_back=False)
+    sch.check()
+    assert np.array_equal(to_u64_numpy(sch.ppmm_output[:exp.size]).reshape(exp.shape), exp)
     pc.close(); ctx.close()
 
 
