@@ -21,7 +21,7 @@ SYMBOLS = [
     "ckks_b200_modup_qj_to_t", "ckks_b200_modup_qj_to_t_host", "ckks_b200_modup_set_algo", "ckks_b200_context_check",
     "ckks_b200_rescale", "ckks_b200_modup_q0_to_ql",
     "ckks_b200_external_product_t", "ckks_b200_ntt_inverse_ext", "ckks_b200_modup_t_to_pql",
-    "ckks_b200_moddown_pql_to_ql", "ckks_b200_keyswitch", "ckks_b200_mult",
+    "ckks_b200_moddown_pql_to_ql", "ckks_b200_keyswitch", "ckks_b200_mult", "ckks_b200_conjugate", "ckks_b200_rotate",
     "ckks_b200_rlwe_decompose", "ckks_b200_mlwe_packing",
     "ckks_b200_pcmm_create", "ckks_b200_pcmm_destroy", "ckks_b200_pcmm_ppmm",
     "ckks_b200_pcmm_ppmm_host", "ckks_b200_pcmm_ppmm_rlwe", "ckks_b200_pcmm_copy_back", "ckks_b200_pcmm_check", "ckks_b200_pcmm_set_peer_outputs", "ckks_b200_pcmm_set_host_chunks", "ckks_b200_ipc_open", "ckks_b200_ipc_close", "ckks_b200_pcmm_last_timing", "ckks_b200_pcmm_ppmm_static",
@@ -83,6 +83,8 @@ def load():
     L.ckks_b200_ipc_close.argtypes = [i, vp]
     L.ckks_b200_keyswitch.argtypes = [vp, vp, vp, vp, i, i, vp]
     L.ckks_b200_mult.argtypes = [vp, vp, vp, vp, vp, i, i, vp]
+    L.ckks_b200_conjugate.argtypes = [vp, vp, vp, vp, i, i, vp]
+    L.ckks_b200_rotate.argtypes = [vp, vp, vp, vp, lng, i, i, vp]
     L.ckks_b200_modup_q0_to_ql.argtypes = [vp, vp, i, i, C.c_longlong, vp]
     L.ckks_b200_rlwe_decompose.argtypes = [vp, vp, i, i, C.POINTER(vp), i, i, i, i, vp]
     L.ckks_b200_mlwe_packing.argtypes = [vp, vp, i, C.POINTER(vp), i, i, i, vp, vp]

@@ -189,6 +189,42 @@ __global__ void __launch_bounds__(kThreads) add_switched_kernel(u64* __restrict_
     cipher[b] = csub(cipher[b] + bx[a], qi);
 }
 
+// sk_and_poly_conjugate_kernel (poly_arithmetic.cuh:666-674): conjugation reverses a polynomial's words in the NTT domain.
+__global__ void __launch_bounds__(kThreads) reverse_kernel(u64* __restrict__ out, const u64* __restrict__ in, uint32_t N) {
+    const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
+    const int i = blockIdx.y;
+    if (x >= N) return;
+    out[(size_t)i * N + x] = in[(size_t)i * N + (N - 1 - x)];
+}
+
+// b half of the switched pair += reversed b of the input (conjugate_23's closing poly_add_batch_device, KeySwitch_23.cuh:469)
+__global__ void __launch_bounds__(kThreads) add_reversed_b_kernel(u64* __restrict__ sw, const u64* __restrict__ cipher, uint32_t N,
+                                                                  int stride, const u64* __restrict__ q) {
+    const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
+    const int i = blockIdx.y;
+    if (x >= N) return;
+    const size_t b = ((size_t)stride + i) * N;
+    sw[b + x] = csub(sw[b + x] + cipher[b + (N - 1 - x)], q[i]);
+}
+
+// leftRotate_23's last two steps in one pass (KeySwitch_23.cuh:577-580): b added to the switched b half
+// (poly_add_batch_device), then both halves permuted in the NTT domain (sk_and_poly_LeftRot_ntt_kernel,
+// poly_arithmetic.cuh:581-596): word x holds the value at the odd power 2*bitrev(x)+1 and goes to the position of
+// the power pow*(2*bitrev(x)+1) mod 2N.
+__global__ void __launch_bounds__(kThreads) rotate_add_kernel(u64* __restrict__ out, const u64* __restrict__ sw,
+                                                              const u64* __restrict__ cipher, uint32_t N, int logN, int stride,
+                                                              const u64* __restrict__ q, u64 pow) {
+    const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
+    const int i = blockIdx.y, half = blockIdx.z;
+    if (x >= N) return;
+    const size_t base = ((size_t)half * stride + i) * N;
+    u64 v = sw[base + x];
+    if (half == 1) v = csub(v + cipher[base + x], q[i]);
+    const u64 odd = 2 * (u64)(__brev(x) >> (32 - logN)) + 1;
+    const uint32_t t = (uint32_t)(((pow * odd) & (2 * (u64)N - 1)) - 1) >> 1;
+    out[base + (__brev(t) >> (32 - logN))] = v;
+}
+
 int check_chain(ckks_b200_context* c, int l, int gamma) {
     CKB_REQUIRE(c != nullptr, CKKS_B200_ERR_ARG, "null argument");
     CKB_REQUIRE(c->t_num > 0 && c->p_num > 0, CKKS_B200_ERR_ARG, "the context has no T basis or no special primes");
@@ -367,5 +403,64 @@ extern "C" int ckks_b200_mult(ckks_b200_context* c, uint64_t* d_res, const uint6
     CKB_CUDA(cudaGetLastError());
     // the switched pair lives in the workspace so that d_res may alias an operand; only limbs 0..l are copied
     CKB_CUDA(cudaMemcpy2DAsync(d_res, limb_words * 8, sw, limb_words * 8, (size_t)(l + 1) * n * 8, 2, cudaMemcpyDeviceToDevice, st));
+    return CKKS_B200_OK;
+}
+
+// Scheme_23::conjugate_23 / conjugateAndEqual_23 (KeySwitch_23.cuh:433-507): a and b reversed in the NTT domain, the
+// chain on the reversed a with the conjugation key, the reversed b added to the b half.  d_res may be d_cipher.
+extern "C" int ckks_b200_conjugate(ckks_b200_context* c, uint64_t* d_res, const uint64_t* d_cipher, const uint64_t* d_conj_key,
+                                   int l, int gamma, void* stream) {
+    int rc = check_chain(c, l, gamma);
+    if (rc) return rc;
+    CKB_REQUIRE(d_res && d_cipher && d_conj_key, CKKS_B200_ERR_ARG, "null argument");
+    DeviceGuard guard(c->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", c->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t n = c->N, limb_words = (size_t)c->q_num * n;
+    rc = ensure_buf(&c->mul_buf, &c->mul_cap, 5 * limb_words);
+    if (rc) return rc;
+    u64 *arev = c->mul_buf, *sw = c->mul_buf + 3 * limb_words;
+    const u64* q = c->d_moduli + c->p_num;
+    dim3 grid((c->N + kThreads - 1) / kThreads, l + 1);
+    reverse_kernel<<<grid, kThreads, 0, st>>>(arev, (const u64*)d_cipher, c->N);
+    count_launch();
+    CKB_CUDA(cudaGetLastError());
+    rc = ckks_b200_keyswitch(c, (uint64_t*)sw, (const uint64_t*)arev, d_conj_key, l, gamma, stream);
+    if (rc) return rc;
+    add_reversed_b_kernel<<<grid, kThreads, 0, st>>>(sw, (const u64*)d_cipher, c->N, c->q_num, q);
+    count_launch();
+    CKB_CUDA(cudaGetLastError());
+    CKB_CUDA(cudaMemcpy2DAsync(d_res, limb_words * 8, sw, limb_words * 8, (size_t)(l + 1) * n * 8, 2, cudaMemcpyDeviceToDevice, st));
+    return CKKS_B200_OK;
+}
+
+// Scheme_23::leftRotate_23 / leftRotateAndEqual_23 (KeySwitch_23.cuh:509-581): the chain on a with the key of this
+// rotation, b added, both halves permuted by the Galois element 5^(N/2 - rot_slots) mod 2N.  d_res may be d_cipher.
+extern "C" int ckks_b200_rotate(ckks_b200_context* c, uint64_t* d_res, const uint64_t* d_cipher, const uint64_t* d_rot_key,
+                                long rot_slots, int l, int gamma, void* stream) {
+    int rc = check_chain(c, l, gamma);
+    if (rc) return rc;
+    CKB_REQUIRE(d_res && d_cipher && d_rot_key, CKKS_B200_ERR_ARG, "null argument");
+    // the reference indexes rotGroups[N/2 - rot_slots], an array of N/2 entries (Context_23.cuh:650-656)
+    CKB_REQUIRE(rot_slots >= 1 && rot_slots <= (long)(c->N / 2), CKKS_B200_ERR_ARG, "rotation by %ld slots outside [1,%u]",
+                rot_slots, c->N / 2);
+    DeviceGuard guard(c->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", c->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t n = c->N, limb_words = (size_t)c->q_num * n;
+    rc = ensure_buf(&c->mul_buf, &c->mul_cap, 5 * limb_words);
+    if (rc) return rc;
+    u64 *out = c->mul_buf, *sw = c->mul_buf + 3 * limb_words;
+    u64 pow = 1;
+    for (long e = 0; e < (long)(c->N / 2) - rot_slots; e++) pow = pow * 5 % (2 * (u64)c->N);
+    rc = ckks_b200_keyswitch(c, (uint64_t*)sw, d_cipher, d_rot_key, l, gamma, stream);
+    if (rc) return rc;
+    int logN = 0;
+    while ((1u << logN) < c->N) logN++;
+    dim3 grid((c->N + kThreads - 1) / kThreads, l + 1, 2);
+    rotate_add_kernel<<<grid, kThreads, 0, st>>>(out, sw, (const u64*)d_cipher, c->N, logN, c->q_num, c->d_moduli + c->p_num, pow);
+    count_launch();
+    CKB_CUDA(cudaGetLastError());
+    CKB_CUDA(cudaMemcpy2DAsync(d_res, limb_words * 8, out, limb_words * 8, (size_t)(l + 1) * n * 8, 2, cudaMemcpyDeviceToDevice, st));
     return CKKS_B200_OK;
 }

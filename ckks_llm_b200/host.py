@@ -159,6 +159,7 @@ class Scheme_23:
 
     def __init__(self, context):
         self.context = context
+        self.rotKey_vec_23 = {}
 
     # Scheme_23::mult_23(cipher_res, cipher1, cipher2), src/ckks/include/KeySwitch_23.cuh:192-236.  rlk_23 is the
     # relinearisation key block [2][dnum][R][t_num][N] (key generation is the caller's).
@@ -176,6 +177,38 @@ class Scheme_23:
                                           _stream_ptr(ctx.device)))
         cipher_res.l = l
         cipher_res.scale = cipher1.scale * cipher2.scale
+
+    # Scheme_23::conjugate_23(cipher_res, cipher) and conjugateAndEqual_23, src/ckks/include/KeySwitch_23.cuh:433-507.
+    # ConjKey_23 is the conjugation key block, laid out like rlk_23.
+    ConjKey_23 = None
+
+    def conjugate_23(self, cipher_res, cipher):
+        if self.ConjKey_23 is None:
+            raise ValueError("conjKey_23 not exists")                      # :435-438
+        ctx = self.context
+        capi.check(ctx.lib.ckks_b200_conjugate(ctx._h, cipher_res.cipher_device.data_ptr(), cipher.cipher_device.data_ptr(),
+                                               self.ConjKey_23.data_ptr(), cipher.l, ctx.gamma, _stream_ptr(ctx.device)))
+        cipher_res.l = cipher.l
+        cipher_res.scale = cipher.scale
+
+    def conjugateAndEqual_23(self, cipher):
+        self.conjugate_23(cipher, cipher)
+
+    # Scheme_23::leftRotate_23(cipher_res, cipher, rotSlots) and leftRotateAndEqual_23, KeySwitch_23.cuh:509-581.
+    # rotKey_vec_23 maps a rotation to its key block (addLeftRotKey_23 of the reference fills it; key generation is
+    # the caller's here).
+    def leftRotate_23(self, cipher_res, cipher, rotSlots):
+        key = self.rotKey_vec_23.get(rotSlots)
+        if key is None:
+            raise ValueError("rotKey_23 not exists")                       # :511-514
+        ctx = self.context
+        capi.check(ctx.lib.ckks_b200_rotate(ctx._h, cipher_res.cipher_device.data_ptr(), cipher.cipher_device.data_ptr(),
+                                            key.data_ptr(), int(rotSlots), cipher.l, ctx.gamma, _stream_ptr(ctx.device)))
+        cipher_res.l = cipher.l
+        cipher_res.scale = cipher.scale
+
+    def leftRotateAndEqual_23(self, cipher, rotSlots):
+        self.leftRotate_23(cipher, cipher, rotSlots)
 
     # Scheme_23::rescaleAndEqual(Ciphertext&), src/ckks/include/Scheme_23.cuh:368-385
     def rescaleAndEqual(self, cipher):

@@ -150,6 +150,18 @@ int ckks_b200_keyswitch(ckks_b200_context* ctx, uint64_t* d_out, const uint64_t*
  * d_res may be one of the operands.  The caller multiplies the scales and sets the level (:211-212). */
 int ckks_b200_mult(ckks_b200_context* ctx, uint64_t* d_res, const uint64_t* d_c1, const uint64_t* d_c2,
                    const uint64_t* d_rlk, int l, int gamma, void* stream);
+/* Scheme_23::conjugate_23 and conjugateAndEqual_23 (KeySwitch_23.cuh:433-507): both polynomials reversed in the NTT
+ * domain (sk_and_poly_conjugate_kernel, poly_arithmetic.cuh:666-674), the key-switch chain on the reversed a with
+ * the conjugation key d_conj_key (laid out like every switching key above), the reversed b added to the b half.
+ * d_res and d_cipher: Ciphertext buffers [2][q_num][N], NTT domain, level l; d_res may be d_cipher. */
+int ckks_b200_conjugate(ckks_b200_context* ctx, uint64_t* d_res, const uint64_t* d_cipher, const uint64_t* d_conj_key,
+                        int l, int gamma, void* stream);
+/* Scheme_23::leftRotate_23 and leftRotateAndEqual_23 (KeySwitch_23.cuh:509-581): the chain on a with the key of
+ * this rotation, b added to the b half, both halves permuted in the NTT domain by the Galois element
+ * 5^(N/2 - rot_slots) mod 2N (sk_and_poly_LeftRot_ntt_kernel, poly_arithmetic.cuh:581-596; rotGroups,
+ * Context_23.cuh:650-656).  1 <= rot_slots <= N/2.  d_res may be d_cipher. */
+int ckks_b200_rotate(ckks_b200_context* ctx, uint64_t* d_res, const uint64_t* d_cipher, const uint64_t* d_rot_key,
+                     long rot_slots, int l, int gamma, void* stream);
 
 /* ---- ring packing, RLWE -> MLWE ---------------------------------------------
  * PCMM_Scheme::rlweCipherDecompose (pcmm/PCMM_Scheme.cuh:51-125): d_rlwe is the

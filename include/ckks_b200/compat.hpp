@@ -19,6 +19,7 @@
 #include <iostream>
 #include <stdexcept>
 #include <string>
+#include <map>
 #include <vector>
 
 #include "../ckks_b200.h"
@@ -109,6 +110,30 @@ public:
                              (const uint64_t*)cipher2.cipher_device, (const uint64_t*)rlk_23, l, context.gamma, stream));
         cipher_res.l = l;
         cipher_res.scale = cipher1.scale * cipher2.scale;
+    }
+    // Scheme_23::conjugate_23 / conjugateAndEqual_23 (KeySwitch_23.cuh:433-507); ConjKey_23 is the key block on the device.
+    uint64_tt* ConjKey_23 = nullptr;
+    void conjugate_23(Ciphertext& cipher_res, Ciphertext& cipher, cudaStream_t stream = 0) {
+        if (ConjKey_23 == nullptr) throw std::invalid_argument("conjKey_23 not exists");
+        check(ckks_b200_conjugate(context.b200, (uint64_t*)cipher_res.cipher_device, (const uint64_t*)cipher.cipher_device,
+                                  (const uint64_t*)ConjKey_23, cipher.l, context.gamma, stream));
+        cipher_res.l = cipher.l;
+        cipher_res.scale = cipher.scale;
+    }
+    void conjugateAndEqual_23(Ciphertext& cipher, cudaStream_t stream = 0) { conjugate_23(cipher, cipher, stream); }
+    // Scheme_23::leftRotate_23 / leftRotateAndEqual_23 (KeySwitch_23.cuh:509-581); rotKey_vec_23[rotSlots] is the key
+    // block of that rotation on the device (the reference's addLeftRotKey_23 fills it).
+    std::map<long, uint64_tt*> rotKey_vec_23;
+    void leftRotate_23(Ciphertext& cipher_res, Ciphertext& cipher, long rotSlots, cudaStream_t stream = 0) {
+        auto it = rotKey_vec_23.find(rotSlots);
+        if (it == rotKey_vec_23.end() || it->second == nullptr) throw std::invalid_argument("rotKey_23 not exists");
+        check(ckks_b200_rotate(context.b200, (uint64_t*)cipher_res.cipher_device, (const uint64_t*)cipher.cipher_device,
+                               (const uint64_t*)it->second, rotSlots, cipher.l, context.gamma, stream));
+        cipher_res.l = cipher.l;
+        cipher_res.scale = cipher.scale;
+    }
+    void leftRotateAndEqual_23(Ciphertext& cipher, long rotSlots, cudaStream_t stream = 0) {
+        leftRotate_23(cipher, cipher, rotSlots, stream);
     }
     void rescaleAndEqual(Ciphertext& cipher, cudaStream_t stream = 0) {
         check(ckks_b200_rescale(context.b200, (uint64_t*)cipher.cipher_device, cipher.L, cipher.l, stream));

@@ -368,3 +368,57 @@ def mult(c1, c2, rlk, tables, KT, l, gamma):
     lib().orc_add_switched(res.reshape(-1), axbx.reshape(-1), bxbx.reshape(-1), n, len(KT.q), l + 1,
                            np.array(KT.q, dtype=np.uint64))
     return res
+
+
+def _bitrev(x, bits):
+    x = np.asarray(x, dtype=np.int64)
+    r = np.zeros_like(x)
+    for b in range(bits):
+        r |= ((x >> b) & 1) << (bits - 1 - b)
+    return r
+
+
+def rotation_map(n, rot_slots):
+    """Destination index of every NTT-domain word under sk_and_poly_LeftRot_ntt_kernel
+    (poly_arithmetic.cuh:581-596): pow = rotGroups[n/2 - rot_slots] with rotGroups[i] = 5^i mod 2n
+    (Context_23.cuh:648-659); word j, which holds the value at the odd power 2*bitrev(j)+1, goes to the
+    position that holds the power pow*(2*bitrev(j)+1) mod 2n."""
+    logn = n.bit_length() - 1
+    power = pow(5, n // 2 - rot_slots, 2 * n)
+    j = np.arange(n, dtype=np.int64)
+    t = 2 * _bitrev(j, logn) + 1
+    t = (((power * t) & (2 * n - 1)) - 1) >> 1
+    return _bitrev(t, logn)
+
+
+def conjugate(cipher, conj_key, tables, KT, l, gamma):
+    """Scheme_23::conjugate_23 (KeySwitch_23.cuh:433-470): both polynomials reversed in the NTT domain
+    (sk_and_poly_conjugate_kernel, poly_arithmetic.cuh:666-674), the chain on the reversed a with the
+    conjugation key, the reversed b added to the b half (poly_add_batch_device).  cipher [2][q_num][n]."""
+    q_num = len(KT.q)
+    cipher = np.ascontiguousarray(cipher, dtype=np.uint64).reshape(2, q_num, tables.n)
+    ac = np.ascontiguousarray(cipher[0, :l + 1, ::-1])
+    bc = cipher[1, :l + 1, ::-1]
+    res = keyswitch(ac, conj_key, tables, KT, l, gamma)
+    for i in range(l + 1):
+        qi = np.uint64(KT.q[i])
+        s = res[1, i] + bc[i]
+        res[1, i] = np.where(s >= qi, s - qi, s)
+    return res
+
+
+def rotate(cipher, rot_key, rot_slots, tables, KT, l, gamma):
+    """Scheme_23::leftRotate_23 (KeySwitch_23.cuh:548-581): the chain on a with the rotation key, b added to
+    the b half, then both halves permuted in the NTT domain (sk_and_poly_LeftRot_ntt_double,
+    poly_arithmetic.cuh:581-603).  cipher [2][q_num][n]."""
+    n, q_num = tables.n, len(KT.q)
+    cipher = np.ascontiguousarray(cipher, dtype=np.uint64).reshape(2, q_num, n)
+    sw = keyswitch(np.ascontiguousarray(cipher[0, :l + 1]), rot_key, tables, KT, l, gamma)
+    for i in range(l + 1):
+        qi = np.uint64(KT.q[i])
+        s = sw[1, i] + cipher[1, i]
+        sw[1, i] = np.where(s >= qi, s - qi, s)
+    dst = rotation_map(n, rot_slots)
+    res = np.zeros_like(sw)
+    res[:, :l + 1, dst] = sw[:, :l + 1, :]
+    return res

@@ -35,6 +35,8 @@ def lib():
         L.ref_keyswitch_stage.argtypes = [_U64P, _U64P, _U64P, C.c_int, _U64P] + [C.c_int] * 6 + [_U64P] * 10
         if hasattr(L, "ref_tensor_product"):
             L.ref_tensor_product.argtypes = [_U64P, _U64P, _U64P, C.c_int, _U64P, C.c_int, C.c_int, C.c_int, C.c_int]
+        if hasattr(L, "ref_galois"):
+            L.ref_galois.argtypes = [_U64P, _U64P, C.c_int, _U64P, C.c_int, C.c_int, C.c_int, C.c_long, C.c_int]
         L.ref_decompose.argtypes = [_U64P, _U64P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _U64P]
         _lib = L
     return _lib
@@ -206,3 +208,16 @@ def add_switched(cipher, axbx, logN, pq, p_num, l):
                                   np.ascontiguousarray(pq, dtype=np.uint64), p_num, q_num, l, 1)
     assert rc == 0, rc
     return c
+
+
+def galois(cipher, logN, pq, p_num, l, mode, rot_slots=0, into=None):
+    """The reference's own kernels for the steps conjugate_23 and leftRotate_23 add around the chain, on a
+    Ciphertext buffer [2][q_num][N]: mode 0 = sk_and_poly_conjugate of both halves, mode 1 =
+    sk_and_poly_LeftRot_ntt_double by rot_slots, mode 2 = poly_add_batch_device of the b half onto `into`."""
+    c = np.ascontiguousarray(cipher, dtype=np.uint64)
+    q_num = c.shape[1]
+    out = np.zeros_like(c) if into is None else np.ascontiguousarray(into, dtype=np.uint64).copy()
+    rc = lib().ref_galois(out.reshape(-1), c.reshape(-1), logN, np.ascontiguousarray(pq, dtype=np.uint64), p_num, q_num, l,
+                          int(rot_slots), mode)
+    assert rc == 0, rc
+    return out

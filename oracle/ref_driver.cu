@@ -484,3 +484,43 @@ extern "C" int ref_tensor_product(unsigned long long* h_out, unsigned long long*
     cudaFree(d1); cudaFree(d2); cudaFree(d3);
     return 0;
 }
+
+// The three small steps Scheme_23::conjugate_23 and leftRotate_23 add around the key-switch chain
+// (KeySwitch_23.cuh:452-453, :469, :577-580), on Ciphertext buffers [2][q_num][N]; pq = [p | q].
+//   mode 0: sk_and_poly_conjugate on limbs 0..l of both halves of h_in -> h_out          (poly_arithmetic.cuh:666-680)
+//   mode 1: sk_and_poly_LeftRot_ntt_double of h_in by rot_slots -> h_out, with rotGroups built as
+//           Context_23.cuh:650-656 builds them                                            (poly_arithmetic.cuh:581-603)
+//   mode 2: poly_add_batch_device: b half of h_out (preloaded) += b half of h_in        (poly_arithmetic.cuh:111-121, :395-399)
+extern "C" int ref_galois(unsigned long long* h_out, const unsigned long long* h_in, int logN,
+                          const unsigned long long* pq, int p_num, int q_num, int l, long rot_slots, int mode) {
+    const int n_mod = p_num + q_num;
+    if (n_mod > max_pqt_num) return 1;
+    const long N = 1L << logN, Nh = N / 2, M = 2 * N;
+    int rc = upload_pqt(pq, n_mod);
+    if (rc) return rc;
+    const size_t half = (size_t)q_num * N, bytes = 8 * 2 * half;
+    uint64_tt *din = nullptr, *dout = nullptr, *drot = nullptr;
+    RD_CUDA(cudaMalloc(&din, bytes));
+    RD_CUDA(cudaMalloc(&dout, bytes));
+    RD_CUDA(cudaMemcpy(din, h_in, bytes, cudaMemcpyHostToDevice));
+    RD_CUDA(cudaMemcpy(dout, h_out, bytes, cudaMemcpyHostToDevice));
+    if (mode == 0) {
+        sk_and_poly_conjugate(dout, din, N, q_num, 0, 0, l + 1);
+        sk_and_poly_conjugate(dout + half, din + half, N, q_num, 0, 0, l + 1);
+    } else if (mode == 1) {
+        std::vector<uint64_tt> rot(Nh);
+        long five = 1;
+        for (long i = 0; i < Nh; ++i) { rot[i] = five; five = five * 5 % M; }
+        RD_CUDA(cudaMalloc(&drot, 8 * Nh));
+        RD_CUDA(cudaMemcpy(drot, rot.data(), 8 * Nh, cudaMemcpyHostToDevice));
+        sk_and_poly_LeftRot_ntt_double(dout, din, drot, N, p_num, q_num, rot_slots, 0, 0, l + 1);
+    } else {
+        poly_add_batch_device(dout + half, din + half, N, 0, 0, p_num, l + 1);
+    }
+    RD_CUDA(cudaGetLastError());
+    RD_CUDA(cudaDeviceSynchronize());
+    RD_CUDA(cudaMemcpy(h_out, dout, bytes, cudaMemcpyDeviceToHost));
+    cudaFree(din); cudaFree(dout);
+    if (drot) cudaFree(drot);
+    return 0;
+}

@@ -110,3 +110,50 @@ def test_mult_23(oracle, cuda_device, logN, p_num, q_num, t_num, gamma, l):
     with pytest.raises(ValueError):
         sch.mult_23(a, a, zero)
     ctx.close()
+
+
+@pytest.mark.parametrize("logN,p_num,q_num,t_num,gamma,l", [(12, 2, 6, 4, 3, 5), (13, 1, 4, 3, 3, 2)])
+def test_conjugate_and_rotate(oracle, cuda_device, logN, p_num, q_num, t_num, gamma, l):
+    """conjugate_23 and leftRotate_23 through the Scheme_23 mirror, out of place and in place, against the oracle."""
+    from ckks_llm_b200.host import Ciphertext, Scheme_23
+    N, p, q, t, ctx, KT = _setup(oracle, logN, p_num, q_num, t_num, gamma)
+    R, cb, dnum, blocks = _shapes(p, q, t, l, gamma)
+    rng = np.random.default_rng(21 + logN)
+    T = oracle.NttTables(N, p + q + t)
+    c = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)])
+    c[:, :, :2] = (np.array(q, dtype=np.uint64) - np.uint64(1))[None, :, None]
+    key = np.stack([H.uniform_residues(rng, t, (N,)) for _ in range(2 * dnum * R)]).reshape(2, dnum, R, t_num, N)
+    L = len(q) - 1
+    sch = Scheme_23(ctx)
+    src = Ciphertext(N, L, l, N // 2, 2.0 ** 40, cipher=as_u64_tensor(c.reshape(-1), ctx.device))
+    res = Ciphertext(N, L, L, N // 2, 1.0, cipher=torch.zeros(2 * len(q) * N, dtype=torch.int64, device=ctx.device))
+    with pytest.raises(ValueError):
+        sch.conjugate_23(res, src)                                                    # no key yet
+    with pytest.raises(ValueError):
+        sch.leftRotate_23(res, src, 3)
+    kd = as_u64_tensor(key.reshape(-1), ctx.device)
+    sch.ConjKey_23 = kd
+    exp = oracle.conjugate(c, key, T, KT, l, gamma)
+    sch.conjugate_23(res, src)
+    got = to_u64_numpy(res.cipher_device).reshape(2, len(q), N)
+    assert np.array_equal(got[:, :l + 1], exp[:, :l + 1]) and not got[:, l + 1:].any()
+    assert res.l == l and res.scale == 2.0 ** 40
+    assert np.array_equal(to_u64_numpy(src.cipher_device).reshape(c.shape), c)        # the source is untouched
+    for rot in (1, N // 2, 37):
+        sch.rotKey_vec_23[rot] = kd
+        exp = oracle.rotate(c, key, rot, T, KT, l, gamma)
+        sch.leftRotate_23(res, src, rot)
+        got = to_u64_numpy(res.cipher_device).reshape(2, len(q), N)
+        assert np.array_equal(got[:, :l + 1], exp[:, :l + 1]), rot
+    inplace = Ciphertext(N, L, l, N // 2, 1.0, cipher=as_u64_tensor(c.reshape(-1), ctx.device))
+    sch.leftRotateAndEqual_23(inplace, 37)
+    got = to_u64_numpy(inplace.cipher_device).reshape(2, len(q), N)
+    assert np.array_equal(got[:, :l + 1], exp[:, :l + 1]) and np.array_equal(got[:, l + 1:], c[:, l + 1:])
+    inplace = Ciphertext(N, L, l, N // 2, 1.0, cipher=as_u64_tensor(c.reshape(-1), ctx.device))
+    sch.conjugateAndEqual_23(inplace)
+    exp = oracle.conjugate(c, key, T, KT, l, gamma)
+    assert np.array_equal(to_u64_numpy(inplace.cipher_device).reshape(2, len(q), N)[:, :l + 1], exp[:, :l + 1])
+    L_ = ctx.lib
+    assert L_.ckks_b200_rotate(ctx._h, res.cipher_device.data_ptr(), src.cipher_device.data_ptr(), kd.data_ptr(), 0, l, gamma,
+                               None) != 0                                             # outside the rotation group table
+    ctx.close()

@@ -209,3 +209,30 @@ def test_reference_tensor_product_and_addition(oracle, cuda_device):
     oracle.lib().orc_add_switched(exp.reshape(-1), np.ascontiguousarray(ref[0]).reshape(-1), np.ascontiguousarray(ref[2]).reshape(-1),
                                   N, len(q), l + 1, np.array(q, dtype=np.uint64))
     assert np.array_equal(exp, summed)
+
+
+def test_reference_conjugation_and_rotation_steps(oracle, cuda_device):
+    """sk_and_poly_conjugate, sk_and_poly_LeftRot_ntt_double and poly_add_batch_device (poly_arithmetic.cuh:666-680,
+    :581-603, :395-399) == the oracle's index maps and addition, at the two ring sizes the reference runs."""
+    if not hasattr(R_.lib(), "ref_galois"):
+        pytest.skip("reference driver built without the conjugation / rotation entry")
+    for logN, rots in ((12, (1, 5, 1000, 2048)), (14, (3, 8191))):
+        N, l = 1 << logN, 2
+        p = params.ntt_primes(51, 2 * N, 1)
+        q = params.ntt_primes(50, 2 * N, 4)
+        rng = np.random.default_rng(50 + logN)
+        c = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)])
+        rev = R_.galois(c, logN, p + q, len(p), l, 0)
+        assert np.array_equal(rev[:, :l + 1], c[:, :l + 1, ::-1]) and not rev[:, l + 1:].any()
+        for rot in rots:
+            out = R_.galois(c, logN, p + q, len(p), l, 1, rot_slots=rot)
+            exp = np.zeros_like(c)
+            exp[:, :l + 1, oracle.rotation_map(N, rot)] = c[:, :l + 1]
+            assert np.array_equal(out, exp), rot
+        other = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)])
+        other[1, :, 0] = c[1, :, 0] = np.array(q, dtype=np.uint64) - np.uint64(1)
+        summed = R_.galois(c, logN, p + q, len(p), l, 2, into=other)
+        exp = other.copy()
+        for i in range(l + 1):
+            exp[1, i] = ((other[1, i].astype(object) + c[1, i].astype(object)) % q[i]).astype(np.uint64)
+        assert np.array_equal(summed, exp)

@@ -81,3 +81,65 @@ def test_moddown_subtracts_the_p_part(oracle):
                         part = sum((int(inp[c, j, x]) * pow(P // p[j], -1, p[j]) % p[j]) * (P // p[j]) for j in range(p_num)) % qi
                     exp.append((int(inp[c, p_num + i, x]) - part) * pow(P, -1, qi) % qi)
                 assert out[c, i].tolist() == exp
+
+
+def _automorphism(f, e, q):
+    """f(X^e) modulo X^n + 1 and q, e odd."""
+    n = len(f)
+    g = [0] * n
+    for j, v in enumerate(f):
+        k = j * e % (2 * n)
+        if k < n:
+            g[k] = (g[k] + int(v)) % q
+        else:
+            g[k - n] = (g[k - n] - int(v)) % q
+    return np.array(g, dtype=np.uint64)
+
+
+def test_rotation_map_and_reversal_are_the_galois_automorphisms(oracle):
+    """In the NTT domain the reference rotates by permuting words and conjugates by reversing them
+    (poly_arithmetic.cuh:581-596, :666-674).  The oracle's maps must be the automorphisms X -> X^(5^r) and
+    X -> X^-1 of the coefficient domain."""
+    n = 64
+    q = params.ntt_primes(40, 2 * n, 1)
+    T = oracle.NttTables(n, q)
+    rng = np.random.default_rng(3)
+    f = H.uniform_residues(rng, q, (n,))[0]
+
+    def ntt(x):
+        y = np.ascontiguousarray(x, dtype=np.uint64).copy()
+        oracle.ntt_batch(y, T, 0, 0, 1, 1, 1)
+        return y
+
+    F = ntt(f)
+    for rot in (1, 2, 7, 31, 32):
+        dst = oracle.rotation_map(n, rot)
+        assert sorted(dst.tolist()) == list(range(n))
+        out = np.zeros_like(F)
+        out[dst] = F
+        assert np.array_equal(out, ntt(_automorphism(f, pow(5, rot, 2 * n), q[0]))), rot
+    assert np.array_equal(F[::-1], ntt(_automorphism(f, 2 * n - 1, q[0])))
+
+
+def test_conjugate_and_rotate_compose_the_chain(oracle):
+    """conjugate_23 / leftRotate_23 = index map, chain, addition (KeySwitch_23.cuh:433-470, :548-581)."""
+    n, gamma, l = 64, 3, 3
+    p, q, t, KT = _setup(oracle)
+    T = oracle.NttTables(n, p + q + t)
+    rng = np.random.default_rng(5)
+    R = (len(p) + len(q) + gamma - 1) // gamma
+    dnum = len(q) // len(p)
+    c = np.stack([H.uniform_residues(rng, q, (n,)) for _ in range(2)])
+    key = np.stack([H.uniform_residues(rng, t, (n,)) for _ in range(2 * dnum * R)]).reshape(2, dnum, R, len(t), n)
+    got = oracle.conjugate(c, key, T, KT, l, gamma)
+    sw = oracle.keyswitch(np.ascontiguousarray(c[0, :l + 1, ::-1]), key, T, KT, l, gamma)
+    for i in range(l + 1):
+        assert np.array_equal(got[0, i], sw[0, i])
+        assert got[1, i].tolist() == [(int(a) + int(b)) % q[i] for a, b in zip(sw[1, i], c[1, i, ::-1])]
+    rot = 9
+    got = oracle.rotate(c, key, rot, T, KT, l, gamma)
+    sw = oracle.keyswitch(np.ascontiguousarray(c[0, :l + 1]), key, T, KT, l, gamma)
+    dst = oracle.rotation_map(n, rot)
+    for i in range(l + 1):
+        assert np.array_equal(got[0, i][dst], sw[0, i])
+        assert got[1, i][dst].tolist() == [(int(a) + int(b)) % q[i] for a, b in zip(sw[1, i], c[1, i])]
