@@ -319,12 +319,12 @@ extern "C" int ckks_b200_pcmm_ppmm_rlwe(ckks_b200_pcmm* pc, const float* d_W, co
     int w_bits = 0;
     rc = prepare(pc, d_W, nullptr, mat_M, mat_N, scaler, st, &w_bits);      // synchronises: `slots` may go out of scope
     if (rc) return rc;
-    // the pre-pass that shares RLWE words between polynomials wants whole K blocks of 64 from one source
+    // the pre-pass that shares RLWE words between polynomials wants every aligned run of 16 ciphertexts from one source
     bool regular = pc->N1 % 32 == 0 && (long)pc->rank * pc->N1 >= 256;     // its index arithmetic wraps at most once
-    for (int n0 = 0; n0 < mlwe_num && regular; n0 += 64) {
+    for (int n0 = 0; n0 < mlwe_num && regular; n0 += 16) {
         const RlweSlot& f = slots[n0];
         if (f.gap > pcmm_slots_max_gap()) regular = false;
-        for (int n = n0 + 1; n < mlwe_num && n < n0 + 64 && regular; n++)
+        for (int n = n0 + 1; n < mlwe_num && n < n0 + 16 && regular; n++)
             regular = slots[n].rlwe == f.rlwe && slots[n].L == f.L && slots[n].gap == f.gap && slots[n].i == f.i + (n - n0);
     }
     return pcmm_tensor(pc, pc->d_w, nullptr, pc->d_slots, regular, (u64*)d_out, mat_M, mat_N, col_begin, col_end, w_bits,

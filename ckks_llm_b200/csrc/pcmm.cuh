@@ -81,7 +81,7 @@ int ensure_dev(T** buf, size_t* cap, size_t count) {
 // Tensor-core path (pcmm_umma.cu).  w_bits = bit length of the largest |w|.  The ciphertext words come from
 // the pointer table d_xptrs, or, when d_slots is given, straight from RLWE ciphertexts through the
 // decomposition's index map.
-// slots_regular: N1 is a multiple of 32, every 64-ciphertext K block lies in one source with consecutive
+// slots_regular: N1 is a multiple of 32, every aligned run of 16 ciphertexts lies in one source with consecutive
 // indices and no gap exceeds pcmm_slots_max_gap(), which lets the pre-pass share RLWE words between polynomials.
 int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots,
                 bool slots_regular, u64* d_out, int M, int K, long col_begin, long col_end, int w_bits, cudaStream_t st);

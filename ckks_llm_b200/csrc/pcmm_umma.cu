@@ -213,18 +213,19 @@ __global__ void __launch_bounds__(256) slice_rlwe_kernel(const RlweSlot* __restr
     }
 }
 
-// The same pre-pass for the usual case (N1 a multiple of 32, every 64-ciphertext K block
-// inside one source, gaps of at most 2), using the structure of the decomposition: with
-// the negacyclic convention A[x +- N] = -A[x], word g of polynomial r < k of ciphertext i is
+// The same pre-pass for the usual case (N1 a multiple of 32, every aligned run of 16
+// ciphertexts inside one source, gaps of at most 2), using the structure of the
+// decomposition: with the negacyclic convention A[x +- N] = -A[x], word g of polynomial
+// r < k of ciphertext i is
 //   a_i,r[g] = A[g*k + i*gap - r]          (b_i[g] = B[g*k + i*gap])
 // so ciphertexts i and polynomials r see the same RLWE words shifted against one another.
-// A block takes 32 values of g, one K block of 64 ciphertexts and RB polynomials: it loads
-// the 32 runs of 63*gap + RB words those share (7 % of the words it emits, at a gap of one)
-// into shared memory and cuts the planes of its RB column tiles from them.  The last
-// "row block" is the b polynomial alone.
+// A block takes 32 values of g, one K block of 64 ciphertexts (four runs of 16, each from
+// its own source) and RB polynomials: per run and g it loads the 15*gap + RB words those
+// share (12 % of the words it emits, at a gap of one) into shared memory and cuts the
+// planes of its RB column tiles from them.  The last "row block" is the b polynomial alone.
 constexpr int RB = 16;
 constexpr int SEG_MAX_GAP = 2;
-constexpr int SEG = 63 * SEG_MAX_GAP + RB + 1;     // odd: lanes along g fall into distinct banks (32-bit words)
+constexpr int SEG = 15 * SEG_MAX_GAP + RB + 1;     // odd: lanes along g fall into distinct banks (32-bit words)
 
 __global__ void __launch_bounds__(256) slice_rlwe_rows_kernel(const RlweSlot* __restrict__ slots, uint8_t* __restrict__ planes,
                                                               const PcmmLimb* __restrict__ limbs, int K, long N, int N1,
@@ -232,7 +233,7 @@ __global__ void __launch_bounds__(256) slice_rlwe_rows_kernel(const RlweSlot* __
                                                               int SC) {
     static_assert(KB == 64 && TC == 32, "the thread mapping below is written for 64 x 32 tiles");
     // low and high words apart: a thread cuts either planes 0-3 or planes 4-7 and reads only the words it needs
-    __shared__ uint32_t seg[2][TC][SEG];
+    __shared__ uint32_t seg[2][4][TC][SEG];
     const int g_tiles = N1 / TC, rbn = (rank + RB - 1) / RB;
     const int gt = blockIdx.x % g_tiles, rb = blockIdx.x / g_tiles;
     const int kb = blockIdx.y, limb = blockIdx.z;
@@ -247,36 +248,41 @@ __global__ void __launch_bounds__(256) slice_rlwe_rows_kernel(const RlweSlot* __
     }
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int n0 = kb * KB;
-    const RlweSlot s = slots[n0];
-    const int gap = s.gap;
-    const int span = 63 * gap + RB;
-    const u64* src = s.rlwe + N * ((bpoly ? s.L + 1 : 0) + limb);
     const u64 q = limbs[limb].q;
-    // seg[.][g][x] = A[(g0+g)*k + i0*gap - (r0 + RB - 1) + x], sign folded in
-    for (int g = warp; g < TC; g += 8) {
-        const long base = (long)(g0 + g) * rank + (long)s.i * gap - (r0 + RB - 1);
-        for (int x = lane; x < span; x += 32) {
-            long idx = base + x;
-            bool neg = false;
-            if (idx < 0) { idx += N; neg = true; }
-            else if (idx >= N) { idx -= N; neg = true; }
-            u64 v = src[idx];
-            if (neg) v = v == 0 ? 0 : q - v;
-            seg[0][g][x] = (uint32_t)v;
-            seg[1][g][x] = (uint32_t)(v >> 32);
+    {
+        // warp w loads run w & 3 for every other g: seg[.][run][g][x] = A[(g0+g)*k + i0*gap - (r0 + RB - 1) + x], signed
+        const int run = warp & 3, nr = n0 + run * 16;
+        if (nr < K) {
+            const RlweSlot s = slots[nr];
+            const int span = 15 * s.gap + RB;
+            const u64* src = s.rlwe + N * ((bpoly ? s.L + 1 : 0) + limb);
+            for (int g = warp >> 2; g < TC; g += 2) {
+                const long base = (long)(g0 + g) * rank + (long)s.i * s.gap - (r0 + RB - 1);
+                for (int x = lane; x < span; x += 32) {
+                    long idx = base + x;
+                    bool neg = false;
+                    if (idx < 0) { idx += N; neg = true; }
+                    else if (idx >= N) { idx -= N; neg = true; }
+                    u64 v = src[idx];
+                    if (neg) v = v == 0 ? 0 : q - v;
+                    seg[0][run][g][x] = (uint32_t)v;
+                    seg[1][run][g][x] = (uint32_t)(v >> 32);
+                }
+            }
         }
     }
     __syncthreads();
     const int cc = t & 31, k16 = (t >> 5) & 3, half = t >> 7;
     const int ks = k16 / 2, kc = k16 % 2;
-    const uint32_t* row = seg[half][cc];
-    const int valid = K - n0 - k16 * 16;                                   // ciphertexts of this 16-chunk that exist
+    const uint32_t* row = seg[half][k16][cc];
+    const int valid = K - n0 - k16 * 16;                                   // ciphertexts of this run that exist
+    const int gap = valid > 0 ? slots[n0 + k16 * 16].gap : 1;
     for (int rr = 0; rr < rows; rr++) {
         const long c = (long)(crow0 + rr) * N1 + g0;
         if (c < col_begin || c >= col_end) continue;                       // block-uniform
         const int ct = (int)((c - col_begin) / TC);
         uint32_t w[16];
-        int x = k16 * 16 * gap - rr + (RB - 1);
+        int x = (RB - 1) - rr;
 #pragma unroll
         for (int e = 0; e < 16; e++, x += gap) w[e] = e < valid ? row[x] : 0u;
         uint8_t* dst = planes + ((((size_t)limb * CT + ct) * KBN + kb) * KS + ks) * SC * B_PLANE_STEP +
@@ -520,10 +526,28 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                 // Transpose through the warp's staging tile so that every store instruction
                 // writes whole 128-byte lines: lane = row while writing the tile, lanes run
                 // along a row while reading it back.
+                if (PEERS) bulk_wait_read();              // the copy engine is done reading this lane's row of the tile
                 __syncwarp();
 #pragma unroll
                 for (int e = 0; e < 8; e++)
                     *reinterpret_cast<ulonglong2*>(stg + lane * STG_ROW + e * 16) = make_ulonglong2(res[2 * e], res[2 * e + 1]);
+                if (PEERS) {
+                    // A lane's row of the tile is 128 contiguous bytes of the output: one bulk copy per destination
+                    // (the local buffer and every peer's, over NVLink) straight from the staging tile.  The copies
+                    // run on the copy engine, so the warp does not issue 8 x 8 sixteen-byte stores per row and
+                    // goes back to the next tile while they drain.
+                    const bool whole = vec_ok && c0 + 16 <= P.col_end && mt * TM + quarter * 32 + 32 <= P.M;    // warp-uniform
+                    if (whole) {
+                        fence_proxy_async_smem();
+                        const size_t off = ((size_t)(mt * TM + quarter * 32 + lane) * limbs_n + limb) * P.C + c0;
+                        const uint32_t src = smem_u32(stg + lane * STG_ROW);
+                        bulk_s2g(P.out + off, src, 128);
+                        for (int dest = 0; dest < P.n_peers; dest++) bulk_s2g(P.peers[dest] + off, src, 128);
+                        bulk_commit();
+                        CKB_PROF_END(2);
+                        continue;
+                    }
+                }
                 __syncwarp();
                 const int sub_r = lane >> 3, pair = lane & 7;
                 const long c = c0 + pair * 2;
@@ -553,6 +577,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
 #ifdef CKB_PROFILE
         if (blockIdx.x == 0 && warp == 2 && lane == 0) { P.flags[12] = (int)(prof_acc_[0] >> 10); P.flags[13] = (int)(prof_acc_[1] >> 10); P.flags[14] = (int)(prof_acc_[2] >> 10); }
 #endif
+        if (PEERS) bulk_wait_all();                       // every destination is written before the CTA retires
         if (!ok) atomicExch(&abort_flag, 1);
     }
 

@@ -171,7 +171,7 @@ def test_peer_output_buffers_receive_the_same_words(oracle, cuda_device):
     """The epilogue's extra stores into other GPUs' output buffers, exercised with two more buffers on this GPU:
     each must end up with exactly the words of the local output, inside the column range only."""
     q = params.ntt_primes(50, 1 << 13, 3)
-    N1, rank, M, K = 64, 3, 160, 96              # M spans two 128-row tiles, the second one ragged
+    N1, rank, M, K = 64, 3, 150, 96              # M spans two 128-row tiles; the second ends inside a 32-row group
     Cw = (rank + 1) * N1
     rng = np.random.default_rng(12)
     W = rng.uniform(-1, 1, (M, K)).astype(np.float32)

@@ -179,6 +179,7 @@ def test_packing_stages_match_reference_kernels(oracle, cuda_device):
     (13, 32, [(128, 0), (256, 128)], 130),       # the pipeline's pattern: one source half taken, one whole
     (12, 64, [(64, 0), (36, 64)], 33),           # whole K blocks per source, the last one ragged
     (12, 32, [(128, 0)], 16),                    # rank 128: eight row blocks of polynomials per tile column
+    (12, 128, [(32, 0), (16, 32), (32, 48)], 24),  # rank 32: K blocks of 64 made of runs of 16 from different sources
 ])
 def test_decompose_and_ppmm_in_one_call(oracle, cuda_device, logN, N1, parts, M):
     """The multiply that reads RLWE ciphertexts through the decomposition's index map gives, word for word,
