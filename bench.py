@@ -401,7 +401,7 @@ def bench_pcmm_shape(torch, device, steps, warmup, peaks, name, rank=0, world=1,
         dist.all_reduce(okt, op=dist.ReduceOp.MIN)
         fused = {"ms": float(tt.item()), "ct_rows_per_sec": c["M"] / (float(tt.item()) * 1e-3),
                  "matches_nccl_gather": bool(okt.item()),
-                 "note": "one launch per rank: every output word is stored locally and into the 7 peers' buffers by the epilogue"}
+                 "note": "one launch per rank: every output word is stored locally and into every peer's buffer by the epilogue (whole rows as bulk copies)"}
         pc.set_peer_outputs([])
         dist.barrier()
         sharding.close_peer_buffers(device.index, bases)
