@@ -595,6 +595,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--host-chunks", type=int, default=0, help="column chunks of the host-buffer call (0 = the library's choice)")
     ap.add_argument("--no-side", action="store_true", help="skip the NTT / ModUp side measurements")
+    ap.add_argument("--only-rlwe-side", action="store_true",
+                    help="of the side measurements run only the decompose-and-multiply comparison (profiling)")
     ap.add_argument("--small", action="store_true",
                     help="profiling-sized case: PCMM with 2 limbs, NTT with 8 polys, ModUp batch 8 (not a bench value)")
     args = ap.parse_args()
@@ -741,7 +743,7 @@ def main():
                 v, dt_cpu, cores, sample = cpu_pcmm_sample(q, Xd, Wh, Cw)
                 cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample, "seconds": dt_cpu}
         pc.close()
-        if rank == 0 and world == 1 and not args.no_side:
+        if rank == 0 and world == 1 and not args.no_side and not args.only_rlwe_side:
             try:
                 extra["ntt"] = bench_ntt(torch, device, max(args.steps, 10), args.warmup, peaks)
                 extra["modup"] = bench_modup(torch, device, max(args.steps, 10), args.warmup, peaks)
