@@ -19,7 +19,7 @@ SYMBOLS = [
     "ckks_b200_ntt_forward", "ckks_b200_ntt_inverse",
     "ckks_b200_ntt_forward_host", "ckks_b200_ntt_inverse_host",
     "ckks_b200_modup_qj_to_t", "ckks_b200_modup_qj_to_t_host", "ckks_b200_modup_set_algo", "ckks_b200_context_check",
-    "ckks_b200_rescale", "ckks_b200_modup_q0_to_ql",
+    "ckks_b200_rescale", "ckks_b200_modup_q0_to_ql", "ckks_b200_rescale_batch", "ckks_b200_modup_q0_to_ql_batch",
     "ckks_b200_external_product_t", "ckks_b200_ntt_inverse_ext", "ckks_b200_modup_t_to_pql",
     "ckks_b200_moddown_pql_to_ql", "ckks_b200_keyswitch", "ckks_b200_mult", "ckks_b200_conjugate", "ckks_b200_rotate",
     "ckks_b200_rlwe_decompose", "ckks_b200_mlwe_packing",
@@ -73,6 +73,8 @@ def load():
     L.ckks_b200_modup_set_algo.argtypes = [vp, i]
     L.ckks_b200_context_check.argtypes = [vp, vp]
     L.ckks_b200_rescale.argtypes = [vp, vp, i, i, vp]
+    L.ckks_b200_rescale_batch.argtypes = [vp, vp, i, i, i, vp]
+    L.ckks_b200_modup_q0_to_ql_batch.argtypes = [vp, vp, i, i, i, C.c_longlong, vp]
     L.ckks_b200_external_product_t.argtypes = [vp, vp, vp, vp, i, i, vp]
     L.ckks_b200_ntt_inverse_ext.argtypes = [vp, vp, i, i, vp]
     L.ckks_b200_modup_t_to_pql.argtypes = [vp, vp, vp, i, i, i, vp]

@@ -71,50 +71,65 @@ __global__ void __launch_bounds__(kThreads) modup_q0_kernel(u64* __restrict__ ci
 
 }  // namespace
 
-extern "C" int ckks_b200_rescale(ckks_b200_context* c, uint64_t* d_cipher, int L, int l, void* stream) {
-    CKB_REQUIRE(c && d_cipher, CKKS_B200_ERR_ARG, "null argument");
+// `count` ciphertexts laid out one after another ([count][2][L+1][N]) go through every stage together: the
+// transforms see 2*count polynomials, the elementwise kernels 2*count slices.  One ciphertext alone leaves most
+// of the GPU idle (its inverse transform is two limb-polynomials), so callers that keep their ciphertexts in one
+// pool should use the batched forms.
+extern "C" int ckks_b200_rescale_batch(ckks_b200_context* c, uint64_t* d_ciphers, int count, int L, int l, void* stream) {
+    CKB_REQUIRE(c && d_ciphers, CKKS_B200_ERR_ARG, "null argument");
+    CKB_REQUIRE(count >= 1 && count <= 16384, CKKS_B200_ERR_ARG, "ciphertext count %d outside [1,16384]", count);
     CKB_REQUIRE(L >= 1 && L + 1 <= c->q_num, CKKS_B200_ERR_ARG, "L=%d needs %d q moduli, the context has %d", L, L + 1,
                 c->q_num);
     CKB_REQUIRE(l >= 1 && l <= L, CKKS_B200_ERR_ARG, "level %d outside [1,%d]: nothing to rescale by", l, L);
     DeviceGuard guard(c->device);
     CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", c->device);
     cudaStream_t st = (cudaStream_t)stream;
-    const int K = c->p_num, stride = L + 1;
-    int rc = ensure_buf(&c->resc_buf, &c->resc_cap, (size_t)2 * stride * c->N);
+    const int K = c->p_num, stride = L + 1, polys = 2 * count;
+    int rc = ensure_buf(&c->resc_buf, &c->resc_cap, (size_t)polys * stride * c->N);
     if (rc) return rc;
-    rc = ckks_b200_ntt_inverse(c, d_cipher, l, K + l, 2, 1, stride, stream);
+    rc = ckks_b200_ntt_inverse(c, d_ciphers, l, K + l, polys, 1, stride, stream);
     if (rc) return rc;
     const u64* q = c->d_moduli + K;
-    dim3 g1((c->N + kThreads - 1) / kThreads, 2);
-    rescale_spread_kernel<<<g1, kThreads, 0, st>>>(c->resc_buf, (const u64*)d_cipher, c->N, stride, l, q, c->d_qinv64 + K);
+    dim3 g1((c->N + kThreads - 1) / kThreads, polys);
+    rescale_spread_kernel<<<g1, kThreads, 0, st>>>(c->resc_buf, (const u64*)d_ciphers, c->N, stride, l, q, c->d_qinv64 + K);
     count_launch();
     CKB_CUDA(cudaGetLastError());
-    rc = ckks_b200_ntt_forward(c, (uint64_t*)c->resc_buf, 0, K, 2, l, stride, stream);
+    rc = ckks_b200_ntt_forward(c, (uint64_t*)c->resc_buf, 0, K, polys, l, stride, stream);
     if (rc) return rc;
-    dim3 g2((c->N + kThreads - 1) / kThreads, l, 2);
-    rescale_combine_kernel<<<g2, kThreads, 0, st>>>((u64*)d_cipher, c->resc_buf, c->N, stride, l, q,
+    dim3 g2((c->N + kThreads - 1) / kThreads, l, polys);
+    rescale_combine_kernel<<<g2, kThreads, 0, st>>>((u64*)d_ciphers, c->resc_buf, c->N, stride, l, q,
                                                     c->d_qlinv + (size_t)l * c->q_num);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
 }
 
-extern "C" int ckks_b200_modup_q0_to_ql(ckks_b200_context* c, uint64_t* d_cipher, int L, int target_level,
-                                        long long scale_up, void* stream) {
-    CKB_REQUIRE(c && d_cipher, CKKS_B200_ERR_ARG, "null argument");
+extern "C" int ckks_b200_rescale(ckks_b200_context* c, uint64_t* d_cipher, int L, int l, void* stream) {
+    return ckks_b200_rescale_batch(c, d_cipher, 1, L, l, stream);
+}
+
+extern "C" int ckks_b200_modup_q0_to_ql_batch(ckks_b200_context* c, uint64_t* d_ciphers, int count, int L, int target_level,
+                                              long long scale_up, void* stream) {
+    CKB_REQUIRE(c && d_ciphers, CKKS_B200_ERR_ARG, "null argument");
+    CKB_REQUIRE(count >= 1 && count <= 16384, CKKS_B200_ERR_ARG, "ciphertext count %d outside [1,16384]", count);
     CKB_REQUIRE(L >= 1 && L + 1 <= c->q_num, CKKS_B200_ERR_ARG, "L=%d needs %d q moduli, the context has %d", L, L + 1,
                 c->q_num);
     CKB_REQUIRE(target_level >= 1 && target_level <= L, CKKS_B200_ERR_ARG, "target level %d outside [1,%d]", target_level, L);
     DeviceGuard guard(c->device);
     CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", c->device);
     cudaStream_t st = (cudaStream_t)stream;
-    const int K = c->p_num, stride = L + 1;
-    int rc = ckks_b200_ntt_inverse(c, d_cipher, 0, K, 2, 1, stride, stream);
+    const int K = c->p_num, stride = L + 1, polys = 2 * count;
+    int rc = ckks_b200_ntt_inverse(c, d_ciphers, 0, K, polys, 1, stride, stream);
     if (rc) return rc;
-    dim3 g((c->N + kThreads - 1) / kThreads, 2);
-    modup_q0_kernel<<<g, kThreads, 0, st>>>((u64*)d_cipher, c->N, stride, target_level, c->d_moduli + K, c->d_qinv64 + K,
+    dim3 g((c->N + kThreads - 1) / kThreads, polys);
+    modup_q0_kernel<<<g, kThreads, 0, st>>>((u64*)d_ciphers, c->N, stride, target_level, c->d_moduli + K, c->d_qinv64 + K,
                                             (u64)scale_up);
     count_launch();
     CKB_CUDA(cudaGetLastError());
-    return ckks_b200_ntt_forward(c, d_cipher, 0, K, 2, target_level + 1, stride, stream);
+    return ckks_b200_ntt_forward(c, d_ciphers, 0, K, polys, target_level + 1, stride, stream);
+}
+
+extern "C" int ckks_b200_modup_q0_to_ql(ckks_b200_context* c, uint64_t* d_cipher, int L, int target_level,
+                                        long long scale_up, void* stream) {
+    return ckks_b200_modup_q0_to_ql_batch(c, d_cipher, 1, L, target_level, scale_up, stream);
 }

@@ -218,6 +218,20 @@ class Scheme_23:
         cipher.scale = cipher.scale / ctx.qVec[cipher.l]
         cipher.l -= 1
 
+    def rescaleAndEqual_batch(self, ciphers):
+        """rescaleAndEqual of several ciphertexts in one pass.  They must be views, in order, of one contiguous device
+        buffer (ciphertext i at offset i * 2 * (L+1) * N words) and share L and l."""
+        ctx, first = self.context, ciphers[0]
+        words = 2 * (first.L + 1) * ctx.N
+        base = first.cipher_device.data_ptr()
+        for i, c in enumerate(ciphers):
+            if c.cipher_device.data_ptr() != base + 8 * i * words or (c.L, c.l) != (first.L, first.l):
+                raise ValueError("the batched form needs equally shaped ciphertexts stored one after another")
+        capi.check(ctx.lib.ckks_b200_rescale_batch(ctx._h, base, len(ciphers), first.L, first.l, _stream_ptr(ctx.device)))
+        for c in ciphers:
+            c.scale = c.scale / ctx.qVec[c.l]
+            c.l -= 1
+
 
 class Bootstrapper:
     """The level-raising step in front of the bootstrapping pipeline
@@ -236,6 +250,20 @@ class Bootstrapper:
         capi.check(ctx.lib.ckks_b200_modup_q0_to_ql(ctx._h, cipher.cipher_device.data_ptr(), cipher.L, target_level,
                                                     scale_up, _stream_ptr(ctx.device)))
         cipher.l = target_level
+
+    def modUpQ0toQL_batch(self, ciphers, target_level):
+        """modUpQ0toQL of several level-0 ciphertexts in one pass; the same layout rule as Scheme_23.rescaleAndEqual_batch."""
+        ctx, first = self.context, ciphers[0]
+        words = 2 * (first.L + 1) * ctx.N
+        base = first.cipher_device.data_ptr()
+        for i, c in enumerate(ciphers):
+            if c.cipher_device.data_ptr() != base + 8 * i * words or c.L != first.L or c.l != 0:
+                raise ValueError("the batched form needs level-0 ciphertexts of one shape stored one after another")
+        scale_up = C.c_int(ctx.qVec[0] // self.precision).value
+        capi.check(ctx.lib.ckks_b200_modup_q0_to_ql_batch(ctx._h, base, len(ciphers), first.L, target_level, scale_up,
+                                                          _stream_ptr(ctx.device)))
+        for c in ciphers:
+            c.l = target_level
 
 
 class MLWECiphertext:

@@ -115,6 +115,13 @@ int ckks_b200_rescale(ckks_b200_context* ctx, uint64_t* d_cipher, int L, int l, 
  * domain.  scale_up is the reference's qVec[0] / precision (:203). */
 int ckks_b200_modup_q0_to_ql(ckks_b200_context* ctx, uint64_t* d_cipher, int L, int target_level,
                              long long scale_up, void* stream);
+/* The same two steps on `count` ciphertexts stored one after another, [count][2][L+1][N], all at the same
+ * level: every transform and elementwise kernel runs once over all of them.  A single ciphertext leaves most
+ * of the GPU idle (its inverse transform is two limb-polynomials); callers that keep their ciphertexts in one
+ * pool get several times the rate from these forms.  Results are those of `count` single calls. */
+int ckks_b200_rescale_batch(ckks_b200_context* ctx, uint64_t* d_ciphers, int count, int L, int l, void* stream);
+int ckks_b200_modup_q0_to_ql_batch(ckks_b200_context* ctx, uint64_t* d_ciphers, int count, int L, int target_level,
+                                   long long scale_up, void* stream);
 
 /* ---- key-switch chain -------------------------------------------------------
  * The steps of Scheme_23::mult_23 / rotate / conjugate between the tensor product and the final

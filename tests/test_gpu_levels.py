@@ -70,3 +70,30 @@ def test_level_arguments_are_checked(oracle, cuda_device):
     with pytest.raises(CkksB200Error):
         Bootstrapper(ctx, 1 << 40).modUpQ0toQL(ct, 3)  # beyond L
     ctx.close()
+
+
+def test_batched_forms_equal_single_calls(oracle, cuda_device):
+    """Three ciphertexts in one pool: the batched level changes give what the oracle gives for each alone."""
+    logN, q_num, q_bits = 13, 5, 50
+    N, p, q, ctx, T, rng = _setup(oracle, logN, 1, q_num, q_bits, seed=77)
+    L, l, B = q_num - 1, 3, 3
+    pool = np.stack([np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)]) for _ in range(B)])   # [B][2][L+1][N]
+    exp = np.stack([oracle.rescale(pool[b].copy(), T, len(p), L, l) for b in range(B)])
+    dev = as_u64_tensor(pool.reshape(-1), ctx.device)
+    words = 2 * (L + 1) * N
+    cts = [Ciphertext(N, L, l, N // 2, 2.0 ** 40, cipher=dev[b * words:(b + 1) * words]) for b in range(B)]
+    Scheme_23(ctx).rescaleAndEqual_batch(cts)
+    assert np.array_equal(to_u64_numpy(dev).reshape(pool.shape), exp)
+    assert all(c.l == l - 1 for c in cts)
+    with pytest.raises(ValueError):
+        Scheme_23(ctx).rescaleAndEqual_batch([cts[0], cts[2]])                   # not adjacent
+    # level 0 -> target
+    target, precision = 4, 1 << (q_bits - 10)
+    pool0 = np.stack([np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)]) for _ in range(B)])
+    exp0 = np.stack([oracle.modup_q0_to_ql(pool0[b].copy(), T, len(p), L, target, q[0] // precision) for b in range(B)])
+    dev0 = as_u64_tensor(pool0.reshape(-1), ctx.device)
+    cts0 = [Ciphertext(N, L, 0, N // 2, 1.0, cipher=dev0[b * words:(b + 1) * words]) for b in range(B)]
+    Bootstrapper(ctx, precision).modUpQ0toQL_batch(cts0, target)
+    assert np.array_equal(to_u64_numpy(dev0).reshape(pool0.shape), exp0)
+    assert all(c.l == target for c in cts0)
+    ctx.close()
