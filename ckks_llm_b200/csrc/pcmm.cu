@@ -359,8 +359,21 @@ extern "C" int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, co
     cudaStream_t s_in = pc->hs[0], s_mm = pc->hs[1], s_out = pc->hs[2];
     const long tiles = (pc->C + 31) / 32;
     const size_t total_bytes = 8 * ct_words * ((size_t)mlwe_num + mat_M);
-    int nchunk = pc->host_chunks > 0 ? pc->host_chunks : total_bytes > ((size_t)256 << 20) ? 16 : 1;
-    if (nchunk > tiles) nchunk = (int)tiles;
+    // Equal chunks of 32-column tiles.  Sixteen is the measured optimum at the BERT shape (8.07 GB each way): fewer
+    // leave the link idle while the first chunk comes in and the last goes out, more make the rows of the strided
+    // host copies short (8 chunks 204 ms, 16 chunks 195 ms, 64 chunks 264 ms; small chunks at the two ends only,
+    // 220 ms).
+    std::vector<long> widths;
+    {
+        long n = pc->host_chunks > 0 ? pc->host_chunks : total_bytes > ((size_t)256 << 20) ? 16 : 1;
+        if (n > tiles) n = tiles;
+        for (long i = 0; i < n; i++) widths.push_back(tiles / n + (i < tiles % n ? 1 : 0));
+    }
+    const int nchunk = (int)widths.size();
+    long widest = 0;
+    for (long w : widths) widest = w > widest ? w : widest;
+    rc = pcmm_reserve_planes(pc, mat_M, mat_N, widest * 32);
+    if (rc) return rc;
     while ((int)pc->hev.size() < 2 * nchunk) {
         cudaEvent_t e;
         CKB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
@@ -370,10 +383,9 @@ extern "C" int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, co
     std::vector<const uint64_t*> ptrs(mlwe_num);
     for (int n = 0; n < mlwe_num; n++) ptrs[n] = (const uint64_t*)(pc->d_X_host + ct_words * n);
     const size_t pitch = (size_t)pc->C * 8;
-    const long tbase = tiles / nchunk, textra = tiles % nchunk;   // the first chunks are the widest, so
-    long t0 = 0;                                                  // workspaces are sized once
+    long t0 = 0;
     for (int i = 0; i < nchunk; i++) {
-        const long t1 = t0 + tbase + (i < textra ? 1 : 0);
+        const long t1 = t0 + widths[i];
         const long c0 = t0 * 32;
         long c1 = t1 * 32;
         t0 = t1;

@@ -86,4 +86,5 @@ int ensure_dev(T** buf, size_t* cap, size_t count) {
 int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots,
                 bool slots_regular, u64* d_out, int M, int K, long col_begin, long col_end, int w_bits, cudaStream_t st);
 int pcmm_slots_max_gap();
+int pcmm_reserve_planes(ckks_b200_pcmm* pc, int M, int K, long ncols);
 }  // namespace ckb

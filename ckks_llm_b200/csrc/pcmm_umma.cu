@@ -664,6 +664,16 @@ namespace ckb {
 
 int pcmm_slots_max_gap() { return SEG_MAX_GAP; }
 
+// Grows the plane workspaces to what any plane configuration needs for ncols columns, so that a pipeline of
+// multiplies over column chunks of different widths never reallocates (and synchronises) in mid-flight.
+int pcmm_reserve_planes(ckks_b200_pcmm* pc, int M, int K, long ncols) {
+    const int MT = (M + TM - 1) / TM, KBN = (K + KB - 1) / KB;
+    const long CT = (ncols + TC - 1) / TC;
+    int rc = ensure_dev(&pc->d_wplanes, &pc->wplanes_cap, (size_t)MT * KBN * Cfg<8, 8>::A_STAGE);
+    if (!rc) rc = ensure_dev(&pc->d_xplanes, &pc->xplanes_cap, (size_t)pc->q_count * CT * KBN * Cfg<8, 8>::B_STAGE);
+    return rc;
+}
+
 int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots,
                 bool slots_regular, u64* d_out, int M, int K, long col_begin, long col_end, int w_bits, cudaStream_t st) {
     int q_bits = 0;
