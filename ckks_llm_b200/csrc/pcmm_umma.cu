@@ -277,14 +277,8 @@ __global__ void __launch_bounds__(256) slice_rlwe_rows_kernel(const RlweSlot* __
     const uint32_t* row = seg[half][k16][cc];
     const int valid = K - n0 - k16 * 16;                                   // ciphertexts of this run that exist
     const int gap = valid > 0 ? slots[n0 + k16 * 16].gap : 1;
-    for (int rr = 0; rr < rows; rr++) {
-        const long c = (long)(crow0 + rr) * N1 + g0;
-        if (c < col_begin || c >= col_end) continue;                       // block-uniform
-        const int ct = (int)((c - col_begin) / TC);
-        uint32_t w[16];
-        int x = (RB - 1) - rr;
-#pragma unroll
-        for (int e = 0; e < 16; e++, x += gap) w[e] = e < valid ? row[x] : 0u;
+    // planes of one column tile from the 16 words of this thread's (column, run of 16 ciphertexts)
+    auto emit = [&](const uint32_t (&w)[16], int ct) {
         uint8_t* dst = planes + ((((size_t)limb * CT + ct) * KBN + kb) * KS + ks) * SC * B_PLANE_STEP +
                        (size_t)(cc / 8) * 256 + kc * 128 + (cc % 8) * 16;
 #pragma unroll
@@ -301,6 +295,32 @@ __global__ void __launch_bounds__(256) slice_rlwe_rows_kernel(const RlweSlot* __
                 *reinterpret_cast<uint4*>(dst + (size_t)b * B_PLANE_STEP) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
         }
+    };
+    if (gap == 1 && rows == RB && valid >= 16) {
+        // Gap one, a whole row block, a whole run: polynomial r0 + rr needs words 15 - rr .. 30 - rr of the run, so
+        // the 31 words are read once and every polynomial takes its window of them from registers.
+        uint32_t win[RB + 15];
+#pragma unroll
+        for (int j = 0; j < RB + 15; j++) win[j] = row[j];
+#pragma unroll
+        for (int rr = 0; rr < RB; rr++) {
+            const long c = (long)(crow0 + rr) * N1 + g0;
+            if (c < col_begin || c >= col_end) continue;                   // block-uniform
+            uint32_t w[16];
+#pragma unroll
+            for (int e = 0; e < 16; e++) w[e] = win[(RB - 1) - rr + e];
+            emit(w, (int)((c - col_begin) / TC));
+        }
+        return;
+    }
+    for (int rr = 0; rr < rows; rr++) {
+        const long c = (long)(crow0 + rr) * N1 + g0;
+        if (c < col_begin || c >= col_end) continue;                       // block-uniform
+        uint32_t w[16];
+        int x = (RB - 1) - rr;
+#pragma unroll
+        for (int e = 0; e < 16; e++, x += gap) w[e] = e < valid ? row[x] : 0u;
+        emit(w, (int)((c - col_begin) / TC));
     }
 }
 
