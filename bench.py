@@ -40,8 +40,9 @@ def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         d = json.load(open(path))
-        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
-    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
 class ClockSampler:
@@ -738,7 +739,10 @@ def main():
                 "traffic_note": "dram read+write of the ncu capture of the 2-limb case, scaled by the limb count",
                 "kernel": "pcmm_umma_kernel<5,7>", "kernel_ms": main, "prepass_ms": float(np.mean(pre_ms)),
                 "peak_source": f"2 x bf16 dense {peaks['bf16_tflops']} TFLOP/s ({peaks['source']}); int8 dense is nominally 2x bf16",
-                "algorithmic_ops": "2*5*7 int8 ops per modular MAC x M*K*(N+N1)*limbs"}
+                "algorithmic_ops": "2*5*7 int8 ops per modular MAC x M*K*(N+N1)*limbs",
+                "frac_of_sustained_peak": achieved / (2.0 * peaks["bf16_tflops_sustained"]),
+                "peak_note": "frac is against the burst figure, the stricter of the two; the kernel runs under sw_power_cap "
+                             "for most of its 17 ms, where the sustained figure is the like-for-like one"}
         if rank == 0 and world == 1 and not args.no_side:
             extra["pcmm_from_rlwe"] = bench_pcmm_from_rlwe(torch, device, args.steps, args.warmup, sch, pc, cts, W, q, ms)
         metric, unit = "pcmm_ct_rows_per_sec", "ct-rows/s"
