@@ -555,7 +555,14 @@ int run_ntt(ckks_b200_context* c, u64* d_data, int start_limb_off, int start_mod
     };
     // the contiguous kernel walks over several tiles per CTA so that its prefetch has something to run ahead of
     const int ntile = c->N / (kChunk * kChunksPerCta);
-    const int tiles = ntile >= 4 ? 4 : ntile;
+    // ... unless the call is so small that walking would leave SMs without a CTA: then more, shorter CTAs
+    int tiles = ntile >= 4 ? 4 : ntile;
+    {
+        static int sms = 0;
+        if (sms == 0 && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device) != cudaSuccess) sms = 148;
+        const long transforms = (long)mod_num * poly_num;
+        while (tiles > 1 && transforms * (ntile / tiles) < 2L * sms) tiles >>= 1;
+    }
     const size_t smem_c = 2 * kChunk * kChunksPerCta * sizeof(u64);
     dim3 grid_k(ntile / tiles, mod_num, poly_num);
     if (!inverse) {
