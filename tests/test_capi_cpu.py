@@ -42,6 +42,14 @@ def test_argument_validation_needs_no_device():
     assert L.ckks_b200_pcmm_create(C.byref(h), 0, 64, 64, None, 0) == capi.ERR_ARG
     assert L.ckks_b200_context_destroy(None) == capi.OK
     assert L.ckks_b200_pcmm_destroy(None) == capi.OK
+    # entry points added around the path: a null handle is an argument error everywhere, before any CUDA call
+    assert L.ckks_b200_pcmm_set_host_chunks(None, 4) == capi.ERR_ARG
+    assert L.ckks_b200_pcmm_ppmm_rlwe(None, None, None, 0, None, 1, 1, 1, 1, 1.0, 0, 32, None) == capi.ERR_ARG
+    assert L.ckks_b200_rescale_batch(None, None, 1, 1, 1, None) == capi.ERR_ARG
+    assert L.ckks_b200_modup_q0_to_ql_batch(None, None, 1, 1, 1, 1, None) == capi.ERR_ARG
+    assert L.ckks_b200_conjugate(None, None, None, None, 0, 1, None) == capi.ERR_ARG
+    assert L.ckks_b200_rotate(None, None, None, None, 1, 0, 1, None) == capi.ERR_ARG
+    assert L.ckks_b200_keyswitch(None, None, None, None, 0, 1, None) == capi.ERR_ARG
 
 
 def test_no_cpu_fallback():
