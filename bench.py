@@ -45,6 +45,26 @@ def measured_peaks():
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
+def bind_to_gpu_cpus(gpu_index):
+    """With several ranks on one host, keep this rank's threads, and with them the pinned staging buffers it is about to
+    allocate, on the CPUs NVML lists as close to its GPU, so that host copies do not cross sockets.  Reads only; returns
+    the number of CPUs bound to, or None when the affinity is unknown."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -678,6 +698,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: this library has no CPU path")
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
+    numa = bind_to_gpu_cpus(local_rank) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     capi.load()
@@ -796,7 +817,8 @@ def main():
                 dt = float(tt.item())
             e2e = {"value": world * c["M"] / dt, "unit": unit, "h2d_bytes_per_step": int(Xh.numel() * 8 + Wh.numel() * 4),
                    "d2h_bytes_per_step": int(outh.numel() * 8), "ms_per_step": dt * 1e3, "steps": n_e2e,
-                   "call": "ckks_b200_pcmm_ppmm_host (pinned host buffers, per rank)"}
+                   "call": "ckks_b200_pcmm_ppmm_host (pinned host buffers, per rank)",
+                   "cpus_bound_per_rank": numa}
             if rank == 0 and world == 1 and not args.no_cpu:
                 Xd = Xh[:, :, :16384].contiguous()
                 v, dt_cpu, cores, sample = cpu_pcmm_sample(q, Xd, Wh, Cw)
