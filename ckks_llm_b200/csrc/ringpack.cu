@@ -45,6 +45,66 @@ __global__ void __launch_bounds__(256) rlwe_decompose_kernel(const u64* __restri
     }
 }
 
+// The same decomposition for the usual case (N1 a multiple of 32, gap of at most 2), using its structure: with the
+// negacyclic convention A[x +- N] = -A[x], word g of polynomial r < k of ciphertext i is
+//   a_i,r[g] = A[g*k + i*gap - r]          (b_i[g] = B[g*k + i*gap])
+// so ciphertexts and polynomials see the same RLWE words shifted against one another.  A block takes 32 values of g,
+// 64 ciphertexts (four runs of 16) and DRB polynomials, loads per run and g the 15*gap + DRB words those share into
+// shared memory, and writes their 64 x DRB row segments of 256 bytes from there: 256 KB of output per block against
+// 8 KB for the tile transposes above, and an eighth of their reads.  The last "row block" is the b polynomial alone.
+constexpr int DRB = 16;
+constexpr int DSEG = 15 * 2 + DRB + 1;       // odd row length: lanes along g read distinct banks
+
+__global__ void __launch_bounds__(256) rlwe_decompose_rows_kernel(const u64* __restrict__ rlwe, u64* const* __restrict__ mlwe,
+                                                                  const u64* __restrict__ q_moduli, long N, int N1, int k,
+                                                                  int mlwe_num, int L) {
+    __shared__ u64 seg[4][32][DSEG];
+    const int g_tiles = N1 / 32, rbn = (k + DRB - 1) / DRB;
+    const int gt = blockIdx.x % g_tiles, rb = blockIdx.x / g_tiles;
+    const int limb = blockIdx.z;
+    const bool bpoly = rb == rbn;
+    const int r0 = bpoly ? 0 : rb * DRB;                     // first polynomial, as it enters the index
+    const int rows = bpoly ? 1 : (k - r0 < DRB ? k - r0 : DRB);
+    const int crow0 = bpoly ? k : r0;                        // its row among the k+1 polynomials of a ciphertext
+    const int g0 = gt * 32, n0 = blockIdx.y * 64;
+    const int gap = k / mlwe_num;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const u64 q = q_moduli[limb];
+    const u64* src = rlwe + N * ((bpoly ? L + 1 : 0) + limb);
+    {
+        const int run = warp & 3, i0 = n0 + run * 16;
+        if (i0 < mlwe_num) {
+            const int span = 15 * gap + DRB;
+            for (int g = warp >> 2; g < 32; g += 2) {
+                const long base = (long)(g0 + g) * k + (long)i0 * gap - (r0 + DRB - 1);
+                for (int x = lane; x < span; x += 32) {
+                    long idx = base + x;
+                    bool neg = false;
+                    if (idx < 0) { idx += N; neg = true; }
+                    else if (idx >= N) { idx -= N; neg = true; }
+                    const u64 v = src[idx];
+                    seg[run][g][x] = neg ? (v == 0 ? 0 : q - v) : v;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    const int cc = t & 31, run = (t >> 5) & 3, half = t >> 7;
+    const int i0 = n0 + run * 16 + half * 8;                 // this thread writes ciphertexts i0 .. i0+7
+    const long C = (long)(k + 1) * N1;
+    u64* out[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) out[e] = i0 + e < mlwe_num ? mlwe[i0 + e] + (size_t)limb * C + g0 + cc : nullptr;
+    const u64* row = seg[run][cc];
+    for (int rr = 0; rr < rows; rr++) {
+        const size_t off = (size_t)(crow0 + rr) * N1;
+        int x = half * 8 * gap + (DRB - 1) - rr;
+#pragma unroll
+        for (int e = 0; e < 8; e++, x += gap)
+            if (out[e]) out[e][off] = row[x];
+    }
+}
+
 // ---------------------------------------------------------------------------
 // MLWE -> RLWE packing (PCMM_Scheme::mlweCipherPacking, PCMM_Scheme.cuh:362-430), for the
 // reference's ring-pack shape: one special prime p and one packing limb q0.  Buffers hold
@@ -200,10 +260,16 @@ extern "C" int ckks_b200_rlwe_decompose(ckks_b200_context* c, uint64_t* d_rlwe, 
         rc = ckks_b200_ntt_inverse(c, d_rlwe, 0, c->p_num, 2, l + 1, L + 1, stream);     // :107
         if (rc) return rc;
     }
-    const int g_tiles = (N1 + 31) / 32;
-    dim3 grid((unsigned)((mlwe_rank / 32 + 1) * g_tiles), l + 1, mlwe_num);
-    rlwe_decompose_kernel<<<grid, dim3(32, 8), 0, st>>>((const u64*)d_rlwe, (u64* const*)c->ptr_buf, c->d_moduli + c->p_num,
-                                                        (long)c->N, N1, mlwe_rank, mlwe_num, L, g_tiles);
+    if (N1 % 32 == 0 && mlwe_rank / mlwe_num <= 2 && c->N >= 256) {
+        dim3 grid((unsigned)((N1 / 32) * ((mlwe_rank + DRB - 1) / DRB + 1)), (mlwe_num + 63) / 64, l + 1);
+        rlwe_decompose_rows_kernel<<<grid, 256, 0, st>>>((const u64*)d_rlwe, (u64* const*)c->ptr_buf, c->d_moduli + c->p_num,
+                                                         (long)c->N, N1, mlwe_rank, mlwe_num, L);
+    } else {
+        const int g_tiles = (N1 + 31) / 32;
+        dim3 grid((unsigned)((mlwe_rank / 32 + 1) * g_tiles), l + 1, mlwe_num);
+        rlwe_decompose_kernel<<<grid, dim3(32, 8), 0, st>>>((const u64*)d_rlwe, (u64* const*)c->ptr_buf, c->d_moduli + c->p_num,
+                                                            (long)c->N, N1, mlwe_rank, mlwe_num, L, g_tiles);
+    }
     count_launch();
     CKB_CUDA(cudaGetLastError());
     if (ntt_domain) {

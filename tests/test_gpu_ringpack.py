@@ -77,19 +77,20 @@ def test_decompose_matches_reference_kernel(oracle, cuda_device):
     """rlweCipherDecompose_kernel<256> of the reference (N=2^15, N1=128, rank 256)."""
     if not hasattr(R.lib(), "ref_decompose"):
         pytest.skip("reference driver built without the decomposition entry")
-    logN, N1, L, l, mlwe_num = 15, 128, 1, 1, 8
+    logN, N1, L, l = 15, 128, 1, 1
     N, q, ctx, rlwe = _setup(logN, N1, L, seed=3, p_num=0)
     k = N // N1
-    ref_out = R.decompose(rlwe, logN, N1, k, mlwe_num, L, l, q)
-    exp = oracle.rlwe_decompose(rlwe[0], rlwe[1], N1, k, mlwe_num, q).reshape(ref_out.shape)
-    assert np.array_equal(exp, ref_out)
     pc = PCMM_Context(N1, k, [], q)
     sch = PCMM_Scheme(pc, context=ctx)
     ct = Ciphertext(N, L, l, N // 2, 1.0, cipher=as_u64_tensor(rlwe, ctx.device).reshape(-1))
-    mlwe = [MLWECiphertext(N1, L, l, k, 1.0) for _ in range(mlwe_num)]
-    sch.rlweCipherDecompose(ct, mlwe, mlwe_num, 0, ntt_domain=False)
-    for i in range(mlwe_num):
-        assert np.array_equal(to_u64_numpy(mlwe[i].cipher_device).reshape(l + 1, -1), ref_out[i])
+    for mlwe_num in (8, 128, 256):            # gaps 32 (word-by-word kernel), 2 and 1 (the kernel that shares RLWE words)
+        ref_out = R.decompose(rlwe, logN, N1, k, mlwe_num, L, l, q)
+        exp = oracle.rlwe_decompose(rlwe[0], rlwe[1], N1, k, mlwe_num, q).reshape(ref_out.shape)
+        assert np.array_equal(exp, ref_out)
+        mlwe = [MLWECiphertext(N1, L, l, k, 1.0) for _ in range(mlwe_num)]
+        sch.rlweCipherDecompose(ct, mlwe, mlwe_num, 0, ntt_domain=False)
+        for i in range(mlwe_num):
+            assert np.array_equal(to_u64_numpy(mlwe[i].cipher_device).reshape(l + 1, -1), ref_out[i]), (mlwe_num, i)
     pc.close(); ctx.close()
 
 
