@@ -256,17 +256,25 @@ __global__ void __launch_bounds__(256) slice_rlwe_rows_kernel(const RlweSlot* __
             const RlweSlot s = slots[nr];
             const int span = 15 * s.gap + RB;
             const u64* src = s.rlwe + N * ((bpoly ? s.L + 1 : 0) + limb);
-            for (int g = warp >> 2; g < TC; g += 2) {
-                const long base = (long)(g0 + g) * rank + (long)s.i * s.gap - (r0 + RB - 1);
-                for (int x = lane; x < span; x += 32) {
-                    long idx = base + x;
-                    bool neg = false;
-                    if (idx < 0) { idx += N; neg = true; }
-                    else if (idx >= N) { idx -= N; neg = true; }
-                    u64 v = src[idx];
-                    if (neg) v = v == 0 ? 0 : q - v;
-                    seg[0][run][g][x] = (uint32_t)v;
-                    seg[1][run][g][x] = (uint32_t)(v >> 32);
+            // four values of g per step, so that four loads are in flight before the first is used
+            for (int x = lane; x < span; x += 32) {
+                for (int gq = warp >> 2; gq < TC; gq += 8) {
+                    u64 v[4];
+                    bool neg[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        long idx = (long)(g0 + gq + 2 * u) * rank + (long)s.i * s.gap - (r0 + RB - 1) + x;
+                        neg[u] = false;
+                        if (idx < 0) { idx += N; neg[u] = true; }
+                        else if (idx >= N) { idx -= N; neg[u] = true; }
+                        v[u] = src[idx];
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const u64 w = neg[u] ? (v[u] == 0 ? 0 : q - v[u]) : v[u];
+                        seg[0][run][gq + 2 * u][x] = (uint32_t)w;
+                        seg[1][run][gq + 2 * u][x] = (uint32_t)(w >> 32);
+                    }
                 }
             }
         }

@@ -75,15 +75,21 @@ __global__ void __launch_bounds__(256) rlwe_decompose_rows_kernel(const u64* __r
         const int run = warp & 3, i0 = n0 + run * 16;
         if (i0 < mlwe_num) {
             const int span = 15 * gap + DRB;
-            for (int g = warp >> 2; g < 32; g += 2) {
-                const long base = (long)(g0 + g) * k + (long)i0 * gap - (r0 + DRB - 1);
-                for (int x = lane; x < span; x += 32) {
-                    long idx = base + x;
-                    bool neg = false;
-                    if (idx < 0) { idx += N; neg = true; }
-                    else if (idx >= N) { idx -= N; neg = true; }
-                    const u64 v = src[idx];
-                    seg[run][g][x] = neg ? (v == 0 ? 0 : q - v) : v;
+            // four values of g per step, so that four loads are in flight before the first is used
+            for (int x = lane; x < span; x += 32) {
+                for (int gq = warp >> 2; gq < 32; gq += 8) {
+                    u64 v[4];
+                    bool neg[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        long idx = (long)(g0 + gq + 2 * u) * k + (long)i0 * gap - (r0 + DRB - 1) + x;
+                        neg[u] = false;
+                        if (idx < 0) { idx += N; neg[u] = true; }
+                        else if (idx >= N) { idx -= N; neg[u] = true; }
+                        v[u] = src[idx];
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++) seg[run][gq + 2 * u][x] = neg[u] ? (v[u] == 0 ? 0 : q - v[u]) : v[u];
                 }
             }
         }
