@@ -29,7 +29,7 @@ PCMM_CFG = dict(logN=16, N1=128, rank=512, M=768, K=768, limbs=20, q_bits=50, w_
 NTT_CFG = dict(logN=16, limbs=40, q_bits=50, polys=32)
 MODUP_CFG = dict(logN=16, q_num=24, q_bits=50, t_num=12, t_bits=60, alpha=8, batch=32)
 SW, SC = 5, 7          # byte planes the PCMM workload needs: 40-bit signed weights, 50-bit residues
-# DRAM traffic (bytes) from the ncu captures summarised under profiles/, per unit of work
+# DRAM traffic (bytes) from ncu captures of the --small cases, per unit of work
 PCMM_TRAFFIC_PER_LIMB = (709.12e6 + 766.83e6) / 2                    # pcmm_umma_kernel<5,7,false>, 768x768, per limb
 NTT_TRAFFIC_PER_XFORM = {"forward": (167.90e6 + 113.26e6 + 196.91e6 + 112.88e6) / 320,
                          "inverse": (202.12e6 + 113.41e6 + 167.91e6 + 108.10e6) / 320}
@@ -132,10 +132,11 @@ def cpu_pcmm_sample(q, X, W, Cw, rows=128, cols=16384):
     Xs = np.ascontiguousarray(X[:, :, :cols].cpu().numpy().view(np.uint64))
     Wh = W.cpu().numpy()
     t0 = time.perf_counter()
-    O.ppmm(Wh, Xs, q, c["scaler"], m0=0, m1=rows)
+    res = O.ppmm(Wh, Xs, q, c["scaler"], m0=0, m1=rows)
     dt = time.perf_counter() - t0
     frac_rows = rows * (cols / Cw)           # ct-rows worth of work
-    return frac_rows / dt, dt, O.num_threads(), f"{rows} rows x {cols} of {Cw} columns x {c['limbs']} limbs, K={c['K']}"
+    return (frac_rows / dt, dt, O.num_threads(), f"{rows} rows x {cols} of {Cw} columns x {c['limbs']} limbs, K={c['K']}",
+            res[:rows])
 
 
 def run_reference(args):
@@ -820,9 +821,19 @@ def main():
                    "call": "ckks_b200_pcmm_ppmm_host (pinned host buffers, per rank)",
                    "cpus_bound_per_rank": numa}
             if rank == 0 and world == 1 and not args.no_cpu:
-                Xd = Xh[:, :, :16384].contiguous()
-                v, dt_cpu, cores, sample = cpu_pcmm_sample(q, Xd, Wh, Cw)
+                rows_s, cols_s = 128, 16384
+                Xd = Xh[:, :, :cols_s].contiguous()
+                v, dt_cpu, cores, sample, ref_words = cpu_pcmm_sample(q, Xd, Wh, Cw, rows_s, cols_s)
                 cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample, "seconds": dt_cpu}
+                # the same sample doubles as the parity check of the benched configuration at its full limb count:
+                # the words the timed host-buffer call just produced against the CPU restatement, every one of them
+                gpu_words = outh[:rows_s, :, :cols_s].numpy().view(np.uint64)
+                equal = bool(np.array_equal(gpu_words, ref_words))
+                cfg["parity"] = {"rows": rows_s, "cols": cols_s, "limbs": c["limbs"], "equal": equal,
+                                 "against": "CPU restatement of the reference kernel (oracle/), same inputs"}
+                if not equal:
+                    bad = int((gpu_words != ref_words).sum())
+                    raise SystemExit(f"parity failure: {bad} of {ref_words.size} words of the benched multiply differ from the oracle")
         pc.close()
         if rank == 0 and world == 1 and not args.no_side and not args.only_rlwe_side:
             try:

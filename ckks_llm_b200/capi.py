@@ -19,12 +19,15 @@ SYMBOLS = [
     "ckks_b200_ntt_forward", "ckks_b200_ntt_inverse",
     "ckks_b200_ntt_forward_host", "ckks_b200_ntt_inverse_host",
     "ckks_b200_modup_qj_to_t", "ckks_b200_modup_qj_to_t_host", "ckks_b200_modup_set_algo", "ckks_b200_context_check",
+    "ckks_b200_context_set_wait_budget", "ckks_b200_context_test_withhold_commit",
     "ckks_b200_rescale", "ckks_b200_modup_q0_to_ql", "ckks_b200_rescale_batch", "ckks_b200_modup_q0_to_ql_batch",
     "ckks_b200_external_product_t", "ckks_b200_ntt_inverse_ext", "ckks_b200_modup_t_to_pql",
     "ckks_b200_moddown_pql_to_ql", "ckks_b200_keyswitch", "ckks_b200_mult", "ckks_b200_conjugate", "ckks_b200_rotate",
     "ckks_b200_rlwe_decompose", "ckks_b200_mlwe_packing",
     "ckks_b200_pcmm_create", "ckks_b200_pcmm_destroy", "ckks_b200_pcmm_ppmm",
     "ckks_b200_pcmm_ppmm_host", "ckks_b200_pcmm_ppmm_rlwe", "ckks_b200_pcmm_copy_back", "ckks_b200_pcmm_check", "ckks_b200_pcmm_set_peer_outputs", "ckks_b200_pcmm_set_host_chunks", "ckks_b200_ipc_open", "ckks_b200_ipc_close", "ckks_b200_pcmm_last_timing", "ckks_b200_pcmm_ppmm_static",
+    "ckks_b200_pcmm_prepare_weights", "ckks_b200_pcmm_ppmm_rlwe_host", "ckks_b200_pcmm_set_wait_budget",
+    "ckks_b200_pcmm_test_withhold_stage", "ckks_b200_pcmm_set_row_owners", "ckks_b200_pcmm_row_owner_range",
     "ckks_b200_kernel_launches",
 ]
 
@@ -49,7 +52,7 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    lib_path = os.environ.get("CKKS_B200_LIB", LIB)      # development override of the library path
+    lib_path = LIB
     if not os.path.exists(lib_path):
         raise ImportError(
             f"{LIB} is missing: build it with `python -m ckks_llm_b200._build` "
@@ -99,6 +102,14 @@ def load():
     L.ckks_b200_pcmm_check.argtypes = [vp, vp]
     L.ckks_b200_pcmm_last_timing.argtypes = [vp, C.POINTER(C.c_float), C.POINTER(C.c_float)]
     L.ckks_b200_pcmm_ppmm_static.argtypes = [vp, C.POINTER(vp), vp, i, i, i, i, i, i, u64p, i, dbl, vp]
+    L.ckks_b200_context_set_wait_budget.argtypes = [vp, C.c_longlong]
+    L.ckks_b200_context_test_withhold_commit.argtypes = [vp, i]
+    L.ckks_b200_pcmm_prepare_weights.argtypes = [vp, vp, i, i, dbl, vp]
+    L.ckks_b200_pcmm_ppmm_rlwe_host.argtypes = [vp, vp, C.POINTER(RlweSource), i, vp, i, i, i, i, dbl]
+    L.ckks_b200_pcmm_set_wait_budget.argtypes = [vp, C.c_longlong]
+    L.ckks_b200_pcmm_test_withhold_stage.argtypes = [vp, i]
+    L.ckks_b200_pcmm_set_row_owners.argtypes = [vp, vp, i, i]
+    L.ckks_b200_pcmm_row_owner_range.argtypes = [i, i, i, C.POINTER(i), C.POINTER(i)]
     L.ckks_b200_kernel_launches.restype = lng
     for name in SYMBOLS:
         f = getattr(L, name)

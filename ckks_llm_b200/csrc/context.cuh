@@ -70,6 +70,8 @@ struct ckks_b200_context {
     std::map<int, TpqTables> tpq;            // tables of the T -> [p | q] conversion, by gamma, built on first use
     int modup_algo = 0;                      // CKKS_B200_MODUP_AUTO / _TENSOR / _SIMT
     int* d_flags = nullptr;                  // [16] [1] = site of a device-side wait that ran out
+    long long wait_budget = 0;               // clock cycles a device-side wait may take (0: the library's default)
+    int withhold_commit = 0;                 // test switch of ckks_b200_context_test_withhold_commit, consumed by one launch
     int* h_flags = nullptr;                  // pinned mirror
 
     // Key-switch chain (keyswitch.cu), the reference's tables of Context_23.cuh:60-192 and :286-351:

@@ -122,6 +122,18 @@ extern "C" int ckks_b200_modup_set_algo(ckks_b200_context* c, int algo) {
     return CKKS_B200_OK;
 }
 
+extern "C" int ckks_b200_context_set_wait_budget(ckks_b200_context* c, long long cycles) {
+    CKB_REQUIRE(c != nullptr && cycles >= 0, CKKS_B200_ERR_ARG, "null handle or negative budget");
+    c->wait_budget = cycles;
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_context_test_withhold_commit(ckks_b200_context* c, int on) {
+    CKB_REQUIRE(c != nullptr, CKKS_B200_ERR_ARG, "null handle");
+    c->withhold_commit = on ? 1 : 0;
+    return CKKS_B200_OK;
+}
+
 // Synchronise `stream` and report whether a bounded device-side wait of a tensor-core
 // ModUp on this context ran out since the last check.
 extern "C" int ckks_b200_context_check(ckks_b200_context* c, void* stream) {

@@ -57,6 +57,8 @@ struct BconvArgs {
     uint32_t N;
     int blocks, batch, tg, npad;
     int tgt_limit;                // target k of block blk exists iff blk*tg + k < tgt_limit
+    long long wait_budget;        // clock cycles a wait on a group's mbarrier may take
+    int withhold;                 // test switch: group 0 of CTA 0 leaves out the commit of its first tile
     size_t in_batch, in_blk, out_batch, out_blk;      // strides in words; limb j / target k sits j*N / k*N further
 };
 
@@ -238,9 +240,11 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
             for (int ks = 0; ks < KSTEPS; ks++)
                 umma_i8(tmem_g, smem_desc(a16 + (ks * TM * 32 >> 4)),
                         smem_desc(b16 + ((blk * b_tile + ks * P.npad * 32) >> 4)), idesc, ks > 0);
-            umma_commit(bar);
+            // Test switch: without the commit nothing ever arrives on the group's barrier, and the wait below runs
+            // into its clock budget.
+            if (!(P.withhold && blockIdx.x == 0 && g == 0 && phase == 0)) umma_commit(bar);
         }
-        bool mine = mbar_wait(bar, phase, P.flags, 10 + g, &abort_flag);
+        bool mine = mbar_wait(bar, phase, P.flags, 10 + g, &abort_flag, P.wait_budget);
         phase ^= 1;
         ok = group_all(mine, 1 + g);
         if (!ok) break;
@@ -306,7 +310,11 @@ int launch_groups(ckks_b200_context* c, const BconvArgs& P, cudaStream_t st) {
     const long total = (long)P.batch * P.blocks * (P.N / TM);
     const long want = (total + GROUPS - 1) / GROUPS;
     const int grid = (int)(want < sms ? want : sms);
-    bconv_umma_kernel<APAD, F64Q, NG><<<grid, THREADS, smem, st>>>(P);
+    BconvArgs Q = P;
+    Q.wait_budget = c->wait_budget > 0 ? c->wait_budget : WAIT_BUDGET;
+    Q.withhold = c->withhold_commit;
+    c->withhold_commit = 0;                                 // the test switch arms one launch
+    bconv_umma_kernel<APAD, F64Q, NG><<<grid, THREADS, smem, st>>>(Q);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;

@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "pcmm.cuh"
+#include "pcmm_simt.cuh"
 
 using namespace ckb;
 
@@ -32,89 +33,15 @@ __global__ void scale_weights_kernel(const float* W, long long* w, size_t count,
     if ((threadIdx.x & 31) == 0 && bits > 0) atomicMax(&flags[0], bits);
 }
 
-// ---------------------------------------------------------------------------
-// CUDA-core multiply: 64x64 output tile per CTA, 4x4 outputs per thread, 128-bit
-// accumulators, limbs last to first with the rescale fused (PPMM_kernel.cuh:213-249).
-// ---------------------------------------------------------------------------
-constexpr int TS = 64, TK = 16;
-
-__global__ void __launch_bounds__(256) pcmm_simt_kernel(const long long* __restrict__ w,
-                                                        const u64* const* __restrict__ X,
-                                                        u64* __restrict__ out, const PcmmLimb* limbs,
-                                                        int M, int K, long C, int limb_num,
-                                                        long col_begin, long col_end) {
-    __shared__ u64 As[TK][TS + 1];
-    __shared__ u64 Xs[TK][TS];
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-    const long c0 = col_begin + (long)blockIdx.x * TS;
-    const int m0 = blockIdx.y * TS;
-    u64 last[4][4];
-
-    for (int i = limb_num - 1; i >= 0; i--) {
-        const PcmmLimb L = limbs[i];
-        u64 lo[4][4], hi[4][4];
-#pragma unroll
-        for (int r = 0; r < 4; r++)
-#pragma unroll
-            for (int s = 0; s < 4; s++) lo[r][s] = hi[r][s] = 0;
-
-        for (int k0 = 0; k0 < K; k0 += TK) {
-            __syncthreads();
-            for (int e = threadIdx.x; e < TS * TK; e += 256) {
-                int kk = e % TK, mm = e / TK;
-                long long wv = (m0 + mm < M && k0 + kk < K) ? w[(size_t)(m0 + mm) * K + k0 + kk] : 0;
-                // a = w > 0 ? w : q + w   (PPMM_kernel.cuh:23-25); padding contributes q*0
-                As[kk][mm] = wv > 0 ? (u64)wv : L.q + (u64)wv;
-            }
-            for (int e = threadIdx.x; e < TS * TK; e += 256) {
-                int cc = e % TS, kk = e / TS;
-                u64 xv = 0;
-                if (k0 + kk < K && c0 + cc < col_end) xv = X[k0 + kk][(size_t)i * C + c0 + cc];
-                Xs[kk][cc] = xv;
-            }
-            __syncthreads();
-#pragma unroll 4
-            for (int kk = 0; kk < TK; kk++) {
-                u64 a[4], x[4];
-#pragma unroll
-                for (int r = 0; r < 4; r++) a[r] = As[kk][ty + 16 * r];
-#pragma unroll
-                for (int s = 0; s < 4; s++) x[s] = Xs[kk][tx + 16 * s];
-#pragma unroll
-                for (int r = 0; r < 4; r++)
-#pragma unroll
-                    for (int s = 0; s < 4; s++) mac128(lo[r][s], hi[r][s], a[r], x[s]);
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < 4; r++) {
-            const int m = m0 + ty + 16 * r;
-#pragma unroll
-            for (int s = 0; s < 4; s++) {
-                const long c = c0 + tx + 16 * s;
-                u64 res = barrett128(lo[r][s], hi[r][s], L.q, L.mu_hi, L.mu_lo);
-                if (i == limb_num - 1) {
-                    last[r][s] = res;
-                } else {
-                    u64 tmp = res + L.q - last[r][s];            // wraps mod 2^64 as in :244
-                    res = shoup_mul(tmp, L.inv, L.inv_shoup, L.q);
-                }
-                if (m < M && c < col_end) out[((size_t)m * limb_num + i) * C + c] = res;
-            }
-        }
-    }
-}
-
-int prepare(ckks_b200_pcmm* pc, const float* d_W, const u64* const* h_X_ptrs, int M, int K,
-            double scaler, cudaStream_t st, int* w_bits) {
+// Scales the weights into pc->d_w (one kernel, one read-back of the flags: the stream is synchronised) and
+// returns the bit length of the largest |w|.
+int scale_weights(ckks_b200_pcmm* pc, const float* d_W, int M, int K, double scaler, cudaStream_t st, int* w_bits) {
     int rc = ensure_dev(&pc->d_w, &pc->w_cap, (size_t)M * K);
     if (rc) return rc;
-    if (h_X_ptrs) {
-        rc = ensure_dev(&pc->d_xptrs, &pc->xptrs_cap, (size_t)K);
-        if (rc) return rc;
-        CKB_CUDA(cudaMemcpyAsync((void*)pc->d_xptrs, h_X_ptrs, sizeof(u64*) * K, cudaMemcpyHostToDevice, st));
-    }
-    CKB_CUDA(cudaMemsetAsync(pc->d_flags, 0, 16 * sizeof(int), st));
+    pc->prep_valid = false;                                        // d_w is about to change
+    // words 0 and 2 belong to this pre-pass; word 1 (a wait that ran out) is only cleared by the check that reports it
+    CKB_CUDA(cudaMemsetAsync(pc->d_flags, 0, sizeof(int), st));
+    CKB_CUDA(cudaMemsetAsync(pc->d_flags + 2, 0, sizeof(int), st));
     size_t count = (size_t)M * K;
     scale_weights_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(d_W, pc->d_w, count, scaler, pc->d_flags);
     count_launch();
@@ -124,6 +51,85 @@ int prepare(ckks_b200_pcmm* pc, const float* d_W, const u64* const* h_X_ptrs, in
     CKB_REQUIRE(pc->h_flags[2] == 0, CKKS_B200_ERR_RANGE,
                 "a scaled weight is not finite or exceeds 2^62 in magnitude");
     *w_bits = pc->h_flags[0];
+    return CKKS_B200_OK;
+}
+
+// The 64-bit kernel accumulates a * x in 128 bits without a range check, like the reference kernel
+// (PPMM_kernel.cuh:28,106).  Inside this bound the sum cannot wrap and q + w cannot either, so the CUDA-core and the
+// tensor-core paths agree; beyond it the call is refused instead of returning the reference's wrapped words.
+int simt_range_check(const ckks_b200_pcmm* pc, int K, int w_bits) {
+    int q_bits = 0;
+    for (u64 q : pc->q) {
+        int b = 64 - __builtin_clzll(q);
+        q_bits = b > q_bits ? b : q_bits;
+    }
+    int klog = 0;
+    while ((1 << klog) < K) klog++;
+    CKB_REQUIRE(w_bits < q_bits, CKKS_B200_ERR_RANGE, "a scaled weight of %d bits is not below the %d-bit moduli", w_bits, q_bits);
+    CKB_REQUIRE(klog + 2 * q_bits <= 128, CKKS_B200_ERR_UNSUPPORTED,
+                "K=%d products of two %d-bit factors do not fit the 128-bit accumulator of the CUDA-core kernel", K, q_bits);
+    return CKKS_B200_OK;
+}
+
+// Uploads the pointer table unless the ciphertexts sit at one stride from one another (then base + n * stride
+// addresses them and nothing is copied).
+int make_source(ckks_b200_pcmm* pc, const u64* const* h_X_ptrs, int K, cudaStream_t st, PcmmSource* src) {
+    bool strided = K >= 2 && h_X_ptrs[1] > h_X_ptrs[0];
+    const size_t stride = strided ? (size_t)(h_X_ptrs[1] - h_X_ptrs[0]) : 0;
+    for (int n = 2; n < K && strided; n++) strided = h_X_ptrs[n] == h_X_ptrs[0] + (size_t)n * stride;
+    if (strided) {
+        src->base = h_X_ptrs[0];
+        src->stride = stride;
+        return CKKS_B200_OK;
+    }
+    int rc = ensure_dev(&pc->d_xptrs, &pc->xptrs_cap, (size_t)K);
+    if (rc) return rc;
+    CKB_CUDA(cudaMemcpyAsync((void*)pc->d_xptrs, h_X_ptrs, sizeof(u64*) * K, cudaMemcpyHostToDevice, st));
+    src->table = pc->d_xptrs;
+    return CKKS_B200_OK;
+}
+
+int check_shape(const ckks_b200_pcmm* pc, int mat_M, int mat_N, int mat_K, int mlwe_num, long col_begin, long col_end) {
+    // the reference's two shape rules (PPMM_kernel.cuh:256-263)
+    CKB_REQUIRE(mat_K == pc->N1, CKKS_B200_ERR_SHAPE, "matrix K should be equal to N1!");
+    CKB_REQUIRE(mat_N == mlwe_num, CKKS_B200_ERR_SHAPE, "matrix N should be equal to mlwe number!");
+    CKB_REQUIRE(mat_M >= 1 && mat_N >= 1, CKKS_B200_ERR_ARG, "M and N must be positive");
+    CKB_REQUIRE(mat_N <= (1 << 20), CKKS_B200_ERR_UNSUPPORTED, "contraction length above 2^20");
+    CKB_REQUIRE(col_begin >= 0 && col_begin < col_end && col_end <= pc->C, CKKS_B200_ERR_ARG,
+                "column range [%ld,%ld) outside [0,%ld)", col_begin, col_end, pc->C);
+    CKB_REQUIRE(col_begin % 32 == 0 && (col_end % 32 == 0 || col_end == pc->C), CKKS_B200_ERR_ARG,
+                "column range must start and end on multiples of 32");
+    return CKKS_B200_OK;
+}
+
+// Weights of a multiply: scaled now from d_W, or, with d_W null, the ones ckks_b200_pcmm_prepare_weights left.
+int resolve_weights(ckks_b200_pcmm* pc, const float* d_W, int mat_M, int mat_N, double scaler, cudaStream_t st, int* w_bits,
+                    bool* ready) {
+    if (d_W == nullptr) {
+        CKB_REQUIRE(pc->prep_valid, CKKS_B200_ERR_ARG, "null weight pointer and no prepared weights on this handle");
+        CKB_REQUIRE(pc->prep_M == mat_M && pc->prep_K == mat_N && pc->prep_scaler == scaler, CKKS_B200_ERR_ARG,
+                    "the prepared weights are %dx%d at scaler %g, the call asks for %dx%d at %g", pc->prep_M, pc->prep_K,
+                    pc->prep_scaler, mat_M, mat_N, scaler);
+        *w_bits = pc->prep_w_bits;
+        *ready = true;
+        return CKKS_B200_OK;
+    }
+    *ready = false;
+    return scale_weights(pc, d_W, mat_M, mat_N, scaler, st, w_bits);
+}
+
+int run_simt(ckks_b200_pcmm* pc, const PcmmSource& src, u64* d_out, int mat_M, int mat_N, long col_begin, long col_end,
+             int w_bits, cudaStream_t st) {
+    CKB_REQUIRE(pc->n_peers == 0 && pc->n_owners == 0, CKKS_B200_ERR_UNSUPPORTED,
+                "outputs on other GPUs are written by the tensor-core kernel only");
+    int rc = simt_range_check(pc, mat_N, w_bits);
+    if (rc) return rc;
+    dim3 grid((unsigned)((col_end - col_begin + TS - 1) / TS), (mat_M + TS - 1) / TS);
+    SimtOperands ops{pc->d_w, src.table, src.base, src.stride};
+    pcmm_simt_kernel<SimtLimbsPtr><<<grid, 256, 0, st>>>(ops, (u64*)d_out, SimtLimbsPtr{pc->d_limbs}, mat_M, mat_N, pc->C,
+                                                         pc->q_count, col_begin, col_end);
+    count_launch();
+    CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
 }
 
@@ -231,6 +237,67 @@ extern "C" int ckks_b200_pcmm_set_peer_outputs(ckks_b200_pcmm* pc, uint64_t* con
     for (int i = 0; i < count; i++) CKB_REQUIRE(d_peer_out[i] != nullptr, CKKS_B200_ERR_ARG, "peer pointer %d is null", i);
     for (int i = 0; i < 7; i++) pc->peer_out[i] = i < count ? (u64*)d_peer_out[i] : nullptr;
     pc->n_peers = count;
+    if (count > 0) pc->n_owners = 0;            // one scheme at a time
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_pcmm_set_row_owners(ckks_b200_pcmm* pc, uint64_t* const* d_out_by_rank, int world, int self_rank) {
+    CKB_REQUIRE(pc != nullptr && world >= 0 && world <= 8, CKKS_B200_ERR_ARG, "null handle or world size outside [0,8]");
+    CKB_REQUIRE(world == 0 || (d_out_by_rank != nullptr && self_rank >= 0 && self_rank < world), CKKS_B200_ERR_ARG,
+                "null pointer table or rank %d outside [0,%d)", self_rank, world);
+    for (int i = 0; i < world; i++)
+        CKB_REQUIRE(i == self_rank || d_out_by_rank[i] != nullptr, CKKS_B200_ERR_ARG, "output pointer of rank %d is null", i);
+    for (int i = 0; i < 8; i++) pc->owner_out[i] = (i < world && i != self_rank) ? (u64*)d_out_by_rank[i] : nullptr;
+    pc->n_owners = world;
+    pc->self_rank = world > 0 ? self_rank : 0;
+    if (world > 0) pc->n_peers = 0;
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_pcmm_row_owner_range(int mat_M, int world, int rank, int* row_begin, int* row_end) {
+    CKB_REQUIRE(mat_M >= 1 && world >= 1 && rank >= 0 && rank < world && row_begin && row_end, CKKS_B200_ERR_ARG,
+                "bad argument");
+    const int per = ((mat_M + world - 1) / world + 31) / 32 * 32;
+    const long b = (long)per * rank, e = b + per;
+    *row_begin = (int)(b < mat_M ? b : mat_M);
+    *row_end = (int)(e < mat_M ? e : mat_M);
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_pcmm_set_wait_budget(ckks_b200_pcmm* pc, long long cycles) {
+    CKB_REQUIRE(pc != nullptr && cycles >= 0, CKKS_B200_ERR_ARG, "null handle or negative budget");
+    pc->wait_budget = cycles;
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_pcmm_test_withhold_stage(ckks_b200_pcmm* pc, int stage) {
+    CKB_REQUIRE(pc != nullptr && stage >= -1, CKKS_B200_ERR_ARG, "null handle or stage below -1");
+    pc->withhold_stage = stage;
+    return CKKS_B200_OK;
+}
+
+extern "C" int ckks_b200_pcmm_prepare_weights(ckks_b200_pcmm* pc, const float* d_W, int mat_M, int mat_N, double scaler,
+                                              void* stream) {
+    CKB_REQUIRE(pc && d_W, CKKS_B200_ERR_ARG, "null argument");
+    CKB_REQUIRE(mat_M >= 1 && mat_N >= 1 && mat_N <= (1 << 20), CKKS_B200_ERR_ARG, "M and N must be positive, N at most 2^20");
+    DeviceGuard guard(pc->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    int w_bits = 0;
+    int rc = scale_weights(pc, d_W, mat_M, mat_N, scaler, st, &w_bits);
+    if (rc) return rc;
+    // cut the byte planes now; a handle whose moduli or weights the tensor-core path cannot take keeps the scaled
+    // weights for the CUDA-core kernel
+    int sw = 0, sc = 0, kpass = 0;
+    if (pcmm_tensor_plan(pc, mat_N, w_bits, &sw, &sc, &kpass) == CKKS_B200_OK) {
+        rc = pcmm_tensor(pc, pc->d_w, PcmmSource{}, nullptr, mat_M, mat_N, 0, 0, w_bits, false, st);
+        if (rc) return rc;
+    }
+    pc->prep_valid = true;
+    pc->prep_M = mat_M;
+    pc->prep_K = mat_N;
+    pc->prep_w_bits = w_bits;
+    pc->prep_scaler = scaler;
     return CKKS_B200_OK;
 }
 
@@ -238,16 +305,9 @@ extern "C" int ckks_b200_pcmm_ppmm(ckks_b200_pcmm* pc, const float* d_W,
                                    const uint64_t* const* h_X_ptrs, uint64_t* d_out, int mat_M,
                                    int mat_N, int mat_K, int mlwe_num, double scaler,
                                    long col_begin, long col_end, int algo, void* stream) {
-    CKB_REQUIRE(pc && d_W && h_X_ptrs && d_out, CKKS_B200_ERR_ARG, "null argument");
-    // the reference's two shape rules (PPMM_kernel.cuh:256-263)
-    CKB_REQUIRE(mat_K == pc->N1, CKKS_B200_ERR_SHAPE, "matrix K should be equal to N1!");
-    CKB_REQUIRE(mat_N == mlwe_num, CKKS_B200_ERR_SHAPE, "matrix N should be equal to mlwe number!");
-    CKB_REQUIRE(mat_M >= 1 && mat_N >= 1, CKKS_B200_ERR_ARG, "M and N must be positive");
-    CKB_REQUIRE(mat_N <= (1 << 20), CKKS_B200_ERR_UNSUPPORTED, "contraction length above 2^20");
-    CKB_REQUIRE(col_begin >= 0 && col_begin < col_end && col_end <= pc->C, CKKS_B200_ERR_ARG,
-                "column range [%ld,%ld) outside [0,%ld)", col_begin, col_end, pc->C);
-    CKB_REQUIRE(col_begin % 32 == 0 && (col_end % 32 == 0 || col_end == pc->C), CKKS_B200_ERR_ARG,
-                "column range must start and end on multiples of 32");
+    CKB_REQUIRE(pc && h_X_ptrs && d_out, CKKS_B200_ERR_ARG, "null argument");
+    int rc = check_shape(pc, mat_M, mat_N, mat_K, mlwe_num, col_begin, col_end);
+    if (rc) return rc;
     CKB_REQUIRE(algo >= 0 && algo <= 2, CKKS_B200_ERR_ARG, "unknown algorithm %d", algo);
     for (int n = 0; n < mlwe_num; n++)
         CKB_REQUIRE(h_X_ptrs[n] != nullptr, CKKS_B200_ERR_ARG, "ciphertext pointer %d is null", n);
@@ -255,40 +315,25 @@ extern "C" int ckks_b200_pcmm_ppmm(ckks_b200_pcmm* pc, const float* d_W,
     CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
     cudaStream_t st = (cudaStream_t)stream;
     int w_bits = 0;
-    int rc = prepare(pc, d_W, (const u64* const*)h_X_ptrs, mat_M, mat_N, scaler, st, &w_bits);
+    bool ready = false;
+    rc = resolve_weights(pc, d_W, mat_M, mat_N, scaler, st, &w_bits, &ready);
     if (rc) return rc;
-    if (algo == CKKS_B200_PCMM_SIMT) {
-        CKB_REQUIRE(pc->n_peers == 0, CKKS_B200_ERR_UNSUPPORTED, "peer outputs are written by the tensor-core kernel only");
-        dim3 grid((unsigned)((col_end - col_begin + TS - 1) / TS), (mat_M + TS - 1) / TS);
-        pcmm_simt_kernel<<<grid, 256, 0, st>>>(pc->d_w, pc->d_xptrs, (u64*)d_out, pc->d_limbs, mat_M,
-                                               mat_N, pc->C, pc->q_count, col_begin, col_end);
-        count_launch();
-        CKB_CUDA(cudaGetLastError());
-        return CKKS_B200_OK;
-    }
-    return pcmm_tensor(pc, pc->d_w, pc->d_xptrs, nullptr, false, (u64*)d_out, mat_M, mat_N, col_begin, col_end,
-                       w_bits, st);
+    PcmmSource src;
+    rc = make_source(pc, (const u64* const*)h_X_ptrs, mat_N, st, &src);
+    if (rc) return rc;
+    if (algo == CKKS_B200_PCMM_SIMT) return run_simt(pc, src, (u64*)d_out, mat_M, mat_N, col_begin, col_end, w_bits, st);
+    return pcmm_tensor(pc, pc->d_w, src, (u64*)d_out, mat_M, mat_N, col_begin, col_end, w_bits, ready && pc->prep_sw != 0, st);
 }
 
-// PCMM_Scheme::rlweCipherDecompose (PCMM_Scheme.cuh:51-125) followed by PCMM_Scheme::PPMM
-// (PPMM_kernel.cuh:254-349) as one call: the multiply's slicing pre-pass reads the RLWE
-// ciphertexts through the decomposition's index map, so the K MLWE ciphertexts (K times the
-// size of what they are made from) are never written to or read from HBM.
-extern "C" int ckks_b200_pcmm_ppmm_rlwe(ckks_b200_pcmm* pc, const float* d_W, const ckks_b200_rlwe_source* sources,
-                                        int n_sources, uint64_t* d_out, int mat_M, int mat_N, int mat_K,
-                                        int mlwe_num, double scaler, long col_begin, long col_end, void* stream) {
-    CKB_REQUIRE(pc && d_W && sources && d_out, CKKS_B200_ERR_ARG, "null argument");
-    CKB_REQUIRE(mat_K == pc->N1, CKKS_B200_ERR_SHAPE, "matrix K should be equal to N1!");
-    CKB_REQUIRE(mat_N == mlwe_num, CKKS_B200_ERR_SHAPE, "matrix N should be equal to mlwe number!");
-    CKB_REQUIRE(mat_M >= 1 && mat_N >= 1, CKKS_B200_ERR_ARG, "M and N must be positive");
-    CKB_REQUIRE(mat_N <= (1 << 20), CKKS_B200_ERR_UNSUPPORTED, "contraction length above 2^20");
-    CKB_REQUIRE(col_begin >= 0 && col_begin < col_end && col_end <= pc->C, CKKS_B200_ERR_ARG,
-                "column range [%ld,%ld) outside [0,%ld)", col_begin, col_end, pc->C);
-    CKB_REQUIRE(col_begin % 32 == 0 && (col_end % 32 == 0 || col_end == pc->C), CKKS_B200_ERR_ARG,
-                "column range must start and end on multiples of 32");
+namespace {
+
+// Checks the sources of a decompose-and-multiply call and fills one slot per MLWE ciphertext; `regular` says whether
+// the pre-pass that shares RLWE words between polynomials applies.
+int build_slots(const ckks_b200_pcmm* pc, const ckks_b200_rlwe_source* sources, int n_sources, int mlwe_num,
+                std::vector<RlweSlot>* slots_out, bool* regular_out) {
     CKB_REQUIRE(n_sources >= 1, CKKS_B200_ERR_ARG, "no source ciphertext");
-    // every MLWE index must be produced by exactly one source
-    std::vector<RlweSlot> slots(mlwe_num, RlweSlot{nullptr, 0, 0, 0, 0});
+    std::vector<RlweSlot>& slots = *slots_out;
+    slots.assign(mlwe_num, RlweSlot{nullptr, 0, 0, 0, 0});
     for (int s = 0; s < n_sources; s++) {
         const ckks_b200_rlwe_source& S = sources[s];
         CKB_REQUIRE(S.d_rlwe != nullptr, CKKS_B200_ERR_ARG, "source %d is null", s);
@@ -310,15 +355,6 @@ extern "C" int ckks_b200_pcmm_ppmm_rlwe(ckks_b200_pcmm* pc, const float* d_W, co
     }
     for (int n = 0; n < mlwe_num; n++)
         CKB_REQUIRE(slots[n].rlwe != nullptr, CKKS_B200_ERR_ARG, "ciphertext %d is filled by no source", n);
-    DeviceGuard guard(pc->device);
-    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
-    cudaStream_t st = (cudaStream_t)stream;
-    int rc = ensure_dev(&pc->d_slots, &pc->slots_cap, (size_t)mlwe_num);
-    if (rc) return rc;
-    CKB_CUDA(cudaMemcpyAsync(pc->d_slots, slots.data(), sizeof(RlweSlot) * mlwe_num, cudaMemcpyHostToDevice, st));
-    int w_bits = 0;
-    rc = prepare(pc, d_W, nullptr, mat_M, mat_N, scaler, st, &w_bits);      // synchronises: `slots` may go out of scope
-    if (rc) return rc;
     // the pre-pass that shares RLWE words between polynomials wants every aligned run of 16 ciphertexts from one source
     bool regular = pc->N1 % 32 == 0 && (long)pc->rank * pc->N1 >= 256;     // its index arithmetic wraps at most once
     for (int n0 = 0; n0 < mlwe_num && regular; n0 += 16) {
@@ -327,8 +363,41 @@ extern "C" int ckks_b200_pcmm_ppmm_rlwe(ckks_b200_pcmm* pc, const float* d_W, co
         for (int n = n0 + 1; n < mlwe_num && n < n0 + 16 && regular; n++)
             regular = slots[n].rlwe == f.rlwe && slots[n].L == f.L && slots[n].gap == f.gap && slots[n].i == f.i + (n - n0);
     }
-    return pcmm_tensor(pc, pc->d_w, nullptr, pc->d_slots, regular, (u64*)d_out, mat_M, mat_N, col_begin, col_end, w_bits,
-                       st);
+    *regular_out = regular;
+    return CKKS_B200_OK;
+}
+
+}  // namespace
+
+// PCMM_Scheme::rlweCipherDecompose (PCMM_Scheme.cuh:51-125) followed by PCMM_Scheme::PPMM
+// (PPMM_kernel.cuh:254-349) as one call: the multiply's slicing pre-pass reads the RLWE
+// ciphertexts through the decomposition's index map, so the K MLWE ciphertexts (K times the
+// size of what they are made from) are never written to or read from HBM.
+extern "C" int ckks_b200_pcmm_ppmm_rlwe(ckks_b200_pcmm* pc, const float* d_W, const ckks_b200_rlwe_source* sources,
+                                        int n_sources, uint64_t* d_out, int mat_M, int mat_N, int mat_K,
+                                        int mlwe_num, double scaler, long col_begin, long col_end, void* stream) {
+    CKB_REQUIRE(pc && sources && d_out, CKKS_B200_ERR_ARG, "null argument");
+    int rc = check_shape(pc, mat_M, mat_N, mat_K, mlwe_num, col_begin, col_end);
+    if (rc) return rc;
+    std::vector<RlweSlot> slots;
+    bool regular = false;
+    rc = build_slots(pc, sources, n_sources, mlwe_num, &slots, &regular);
+    if (rc) return rc;
+    DeviceGuard guard(pc->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    rc = ensure_dev(&pc->d_slots, &pc->slots_cap, (size_t)mlwe_num);
+    if (rc) return rc;
+    // from pageable memory: the runtime has taken its copy of `slots` when this call returns
+    CKB_CUDA(cudaMemcpyAsync(pc->d_slots, slots.data(), sizeof(RlweSlot) * mlwe_num, cudaMemcpyHostToDevice, st));
+    int w_bits = 0;
+    bool ready = false;
+    rc = resolve_weights(pc, d_W, mat_M, mat_N, scaler, st, &w_bits, &ready);
+    if (rc) return rc;
+    PcmmSource src;
+    src.slots = pc->d_slots;
+    src.slots_regular = regular;
+    return pcmm_tensor(pc, pc->d_w, src, (u64*)d_out, mat_M, mat_N, col_begin, col_end, w_bits, ready && pc->prep_sw != 0, st);
 }
 
 extern "C" int ckks_b200_pcmm_set_host_chunks(ckks_b200_pcmm* pc, int chunks) {
@@ -338,27 +407,24 @@ extern "C" int ckks_b200_pcmm_set_host_chunks(ckks_b200_pcmm* pc, int chunks) {
     return CKKS_B200_OK;
 }
 
-extern "C" int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, const uint64_t* h_X,
-                                        uint64_t* h_out, int mat_M, int mat_N, int mat_K,
-                                        int mlwe_num, double scaler, int algo) {
-    CKB_REQUIRE(pc && h_W && h_X && h_out, CKKS_B200_ERR_ARG, "null argument");
-    CKB_REQUIRE(mat_K == pc->N1, CKKS_B200_ERR_SHAPE, "matrix K should be equal to N1!");
-    CKB_REQUIRE(mat_N == mlwe_num, CKKS_B200_ERR_SHAPE, "matrix N should be equal to mlwe number!");
-    CKB_REQUIRE(mat_M >= 1 && mat_N >= 1, CKKS_B200_ERR_ARG, "M and N must be positive");
-    DeviceGuard guard(pc->device);
-    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
+namespace {
+
+// Shared body of the two host-buffer entry points.  The weights are scaled (and their planes cut) once, then the
+// columns are cut into chunks that move through three streams as a pipeline: while chunk i is multiplied, chunk i+1
+// is on its way in (only when the ciphertexts themselves come from the host) and chunk i-1 on its way out.  Nothing
+// in the chunk loop waits on the host, and the flags are read once at the end.
+int host_pipeline(ckks_b200_pcmm* pc, const float* h_W, const uint64_t* h_X, const std::vector<RlweSlot>* slots,
+                  bool slots_regular, uint64_t* h_out, int mat_M, int mat_N, double scaler, int algo) {
     const size_t ct_words = (size_t)pc->q_count * pc->C;
     int rc = ensure_dev(&pc->d_W_host, &pc->W_host_cap, (size_t)mat_M * mat_N);
-    if (!rc) rc = ensure_dev(&pc->d_X_host, &pc->X_host_cap, ct_words * mlwe_num);
+    if (!rc && h_X) rc = ensure_dev(&pc->d_X_host, &pc->X_host_cap, ct_words * mat_N);
     if (!rc) rc = ensure_dev(&pc->d_out_host, &pc->out_host_cap, ct_words * mat_M);
     if (rc) return rc;
-    // Column chunks are pipelined over three streams: while chunk i is multiplied, chunk i+1
-    // is on its way in and chunk i-1 on its way out (columns are independent of one another).
     for (int i = 0; i < 3; i++)
         if (!pc->hs[i]) CKB_CUDA(cudaStreamCreateWithFlags(&pc->hs[i], cudaStreamNonBlocking));
     cudaStream_t s_in = pc->hs[0], s_mm = pc->hs[1], s_out = pc->hs[2];
     const long tiles = (pc->C + 31) / 32;
-    const size_t total_bytes = 8 * ct_words * ((size_t)mlwe_num + mat_M);
+    const size_t total_bytes = 8 * ct_words * ((size_t)(h_X ? mat_N : 0) + mat_M);
     // Equal chunks of 32-column tiles.  Sixteen is the measured optimum at the BERT shape (8.07 GB each way): fewer
     // leave the link idle while the first chunk comes in and the last goes out, more make the rows of the strided
     // host copies short (8 chunks 204 ms, 16 chunks 195 ms, 64 chunks 264 ms; small chunks at the two ends only,
@@ -372,16 +438,39 @@ extern "C" int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, co
     const int nchunk = (int)widths.size();
     long widest = 0;
     for (long w : widths) widest = w > widest ? w : widest;
-    rc = pcmm_reserve_planes(pc, mat_M, mat_N, widest * 32);
-    if (rc) return rc;
-    while ((int)pc->hev.size() < 2 * nchunk) {
+    if (algo != CKKS_B200_PCMM_SIMT) {
+        rc = pcmm_reserve_planes(pc, mat_M, mat_N, widest * 32);
+        if (rc) return rc;
+    }
+    while ((int)pc->hev.size() < 2 * nchunk + 1) {
         cudaEvent_t e;
         CKB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         pc->hev.push_back(e);
     }
-    CKB_CUDA(cudaMemcpyAsync(pc->d_W_host, h_W, sizeof(float) * mat_M * mat_N, cudaMemcpyHostToDevice, s_in));
-    std::vector<const uint64_t*> ptrs(mlwe_num);
-    for (int n = 0; n < mlwe_num; n++) ptrs[n] = (const uint64_t*)(pc->d_X_host + ct_words * n);
+    CKB_CUDA(cudaMemcpyAsync(pc->d_W_host, h_W, sizeof(float) * mat_M * mat_N, cudaMemcpyHostToDevice, s_mm));
+    if (slots) {
+        rc = ensure_dev(&pc->d_slots, &pc->slots_cap, (size_t)mat_N);
+        if (rc) return rc;
+        CKB_CUDA(cudaMemcpyAsync(pc->d_slots, slots->data(), sizeof(RlweSlot) * mat_N, cudaMemcpyHostToDevice, s_mm));
+    }
+    int w_bits = 0;
+    rc = scale_weights(pc, pc->d_W_host, mat_M, mat_N, scaler, s_mm, &w_bits);       // the one host wait before the loop
+    if (rc) return rc;
+    if (algo == CKKS_B200_PCMM_SIMT) {
+        CKB_REQUIRE(slots == nullptr, CKKS_B200_ERR_UNSUPPORTED, "the CUDA-core kernel reads stored MLWE ciphertexts only");
+        rc = simt_range_check(pc, mat_N, w_bits);
+    } else {
+        rc = pcmm_tensor(pc, pc->d_w, PcmmSource{}, nullptr, mat_M, mat_N, 0, 0, w_bits, false, s_mm);     // weight planes
+    }
+    if (rc) return rc;
+    PcmmSource src;
+    if (slots) {
+        src.slots = pc->d_slots;
+        src.slots_regular = slots_regular;
+    } else {
+        src.base = pc->d_X_host;
+        src.stride = ct_words;
+    }
     const size_t pitch = (size_t)pc->C * 8;
     long t0 = 0;
     for (int i = 0; i < nchunk; i++) {
@@ -390,12 +479,14 @@ extern "C" int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, co
         long c1 = t1 * 32;
         t0 = t1;
         if (c1 > pc->C) c1 = pc->C;
-        CKB_CUDA(cudaMemcpy2DAsync(pc->d_X_host + c0, pitch, h_X + c0, pitch, (size_t)(c1 - c0) * 8,
-                                   (size_t)mlwe_num * pc->q_count, cudaMemcpyHostToDevice, s_in));
-        CKB_CUDA(cudaEventRecord(pc->hev[2 * i], s_in));
-        CKB_CUDA(cudaStreamWaitEvent(s_mm, pc->hev[2 * i], 0));
-        rc = ckks_b200_pcmm_ppmm(pc, pc->d_W_host, ptrs.data(), (uint64_t*)pc->d_out_host, mat_M, mat_N, mat_K,
-                                 mlwe_num, scaler, c0, c1, algo, s_mm);
+        if (h_X) {
+            CKB_CUDA(cudaMemcpy2DAsync(pc->d_X_host + c0, pitch, h_X + c0, pitch, (size_t)(c1 - c0) * 8,
+                                       (size_t)mat_N * pc->q_count, cudaMemcpyHostToDevice, s_in));
+            CKB_CUDA(cudaEventRecord(pc->hev[2 * i], s_in));
+            CKB_CUDA(cudaStreamWaitEvent(s_mm, pc->hev[2 * i], 0));
+        }
+        if (algo == CKKS_B200_PCMM_SIMT) rc = run_simt(pc, src, pc->d_out_host, mat_M, mat_N, c0, c1, w_bits, s_mm);
+        else rc = pcmm_tensor(pc, pc->d_w, src, pc->d_out_host, mat_M, mat_N, c0, c1, w_bits, true, s_mm);
         if (rc) return rc;
         CKB_CUDA(cudaEventRecord(pc->hev[2 * i + 1], s_mm));
         CKB_CUDA(cudaStreamWaitEvent(s_out, pc->hev[2 * i + 1], 0));
@@ -408,6 +499,57 @@ extern "C" int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, co
         if (rc) return rc;
     }
     return CKKS_B200_OK;
+}
+
+}  // namespace
+
+extern "C" int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, const uint64_t* h_X,
+                                        uint64_t* h_out, int mat_M, int mat_N, int mat_K,
+                                        int mlwe_num, double scaler, int algo) {
+    CKB_REQUIRE(pc && h_W && h_X && h_out, CKKS_B200_ERR_ARG, "null argument");
+    int rc = check_shape(pc, mat_M, mat_N, mat_K, mlwe_num, 0, pc->C);
+    if (rc) return rc;
+    CKB_REQUIRE(algo >= 0 && algo <= 2, CKKS_B200_ERR_ARG, "unknown algorithm %d", algo);
+    DeviceGuard guard(pc->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
+    return host_pipeline(pc, h_W, h_X, nullptr, false, h_out, mat_M, mat_N, scaler, algo);
+}
+
+// Host-buffer form of ckks_b200_pcmm_ppmm_rlwe: the RLWE ciphertexts (2*(L+1)*N words each, K times smaller than the
+// MLWE ciphertexts cut from them) are what crosses the bus on the way in.
+extern "C" int ckks_b200_pcmm_ppmm_rlwe_host(ckks_b200_pcmm* pc, const float* h_W, const ckks_b200_rlwe_source* h_sources,
+                                             int n_sources, uint64_t* h_out, int mat_M, int mat_N, int mat_K, int mlwe_num,
+                                             double scaler) {
+    CKB_REQUIRE(pc && h_W && h_sources && h_out, CKKS_B200_ERR_ARG, "null argument");
+    int rc = check_shape(pc, mat_M, mat_N, mat_K, mlwe_num, 0, pc->C);
+    if (rc) return rc;
+    CKB_REQUIRE(n_sources >= 1 && n_sources <= 64, CKKS_B200_ERR_ARG, "source count %d outside [1,64]", n_sources);
+    DeviceGuard guard(pc->device);
+    CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
+    // device copies of the sources, one after another in the staging buffer of the ciphertexts
+    const size_t N = (size_t)pc->rank * pc->N1;
+    size_t words = 0;
+    for (int s = 0; s < n_sources; s++) {
+        CKB_REQUIRE(h_sources[s].d_rlwe != nullptr && h_sources[s].L >= 0, CKKS_B200_ERR_ARG, "source %d is null", s);
+        words += 2 * (size_t)(h_sources[s].L + 1) * N;
+    }
+    rc = ensure_dev(&pc->d_X_host, &pc->X_host_cap, words);
+    if (rc) return rc;
+    for (int i = 0; i < 3; i++)
+        if (!pc->hs[i]) CKB_CUDA(cudaStreamCreateWithFlags(&pc->hs[i], cudaStreamNonBlocking));
+    std::vector<ckks_b200_rlwe_source> dev(h_sources, h_sources + n_sources);
+    size_t off = 0;
+    for (int s = 0; s < n_sources; s++) {
+        const size_t w = 2 * (size_t)(h_sources[s].L + 1) * N;
+        CKB_CUDA(cudaMemcpyAsync(pc->d_X_host + off, h_sources[s].d_rlwe, w * 8, cudaMemcpyHostToDevice, pc->hs[1]));
+        dev[s].d_rlwe = (const uint64_t*)(pc->d_X_host + off);
+        off += w;
+    }
+    std::vector<RlweSlot> slots;
+    bool regular = false;
+    rc = build_slots(pc, dev.data(), n_sources, mlwe_num, &slots, &regular);
+    if (rc) return rc;
+    return host_pipeline(pc, h_W, nullptr, &slots, regular, h_out, mat_M, mat_N, scaler, CKKS_B200_PCMM_TENSOR);
 }
 
 // The reference copies the first limb of row i of ppmm_output back over ciphertext i,

@@ -35,8 +35,22 @@ struct ckks_b200_pcmm {
     size_t slots_cap = 0;
     u64* peer_out[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // see ckks_b200_pcmm_set_peer_outputs
     int n_peers = 0;
-    int* d_flags = nullptr;           // [0] max |w| bits seen, [1] device-side wait timeout, ...
+    // see ckks_b200_pcmm_set_row_owners: output buffer of every rank (nullptr = the call's d_out), rows per owner
+    u64* owner_out[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int n_owners = 0, self_rank = 0;
+    // [0] max |w| bits seen, [2] a scaled weight out of range: both cleared by every weight scaling;
+    // [1] site of a device-side wait that ran out: set by kernels, cleared only by ckks_b200_pcmm_check
+    int* d_flags = nullptr;
     int* h_flags = nullptr;           // pinned mirror
+    long long wait_budget = 0;        // clock cycles a device-side wait may take (0: the library's default)
+    int withhold_stage = -1;          // see ckks_b200_pcmm_test_withhold_stage; consumed by the next tensor-core launch
+
+    // weights kept by ckks_b200_pcmm_prepare_weights: d_w and d_wplanes hold them, multiplies that pass a null
+    // weight pointer use them
+    bool prep_valid = false;
+    int prep_M = 0, prep_K = 0, prep_w_bits = 0;
+    int prep_sw = 0, prep_sc = 0;     // plane configuration d_wplanes was cut for (0: not cut yet)
+    double prep_scaler = 0.0;
 
     // tensor-core path workspaces
     uint8_t* d_wplanes = nullptr;     // weight byte planes in MMA tile order
@@ -83,8 +97,20 @@ int ensure_dev(T** buf, size_t* cap, size_t count) {
 // decomposition's index map.
 // slots_regular: N1 is a multiple of 32, every aligned run of 16 ciphertexts lies in one source with consecutive
 // indices and no gap exceeds pcmm_slots_max_gap(), which lets the pre-pass share RLWE words between polynomials.
-int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots,
-                bool slots_regular, u64* d_out, int M, int K, long col_begin, long col_end, int w_bits, cudaStream_t st);
+// Where the ciphertext words of a multiply come from: a device table of pointers, or (table == nullptr) ciphertext n
+// at base + n * stride words, or RLWE ciphertexts through the decomposition's index map (slots != nullptr).
+struct PcmmSource {
+    const u64* const* table = nullptr;
+    const u64* base = nullptr;
+    size_t stride = 0;
+    const RlweSlot* slots = nullptr;
+    bool slots_regular = false;
+};
+// weights_ready: d_wplanes already holds the planes of these weights (prepared weights), skip their slicing.
+int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const PcmmSource& src, u64* d_out, int M, int K,
+                long col_begin, long col_end, int w_bits, bool weights_ready, cudaStream_t st);
+// Plane configuration (SW, SC) and K blocks per accumulation pass the tensor-core path takes for these weights.
+int pcmm_tensor_plan(const ckks_b200_pcmm* pc, int K, int w_bits, int* sw_out, int* sc_out, int* kpass_out);
 int pcmm_slots_max_gap();
 int pcmm_reserve_planes(ckks_b200_pcmm* pc, int M, int K, long ncols);
 }  // namespace ckb

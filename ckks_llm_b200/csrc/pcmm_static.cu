@@ -10,10 +10,18 @@
 //
 // ckks_b200_pcmm_ppmm_static is the same multiply on the 64-bit CUDA-core kernel with
 // every byte of working memory taken from one array that is part of the library image:
-// a file-scope __device__ array, present on every GPU that loads the library from load
-// until exit.  It takes no handle; the per-limb constants are computed on the host and
-// travel as kernel arguments.  The array holds, in this order, 256 bytes of flags, the
-// table of ciphertext pointers (kMaxK entries) and the scaled weights (kMaxWeights int64).
+// a file-scope __device__ array.  It takes no handle; the per-limb constants are computed
+// on the host and travel as kernel arguments.  The array holds, in this order, 256 bytes of
+// flags, the table of ciphertext pointers (kMaxK entries) and the scaled weights
+// (kMaxWeights int64).
+//
+// When the array comes to exist: the CUDA runtime loads a library's device code lazily by
+// default, so the 8 MB are claimed on a GPU when this file's code is first touched there,
+// which is the first call of the entry point on that GPU (its address look-up), not the
+// moment the shared library is opened.  A host whose memory pool is about to take all of
+// the GPU should therefore make one small warm-up call per device before the pool is
+// created (or run with CUDA_MODULE_LOADING=EAGER); from then on the array stays until the
+// process exits.
 //
 // Rules that follow from sharing one array:
 //   * sizes above the stated maxima are refused with CKKS_B200_ERR_UNSUPPORTED;
@@ -21,11 +29,12 @@
 //     of every call and everything else is overwritten before it is read;
 //   * two calls whose work overlaps on the same GPU (different streams or threads) race
 //     on the array: callers serialise them;
-//   * the first call on each device looks up the array's device address (that look-up is
-//     the only set-up), so make that first call outside any stream capture.
+//   * every call copies its flags back to the host and waits for the stream once, so no
+//     call may be issued while the stream is being captured into a CUDA graph; the first
+//     call on each device additionally looks up the array's device address.
 #include <mutex>
 
-#include "common.cuh"
+#include "pcmm_simt.cuh"
 
 using namespace ckb;
 
@@ -33,7 +42,7 @@ namespace {
 
 constexpr int kMaxK = 4096;                        // ciphertexts (= mat_N) per call
 constexpr size_t kMaxWeights = (size_t)1 << 20;    // mat_M * mat_N per call
-constexpr int kMaxLimbs = 24;                      // ring-pack q moduli per call
+constexpr int kMaxLimbs = kSimtMaxLimbsByValue;    // ring-pack q moduli per call (24): their constants travel by value
 constexpr int kMaxDevices = 64;
 constexpr size_t kFlagsBytes = 256;
 constexpr size_t kPtrBytes = (size_t)kMaxK * sizeof(u64*);
@@ -43,13 +52,6 @@ constexpr size_t kScratchBytes = kWeightsOffset + kMaxWeights * sizeof(long long
 // About 8.03 MB per GPU.  In host code this name is only a handle for the runtime's
 // symbol look-up, never a pointer a kernel could use.
 static __device__ __align__(256) unsigned char g_static_scratch[kScratchBytes];
-
-struct StaticLimb {
-    u64 q, mu_hi, mu_lo, inv, inv_shoup;
-};
-struct StaticLimbs {
-    StaticLimb l[kMaxLimbs];
-};
 
 std::mutex g_setup_mutex;
 unsigned char* g_scratch_addr[kMaxDevices] = {};
@@ -73,8 +75,9 @@ int scratch_on_current_device(unsigned char** out) {
     return CKKS_B200_OK;
 }
 
-// w = (int64) trunc((double)W * scaler) into the scratch; flags[2] marks a value that does
-// not fit (src/ckks/include/pcmm/PPMM_kernel.cuh:148 for the conversion).
+// w = (int64) trunc((double)W * scaler) into the scratch; flags[0] collects the bit length of the
+// largest |w|, flags[2] marks a value that does not fit (src/ckks/include/pcmm/PPMM_kernel.cuh:148
+// for the conversion).
 __global__ void static_scale_kernel(const float* W, unsigned char* scratch, size_t count, double scaler) {
     long long* w = reinterpret_cast<long long*>(scratch + kWeightsOffset);
     int* flags = reinterpret_cast<int*>(scratch);
@@ -85,73 +88,8 @@ __global__ void static_scale_kernel(const float* W, unsigned char* scratch, size
     if (!(fabs(v) < 4611686018427387904.0)) atomicOr(&flags[2], 1);
     else iv = (long long)v;
     w[i] = iv;
-}
-
-constexpr int TS = 64, TK = 16;
-
-// The multiply of pcmm_simt_kernel with weights and pointer table read from the scratch
-// and the limb constants passed by value (PPMM_kernel.cuh:12-31,213-249).
-__global__ void __launch_bounds__(256) static_simt_kernel(const unsigned char* scratch, u64* __restrict__ out,
-                                                          StaticLimbs limbs, int M, int K, long C, int limb_num) {
-    const long long* w = reinterpret_cast<const long long*>(scratch + kWeightsOffset);
-    const u64* const* X = reinterpret_cast<const u64* const*>(scratch + kFlagsBytes);
-    __shared__ u64 As[TK][TS + 1];
-    __shared__ u64 Xs[TK][TS];
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-    const long c0 = (long)blockIdx.x * TS;
-    const int m0 = blockIdx.y * TS;
-    u64 last[4][4];
-    for (int i = limb_num - 1; i >= 0; i--) {
-        const StaticLimb L = limbs.l[i];
-        u64 lo[4][4], hi[4][4];
-#pragma unroll
-        for (int r = 0; r < 4; r++)
-#pragma unroll
-            for (int s = 0; s < 4; s++) lo[r][s] = hi[r][s] = 0;
-        for (int k0 = 0; k0 < K; k0 += TK) {
-            __syncthreads();
-            for (int e = threadIdx.x; e < TS * TK; e += 256) {
-                int kk = e % TK, mm = e / TK;
-                long long wv = (m0 + mm < M && k0 + kk < K) ? w[(size_t)(m0 + mm) * K + k0 + kk] : 0;
-                As[kk][mm] = wv > 0 ? (u64)wv : L.q + (u64)wv;
-            }
-            for (int e = threadIdx.x; e < TS * TK; e += 256) {
-                int cc = e % TS, kk = e / TS;
-                u64 xv = 0;
-                if (k0 + kk < K && c0 + cc < C) xv = X[k0 + kk][(size_t)i * C + c0 + cc];
-                Xs[kk][cc] = xv;
-            }
-            __syncthreads();
-#pragma unroll 4
-            for (int kk = 0; kk < TK; kk++) {
-                u64 a[4], x[4];
-#pragma unroll
-                for (int r = 0; r < 4; r++) a[r] = As[kk][ty + 16 * r];
-#pragma unroll
-                for (int s = 0; s < 4; s++) x[s] = Xs[kk][tx + 16 * s];
-#pragma unroll
-                for (int r = 0; r < 4; r++)
-#pragma unroll
-                    for (int s = 0; s < 4; s++) mac128(lo[r][s], hi[r][s], a[r], x[s]);
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < 4; r++) {
-            const int m = m0 + ty + 16 * r;
-#pragma unroll
-            for (int s = 0; s < 4; s++) {
-                const long c = c0 + tx + 16 * s;
-                u64 res = barrett128(lo[r][s], hi[r][s], L.q, L.mu_hi, L.mu_lo);
-                if (i == limb_num - 1) {
-                    last[r][s] = res;
-                } else {
-                    u64 tmp = res + L.q - last[r][s];
-                    res = shoup_mul(tmp, L.inv, L.inv_shoup, L.q);
-                }
-                if (m < M && c < C) out[((size_t)m * limb_num + i) * C + c] = res;
-            }
-        }
-    }
+    const unsigned long long mag = iv < 0 ? (unsigned long long)(-iv) : (unsigned long long)iv;
+    if (mag) atomicMax(&flags[0], 64 - __clzll(mag));       // bit length of the largest |w|
 }
 
 }  // namespace
@@ -174,7 +112,7 @@ extern "C" int ckks_b200_pcmm_ppmm_static(const float* d_W, const uint64_t* cons
     for (int n = 0; n < mlwe_num; n++)
         CKB_REQUIRE(h_X_ptrs[n] != nullptr, CKKS_B200_ERR_ARG, "ciphertext pointer %d is null", n);
 
-    StaticLimbs limbs = {};
+    SimtLimbsVal limbs = {};
     for (int i = 0; i < q_count; i++) {
         const u64 q = q_ringpack[i];
         CKB_REQUIRE((q & 1) && q > 2 && q < (1ull << 62), CKKS_B200_ERR_ARG,
@@ -215,8 +153,21 @@ extern "C" int ckks_b200_pcmm_ppmm_static(const float* d_W, const uint64_t* cons
     CKB_CUDA(cudaMemcpyAsync(flags, scratch, sizeof(flags), cudaMemcpyDeviceToHost, st));
     CKB_CUDA(cudaStreamSynchronize(st));
     CKB_REQUIRE(flags[2] == 0, CKKS_B200_ERR_RANGE, "a scaled weight is not finite or exceeds 2^62 in magnitude");
+    // The 128-bit accumulator of the kernel has no range check (neither has the reference's, PPMM_kernel.cuh:28,106):
+    // refuse what could wrap it instead of returning wrapped words.
+    int w_bits = flags[0], q_bits = 0, klog = 0;
+    for (int i = 0; i < q_count; i++) {
+        const int b = 64 - __builtin_clzll(q_ringpack[i]);
+        q_bits = b > q_bits ? b : q_bits;
+    }
+    while ((1 << klog) < mat_N) klog++;
+    CKB_REQUIRE(w_bits < q_bits, CKKS_B200_ERR_RANGE, "a scaled weight of %d bits is not below the %d-bit moduli", w_bits, q_bits);
+    CKB_REQUIRE(klog + 2 * q_bits <= 128, CKKS_B200_ERR_UNSUPPORTED,
+                "K=%d products of two %d-bit factors do not fit the 128-bit accumulator of the CUDA-core kernel", mat_N, q_bits);
     dim3 grid((unsigned)((C + TS - 1) / TS), (mat_M + TS - 1) / TS);
-    static_simt_kernel<<<grid, 256, 0, st>>>(scratch, (u64*)d_out, limbs, mat_M, mat_N, C, q_count);
+    SimtOperands ops{reinterpret_cast<const long long*>(scratch + kWeightsOffset),
+                     reinterpret_cast<const u64* const*>(scratch + kFlagsBytes), nullptr, 0};
+    pcmm_simt_kernel<SimtLimbsVal><<<grid, 256, 0, st>>>(ops, (u64*)d_out, limbs, mat_M, mat_N, C, q_count, 0, C);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;

@@ -34,10 +34,7 @@ using namespace ckb::umma;
 namespace {
 
 constexpr int TC = 32;             // ciphertext columns per tile
-#ifndef CKB_KB
-#define CKB_KB 64
-#endif
-constexpr int KB = CKB_KB;         // contraction depth per pipeline stage
+constexpr int KB = 64;             // contraction depth per pipeline stage
 constexpr int KS = KB / 32;        // UMMA K steps per stage
 constexpr int A_PLANE_STEP = TM * 32;   // bytes of one weight plane, one K step
 constexpr int B_PLANE_STEP = TC * 32;   // bytes of one ciphertext plane, one K step
@@ -49,24 +46,18 @@ constexpr int STG_ROW = 144;
 constexpr int STG_WARP = 32 * STG_ROW;
 constexpr int STG_BYTES = NUM_EPI_WARPS * STG_WARP;
 
-#ifdef CKB_PROFILE
-#define CKB_PROF_DECL long long prof_t0_ = 0, prof_acc_[4] = {0, 0, 0, 0};
-#define CKB_PROF_BEGIN() prof_t0_ = clock64()
-#define CKB_PROF_END(i) prof_acc_[i] += clock64() - prof_t0_
-#define CKB_PROF_FLUSH(base) if (blockIdx.x == 0) { for (int i_ = 0; i_ < 4; i_++) P.flags[(base) + i_] = (int)(prof_acc_[i_] >> 10); }
-#else
-#define CKB_PROF_DECL
-#define CKB_PROF_BEGIN()
-#define CKB_PROF_END(i)
-#define CKB_PROF_FLUSH(base)
-#endif
+// Where the epilogue stores a word besides (or instead of) the call's own output buffer.
+constexpr int DEST_LOCAL = 0;      // the call's output buffer only
+constexpr int DEST_BROADCAST = 1;  // also, at the same offset, into every buffer of dests[0..n_dests)
+constexpr int DEST_OWNERS = 2;     // row m goes, at the same offset, into dests[m / rows_per_owner] only
 
 struct UmmaArgs {
     const uint8_t* wplanes;    // [mt][kb][a][ks][4096]
     const uint8_t* xplanes;    // [limb][ct][kb][ks][b][1024]
     u64* out;                  // [M][limbs][C]
-    u64* peers[7];             // output buffers of the same shape on other GPUs that also receive every word written
-    int n_peers;
+    u64* dests[8];             // output buffers of the same shape, most of them on other GPUs (see DEST_*)
+    int n_dests;
+    int rows_per_owner;
     const PcmmLimb* limbs;
     int* flags;
     int M, limbs_n;
@@ -74,6 +65,9 @@ struct UmmaArgs {
     long col_begin, col_end;   // columns covered by xplanes: ct 0 starts at col_begin
     int MT, CT, KBN;           // tiles in M, tiles in columns, pipeline stages per tile
     int num_stages;
+    int kpass;                 // K blocks accumulated in tensor memory before the epilogue takes the partial sums over
+    long long wait_budget;     // clock cycles a wait on an mbarrier may take
+    int withhold;              // test switch: the producer stops before its copy number `withhold` (-1: off)
 };
 
 template <int SW, int SC>
@@ -126,8 +120,9 @@ __global__ void slice_weights_kernel(const long long* __restrict__ w, uint8_t* _
 // Pre-pass 2: ciphertext planes for columns [col_begin, col_begin + CT*32).  One thread
 // per (limb, column, 16-wide K chunk); lanes run over columns so every ciphertext read is
 // coalesced.
-__global__ void slice_cipher_kernel(const u64* const* __restrict__ X, uint8_t* __restrict__ planes, int K,
-                                    long C, int limbs_n, long col_begin, long col_end, int CT, int KBN, int SC) {
+__global__ void slice_cipher_kernel(const u64* const* __restrict__ X, const u64* __restrict__ xbase, size_t xstride,
+                                    uint8_t* __restrict__ planes, int K, long C, int limbs_n, long col_begin, long col_end,
+                                    int CT, int KBN, int SC) {
     const long ncol = (long)CT * TC;
     const long col = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (col >= ncol) return;
@@ -140,7 +135,8 @@ __global__ void slice_cipher_kernel(const u64* const* __restrict__ X, uint8_t* _
 #pragma unroll
     for (int e = 0; e < 16; e++) {
         int n = k16g * 16 + e;
-        v[e] = (n < K && c < col_end) ? X[n][(size_t)limb * C + c] : 0;
+        // ciphertext n: entry n of the pointer table, or base + n * stride when there is no table
+        v[e] = (n < K && c < col_end) ? (X ? X[n] : xbase + (size_t)n * xstride)[(size_t)limb * C + c] : 0;
     }
     const int ct = (int)(col / TC), cc = (int)(col % TC);
     for (int b = 0; b < SC; b++) {
@@ -332,17 +328,51 @@ __global__ void __launch_bounds__(256) slice_rlwe_rows_kernel(const RlweSlot* __
     }
 }
 
+// Reads the ND diagonal accumulators of 16 output columns (this thread's row) out of tensor memory and recombines
+// them, sum_d v_d * 2^(8d), into signed 128-bit sums; ADD accumulates onto acc instead of overwriting it.
+template <int ND, bool ADD>
+__device__ __forceinline__ void drain_accumulators(uint32_t taddr, unsigned __int128 (&acc)[16]) {
+#pragma unroll
+    for (int g = 0; g < 2; g++) {
+        int32_t v[ND][8];
+#pragma unroll
+        for (int d = 0; d < ND; d++) tmem_ld8(taddr + d * TC + g * 8, v[d]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            // groups of four diagonals fit a signed 64-bit word (|v_d| < 2^31, top shift 24), and the groups sit
+            // 32 bits apart
+            long long grp[(ND + 3) / 4];
+#pragma unroll
+            for (int gi = 0; gi < (ND + 3) / 4; gi++) {
+                long long t = 0;
+#pragma unroll
+                for (int k = 3; k >= 0; k--)
+                    if (gi * 4 + k < ND) t = t * 256 + (long long)v[gi * 4 + k][e];
+                grp[gi] = t;
+            }
+            __int128 s = 0;
+#pragma unroll
+            for (int gi = (ND + 3) / 4 - 1; gi >= 0; gi--) s = s * ((__int128)1 << 32) + grp[gi];
+            if (ADD) acc[g * 8 + e] += (unsigned __int128)s;
+            else acc[g * 8 + e] = (unsigned __int128)s;
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Main kernel
 // ---------------------------------------------------------------------------
-// PEERS: every stored word also goes into the other GPUs' output buffers listed in P.peers.
-template <int SW, int SC, bool PEERS>
+// DEST: one of DEST_LOCAL / DEST_BROADCAST / DEST_OWNERS.  KSPLIT: the contraction is accumulated in passes of P.kpass
+// K blocks (a K too deep for one pass of s32 accumulators); without it one pass takes all P.KBN blocks.
+template <int SW, int SC, int DEST, bool KSPLIT>
 __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
     using C_ = Cfg<SW, SC>;
+    constexpr bool PEERS = DEST != DEST_LOCAL;
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ uint64_t bars[2 * 8 + 2];
+    __shared__ uint64_t bars[2 * 8 + 3];
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int abort_flag;
+    __shared__ int abort_flag, never_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NS = P.num_stages;
@@ -351,6 +381,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
     const uint32_t empty_bar = smem_u32(&bars[8]);         // [NS]
     const uint32_t tmem_full_bar = smem_u32(&bars[16]);
     const uint32_t tmem_empty_bar = smem_u32(&bars[17]);
+    const uint32_t mma_done_bar = smem_u32(&bars[18]);     // used on the way out of a launch that gave up
+    const long long budget = P.wait_budget;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; s++) {
@@ -359,7 +391,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
         }
         mbar_init(tmem_full_bar, 1);
         mbar_init(tmem_empty_bar, NUM_EPI_WARPS);
+        mbar_init(mma_done_bar, 1);
         abort_flag = 0;
+        never_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -377,8 +411,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            uint32_t s = 0, ph = 0, issued = 0;    // ring position, its phase parity, copies in flight at most NS
-            bool ok = true;
+            uint32_t s = 0, ph = 0, issued = 0;    // ring position, its phase parity, stages issued so far
+            bool ok = true, withheld = false;
             const int krot = (int)((blockIdx.x / P.MT) % P.KBN);
             for (long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 const int mt = (int)(item % P.MT);
@@ -390,7 +424,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                     // K block, which keeps the CTAs from asking L2 for the same weight block at once.
                     int kbr = krot;
                     for (int kb = 0; kb < P.KBN; kb++) {
-                        if (issued >= (uint32_t)NS && !mbar_wait(empty_bar + 8 * s, ph ^ 1, P.flags, 1, &abort_flag)) { ok = false; break; }
+                        // Test switch: stop producing in front of this stage and say nothing, so that the wait of
+                        // the MMA issuer on this stage's barrier runs into its clock budget.
+                        if ((int)issued == P.withhold) { withheld = true; ok = false; break; }
+                        if (issued >= (uint32_t)NS && !mbar_wait(empty_bar + 8 * s, ph ^ 1, P.flags, 1, &abort_flag, budget)) { ok = false; break; }
                         const uint32_t dst = smem_base + s * C_::STAGE;
                         mbar_arrive_expect_tx(full_bar + 8 * s, C_::STAGE);
                         bulk_g2s(dst, asrc0 + (size_t)kbr * C_::A_STAGE, C_::A_STAGE, full_bar + 8 * s);
@@ -401,7 +438,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                     }
                 }
             }
-            if (!ok) atomicExch(&abort_flag, 1);
+            if (!ok && !withheld) atomicExch(&abort_flag, 1);
             // Drain: every copy this thread issued must have landed before the CTA exits.  The last
             // min(issued, NS) copies sit in the ring positions before s, going backwards.
             uint32_t n = issued < (uint32_t)NS ? issued : (uint32_t)NS;
@@ -409,7 +446,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
             for (uint32_t j = 0; j < n; j++) {
                 if (ds == 0) { ds = NS; dph ^= 1; }
                 ds--;
-                mbar_wait(full_bar + 8 * ds, dph, P.flags, 2, &abort_flag);
+                mbar_wait(full_bar + 8 * ds, dph, P.flags, 2, &never_flag, budget);
             }
         }
     } else if (warp == 1) {
@@ -417,9 +454,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
         if (lane == 0) {
             uint32_t s = 0, ph = 0, tile = 0;
             bool ok = true;
-            CKB_PROF_DECL
-            const long long prof_start = clock64();
-            (void)prof_start;
             constexpr uint32_t idesc_full_u = instr_desc(TC * SC, false);
             constexpr uint32_t idesc_full_s = instr_desc(TC * SC, true);
             constexpr uint32_t idesc_head_u = instr_desc(TC * (SC - 1), false);
@@ -427,20 +461,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
             constexpr uint32_t idesc_tail_u = instr_desc(TC, false);
             constexpr uint32_t idesc_tail_s = instr_desc(TC, true);
             const uint32_t base16 = smem_base >> 4;
+            // A "tile" of the tensor-memory handshake is one accumulation pass: all K blocks of an (item, limb)
+            // pair, or P.kpass of them at a time when the whole K would overflow the s32 accumulators.
             for (long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-                for (int limb = limbs_n - 1; limb >= 0 && ok; limb--, tile++) {
-                    CKB_PROF_BEGIN();
-                    if (tile > 0 && !mbar_wait(tmem_empty_bar, (tile - 1) & 1, P.flags, 3, &abort_flag)) { ok = false; break; }
-                    CKB_PROF_END(0);
+                for (int limb = limbs_n - 1; limb >= 0 && ok; limb--) {
+                  const int kstep = KSPLIT ? P.kpass : P.KBN;
+                  for (int kb0 = 0; kb0 < P.KBN && ok; kb0 += kstep, tile++) {
+                    if (tile > 0 && !mbar_wait(tmem_empty_bar, (tile - 1) & 1, P.flags, 3, &abort_flag, budget)) { ok = false; break; }
                     tc_fence_after();
-                    for (int kb = 0; kb < P.KBN; kb++) {
-                        CKB_PROF_BEGIN();
-                        if (!mbar_wait(full_bar + 8 * s, ph, P.flags, 4, &abort_flag)) { ok = false; break; }
-                        CKB_PROF_END(1);
+                    const int kb1 = (KSPLIT && kb0 + kstep < P.KBN) ? kb0 + kstep : P.KBN;
+                    for (int kb = kb0; kb < kb1; kb++) {
+                        if (!mbar_wait(full_bar + 8 * s, ph, P.flags, 4, &abort_flag, budget)) { ok = false; break; }
                         tc_fence_after();
                         const uint32_t a16 = base16 + s * (C_::STAGE >> 4);
                         const uint32_t b16 = a16 + (C_::A_STAGE >> 4);
-                        if (kb == 0) {
+                        if (kb == kb0) {
                             // First K step of the tile: plane 0 overwrites its columns; every later plane
                             // accumulates into the columns it shares with earlier planes and overwrites
                             // the new top diagonal (ciphertext plane SC-1) with a second instruction.
@@ -460,7 +495,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                         }
 #pragma unroll
                         for (int ks = 0; ks < KS; ks++) {
-                            if (ks == 0 && kb == 0) continue;
+                            if (ks == 0 && kb == kb0) continue;
                             const uint64_t bdesc = smem_desc(b16 + (ks * SC * B_PLANE_STEP >> 4));
 #pragma unroll
                             for (int a = 0; a < SW; a++)
@@ -471,14 +506,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                         if (++s == (uint32_t)NS) { s = 0; ph ^= 1; }
                     }
                     if (ok) umma_commit(tmem_full_bar);
+                  }
                 }
             }
-            if (!ok) atomicExch(&abort_flag, 1);
-#ifdef CKB_PROFILE
-            prof_acc_[2] = clock64() - prof_start;
-            prof_acc_[3] = tile;
-            if (blockIdx.x == 0) { P.flags[8] = (int)(prof_acc_[0] >> 10); P.flags[9] = (int)(prof_acc_[1] >> 10); P.flags[10] = (int)(prof_acc_[2] >> 10); P.flags[11] = (int)tile; }
-#endif
+            if (!ok) {
+                atomicExch(&abort_flag, 1);
+                // the instructions already issued still read shared memory and write tensor memory: see them out
+                umma_commit(mma_done_bar);
+                mbar_wait(mma_done_bar, 0, P.flags, 6, &never_flag, budget);
+            }
         }
     } else {
         // ---------------- epilogue ----------------
@@ -489,52 +525,39 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
         u64 last[16];
         bool vec_ok = (P.C & 1) == 0 && (reinterpret_cast<uintptr_t>(P.out) & 15) == 0;   // 16-byte stores stay aligned
         if (PEERS)
-            for (int dest = 0; dest < P.n_peers; dest++) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(P.peers[dest]) & 15) == 0;
+            for (int dest = 0; dest < P.n_dests; dest++) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(P.dests[dest]) & 15) == 0;
         uint32_t tile = 0;
         bool ok = true;
-        CKB_PROF_DECL
         for (long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
             const int mt = (int)(item % P.MT);
             const long ct = item / P.MT;
             const long c0 = P.col_begin + ct * TC + half * 16;
-            for (int limb = limbs_n - 1; limb >= 0 && ok; limb--, tile++) {
-                CKB_PROF_BEGIN();
-                if (!mbar_wait(tmem_full_bar, tile & 1, P.flags, 5, &abort_flag)) { ok = false; break; }
-                CKB_PROF_END(0);
-                tc_fence_after();
-                CKB_PROF_BEGIN();
+            for (int limb = limbs_n - 1; limb >= 0 && ok; limb--) {
                 unsigned __int128 acc[16];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 16;
+                if (!KSPLIT) {
+                    // the usual case: the whole contraction sits in tensor memory
+                    if (!mbar_wait(tmem_full_bar, tile & 1, P.flags, 5, &abort_flag, budget)) { ok = false; break; }
+                    tc_fence_after();
+                    drain_accumulators<C_::ND, false>(taddr, acc);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tmem_empty_bar);
+                    tile++;
+                } else {
+                    // one round per accumulation pass of the MMA issuer; the partial sums add up in 128 bits
 #pragma unroll
-                for (int g = 0; g < 2; g++) {
-                    int32_t v[C_::ND][8];
-#pragma unroll
-                    for (int d = 0; d < C_::ND; d++)
-                        tmem_ld8(tmem_base + ((uint32_t)(quarter * 32) << 16) + d * TC + half * 16 + g * 8, v[d]);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        // sum_d v_d * 2^(8d): groups of four diagonals fit a signed 64-bit word
-                        // (|v_d| < 2^31, top shift 24), and the groups sit 32 bits apart
-                        long long grp[(C_::ND + 3) / 4];
-#pragma unroll
-                        for (int gi = 0; gi < (C_::ND + 3) / 4; gi++) {
-                            long long t = 0;
-#pragma unroll
-                            for (int k = 3; k >= 0; k--)
-                                if (gi * 4 + k < C_::ND) t = t * 256 + (long long)v[gi * 4 + k][e];
-                            grp[gi] = t;
-                        }
-                        __int128 s = 0;
-#pragma unroll
-                        for (int gi = (C_::ND + 3) / 4 - 1; gi >= 0; gi--) s = s * ((__int128)1 << 32) + grp[gi];
-                        acc[g * 8 + e] = (unsigned __int128)s;
+                    for (int e = 0; e < 16; e++) acc[e] = 0;
+                    for (int kb0 = 0; kb0 < P.KBN; kb0 += P.kpass, tile++) {
+                        if (!mbar_wait(tmem_full_bar, tile & 1, P.flags, 5, &abort_flag, budget)) { ok = false; break; }
+                        tc_fence_after();
+                        drain_accumulators<C_::ND, true>(taddr, acc);
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tmem_empty_bar);
                     }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tmem_empty_bar);
-                CKB_PROF_END(1);
-                CKB_PROF_BEGIN();
+                if (!ok) break;
 
                 const PcmmLimb L = P.limbs[limb];
                 const unsigned __int128 off = ((unsigned __int128)L.off_hi << 64) | L.off_lo;
@@ -567,12 +590,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                     const bool whole = vec_ok && c0 + 16 <= P.col_end && mt * TM + quarter * 32 + 32 <= P.M;    // warp-uniform
                     if (whole) {
                         fence_proxy_async_smem();
-                        const size_t off = ((size_t)(mt * TM + quarter * 32 + lane) * limbs_n + limb) * P.C + c0;
+                        const int row = mt * TM + quarter * 32 + lane;
+                        const size_t off = ((size_t)row * limbs_n + limb) * P.C + c0;
                         const uint32_t src = smem_u32(stg + lane * STG_ROW);
-                        bulk_s2g(P.out + off, src, 128);
-                        for (int dest = 0; dest < P.n_peers; dest++) bulk_s2g(P.peers[dest] + off, src, 128);
+                        if (DEST == DEST_OWNERS) {
+                            bulk_s2g(P.dests[row / P.rows_per_owner] + off, src, 128);      // this row's owner, nobody else
+                        } else {
+                            bulk_s2g(P.out + off, src, 128);
+                            for (int dest = 0; dest < P.n_dests; dest++) bulk_s2g(P.dests[dest] + off, src, 128);
+                        }
                         bulk_commit();
-                        CKB_PROF_END(2);
                         continue;
                     }
                 }
@@ -588,8 +615,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                         const size_t off = ((size_t)mm * limbs_n + limb) * P.C + c;
                         // the local output, then the same words into every peer's output buffer (plain
                         // peer stores over NVLink): the gather of a column-sharded multiply rides on the epilogue
-                        for (int dest = -1; dest < (PEERS ? P.n_peers : 0); dest++) {
-                            u64* dst = (dest < 0 ? P.out : P.peers[dest]) + off;
+                        for (int dest = -1; dest < (DEST == DEST_BROADCAST ? P.n_dests : 0); dest++) {
+                            u64* dst = (DEST == DEST_OWNERS ? P.dests[mm / P.rows_per_owner] : dest < 0 ? P.out : P.dests[dest]) + off;
                             if (vec_ok && c + 1 < P.col_end) {
                                 *reinterpret_cast<ulonglong2*>(dst) = v;
                             } else {
@@ -599,12 +626,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
                         }
                     }
                 }
-                CKB_PROF_END(2);
             }
         }
-#ifdef CKB_PROFILE
-        if (blockIdx.x == 0 && warp == 2 && lane == 0) { P.flags[12] = (int)(prof_acc_[0] >> 10); P.flags[13] = (int)(prof_acc_[1] >> 10); P.flags[14] = (int)(prof_acc_[2] >> 10); }
-#endif
         if (PEERS) bulk_wait_all();                       // every destination is written before the CTA retires
         if (!ok) atomicExch(&abort_flag, 1);
     }
@@ -618,8 +641,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) pcmm_umma_kernel(UmmaArgs P) {
 }
 
 template <int SW, int SC>
-int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots, bool slots_regular,
-           u64* d_out, int M, int K, long col_begin, long col_end, cudaStream_t st) {
+int launch(ckks_b200_pcmm* pc, const long long* d_w, const PcmmSource& src, u64* d_out, int M, int K, long col_begin,
+           long col_end, int kpass, bool weights_ready, cudaStream_t st) {
     using C_ = Cfg<SW, SC>;
     const int MT = (M + TM - 1) / TM;
     const long ncol = col_end - col_begin;
@@ -627,28 +650,41 @@ int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, 
     const int KBN = (K + KB - 1) / KB;
     const size_t wbytes = (size_t)MT * KBN * C_::A_STAGE;
     const size_t xbytes = (size_t)pc->q_count * CT * KBN * C_::B_STAGE;
-    int rc = ensure_dev(&pc->d_wplanes, &pc->wplanes_cap, wbytes);
-    if (!rc) rc = ensure_dev(&pc->d_xplanes, &pc->xplanes_cap, xbytes);
+    if (weights_ready) {
+        CKB_REQUIRE(pc->wplanes_cap >= wbytes && pc->prep_sw == SW && pc->prep_sc == SC, CKKS_B200_ERR_ARG,
+                    "the prepared weight planes do not belong to this multiply");
+    } else {
+        int rc = ensure_dev(&pc->d_wplanes, &pc->wplanes_cap, wbytes);
+        if (rc) return rc;
+    }
+    int rc = ensure_dev(&pc->d_xplanes, &pc->xplanes_cap, xbytes);
     if (rc) return rc;
 
     CKB_CUDA(cudaEventRecord(pc->ev[0], st));
     {
-        long total = (long)MT * TM * KBN * (KB / 16);
-        slice_weights_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d_w, pc->d_wplanes, M, K, MT, KBN, SW);
-        if (d_slots && slots_regular) {
+        if (!weights_ready) {
+            long total = (long)MT * TM * KBN * (KB / 16);
+            slice_weights_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d_w, pc->d_wplanes, M, K, MT, KBN, SW);
+            count_launch();
+        }
+        if (d_out == nullptr) {                 // weight preparation only
+            CKB_CUDA(cudaGetLastError());
+            return CKKS_B200_OK;
+        }
+        if (src.slots && src.slots_regular) {
             dim3 grid((unsigned)((pc->N1 / TC) * ((pc->rank + RB - 1) / RB + 1)), KBN, pc->q_count);
-            slice_rlwe_rows_kernel<<<grid, 256, 0, st>>>(d_slots, pc->d_xplanes, pc->d_limbs, K, (long)pc->rank * pc->N1,
+            slice_rlwe_rows_kernel<<<grid, 256, 0, st>>>(src.slots, pc->d_xplanes, pc->d_limbs, K, (long)pc->rank * pc->N1,
                                                          pc->N1, pc->rank, col_begin, col_end, CT, KBN, SC);
-        } else if (d_slots) {
+        } else if (src.slots) {
             dim3 grid((unsigned)CT, KBN, pc->q_count);
-            slice_rlwe_kernel<<<grid, 256, 0, st>>>(d_slots, pc->d_xplanes, pc->d_limbs, K, (long)pc->rank * pc->N1, pc->N1,
+            slice_rlwe_kernel<<<grid, 256, 0, st>>>(src.slots, pc->d_xplanes, pc->d_limbs, K, (long)pc->rank * pc->N1, pc->N1,
                                                     pc->rank, col_begin, col_end, CT, KBN, SC);
         } else {
             dim3 grid((unsigned)(((long)CT * TC + 127) / 128), KBN * (KB / 16), pc->q_count);
-            slice_cipher_kernel<<<grid, 128, 0, st>>>(d_xptrs, pc->d_xplanes, K, pc->C, pc->q_count, col_begin, col_end,
-                                                      CT, KBN, SC);
+            slice_cipher_kernel<<<grid, 128, 0, st>>>(src.table, src.base, src.stride, pc->d_xplanes, K, pc->C, pc->q_count,
+                                                      col_begin, col_end, CT, KBN, SC);
         }
-        count_launch(2);
+        count_launch();
         CKB_CUDA(cudaGetLastError());
     }
 
@@ -658,8 +694,21 @@ int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, 
     P.wplanes = pc->d_wplanes;
     P.xplanes = pc->d_xplanes;
     P.out = d_out;
-    P.n_peers = pc->n_peers;
-    for (int i = 0; i < 7; i++) P.peers[i] = i < pc->n_peers ? pc->peer_out[i] : nullptr;
+    int dest = DEST_LOCAL;
+    P.n_dests = 0;
+    P.rows_per_owner = 1;
+    for (int i = 0; i < 8; i++) P.dests[i] = nullptr;
+    if (pc->n_owners > 0) {
+        // rows are dealt out in equal runs, a whole number of 32-row groups each, so that one warp's rows share an owner
+        dest = DEST_OWNERS;
+        P.n_dests = pc->n_owners;
+        P.rows_per_owner = ((M + pc->n_owners - 1) / pc->n_owners + 31) / 32 * 32;
+        for (int i = 0; i < pc->n_owners; i++) P.dests[i] = (i == pc->self_rank || !pc->owner_out[i]) ? d_out : pc->owner_out[i];
+    } else if (pc->n_peers > 0) {
+        dest = DEST_BROADCAST;
+        P.n_dests = pc->n_peers;
+        for (int i = 0; i < pc->n_peers; i++) P.dests[i] = pc->peer_out[i];
+    }
     P.limbs = pc->d_limbs;
     P.flags = pc->d_flags;
     P.M = M;
@@ -671,14 +720,21 @@ int launch(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, 
     P.CT = CT;
     P.KBN = KBN;
     P.num_stages = C_::MAX_STAGES;
+    P.kpass = kpass;
+    P.wait_budget = pc->wait_budget > 0 ? pc->wait_budget : WAIT_BUDGET;
+    P.withhold = pc->withhold_stage;
+    pc->withhold_stage = -1;                    // the test switch arms one launch
     const size_t smem = (size_t)C_::MAX_STAGES * C_::STAGE + STG_BYTES;
-    CKB_CUDA(cudaFuncSetAttribute(pcmm_umma_kernel<SW, SC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    CKB_CUDA(cudaFuncSetAttribute(pcmm_umma_kernel<SW, SC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     long items = (long)MT * CT;
     int grid = (int)(items < sms ? items : sms);
     CKB_CUDA(cudaEventRecord(pc->ev[1], st));
-    if (pc->n_peers > 0) pcmm_umma_kernel<SW, SC, true><<<grid, NUM_THREADS, smem, st>>>(P);
-    else pcmm_umma_kernel<SW, SC, false><<<grid, NUM_THREADS, smem, st>>>(P);
+    const bool ksplit = kpass < KBN;
+    void (*kernel)(UmmaArgs) =
+        dest == DEST_OWNERS      ? (ksplit ? pcmm_umma_kernel<SW, SC, DEST_OWNERS, true> : pcmm_umma_kernel<SW, SC, DEST_OWNERS, false>)
+        : dest == DEST_BROADCAST ? (ksplit ? pcmm_umma_kernel<SW, SC, DEST_BROADCAST, true> : pcmm_umma_kernel<SW, SC, DEST_BROADCAST, false>)
+                                 : (ksplit ? pcmm_umma_kernel<SW, SC, DEST_LOCAL, true> : pcmm_umma_kernel<SW, SC, DEST_LOCAL, false>);
+    CKB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, NUM_THREADS, smem, st>>>(P);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     CKB_CUDA(cudaEventRecord(pc->ev[2], st));
@@ -702,8 +758,10 @@ int pcmm_reserve_planes(ckks_b200_pcmm* pc, int M, int K, long ncols) {
     return rc;
 }
 
-int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xptrs, const RlweSlot* d_slots,
-                bool slots_regular, u64* d_out, int M, int K, long col_begin, long col_end, int w_bits, cudaStream_t st) {
+// The plane configuration and the number of K blocks per accumulation pass for weights of w_bits bits: the
+// narrowest configuration that holds the planes, with the contraction cut into passes short enough for
+// min(SW,SC) * (blocks * KB) * 255 * 255 to stay below 2^31 in every s32 accumulator.
+int pcmm_tensor_plan(const ckks_b200_pcmm* pc, int K, int w_bits, int* sw_out, int* sc_out, int* kpass_out) {
     int q_bits = 0;
     for (u64 q : pc->q) {
         int b = 64 - __builtin_clzll(q);
@@ -721,16 +779,29 @@ int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const u64* const* d_xp
     for (const Inst& in : insts) {
         if (sw > in.sw || sc > in.sc) continue;
         const int pairs = in.sw < in.sc ? in.sw : in.sc;
-        // |sum| per accumulator <= pairs * K * 255 * 255 must stay below 2^31
-        if ((long long)pairs * ((K + KB - 1) / KB * KB) * 65025ll >= (1ll << 31)) continue;
-        if (in.sw == 4) return launch<4, 5>(pc, d_w, d_xptrs, d_slots, slots_regular, d_out, M, K, col_begin, col_end, st);
-        if (in.sw == 5) return launch<5, 7>(pc, d_w, d_xptrs, d_slots, slots_regular, d_out, M, K, col_begin, col_end, st);
-        if (in.sw == 6) return launch<6, 7>(pc, d_w, d_xptrs, d_slots, slots_regular, d_out, M, K, col_begin, col_end, st);
-        return launch<8, 8>(pc, d_w, d_xptrs, d_slots, slots_regular, d_out, M, K, col_begin, col_end, st);
+        const long long blocks = ((1ll << 31) - 1) / ((long long)pairs * 65025ll * KB);      // K blocks one pass may hold
+        const int KBN = (K + KB - 1) / KB;
+        *sw_out = in.sw;
+        *sc_out = in.sc;
+        *kpass_out = blocks >= KBN ? KBN : (int)blocks;
+        return CKKS_B200_OK;
     }
-    set_error("no tensor-core configuration fits %d weight planes, %d residue planes and K=%d within s32 accumulators",
-              sw, sc, K);
+    set_error("no tensor-core configuration holds %d weight planes and %d residue planes", sw, sc);
     return CKKS_B200_ERR_UNSUPPORTED;
+}
+
+int pcmm_tensor(ckks_b200_pcmm* pc, const long long* d_w, const PcmmSource& src, u64* d_out, int M, int K,
+                long col_begin, long col_end, int w_bits, bool weights_ready, cudaStream_t st) {
+    int sw = 0, sc = 0, kpass = 0;
+    int rc = pcmm_tensor_plan(pc, K, w_bits, &sw, &sc, &kpass);
+    if (rc) return rc;
+    if (!weights_ready) pc->prep_sw = pc->prep_sc = 0;       // the planes are about to be overwritten
+    if (sw == 4) rc = launch<4, 5>(pc, d_w, src, d_out, M, K, col_begin, col_end, kpass, weights_ready, st);
+    else if (sw == 5) rc = launch<5, 7>(pc, d_w, src, d_out, M, K, col_begin, col_end, kpass, weights_ready, st);
+    else if (sw == 6) rc = launch<6, 7>(pc, d_w, src, d_out, M, K, col_begin, col_end, kpass, weights_ready, st);
+    else rc = launch<8, 8>(pc, d_w, src, d_out, M, K, col_begin, col_end, kpass, weights_ready, st);
+    if (!rc && !weights_ready) { pc->prep_sw = sw; pc->prep_sc = sc; }
+    return rc;
 }
 
 }  // namespace ckb
@@ -743,11 +814,8 @@ extern "C" int ckks_b200_pcmm_check(ckks_b200_pcmm* pc, void* stream) {
     CKB_REQUIRE(guard.ok, CKKS_B200_ERR_CUDA, "cudaSetDevice(%d) failed", pc->device);
     cudaStream_t st = (cudaStream_t)stream;
     CKB_CUDA(cudaMemcpyAsync(pc->h_flags, pc->d_flags, 16 * sizeof(int), cudaMemcpyDeviceToHost, st));
+    CKB_CUDA(cudaMemsetAsync(pc->d_flags + 1, 0, sizeof(int), st));      // reported once: cleared by the check that reads it
     CKB_CUDA(cudaStreamSynchronize(st));
-#ifdef CKB_PROFILE
-    fprintf(stderr, "[prof] mma: wait_tmem_empty=%d wait_full=%d total=%d (kcycles) tiles=%d | epi: wait_full=%d drain=%d math+store=%d\n",
-            pc->h_flags[8], pc->h_flags[9], pc->h_flags[10], pc->h_flags[11], pc->h_flags[12], pc->h_flags[13], pc->h_flags[14]);
-#endif
     CKB_REQUIRE(pc->h_flags[1] == 0, CKKS_B200_ERR_TIMEOUT,
                 "a device-side wait ran out of its clock budget (site %d)", pc->h_flags[1]);
     return CKKS_B200_OK;

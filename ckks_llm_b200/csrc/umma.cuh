@@ -8,7 +8,7 @@ namespace ckb {
 namespace umma {
 
 constexpr int TM = 128;            // rows of the M-side operand per instruction (UMMA M)
-constexpr long long WAIT_BUDGET = 4000000000ll;   // clock cycles, about two seconds
+constexpr long long WAIT_BUDGET = 4000000000ll;   // default clock budget of a device-side wait, about two seconds
 
 // ---------------------------------------------------------------------------
 // PTX wrappers
@@ -37,17 +37,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait.  Returns false when the budget ran out (the flag is raised) or when another
-// role of the CTA has given up (abort is the CTA's shared flag, looked at from the slow path only).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* flags, int where, const int* abort) {
+// Bounded wait.  Returns false when the budget (clock cycles) ran out (flags[1] receives `where` and stays
+// set until the host reads and clears it) or when another role of the CTA has given up (abort is the CTA's
+// shared flag, looked at from the slow path only).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* flags, int where, const int* abort,
+                                          long long budget = WAIT_BUDGET) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 63) == 0) {
             if (*(const volatile int*)abort) return false;
-            if (clock64() - t0 > WAIT_BUDGET) {
-                atomicExch(&flags[1], where);
+            if (clock64() - t0 > budget) {
+                atomicCAS(&flags[1], 0, where);      // the first site to give up is the one reported
                 return false;
             }
         }

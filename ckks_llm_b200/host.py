@@ -122,6 +122,14 @@ class Context_23:
     def check(self):
         capi.check(self.lib.ckks_b200_context_check(self._h, _stream_ptr(self.device)))
 
+    def set_wait_budget(self, cycles):
+        """Clock cycles a device-side wait of the tensor-core ModUp may take (0 = the default of about two seconds)."""
+        capi.check(self.lib.ckks_b200_context_set_wait_budget(self._h, int(cycles)))
+
+    def test_withhold_commit(self, on=True):
+        """Test support: the next tensor-core ModUp leaves out one completion signal so that a wait runs out."""
+        capi.check(self.lib.ckks_b200_context_test_withhold_commit(self._h, int(bool(on))))
+
     # host-buffer forms (numpy uint64 arrays, transformed in place / returned)
     def ToNTTInplace_host(self, host_a, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len):
         assert host_a.dtype == np.uint64 and host_a.flags.c_contiguous
@@ -298,6 +306,27 @@ class PCMM_Context:
         ptrs = (C.c_void_p * max(len(peer_pointers), 1))(*[int(p) for p in peer_pointers])
         capi.check(self.lib.ckks_b200_pcmm_set_peer_outputs(self._h, ptrs, len(peer_pointers)))
 
+    def set_row_owners(self, out_by_rank, self_rank):
+        """Device addresses, valid on this GPU, of every rank's output buffer (the entry of self_rank is ignored): from now
+        on a tensor-core multiply stores each output row into its owner's buffer only.  An empty list switches it off."""
+        world = len(out_by_rank)
+        ptrs = (C.c_void_p * max(world, 1))(*[int(p) if p else None for p in out_by_rank])
+        capi.check(self.lib.ckks_b200_pcmm_set_row_owners(self._h, ptrs, world, int(self_rank)))
+
+    def row_owner_range(self, mat_M, world, rank):
+        """Rows [begin, end) of a mat_M-row output that belong to `rank` of `world` under set_row_owners."""
+        b, e = C.c_int(), C.c_int()
+        capi.check(self.lib.ckks_b200_pcmm_row_owner_range(int(mat_M), int(world), int(rank), C.byref(b), C.byref(e)))
+        return b.value, e.value
+
+    def set_wait_budget(self, cycles):
+        """Clock cycles a device-side wait of the tensor-core multiply may take (0 = the default of about two seconds)."""
+        capi.check(self.lib.ckks_b200_pcmm_set_wait_budget(self._h, int(cycles)))
+
+    def test_withhold_stage(self, stage):
+        """Test support: the next tensor-core multiply stops feeding operand tiles before tile `stage` of every CTA."""
+        capi.check(self.lib.ckks_b200_pcmm_test_withhold_stage(self._h, int(stage)))
+
     def set_host_chunks(self, chunks):
         """Number of column chunks the host-buffer multiply pipelines through its copy and compute streams (0 = automatic)."""
         capi.check(self.lib.ckks_b200_pcmm_set_host_chunks(self._h, int(chunks)))
@@ -325,9 +354,17 @@ class PCMM_Scheme:
         self.ppmm_output = None
 
     def scaler_for(self, scale, target_scale=float(1 << 49)):
-        """scaler = (long)(q_ringpack[1] * target / scale), PPMM_kernel.cuh:283-284."""
-        q1 = self.pcmm_context.q_ringpack[1]
-        return float(int(q1 * target_scale / scale))
+        """scaler = (long)(q_last * target / scale): PPMM_kernel.cuh:283-284 writes q_ringpack[1], the last of the
+        reference's two moduli and the one its kernel rescales by; with more limbs that is the last one."""
+        q_last = self.pcmm_context.q_ringpack[-1]
+        return float(int(q_last * target_scale / scale))
+
+    def prepare_weights(self, plain_mat, mat_M, mat_N, scaler):
+        """Scale and slice a weight matrix once (ckks_b200_pcmm_prepare_weights); PPMM / decomposeAndPPMM calls that pass
+        plain_mat=None with the same shape and scaler then multiply by it without a per-call weight pre-pass."""
+        pc = self.pcmm_context
+        capi.check(self.lib.ckks_b200_pcmm_prepare_weights(pc._h, plain_mat.data_ptr(), mat_M, mat_N, float(scaler),
+                                                           _stream_ptr(pc.device)))
 
     def PPMM(self, plain_mat, mlwe_cipher_decomposed, mat_M, mat_N, mat_K, mlwe_num, scaler=None,
              col_begin=0, col_end=None, copy_back=True):
@@ -349,8 +386,8 @@ class PCMM_Scheme:
             self.ppmm_output = torch.empty(need, dtype=torch.int64, device=pc.device)
         ptrs = (C.c_void_p * max(mlwe_num, 1))(*[c.cipher_device.data_ptr() for c in mlwe_cipher_decomposed[:mlwe_num]])
         st = self.lib.ckks_b200_pcmm_ppmm(
-            pc._h, plain_mat.data_ptr(), ptrs, self.ppmm_output.data_ptr(), mat_M, mat_N, mat_K, mlwe_num,
-            float(scaler), col_begin, col_end, self.algo, _stream_ptr(pc.device))
+            pc._h, plain_mat.data_ptr() if plain_mat is not None else None, ptrs, self.ppmm_output.data_ptr(), mat_M, mat_N,
+            mat_K, mlwe_num, float(scaler), col_begin, col_end, self.algo, _stream_ptr(pc.device))
         if st == capi.ERR_SHAPE:
             print(self.lib.ckks_b200_last_error().decode())
             return None
@@ -401,7 +438,8 @@ class PCMM_Scheme:
             for ct, _, _ in sources:
                 capi.check(self.lib.ckks_b200_ntt_inverse(ctx._h, ct.cipher_device.data_ptr(), 0, ctx.p_num, 2, ct.l + 1,
                                                           ct.L + 1, st_ptr))
-        st = self.lib.ckks_b200_pcmm_ppmm_rlwe(pc._h, plain_mat.data_ptr(), arr, len(sources), self.ppmm_output.data_ptr(),
+        st = self.lib.ckks_b200_pcmm_ppmm_rlwe(pc._h, plain_mat.data_ptr() if plain_mat is not None else None, arr,
+                                               len(sources), self.ppmm_output.data_ptr(),
                                                mat_M, mat_N, mat_K, mlwe_num, float(scaler), col_begin, col_end, st_ptr)
         if ntt_domain:
             for ct, _, _ in sources:
@@ -455,4 +493,23 @@ class PCMM_Scheme:
         capi.check(self.lib.ckks_b200_pcmm_ppmm_host(
             pc._h, W.ctypes.data, X.ctypes.data, out.ctypes.data, mat_M, mat_N, mat_K, mlwe_num,
             float(scaler), self.algo))
+        return out
+
+    def PPMM_rlwe_host(self, plain_mat, sources, mat_M, mat_N, mat_K, mlwe_num, scaler, out=None):
+        """Host-buffer form of decomposeAndPPMM: `sources` is a list of (rlwe, L, mlwe_num, offset) with rlwe a contiguous
+        uint64 array [2][L+1][N] in the coefficient domain; returns the output [mat_M][q_count][(k+1)*N1] (numpy, or the
+        given `out`)."""
+        pc = self.pcmm_context
+        W = np.ascontiguousarray(plain_mat, dtype=np.float32)
+        C_ = (pc.mlwe_rank + 1) * pc.N1
+        if out is None:
+            out = np.empty((mat_M, pc.ringpack_q_count, C_), dtype=np.uint64)
+        arr = (capi.RlweSource * max(len(sources), 1))()
+        keep = []
+        for k, (rl, L, num, off) in enumerate(sources):
+            rl = np.ascontiguousarray(rl, dtype=np.uint64)
+            keep.append(rl)
+            arr[k].d_rlwe, arr[k].L, arr[k].mlwe_num, arr[k].offset = rl.ctypes.data, L, num, off
+        capi.check(self.lib.ckks_b200_pcmm_ppmm_rlwe_host(pc._h, W.ctypes.data, arr, len(sources), out.ctypes.data, mat_M,
+                                                          mat_N, mat_K, mlwe_num, float(scaler)))
         return out

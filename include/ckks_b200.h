@@ -98,6 +98,15 @@ int ckks_b200_modup_set_algo(ckks_b200_context* ctx, int algo);
  * of a tensor-core ModUp on this context ran out since the last check (the *_host entry
  * point checks by itself). */
 int ckks_b200_context_check(ckks_b200_context* ctx, void* stream);
+/* Clock cycles a device-side wait of the tensor-core ModUp may take before it gives up (0 = the library's default,
+ * about two seconds).  No reference counterpart: the reference has no bounded waits. */
+int ckks_b200_context_set_wait_budget(ckks_b200_context* ctx, long long cycles);
+/* Test support for the time-out path (no reference counterpart).  With on != 0 the next tensor-core ModUp on this
+ * context leaves out the completion signal of one tile, so the threads that wait for it run into the wait budget:
+ * they raise the flag and leave, the kernel frees its tensor memory and returns normally, and the next
+ * ckks_b200_context_check returns CKKS_B200_ERR_TIMEOUT (the output of that launch is then incomplete).  Nothing
+ * faults or hangs; set a short budget first.  The switch arms one launch. */
+int ckks_b200_context_test_withhold_commit(ckks_b200_context* ctx, int on);
 
 /* ---- level changes around the PCMM ------------------------------------------
  * d_cipher is the reference's Ciphertext buffer, a limbs then b limbs, each [L+1][N], NTT
@@ -210,6 +219,15 @@ int ckks_b200_pcmm_destroy(ckks_b200_pcmm* pc);
 #define CKKS_B200_PCMM_TENSOR 1 /* same, explicit */
 #define CKKS_B200_PCMM_SIMT 2   /* 64-bit CUDA-core path, the reference's formulation */
 
+/* Scales a weight matrix (w = (int64)((double)W*scaler), PPMM_kernel.cuh:148) and cuts its byte planes once, and
+ * keeps both on the handle: multiplies on this handle that pass d_W = NULL with the same mat_M, mat_N and scaler use
+ * them, skip the per-call weight pre-pass and with it the one host wait a multiply otherwise contains (the read-back
+ * of the weight range), so that such a call only enqueues work.  The reference re-converts the weights in every block
+ * of every call (:148); layer weights are static, so a caller prepares each matrix once.  Preparing again, or any
+ * multiply on the handle that passes its own d_W, replaces the kept weights.  Synchronises `stream` once. */
+int ckks_b200_pcmm_prepare_weights(ckks_b200_pcmm* pc, const float* d_W, int mat_M, int mat_N, double scaler,
+                                   void* stream);
+
 /* PCMM_Scheme::PPMM (pcmm/PPMM_kernel.cuh:254-349) and its kernel (:93-252):
  *   out[m][i][c] = rescale_i( sum_n a(m,n,i) * X[n][i][c] mod q_i )
  * with w = (int64)((double)W[m][n]*scaler) truncated toward zero, a = w>0 ? w : q_i+w,
@@ -221,7 +239,15 @@ int ckks_b200_pcmm_destroy(ckks_b200_pcmm* pc);
  * mat_N == mlwe_num, else CKKS_B200_ERR_SHAPE (:256-263).  Only columns
  * [col_begin, col_end) of every row are computed (multiples of 32, or the full
  * width); pass 0 and (k+1)*N1 for the whole product.  The call is asynchronous on
- * `stream`. */
+ * `stream` once the weights are known: with d_W given it waits for the stream once, to
+ * read the range of the scaled weights back; with d_W = NULL it uses the weights kept by
+ * ckks_b200_pcmm_prepare_weights and does not wait.
+ * Ranges: the tensor-core path computes the exact signed sum and needs bits(q) + bits(w) +
+ * ceil(log2 mat_N) <= 110 (a contraction too deep for one pass of 32-bit accumulators is cut
+ * into several, summed in 128 bits).  The CUDA-core path accumulates a*x in 128 bits without
+ * a range check, as the reference kernel does (:28,:106); it is refused
+ * (CKKS_B200_ERR_RANGE / CKKS_B200_ERR_UNSUPPORTED) when |w| is not below the moduli or
+ * ceil(log2 mat_N) + 2*bits(q) > 128, where the reference's sum could wrap. */
 int ckks_b200_pcmm_ppmm(ckks_b200_pcmm* pc, const float* d_W, const uint64_t* const* h_X_ptrs,
                         uint64_t* d_out, int mat_M, int mat_N, int mat_K, int mlwe_num,
                         double scaler, long col_begin, long col_end, int algo, void* stream);
@@ -253,14 +279,32 @@ int ckks_b200_pcmm_set_host_chunks(ckks_b200_pcmm* pc, int chunks);
 int ckks_b200_pcmm_ppmm_host(ckks_b200_pcmm* pc, const float* h_W, const uint64_t* h_X,
                              uint64_t* h_out, int mat_M, int mat_N, int mat_K, int mlwe_num,
                              double scaler, int algo);
+/* Host-buffer form of ckks_b200_pcmm_ppmm_rlwe: the d_rlwe members of h_sources are HOST pointers here.  The RLWE
+ * ciphertexts (2*(L+1)*N words each) are what crosses the bus on the way in, mlwe_num times less than the MLWE
+ * ciphertexts cut from them; h_out as in ckks_b200_pcmm_ppmm_host.  Copies in, multiplies in column chunks
+ * overlapped with the copy-out, synchronises. */
+int ckks_b200_pcmm_ppmm_rlwe_host(ckks_b200_pcmm* pc, const float* h_W, const ckks_b200_rlwe_source* h_sources,
+                                  int n_sources, uint64_t* h_out, int mat_M, int mat_N, int mat_K, int mlwe_num,
+                                  double scaler);
 /* The copy-back PPMM ends with (:345-348): row i of d_out, first `limbs` limbs, is
  * copied over ciphertext i for i < mlwe_num (the reference hard-codes limbs = 2). */
 int ckks_b200_pcmm_copy_back(ckks_b200_pcmm* pc, const uint64_t* d_out,
                              uint64_t* const* h_X_ptrs, int mlwe_num, int limbs, void* stream);
 /* Waits for `stream` and reports CKKS_B200_ERR_TIMEOUT if a bounded device-side wait
- * of a tensor-core multiply on this handle gave up since the last check (no reference
- * counterpart: the reference never checks a CUDA status). */
+ * of a tensor-core multiply on this handle gave up since the last check, however many
+ * multiplies ran in between: the record survives later launches and is cleared by the check
+ * that reports it (no reference counterpart: the reference never checks a CUDA status). */
 int ckks_b200_pcmm_check(ckks_b200_pcmm* pc, void* stream);
+/* Clock cycles a device-side wait of the tensor-core multiply may take before it gives up (0 = the library's
+ * default, about two seconds).  No reference counterpart. */
+int ckks_b200_pcmm_set_wait_budget(ckks_b200_pcmm* pc, long long cycles);
+/* Test support for the time-out path (no reference counterpart).  In the next tensor-core multiply on this handle the
+ * thread that feeds operand tiles to every CTA stops before its tile number `stage` (counted from 0 per CTA) and
+ * signals nothing, so the wait for that tile runs into the wait budget: the kernel raises the flag, waits for its
+ * copies and instructions in flight, frees its tensor memory and returns normally; ckks_b200_pcmm_check then returns
+ * CKKS_B200_ERR_TIMEOUT and the output of that launch is incomplete.  Nothing faults or hangs; set a short budget
+ * first.  -1 switches it off; the switch arms one launch. */
+int ckks_b200_pcmm_test_withhold_stage(ckks_b200_pcmm* pc, int stage);
 /* No counterpart in the reference (which runs on one GPU).  For a multiply split by column range over several
  * GPUs whose consumer wants the whole output on every GPU: d_peer_out holds up to 7 device pointers, valid on
  * this GPU, to the OTHER GPUs' output buffers (same [M][limbs][C] layout; peer mappings, e.g. opened CUDA IPC
@@ -269,6 +313,18 @@ int ckks_b200_pcmm_check(ckks_b200_pcmm* pc, void* stream);
  * separate pass.  The words are in place on the peers once this GPU's stream has been synchronised; the ranks
  * then meet on the host.  count = 0 switches it off.  The CUDA-core algorithm does not support it. */
 int ckks_b200_pcmm_set_peer_outputs(ckks_b200_pcmm* pc, uint64_t* const* d_peer_out, int count);
+/* No counterpart in the reference.  The other way to bring a column-sharded multiply together: every output ROW (one
+ * MLWE ciphertext, the unit PCMM_Scheme::mlweCipherPacking consumes, pcmm/PCMM_Scheme.cuh:362-430) has one owner
+ * among `world` <= 8 GPUs, and the multiply stores each word it computes into its row's owner only (its own buffer or
+ * one plain peer store over NVLink), instead of into everybody.  After every rank's launch and a stream
+ * synchronisation each rank holds ALL columns of ITS rows; a rank sends (world-1)/world of what it computes and
+ * receives as much, against (world-1) times its output for the broadcast above.  Rows are dealt out in equal
+ * contiguous runs of ceil(mat_M/world) rounded up to a multiple of 32 (ckks_b200_pcmm_row_owner_range gives a rank's
+ * run).  d_out_by_rank[r] is rank r's output buffer as addressable from this GPU (same [M][limbs][C] layout; the
+ * entry of self_rank is ignored: the call's d_out is used).  world = 0 switches it off; it replaces
+ * ckks_b200_pcmm_set_peer_outputs while on.  The CUDA-core algorithm does not support it. */
+int ckks_b200_pcmm_set_row_owners(ckks_b200_pcmm* pc, uint64_t* const* d_out_by_rank, int world, int self_rank);
+int ckks_b200_pcmm_row_owner_range(int mat_M, int world, int rank, int* row_begin, int* row_end);
 /* Helpers for the pointers above when the other GPUs belong to other processes: ckks_b200_ipc_open maps the
  * allocation behind a 64-byte CUDA IPC memory handle (cudaIpcGetMemHandle in the owning process) for use by
  * kernels on `device` (cudaIpcOpenMemHandle with lazy peer access, `device` current) and returns its base
@@ -283,13 +339,17 @@ int ckks_b200_pcmm_last_timing(ckks_b200_pcmm* pc, float* prepass_ms, float* mai
  * device memory (a serving process whose pool owns the GPU, a real-time loop, a sandboxed
  * plug-in): the same product as ckks_b200_pcmm_ppmm on the CUDA-core kernel, with no
  * handle and with all working memory (flags, ciphertext pointer table, scaled weights)
- * in one fixed array inside the library image, about 8 MB on every GPU that loads the
- * library.  Runs on the CURRENT device.  Limits: mat_N <= 4096, mat_M*mat_N <= 2^20,
+ * in one fixed array inside the library image, about 8 MB on every GPU the entry point
+ * has been called on.  Runs on the CURRENT device.  Limits: mat_N <= 4096, mat_M*mat_N <= 2^20,
  * q_count <= 24; larger sizes return CKKS_B200_ERR_UNSUPPORTED.  It calls no allocator.
  * The array is shared by all calls: calls whose work overlaps on one GPU race and must be
- * serialised by the caller.  The first call on each device looks up the array's address
- * and should be made outside any stream capture.  The stream is synchronised once inside
- * the call (to read the weight range flag). */
+ * serialised by the caller.  Every call waits for the stream once (it reads the weight range
+ * back), so none may be issued while the stream is being captured into a CUDA graph; the
+ * first call on each device also looks up the array's address.  The CUDA runtime loads device
+ * code lazily by default: the 8 MB are claimed on a GPU at that first call, not when the
+ * library is opened, so make one small warm-up call per device before a memory pool takes
+ * the whole GPU (or set CUDA_MODULE_LOADING=EAGER).  Weight and K ranges as for the CUDA-core
+ * algorithm of ckks_b200_pcmm_ppmm. */
 int ckks_b200_pcmm_ppmm_static(const float* d_W, const uint64_t* const* h_X_ptrs, uint64_t* d_out,
                                int mat_M, int mat_N, int mat_K, int mlwe_num, int N1, int mlwe_rank,
                                const uint64_t* q_ringpack, int q_count, double scaler, void* stream);

@@ -91,3 +91,33 @@ def test_tensor_kernel_refuses_what_it_cannot_reduce(oracle, cuda_device):
     with pytest.raises(CkksB200Error):
         ctx.modUpQjtoT_23_host(inp, 3, 1)
     ctx.close()
+
+
+def test_wait_that_runs_out_is_reported_and_the_context_stays_usable(oracle, cuda_device):
+    """The bounded wait of the tensor-core kernel: with the test switch one tile's completion signal is left out and the
+    threads waiting for it give up after about a millisecond.  The kernel returns by itself (nothing faults or hangs),
+    the check reports the time-out once, and the next conversion on the same context is exact."""
+    logN, alpha, q_num, t_num, l, batch = 12, 4, 8, 6, 7, 2
+    N = 1 << logN
+    p = params.ntt_primes(51, 2 * N, alpha)
+    q = params.ntt_primes(50, 2 * N, q_num)
+    t = params.ntt_primes(60, 2 * N, t_num)
+    ctx = Context_23(logN, p, q, t)
+    ctx.set_modup_algo("tensor")
+    rng = np.random.default_rng(7)
+    inp = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(batch)])
+    d_in = as_u64_tensor(inp, ctx.device)
+    blocks = (l + 1 + alpha - 1) // alpha
+    out = torch.empty(batch * blocks * t_num * N, dtype=torch.int64, device=ctx.device)
+    ctx.set_wait_budget(2_000_000)
+    ctx.test_withhold_commit()
+    ctx.modUpQjtoT_23(out, d_in, l, batch)
+    with pytest.raises(Exception) as e:
+        ctx.check()
+    assert e.value.status == 7 and "site 10" in e.value.message          # CKKS_B200_ERR_TIMEOUT, group 0's wait
+    ctx.check()                                                           # reported once
+    ctx.set_wait_budget(0)
+    ctx.modUpQjtoT_23(out, d_in, l, batch)
+    ctx.check()
+    assert np.array_equal(to_u64_numpy(out).reshape(batch, blocks, t_num, N), oracle.modup(inp, N, q, t, alpha, l, batch))
+    ctx.close()

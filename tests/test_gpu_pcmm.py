@@ -253,3 +253,263 @@ def test_config1_decrypt_through_gpu(oracle, cuda_device):
         worst = max(worst, np.abs(H.centered(dec, moduli[0]) / scale_out - expect[m]).max())
     assert worst / np.abs(expect).max() < 2.0 ** -20
     pc.close()
+
+
+def test_prepared_weights_and_graph_replay(oracle, cuda_device):
+    """Weights scaled and sliced once (ckks_b200_pcmm_prepare_weights), then multiplies with a null weight pointer:
+    same words as the per-call form on both algorithms, and the call, which then contains no host wait, can be
+    recorded into a CUDA graph and replayed on new ciphertext words."""
+    q = params.ntt_primes(50, 1 << 13, 3)
+    N1, rank, M, K = 64, 3, 96, 80
+    Cw = (rank + 1) * N1
+    rng = np.random.default_rng(31)
+    W = rng.normal(0, 0.02, (M, K)).astype(np.float32)
+    scaler = float(1 << 40)
+    pc = PCMM_Context(N1, rank, [], q)
+    X = np.stack([H.uniform_residues(rng, q, (Cw,)) for _ in range(K)])
+    Xd = as_u64_tensor(X, pc.device)                                    # one buffer: the ciphertexts sit at one stride
+    cts = [MLWECiphertext(N1, 2, 2, rank, 1.0, cipher=Xd[n].reshape(-1)) for n in range(K)]
+    Wd = torch.from_numpy(W).to(pc.device)
+    exp = oracle.ppmm(W, X, q, scaler)
+    for algo in ALGOS:
+        sch = PCMM_Scheme(pc, algo=algo)
+        sch.prepare_weights(Wd, M, K, scaler)
+        out = sch.PPMM(None, cts, M, K, N1, K, scaler=scaler, copy_back=False)
+        sch.check()
+        assert np.array_equal(to_u64_numpy(out), exp), algo
+        # another shape or scaler than the prepared one is an argument error, not a wrong product
+        with pytest.raises(capi.CkksB200Error) as e:
+            sch.PPMM(None, cts, M, K, N1, K, scaler=2 * scaler, copy_back=False)
+        assert e.value.status == capi.ERR_ARG
+    sch = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR)
+    sch.prepare_weights(Wd, M, K, scaler)
+    sch.PPMM(None, cts, M, K, N1, K, scaler=scaler, copy_back=False)     # warm: workspaces exist
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            out = sch.PPMM(None, cts, M, K, N1, K, scaler=scaler, copy_back=False)
+    X2 = np.stack([H.uniform_residues(rng, q, (Cw,)) for _ in range(K)])
+    Xd.copy_(as_u64_tensor(X2, pc.device))
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(to_u64_numpy(out), oracle.ppmm(W, X2, q, scaler))
+    # a multiply that brings its own weights replaces the prepared ones
+    sch.PPMM(Wd, cts, M, K, N1, K, scaler=scaler, copy_back=False)
+    with pytest.raises(capi.CkksB200Error):
+        sch.PPMM(None, cts, M, K, N1, K, scaler=scaler, copy_back=False)
+    del graph
+    pc.close()
+
+
+def test_deep_contraction_is_cut_into_passes(oracle, cuda_device):
+    """K = 11008, the depth of the LLaMA down-projection (configuration 5's second weight transposed): with five weight
+    planes one pass of s32 accumulators holds 6592 of it, so the tensor-core path runs two passes and adds the partial
+    sums in 128 bits.  Every word against the oracle."""
+    q = params.ntt_primes(50, 1 << 17, 2)
+    N1, rank, M, K = 32, 1, 40, 11008
+    Cw = (rank + 1) * N1
+    rng = np.random.default_rng(41)
+    W = rng.normal(0, 0.02, (M, K)).astype(np.float32)
+    pc = PCMM_Context(N1, rank, [], q)
+    X = np.stack([H.uniform_residues(rng, q, (Cw,)) for _ in range(K)])
+    Xd = as_u64_tensor(X, pc.device)
+    cts = [MLWECiphertext(N1, 1, 1, rank, 1.0, cipher=Xd[n].reshape(-1)) for n in range(K)]
+    Wd = torch.from_numpy(W).to(pc.device)
+    exp = oracle.ppmm(W, X, q, float(1 << 40))
+    for algo in (capi.PCMM_TENSOR, capi.PCMM_AUTO):
+        sch = PCMM_Scheme(pc, algo=algo)
+        out = sch.PPMM(Wd, cts, M, K, N1, K, scaler=float(1 << 40), copy_back=False)
+        sch.check()
+        assert np.array_equal(to_u64_numpy(out), exp)
+    pc.close()
+
+
+def test_cuda_core_path_refuses_what_could_wrap(oracle, cuda_device):
+    """The 64-bit kernel keeps the reference's unchecked 128-bit accumulator; where K products of two 60-bit factors
+    could wrap it the call is refused, while the tensor-core path (exact signed sums) computes the product."""
+    q = params.ntt_primes(60, 1 << 13, 2)
+    N1, rank, M, K = 32, 1, 8, 512
+    rng = np.random.default_rng(43)
+    W = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    pc = PCMM_Context(N1, rank, [], q)
+    X, cts = _ciphers(rng, q, K, N1, rank, pc.device)
+    Wd = torch.from_numpy(W).to(pc.device)
+    with pytest.raises(capi.CkksB200Error) as e:
+        PCMM_Scheme(pc, algo=capi.PCMM_SIMT).PPMM(Wd, cts, M, K, N1, K, scaler=float(1 << 40), copy_back=False)
+    assert e.value.status == capi.ERR_UNSUPPORTED
+    sch = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR)
+    out = sch.PPMM(Wd, cts, M, K, N1, K, scaler=float(1 << 40), copy_back=False)
+    sch.check()
+    # below the wrap the reference's formula and the exact sum agree, so the oracle (which wraps like the reference)
+    # is the exact product here: 512 * 2^60 * 2^40 < 2^128
+    assert np.array_equal(to_u64_numpy(out), oracle.ppmm(W, X, q, float(1 << 40)))
+    pc.close()
+
+
+def test_wait_that_runs_out_is_reported_once_and_the_handle_stays_usable(oracle, cuda_device):
+    """The bounded device-side waits: with the test switch the operand feed of every CTA stops before tile 5 and the
+    wait for that tile gives up after a budget of about a millisecond.  The kernel returns by itself (nothing faults or
+    hangs), the record survives a second multiply, the check reports it once with the site of the wait, and the
+    handle multiplies correctly afterwards."""
+    q = params.ntt_primes(50, 1 << 13, 3)
+    N1, rank, M, K = 64, 3, 256, 1024                # 16 K blocks per tile: tile 5 is in the middle of the first one
+    rng = np.random.default_rng(47)
+    W = rng.normal(0, 0.02, (M, K)).astype(np.float32)
+    pc = PCMM_Context(N1, rank, [], q)
+    sch = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR)
+    X, cts = _ciphers(rng, q, K, N1, rank, pc.device)
+    Wd = torch.from_numpy(W).to(pc.device)
+    exp = oracle.ppmm(W, X, q, float(1 << 40))
+    pc.set_wait_budget(2_000_000)
+    pc.test_withhold_stage(5)
+    sch.PPMM(Wd, cts, M, K, N1, K, scaler=float(1 << 40), copy_back=False)        # gives up
+    out = sch.PPMM(Wd, cts, M, K, N1, K, scaler=float(1 << 40), copy_back=False)  # a normal multiply before any check
+    with pytest.raises(capi.CkksB200Error) as e:
+        sch.check()
+    # sites 4 and 5 are the waits of the instruction issuer and of the epilogue warps for the tile that never came
+    assert e.value.status == capi.ERR_TIMEOUT and ("site 4" in e.value.message or "site 5" in e.value.message)
+    assert np.array_equal(to_u64_numpy(out), exp)     # the second multiply was not disturbed by the first
+    sch.check()                                       # reported once
+    pc.set_wait_budget(0)
+    out = sch.PPMM(Wd, cts, M, K, N1, K, scaler=float(1 << 40), copy_back=False)
+    sch.check()
+    assert np.array_equal(to_u64_numpy(out), exp)
+    pc.close()
+
+
+def test_row_owner_buffers_receive_their_rows_only(oracle, cuda_device):
+    """ckks_b200_pcmm_set_row_owners with three 'ranks' whose buffers all live on this GPU: every buffer ends up with
+    the rows of its owner's run, all requested columns of them, and nothing else."""
+    q = params.ntt_primes(50, 1 << 13, 3)
+    N1, rank, M, K = 64, 3, 150, 96
+    Cw = (rank + 1) * N1
+    rng = np.random.default_rng(53)
+    W = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    pc = PCMM_Context(N1, rank, [], q)
+    sch = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR)
+    X, cts = _ciphers(rng, q, K, N1, rank, pc.device)
+    world, me = 3, 1
+    bufs = [torch.full((M * len(q) * Cw,), -1, dtype=torch.int64, device=pc.device) for _ in range(world)]
+    sch.ppmm_output = bufs[me]
+    pc.set_row_owners([b.data_ptr() if r != me else 0 for r, b in enumerate(bufs)], me)
+    c0, c1 = 32, 224
+    sch.PPMM(torch.from_numpy(W).to(pc.device), cts, M, K, N1, K, scaler=float(1 << 30), col_begin=c0, col_end=c1, copy_back=False)
+    sch.check()
+    exp = oracle.ppmm(W, X, q, float(1 << 30))
+    untouched = np.uint64(2 ** 64 - 1)
+    covered = 0
+    for r in range(world):
+        got = to_u64_numpy(bufs[r]).reshape(M, len(q), Cw)
+        b, e = pc.row_owner_range(M, world, r)
+        covered += e - b
+        assert np.array_equal(got[b:e, :, c0:c1], exp[b:e, :, c0:c1])
+        mask = np.ones(got.shape, dtype=bool)
+        mask[b:e, :, c0:c1] = False
+        assert (got[mask] == untouched).all()
+    assert covered == M
+    assert pc.row_owner_range(M, world, 0) == (0, 64) and pc.row_owner_range(M, world, 2) == (128, 150)
+    pc.set_row_owners([], 0)
+    pc.close()
+
+
+def test_rlwe_host_entry_point(oracle, cuda_device):
+    """ckks_b200_pcmm_ppmm_rlwe_host: RLWE ciphertexts in host memory in, product in host memory out, equal to the
+    oracle's decomposition followed by its PPMM."""
+    N, N1, k = 1 << 12, 64, 64
+    q = params.ntt_primes(50, 2 * N, 2)
+    rng = np.random.default_rng(59)
+    M, K = 48, 96                                       # 64 ciphertexts from the first source, 32 (gap 2) from the second
+    W = rng.uniform(-0.1, 0.1, (M, K)).astype(np.float32)
+    rl = [np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(2)]) for _ in range(2)]      # [2][2][N] each
+    Xd = np.concatenate([oracle.rlwe_decompose(rl[0][0], rl[0][1], N1, k, 64, q).reshape(64, 2, -1),
+                         oracle.rlwe_decompose(rl[1][0], rl[1][1], N1, k, 32, q).reshape(32, 2, -1)])
+    pc = PCMM_Context(N1, k, [], q)
+    got = PCMM_Scheme(pc).PPMM_rlwe_host(W, [(rl[0], 1, 64, 0), (rl[1], 1, 32, 64)], M, K, N1, K, float(1 << 30))
+    assert np.array_equal(got, oracle.ppmm(W, Xd, q, float(1 << 30)))
+    pc.close()
+
+
+def test_config5_geometry_column_range(oracle, cuda_device):
+    """BASELINE configuration 5 at its stated geometry: N1 = 2048, rank 32 (67584 words per ciphertext and limb),
+    24 limbs of 50-bit primes, 4096 x 4096 weights ~N(0, 0.02) at 2^40.  One 256-column range of the product (the unit
+    a GPU of the 8-way split works on) is computed from seeded ciphertext words and compared with the oracle on sampled
+    rows, all 24 limbs of them.  The ciphertext and output buffers have their full row pitch, as in the sharded job;
+    only the columns of the range are filled and read."""
+    N1, rank, M, K, limbs = 2048, 32, 4096, 4096, 24
+    Cw = (rank + 1) * N1
+    q = params.ntt_primes(50, 1 << 17, limbs)
+    c0, c1 = 33 * N1 - 512, 33 * N1 - 256              # inside the b polynomial, not aligned to its start
+    torch.cuda.empty_cache()
+    free, _ = torch.cuda.mem_get_info()
+    need = 8 * limbs * Cw * (K + M)
+    assert free > need * 1.05, f"the test needs {need / 2**30:.0f} GiB of device memory, {free / 2**30:.0f} are free"
+    pc = PCMM_Context(N1, rank, [], q)
+    dev = pc.device
+    Xd = torch.empty((K, limbs, Cw), dtype=torch.int64, device=dev)
+    g = torch.Generator(device=dev).manual_seed(5)
+    for i, qi in enumerate(q):
+        Xd[:, i, c0:c1] = torch.randint(0, qi, (K, c1 - c0), generator=g, device=dev, dtype=torch.int64)
+    rng = np.random.default_rng(5)
+    W = rng.normal(0, 0.02, (M, K)).astype(np.float32)
+    cts = [MLWECiphertext(N1, limbs - 1, limbs - 1, rank, 1.0, cipher=Xd[n].reshape(-1)) for n in range(K)]
+    sch = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR)
+    sch.ppmm_output = torch.empty(M * limbs * Cw, dtype=torch.int64, device=dev)
+    out = sch.PPMM(torch.from_numpy(W).to(dev), cts, M, K, N1, K, scaler=float(1 << 40), col_begin=c0, col_end=c1,
+                   copy_back=False)
+    sch.check()
+    Xs = to_u64_numpy(Xd[:, :, c0:c1].contiguous())
+    for m in (0, 1, 2047, 2048, 4095):
+        got = to_u64_numpy(out[m, :, c0:c1].contiguous())
+        assert np.array_equal(got, oracle.ppmm(W, Xs, q, float(1 << 40), m0=m, m1=m + 1)[m]), m
+    del out, cts, Xd
+    sch.ppmm_output = None
+    pc.close()
+    torch.cuda.empty_cache()
+
+
+def _pack_features(x_feat_tok, k, gap):
+    """Feature i, token t -> RLWE coefficient i*gap + t*k: the comb ciphertext i of rlweCipherDecompose extracts
+    (PCMM_Scheme.cuh:67-73; gap = k / mlwe_num)."""
+    n_feat, n_tok = x_feat_tok.shape
+    out = np.zeros(k * n_tok, dtype=np.float64)
+    for t in range(n_tok):
+        out[t * k: t * k + n_feat * gap: gap] = x_feat_tok[:, t]
+    return out
+
+
+def test_config4_decrypt_through_gpu(oracle, cuda_device):
+    """BASELINE configuration 4 end to end on a reduced limb count: activations ~N(0,1) clipped to [-8, 8] for 128 tokens
+    x 768 features, encoded at 2^40 into two RLWE ciphertexts of N = 2^16 (512 + 256 features, as Bert.cuh:249-254 cuts
+    them), encrypted, decomposed into 768 MLWE ciphertexts (N1 = 128, rank 512), multiplied by 768 x 768 weights
+    ~N(0, 0.02) at 2^40 on the tensor cores over three 50-bit limbs, decrypted.  Residues of sampled rows equal the
+    oracle's; every decrypted output is within 2^-20 of the fp64 product, relative to its largest entry
+    (test_rlwe_decomp.cu:184-196 is the reference's own check of this kind)."""
+    N, N1, k, feats, toks = 1 << 16, 128, 512, 768, 128
+    q = params.ntt_primes(50, 2 * N, 3)
+    rng = np.random.default_rng(4)
+    W = rng.normal(0, 0.02, (feats, feats)).astype(np.float32)
+    Xf = np.clip(rng.normal(0, 1, (feats, toks)), -8, 8)
+    delta = float(1 << 40)
+    s = H.sparse_ternary(rng, N, 192)
+    parts = []
+    for f0, num in ((0, 512), (512, 256)):
+        msg = H.encode_coeffs(_pack_features(Xf[f0:f0 + num], k, k // num), delta, q)
+        a, b = H.rlwe_encrypt(oracle, rng, msg, s, q)
+        parts.append(oracle.rlwe_decompose(a, b, N1, k, num, q).reshape(num, len(q), (k + 1) * N1))
+    X = np.concatenate(parts)
+    pc = PCMM_Context(N1, k, [], q)
+    out = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR).PPMM_host(W, X, feats, feats, N1, feats, delta)
+    for m in (0, 400, 767):
+        assert np.array_equal(out[m], oracle.ppmm(W, X, q, delta, m0=m, m1=m + 1)[m])
+    s_mlwe = oracle.ring_down(s, N1, k)
+    expect = W.astype(np.float64) @ Xf
+    scale_out = delta * delta / q[-1]
+    worst = 0.0
+    for m in range(0, feats, 16):
+        dec = oracle.mlwe_decrypt(out[m, 0].reshape(k + 1, N1), s_mlwe, q[0])
+        worst = max(worst, np.abs(H.centered(dec, q[0]) / scale_out - expect[m]).max())
+    assert worst / np.abs(expect).max() < 2.0 ** -20
+    pc.close()

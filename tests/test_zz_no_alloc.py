@@ -4,7 +4,8 @@ ckks_b200_pcmm_ppmm_static exists for hosts that may not allocate device memory 
 start-up (a server whose pool owns the GPU, a real-time loop, a sandboxed plug-in): it
 keeps its working memory in a fixed array inside the library.  The test calls it through
 the C ABI twice in a row, with different inputs, and requires the words to equal those of
-ckks_b200_pcmm_ppmm bit for bit (the tolerance of every integer test here is zero).  The
+ckks_b200_pcmm_ppmm and of the CPU oracle bit for bit (the tolerance of every integer test
+here is zero).  The
 second call must not be disturbed by what the first left in the shared array.  This file
 sorts last so that a stop-at-first-failure run has seen every other test before it."""
 import ctypes as C
@@ -20,7 +21,7 @@ from ckks_llm_b200.host import MLWECiphertext, PCMM_Context, PCMM_Scheme, as_u64
 pytestmark = pytest.mark.gpu
 
 
-def _one_call(L, pc, q, M, K, N1, rank, scaler, seed):
+def _one_call(L, pc, q, M, K, N1, rank, scaler, seed, oracle):
     dev = pc.device
     rng = np.random.default_rng(seed)
     W = rng.uniform(-1, 1, (M, K)).astype(np.float32)
@@ -36,17 +37,19 @@ def _one_call(L, pc, q, M, K, N1, rank, scaler, seed):
     capi.check(L.ckks_b200_pcmm_ppmm_static(Wd.data_ptr(), ptrs, out.data_ptr(), M, K, N1, K, N1, rank,
                                             capi.u64_array(q), len(q), scaler, stream))
     torch.cuda.synchronize(dev)
-    assert np.array_equal(to_u64_numpy(out).reshape(M, len(q), Cw), to_u64_numpy(ref))
+    got = to_u64_numpy(out).reshape(M, len(q), Cw)
+    assert np.array_equal(got, to_u64_numpy(ref))
+    assert np.array_equal(got, oracle.ppmm(W, X, q, scaler))           # and the CPU restatement of the reference
 
 
-def test_static_entry_matches_regular_entry_twice(cuda_device):
+def test_static_entry_matches_regular_entry_twice(oracle, cuda_device):
     L = capi.load()
     torch.cuda.set_device(cuda_device)
     q = params.ntt_primes(50, 1 << 13, 3)
     N1, rank = 64, 3
     pc = PCMM_Context(N1, rank, [], q, device=cuda_device)
-    _one_call(L, pc, q, 96, 80, N1, rank, float(1 << 40), seed=21)      # fills most of a tile
-    _one_call(L, pc, q, 40, 33, N1, rank, float(1 << 30), seed=22)      # smaller: stale words remain behind it
+    _one_call(L, pc, q, 96, 80, N1, rank, float(1 << 40), 21, oracle)   # fills most of a tile
+    _one_call(L, pc, q, 40, 33, N1, rank, float(1 << 30), 22, oracle)   # smaller: stale words remain behind it
     pc.close()
 
 
