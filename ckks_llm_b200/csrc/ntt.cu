@@ -1,19 +1,26 @@
 // Batched negacyclic NTT / INTT over RNS limbs for N = 2^12 .. 2^16.
 //
-// A transform is split into a strided phase (the first logN-8 Cooley-Tukey stages,
-// which couple elements 256 apart or more) and a contiguous phase (the last 8 stages
-// on 256-point chunks); the inverse runs the two phases in the opposite order with
-// Gentleman-Sande butterflies.  In both kernels a thread owns 8 values at a time and
-// runs up to three butterfly stages on them in registers ("window" of three index
-// bits); between windows the values are exchanged through shared memory.  The first
-// window of a kernel loads straight from global memory and the last one stores
-// straight back, so a value crosses shared memory twice per kernel at most.
+// A transform is split into a strided phase (the first logN-8 Cooley-Tukey stages, which
+// couple elements 256 apart or more) and a contiguous phase (the last 8 stages on 256-point
+// chunks); the inverse runs the two phases in the opposite order with Gentleman-Sande
+// butterflies.  Each phase is one kernel that reads and writes the data once.
 //
-// Stage s (m = 2^s groups) uses twiddle psi_table[m + group]; with x the position of
-// an element in the polynomial and b the index bit the stage pairs on, that index is
-// (N + x) >> (b + 1).  Outputs are canonical.  Semantics follow
-// Context_23::ToNTTInplace / FromNTTInplace of the reference
-// (src/ckks/include/Context_23.cuh:847-889, butterflies ntt_60bit.cuh:293-318).
+// Both kernels work on tiles of 4096 words with 256 threads.  A thread owns 16 values at a time
+// and runs up to four butterfly stages on them in registers (a "window" of four index bits), so
+// a phase of up to eight stages is two windows with ONE exchange through shared memory in
+// between.  A CTA walks over several tiles; while one is in the butterflies the next is on its
+// way from global memory into the other half of a double buffer (16-byte asynchronous copies),
+// and the first window reads its values from that buffer.  Every global access of a warp covers
+// whole 128-byte lines (the load/store path of an SM takes one line per cycle, and with 16
+// words per thread that, not HBM, is the first limit these kernels meet): results a lane holds as
+// 16 consecutive words leave through shared memory, and the contiguous phase, which uses each of
+// its 4080 twiddles per tile in one butterfly only, copies them into shared memory in order and
+// walks over the polynomials of the call at a fixed tile position so that they are fetched once.
+//
+// Stage s (m = 2^s groups) uses twiddle psi_table[m + group]; with x the position of an element
+// in the polynomial and b the index bit the stage pairs on, that index is (N + x) >> (b + 1).
+// Outputs are canonical.  Semantics follow Context_23::ToNTTInplace / FromNTTInplace of the
+// reference (src/ckks/include/Context_23.cuh:847-889, butterflies ntt_60bit.cuh:293-318).
 //
 // Three arithmetic back ends compute the same residues and are chosen per limb from the
 // size of its modulus:
@@ -180,338 +187,401 @@ struct F64Arith {
 };
 
 // ---------------------------------------------------------------------------
-// Three stages on v[0..7]; v[j] sits at index base | (j << fb).  Stage s of the window
-// pairs on window bit 2-s; S0..S1 selects which stages run.  widx is the twiddle index
-// of stage 0 for this thread's group.
+// Twiddles of a four-stage window: stage s takes 2^s of them, get<s>(w) fetches those.
 // ---------------------------------------------------------------------------
-// RM: bit s set = stage s applies the back end's range reduction.
-template <int S0, int S1, int RM, class A>
-__device__ __forceinline__ void fwd8(const A& ar, typename A::V (&v)[8], uint32_t widx) {
-    if (S0 <= 0 && 0 < S1) {
-        typename A::TW w = ar.twiddle(widx);
+// From the table in global memory: stage s uses psi[(widx << s) + h], widx the index of stage 0.
+template <class A>
+struct TwGlobal {
+    const A& ar;
+    uint32_t widx;
+    template <int s>
+    __device__ __forceinline__ void get(typename A::TW (&w)[1 << s]) const {
 #pragma unroll
-        for (int j = 0; j < 4; j++) ar.template ct<(RM & 1) != 0>(v[j], v[j + 4], w);
+        for (int h = 0; h < (1 << s); h++) w[h] = ar.twiddle((widx << s) + h);
+    }
+};
+
+// The twiddles of one tile of the contiguous phase (16 chunks), staged in shared memory as eight runs that are
+// contiguous in the table: for window A (chunk bits 7..4) stage s has 2^s per chunk, for window B (bits 3..0)
+// 2^s per 16 points.  Offsets in words; the runs of B's last two stages are stored with their 16-byte units
+// permuted so that the lanes of a quarter-warp, each reading its own 32 or 64 bytes, hit different banks.
+__host__ __device__ constexpr int tw_a(int s) { return s == 0 ? 0 : s == 1 ? 16 : s == 2 ? 48 : 112; }
+__host__ __device__ constexpr int tw_b(int s) { return s == 0 ? 240 : s == 1 ? 496 : s == 2 ? 1008 : 2032; }
+constexpr int kTwWords = 4080;
+
+struct TwSharedA {
+    const double* base;
+    int c;                                   // chunk inside the tile
+    template <int s>
+    __device__ __forceinline__ void get(double (&w)[1 << s]) const {
+        const double* p = base + tw_a(s) + (c << s);
+#pragma unroll
+        for (int h = 0; h < (1 << s); h++) w[h] = p[h];
+    }
+};
+struct TwSharedB {
+    const double* base;
+    int lp;                                  // 16-point group inside the tile (chunk * 16 + lane of the chunk)
+    template <int s>
+    __device__ __forceinline__ void get(double (&w)[1 << s]) const {
+        if (s == 0) {
+            w[0] = base[tw_b(0) + lp];
+        } else {
+            constexpr int units = (1 << s) / 2;                             // 16-byte units per lane
+            const int perm = s == 3 ? ((lp >> 1) & 3) : s == 2 ? ((lp >> 2) & 1) : 0;
+            const double2* p = reinterpret_cast<const double2*>(base + tw_b(s)) + lp * units;
+#pragma unroll
+            for (int k = 0; k < units; k++) {
+                const double2 t = p[k ^ perm];
+                w[2 * k] = t.x;
+                w[2 * k + 1] = t.y;
+            }
+        }
+    }
+};
+
+// Copies the twiddle runs of the tile at position xt into shared memory (all threads of the CTA, 16 bytes per copy).
+__device__ __forceinline__ void stage_twiddles(double* dst, const double* table, uint32_t N, uint32_t xt, int tid, int nthreads) {
+    for (int U = tid; U < kTwWords / 2; U += nthreads) {
+        // which run this unit belongs to
+        int s, first, win_b;
+        if (U < 120) { win_b = 0; s = U < 8 ? 0 : U < 24 ? 1 : U < 56 ? 2 : 3; first = tw_a(s) / 2; }
+        else { win_b = 1; s = U < 248 ? 0 : U < 504 ? 1 : U < 1016 ? 2 : 3; first = tw_b(s) / 2; }
+        const int u = U - first;
+        const uint32_t start = (N + xt) >> ((win_b ? 4 : 8) - s);            // first table index of the run
+        const int pu = (win_b && s == 3) ? (u ^ ((u >> 3) & 3)) : (win_b && s == 2) ? (u ^ ((u >> 3) & 1)) : u;
+        __pipeline_memcpy_async(dst + 2 * (first + pu), table + start + 2 * u, 16);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Four stages on v[0..15]; v[j] sits at index base | (j << fb).  Stage s of the window pairs on
+// window bit 3-s; stages S0..S1-1 run.  RM: bit s set = stage s applies the back end's range reduction.
+// ---------------------------------------------------------------------------
+template <int S0, int S1, int RM, class A, class TWS>
+__device__ __forceinline__ void fwd16(const A& ar, typename A::V (&v)[16], const TWS& tws) {
+    if (S0 <= 0 && 0 < S1) {
+        typename A::TW w[1];
+        tws.template get<0>(w);
+#pragma unroll
+        for (int j = 0; j < 8; j++) ar.template ct<(RM & 1) != 0>(v[j], v[j + 8], w[0]);
     }
     if (S0 <= 1 && 1 < S1) {
+        typename A::TW w[2];
+        tws.template get<1>(w);
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            typename A::TW w = ar.twiddle(2 * widx + h);
-            ar.template ct<(RM & 2) != 0>(v[4 * h], v[4 * h + 2], w);
-            ar.template ct<(RM & 2) != 0>(v[4 * h + 1], v[4 * h + 3], w);
-        }
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) ar.template ct<(RM & 2) != 0>(v[8 * h + j], v[8 * h + j + 4], w[h]);
     }
     if (S0 <= 2 && 2 < S1) {
+        typename A::TW w[4];
+        tws.template get<2>(w);
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            typename A::TW w = ar.twiddle(4 * widx + i);
-            ar.template ct<(RM & 4) != 0>(v[2 * i], v[2 * i + 1], w);
-        }
+        for (int h = 0; h < 4; h++)
+#pragma unroll
+            for (int j = 0; j < 2; j++) ar.template ct<(RM & 4) != 0>(v[4 * h + j], v[4 * h + j + 2], w[h]);
+    }
+    if (S0 <= 3 && 3 < S1) {
+        typename A::TW w[8];
+        tws.template get<3>(w);
+#pragma unroll
+        for (int h = 0; h < 8; h++) ar.template ct<(RM & 8) != 0>(v[2 * h], v[2 * h + 1], w[h]);
     }
 }
 
-// The same stages undone, bottom bit first.  K is the number, within its kernel, of the
-// first stage this call executes; odd-numbered stages set R.
-template <int S0, int S1, int K, class A>
-__device__ __forceinline__ void inv8(const A& ar, typename A::V (&v)[8], uint32_t widx) {
-    constexpr int first = S1 - 1;       // window stage executed first
-    if (S0 <= 2 && 2 < S1) {
+// The same stages undone, bottom bit first.
+template <int S0, int S1, class A, class TWS>
+__device__ __forceinline__ void inv16(const A& ar, typename A::V (&v)[16], const TWS& tws) {
+    if (S0 <= 3 && 3 < S1) {
+        typename A::TW w[8];
+        tws.template get<3>(w);
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            typename A::TW w = ar.twiddle(4 * widx + i);
-            ar.template gs<((K + first - 2) & 1) == 1>(v[2 * i], v[2 * i + 1], w);
-        }
+        for (int h = 0; h < 8; h++) ar.template gs<false>(v[2 * h], v[2 * h + 1], w[h]);
+    }
+    if (S0 <= 2 && 2 < S1) {
+        typename A::TW w[4];
+        tws.template get<2>(w);
+#pragma unroll
+        for (int h = 0; h < 4; h++)
+#pragma unroll
+            for (int j = 0; j < 2; j++) ar.template gs<false>(v[4 * h + j], v[4 * h + j + 2], w[h]);
     }
     if (S0 <= 1 && 1 < S1) {
+        typename A::TW w[2];
+        tws.template get<1>(w);
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            typename A::TW w = ar.twiddle(2 * widx + h);
-            ar.template gs<((K + first - 1) & 1) == 1>(v[4 * h], v[4 * h + 2], w);
-            ar.template gs<((K + first - 1) & 1) == 1>(v[4 * h + 1], v[4 * h + 3], w);
-        }
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) ar.template gs<false>(v[8 * h + j], v[8 * h + j + 4], w[h]);
     }
     if (S0 <= 0 && 0 < S1) {
-        typename A::TW w = ar.twiddle(widx);
+        typename A::TW w[1];
+        tws.template get<0>(w);
 #pragma unroll
-        for (int j = 0; j < 4; j++) ar.template gs<((K + first - 0) & 1) == 1>(v[j], v[j + 4], w);
+        for (int j = 0; j < 8; j++) ar.template gs<false>(v[j], v[j + 8], w[0]);
     }
 }
 
+constexpr int kTile = 4096;            // words per tile
+constexpr int kThreads = 256;          // 16 values per thread
+constexpr int kChunk = 256;            // points per chunk of the contiguous phase
+
 // ---------------------------------------------------------------------------
-// Contiguous phase: 16 chunks of 256 points per CTA, one warp per chunk.
-// Shared-memory position of point p of a chunk: the low four bits are XOR-ed with
-// bits 4..6 so that all three windows are bank-conflict free for 64-bit accesses.
+// Contiguous phase.  A tile is 16 chunks of 256 consecutive points; a half-warp owns one chunk.
+// Window A pairs on chunk bits 7..4: lane l of the chunk holds points j*16 + l.  Window B pairs on
+// bits 3..0: lane l holds the 16 consecutive points l*16 + j.  Shared-memory position of point p of
+// a chunk: bits 1..3 are XOR-ed with bits 4..6, which keeps pairs of points together (16-byte
+// copies and 128-bit accesses stay aligned) and makes both windows bank-conflict free.
+// A CTA stays at one tile position of one limb and walks over polynomials, so the tile's twiddles
+// are staged once (back ends whose twiddle is one double; the integer back ends read the table).
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t swz(uint32_t p) {
-    return p ^ ((p >> 4) & 7u) ^ (((p >> 5) & 1u) << 3);
+__device__ __forceinline__ uint32_t swz(uint32_t p) { return p ^ (((p >> 4) & 7u) << 1); }
+
+// This warp's two chunks of a tile, global -> shared, 16 bytes per copy, 8 copies per lane.
+__device__ __forceinline__ void prefetch_chunks(u64* swarp, const u64* gwarp, int lane) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t p = 2 * (i * 32 + lane);                 // word inside the warp's 512
+        __pipeline_memcpy_async(swarp + (p & 256) + swz(p & 255), gwarp + p, 16);
+    }
 }
 
-constexpr int kChunk = 256;
-constexpr int kChunksPerCta = 16;
-constexpr int kThreadsB = 32 * kChunksPerCta;
+template <class A>
+struct StagesTwiddles { static constexpr bool value = false; };
+template <>
+struct StagesTwiddles<F64Arith> { static constexpr bool value = true; };
 
-// A CTA walks over `tiles` consecutive tiles of 16 chunks; warp v owns chunk v of every tile.
-// While a chunk is in the butterflies the next one is already on its way into the warp's
-// other shared-memory buffer (asynchronous 8-byte copies straight to the swizzled positions),
-// so loads stay in flight through the compute phases.
-__device__ __forceinline__ void prefetch_chunk(u64* sbuf, const u64* g, int lane) {
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const uint32_t p = j * 32 + lane;
-        __pipeline_memcpy_async(sbuf + swz(p), g + p, 8);
-    }
+template <bool INV, class A>
+__device__ __forceinline__ void contig_body(const NttArgs& P, u64* S, int poly0, int npoly) {
+    typedef typename A::V V;
+    constexpr bool STAGED = StagesTwiddles<A>::value;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, l = lane & 15;
+    const int limb = blockIdx.y;
+    A ar;
+    ar.init(P, P.start_mod_idx + limb);
+    const uint32_t N = 1u << P.logN;
+    const uint32_t xt = (uint32_t)blockIdx.x * kTile;                           // the tile's position in its polynomial
+    const uint32_t xwarp = xt + warp * 512;                                     // this warp's two chunks
+    const uint32_t coff = (lane >> 4) * kChunk;                                 // this half-warp's chunk
+    const uint32_t x0 = xwarp + coff;
+    u64* sbuf = S + warp * 1024;                                                // two buffers of 512 words per warp
+    const double* stw = reinterpret_cast<const double*>(S + 2 * kTile);         // the staged twiddles
+    auto gpoly = [&](int t) { return P.data + (((size_t)(poly0 + t) * P.poly_mod_len + P.start_limb_off + limb) << P.logN); };
+    V a[16];
+    if (STAGED) stage_twiddles(const_cast<double*>(stw), P.tw_d + ((size_t)(P.start_mod_idx + limb) << P.logN), N, xt, tid, kThreads);
+    prefetch_chunks(sbuf, gpoly(0) + xwarp, lane);
     __pipeline_commit();
-}
+    for (int t = 0; t < npoly; t++) {
+        u64* gl = gpoly(t);
+        u64* s = sbuf + (t & 1) * 512 + coff;
+        __syncwarp();                                             // every lane is done with the other buffer
+        if (t + 1 < npoly) prefetch_chunks(sbuf + ((t + 1) & 1) * 512, gpoly(t + 1) + xwarp, lane);
+        __pipeline_commit();
+        __pipeline_wait_prior(1);
+        if (STAGED && t == 0) __syncthreads();                    // the twiddles came in through every thread's copies
+        else __syncwarp();
 
-template <class A>
-__device__ __forceinline__ void fwd_contig_body(const NttArgs& P, u64* S, int tiles) {
-    typedef typename A::V V;
-    const int lane = threadIdx.x & 31, vv = threadIdx.x >> 5;
-    const int limb = blockIdx.y, poly = blockIdx.z;
-    A ar;
-    ar.init(P, P.start_mod_idx + limb);
-    const uint32_t N = 1u << P.logN;
-    u64* gl = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN);
-    const uint32_t xfirst = (blockIdx.x * tiles * kChunksPerCta + vv) * kChunk;
-    u64* sbuf = S + vv * 2 * kChunk;            // two buffers per warp
-    V a[8];
-    prefetch_chunk(sbuf, gl + xfirst, lane);
-    for (int t = 0; t < tiles; t++) {
-        const uint32_t x0 = xfirst + t * kChunksPerCta * kChunk;      // position of the chunk
-        u64* s = sbuf + (t & 1) * kChunk;
-        __syncwarp();                            // every lane is done with the other buffer
-        if (t + 1 < tiles) {
-            prefetch_chunk(sbuf + ((t + 1) & 1) * kChunk, gl + x0 + kChunksPerCta * kChunk, lane);
-            __pipeline_wait_prior(1);
+        const int c = warp * 2 + (lane >> 4);                     // chunk inside the tile
+        if (!INV) {
+            // window A, chunk bits 7..4: p = j*16 + l
+#pragma unroll
+            for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[j * 16 + (l ^ ((j & 7) << 1))]);
+            // kernel stages 0 (reducing), 1, 2, 3 (reducing)
+            if constexpr (STAGED) fwd16<0, 4, 1 | 8, A>(ar, a, TwSharedA{stw, c});
+            else fwd16<0, 4, 1 | 8, A>(ar, a, TwGlobal<A>{ar, (N + x0) >> 8});
+#pragma unroll
+            for (int j = 0; j < 16; j++) s[j * 16 + (l ^ ((j & 7) << 1))] = ar.to_word(a[j]);
+            __syncwarp();
+            // window B, chunk bits 3..0: p = l*16 + j, read as pairs
+            ulonglong2* s2 = reinterpret_cast<ulonglong2*>(s + l * 16);
+#pragma unroll
+            for (int m = 0; m < 8; m++) {
+                const ulonglong2 w = s2[m ^ (l & 7)];
+                a[2 * m] = ar.from_word(w.x);
+                a[2 * m + 1] = ar.from_word(w.y);
+            }
+            // stages 4, 5, 6 (reducing), 7
+            if constexpr (STAGED) fwd16<0, 4, 4, A>(ar, a, TwSharedB{stw, c * 16 + l});
+            else fwd16<0, 4, 4, A>(ar, a, TwGlobal<A>{ar, ((N + x0) >> 4) + l});
+            // A lane holds 16 consecutive words; storing them from here would touch 32 different 128-byte lines
+            // per instruction.  They go back through the chunk's buffer and leave with 16 lanes per line.
+#pragma unroll
+            for (int m = 0; m < 8; m++) s2[m ^ (l & 7)] = make_ulonglong2(ar.canonical_fwd(a[2 * m]), ar.canonical_fwd(a[2 * m + 1]));
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 16; j++) gl[x0 + j * 16 + l] = s[j * 16 + (l ^ ((j & 7) << 1))];
         } else {
-            __pipeline_wait_prior(0);
+            // window B first: p = l*16 + j
+            ulonglong2* s2 = reinterpret_cast<ulonglong2*>(s + l * 16);
+#pragma unroll
+            for (int m = 0; m < 8; m++) {
+                const ulonglong2 w = s2[m ^ (l & 7)];
+                a[2 * m] = ar.from_canonical(w.x);
+                a[2 * m + 1] = ar.from_canonical(w.y);
+            }
+            if constexpr (STAGED) inv16<0, 4, A>(ar, a, TwSharedB{stw, c * 16 + l});
+            else inv16<0, 4, A>(ar, a, TwGlobal<A>{ar, ((N + x0) >> 4) + l});
+#pragma unroll
+            for (int m = 0; m < 8; m++) s2[m ^ (l & 7)] = make_ulonglong2(ar.to_word(a[2 * m]), ar.to_word(a[2 * m + 1]));
+            __syncwarp();
+            // window A: p = j*16 + l
+#pragma unroll
+            for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[j * 16 + (l ^ ((j & 7) << 1))]);
+            if constexpr (STAGED) inv16<0, 4, A>(ar, a, TwSharedA{stw, c});
+            else inv16<0, 4, A>(ar, a, TwGlobal<A>{ar, (N + x0) >> 8});
+            // values stay lazy; the strided phase finishes the transform
+#pragma unroll
+            for (int j = 0; j < 16; j++) gl[x0 + j * 16 + l] = ar.to_word(a[j]);
         }
-        __syncwarp();
-
-        // window bits 7..5: p = j*32 + lane
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(j * 32 + lane)]);
-        fwd8<0, 3, 1>(ar, a, (N + x0) >> 8);             // kernel stages 0 (reducing), 1, 2
-#pragma unroll
-        for (int j = 0; j < 8; j++) s[swz(j * 32 + lane)] = ar.to_word(a[j]);
-        __syncwarp();
-
-        // window bits 4..2: p = hi*32 + j*4 + lo, lane = hi*4 + lo
-        {
-            const uint32_t lo = lane & 3, hi = lane >> 2;
-#pragma unroll
-            for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(hi * 32 + j * 4 + lo)]);
-            fwd8<0, 3, 1>(ar, a, ((N + x0) >> 5) + hi);  // stages 3 (reducing), 4, 5
-#pragma unroll
-            for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = ar.to_word(a[j]);
-        }
-        __syncwarp();
-
-        // window bits 2..0, stages on bits 1 and 0 only: p = lane*8 + j
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(lane * 8 + j)]);
-        fwd8<1, 3, 2>(ar, a, ((N + x0) >> 3) + lane);    // stages 6 (reducing), 7
-        ulonglong2* go = reinterpret_cast<ulonglong2*>(gl + x0 + lane * 8);
-#pragma unroll
-        for (int j = 0; j < 4; j++) go[j] = make_ulonglong2(ar.canonical_fwd(a[2 * j]), ar.canonical_fwd(a[2 * j + 1]));
     }
 }
 
-template <class A>
-__device__ __forceinline__ void inv_contig_body(const NttArgs& P, u64* S, int tiles) {
-    typedef typename A::V V;
-    const int lane = threadIdx.x & 31, vv = threadIdx.x >> 5;
-    const int limb = blockIdx.y, poly = blockIdx.z;
-    A ar;
-    ar.init(P, P.start_mod_idx + limb);
-    const uint32_t N = 1u << P.logN;
-    u64* gl = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN);
-    const uint32_t xfirst = (blockIdx.x * tiles * kChunksPerCta + vv) * kChunk;
-    u64* sbuf = S + vv * 2 * kChunk;
-    V a[8];
-    prefetch_chunk(sbuf, gl + xfirst, lane);
-    for (int t = 0; t < tiles; t++) {
-        const uint32_t x0 = xfirst + t * kChunksPerCta * kChunk;
-        u64* s = sbuf + (t & 1) * kChunk;
-        __syncwarp();
-        if (t + 1 < tiles) {
-            prefetch_chunk(sbuf + ((t + 1) & 1) * kChunk, gl + x0 + kChunksPerCta * kChunk, lane);
-            __pipeline_wait_prior(1);
-        } else {
-            __pipeline_wait_prior(0);
-        }
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_canonical(s[swz(lane * 8 + j)]);
-        inv8<1, 3, 0>(ar, a, ((N + x0) >> 3) + lane);            // stages 0, 1 of this kernel
-#pragma unroll
-        for (int j = 0; j < 8; j++) s[swz(lane * 8 + j)] = ar.to_word(a[j]);
-        __syncwarp();
-        {
-            const uint32_t lo = lane & 3, hi = lane >> 2;
-#pragma unroll
-            for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(hi * 32 + j * 4 + lo)]);
-            inv8<0, 3, 2>(ar, a, ((N + x0) >> 5) + hi);          // stages 2, 3, 4
-#pragma unroll
-            for (int j = 0; j < 8; j++) s[swz(hi * 32 + j * 4 + lo)] = ar.to_word(a[j]);
-        }
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(s[swz(j * 32 + lane)]);
-        inv8<0, 3, 5>(ar, a, (N + x0) >> 8);                      // stages 5, 6, 7
-        // values stay lazy; the strided phase finishes the transform
-#pragma unroll
-        for (int j = 0; j < 8; j++) gl[x0 + j * 32 + lane] = ar.to_word(a[j]);
-    }
-}
-
+// grid: (tile position, limb, group of `walk` polynomials)
 template <bool INV>
-__global__ void __launch_bounds__(kThreadsB, 2) ntt_contig(NttArgs P, int tiles) {
-    extern __shared__ __align__(16) u64 S[];       // 2 buffers x 16 chunks x 256 words
+__global__ void __launch_bounds__(kThreads, 2) ntt_contig(NttArgs P, int poly_num, int walk) {
+    extern __shared__ __align__(16) u64 S[];       // 2 buffers x 4096 words, then the tile's twiddles
+    const int poly0 = blockIdx.z * walk;
+    const int npoly = poly_num - poly0 < walk ? poly_num - poly0 : walk;
     const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
-    if (q < kF64Bound) {
-        if (INV) inv_contig_body<F64Arith>(P, S, tiles); else fwd_contig_body<F64Arith>(P, S, tiles);
-    } else if (q < kLazyBound) {
-        if (INV) inv_contig_body<IntArith<true>>(P, S, tiles); else fwd_contig_body<IntArith<true>>(P, S, tiles);
-    } else {
-        if (INV) inv_contig_body<IntArith<false>>(P, S, tiles); else fwd_contig_body<IntArith<false>>(P, S, tiles);
-    }
+    if (q < kF64Bound) contig_body<INV, F64Arith>(P, S, poly0, npoly);
+    else if (q < kLazyBound) contig_body<INV, IntArith<true>>(P, S, poly0, npoly);
+    else contig_body<INV, IntArith<false>>(P, S, poly0, npoly);
 }
 
 // ---------------------------------------------------------------------------
 // Strided phase: SA = logN-8 stages on vectors of R = 2^SA points with stride 256.
-// A CTA owns a tile of R rows x CW consecutive columns (CW = min(256, 4096/R)),
-// indexed idx = row*CW + col; the stage bits are the top SA bits of idx.
-// Window w covers idx bits [T-3(w+1), T-3w) and runs min(3, SA-3w) stages.
+// A tile is R rows x CW consecutive columns, CW = 4096/R, indexed idx = row*CW + col (12 bits); the
+// stage bits are the top SA bits of idx.  Window 0 covers idx bits 8..11 (four stages), window 1
+// bits 4..7 (the remaining SA-4 stages, none for logN = 12).  Shared memory holds the tile at its
+// idx, which both windows read and write without bank conflicts.  The phase has 2^SA - 1 twiddles
+// per limb in all, so they are read from the table (they stay in L1).
 // ---------------------------------------------------------------------------
 template <int SA>
 struct StridedCfg {
     static constexpr int R = 1 << SA;
-    static constexpr int CW = (4096 / R) < 256 ? (4096 / R) : 256;
-    static constexpr int LOGCW = CW == 256 ? 8 : CW == 128 ? 7 : CW == 64 ? 6 : CW == 32 ? 5 : 4;
-    static constexpr int T = SA + LOGCW;
-    static constexpr int THREADS = (1 << T) / 8;
-    static constexpr int NWIN = (SA + 2) / 3;
-};
-
-template <int SA, int WIN>
-struct Win {
-    typedef StridedCfg<SA> C;
-    static constexpr int fb = C::T - 3 * (WIN + 1);
-    static constexpr int nst_raw = SA - 3 * WIN;
-    static constexpr int nst = nst_raw < 1 ? 1 : (nst_raw < 3 ? nst_raw : 3);
-    // stages executed before this window in the inverse kernel (windows run high to low)
-    static constexpr int inv_before = (SA - 3 * (WIN + 1)) > 0 ? (SA - 3 * (WIN + 1)) : 0;
-    __device__ static __forceinline__ uint32_t base(uint32_t tid) {
-        return ((tid >> fb) << (fb + 3)) | (tid & ((1u << fb) - 1));
-    }
-    __device__ static __forceinline__ uint32_t widx(uint32_t b) { return ((1u << C::T) + b) >> (fb + 3); }
-    __device__ static __forceinline__ u64* gptr(u64* g, uint32_t idx) {
-        return g + ((size_t)(idx >> C::LOGCW) << 8) + (idx & (C::CW - 1));
+    static constexpr int CW = 4096 / R;
+    static constexpr int LOGCW = 12 - SA;
+    static constexpr int NST1 = SA - 4;            // stages of window 1
+    __device__ static __forceinline__ size_t goff(uint32_t idx) {      // offset of tile element idx from the tile's origin
+        return ((size_t)(idx >> LOGCW) << 8) + (idx & (CW - 1));
     }
 };
-
-template <int SA, class A>
-__device__ __forceinline__ void fwd_strided_body(const NttArgs& P, u64* S) {
-    typedef StridedCfg<SA> C;
-    typedef typename A::V V;
-    const uint32_t tid = threadIdx.x;
-    const int limb = blockIdx.y, poly = blockIdx.z;
-    A ar;
-    ar.init(P, P.start_mod_idx + limb);
-    u64* g = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN) +
-             (size_t)blockIdx.x * C::CW;
-    V a[8];
-    uint32_t b = Win<SA, 0>::base(tid);
-#pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = ar.from_canonical(*Win<SA, 0>::gptr(g, b | (j << Win<SA, 0>::fb)));
-    fwd8<0, Win<SA, 0>::nst, 4>(ar, a, Win<SA, 0>::widx(b));      // the third stage of a window reduces
-    if (C::NWIN >= 2) {
-#pragma unroll
-        for (int j = 0; j < 8; j++) S[b | (j << Win<SA, 0>::fb)] = ar.to_word(a[j]);
-        __syncthreads();
-        b = Win<SA, 1>::base(tid);
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(S[b | (j << Win<SA, 1>::fb)]);
-        fwd8<0, Win<SA, 1>::nst, 4>(ar, a, Win<SA, 1>::widx(b));
-    }
-    if (C::NWIN >= 3) {
-#pragma unroll
-        for (int j = 0; j < 8; j++) S[b | (j << Win<SA, 1>::fb)] = ar.to_word(a[j]);
-        __syncthreads();
-        b = Win<SA, 2>::base(tid);
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(S[b | (j << Win<SA, 2>::fb)]);
-        fwd8<0, Win<SA, 2>::nst, 4>(ar, a, Win<SA, 2>::widx(b));
-    }
-    constexpr int LW = C::NWIN - 1;
-#pragma unroll
-    for (int j = 0; j < 8; j++) *Win<SA, LW>::gptr(g, b | (j << Win<SA, LW>::fb)) = ar.to_word(a[j]);
-}
-
-template <int SA, class A>
-__device__ __forceinline__ void inv_strided_body(const NttArgs& P, u64* S) {
-    typedef StridedCfg<SA> C;
-    typedef typename A::V V;
-    const uint32_t tid = threadIdx.x;
-    const int limb = blockIdx.y, poly = blockIdx.z;
-    A ar;
-    ar.init(P, P.start_mod_idx + limb);
-    u64* g = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN) +
-             (size_t)blockIdx.x * C::CW;
-    V a[8];
-    constexpr int LW = C::NWIN - 1;
-    uint32_t b = Win<SA, LW>::base(tid);
-#pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = ar.from_word(*Win<SA, LW>::gptr(g, b | (j << Win<SA, LW>::fb)));
-    if (C::NWIN == 3) {
-        inv8<0, Win<SA, 2>::nst, Win<SA, 2>::inv_before>(ar, a, Win<SA, 2>::widx(b));
-#pragma unroll
-        for (int j = 0; j < 8; j++) S[b | (j << Win<SA, 2>::fb)] = ar.to_word(a[j]);
-        __syncthreads();
-        b = Win<SA, 1>::base(tid);
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(S[b | (j << Win<SA, 1>::fb)]);
-    }
-    if (C::NWIN >= 2) {
-        inv8<0, Win<SA, 1>::nst, Win<SA, 1>::inv_before>(ar, a, Win<SA, 1>::widx(b));
-#pragma unroll
-        for (int j = 0; j < 8; j++) S[b | (j << Win<SA, 1>::fb)] = ar.to_word(a[j]);
-        __syncthreads();
-        b = Win<SA, 0>::base(tid);
-#pragma unroll
-        for (int j = 0; j < 8; j++) a[j] = ar.from_word(S[b | (j << Win<SA, 0>::fb)]);
-    }
-    inv8<0, Win<SA, 0>::nst, Win<SA, 0>::inv_before>(ar, a, Win<SA, 0>::widx(b));
-    // Final scaling: the last stage's twiddle psiinv[1] already carries N^-1 for the upper
-    // half (a[4..7] of the top window); the lower half is multiplied by N^-1 here
-    // (src/ckks/include/ntt_60bit.cuh:890-898).
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const u64 r = j < 4 ? ar.canonical_inv_lo(a[j]) : ar.canonical_inv_hi(a[j]);
-        *Win<SA, 0>::gptr(g, b | (j << Win<SA, 0>::fb)) = r;
-    }
-}
-
-template <int SA, bool INV>
-__global__ void __launch_bounds__(StridedCfg<SA>::THREADS, 2) ntt_strided(NttArgs P) {
-    typedef StridedCfg<SA> C;
-    __shared__ u64 S[C::NWIN > 1 ? (1 << C::T) : 1];
-    const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
-    if (q < kF64Bound) {
-        if (INV) inv_strided_body<SA, F64Arith>(P, S); else fwd_strided_body<SA, F64Arith>(P, S);
-    } else if (q < kLazyBound) {
-        if (INV) inv_strided_body<SA, IntArith<true>>(P, S); else fwd_strided_body<SA, IntArith<true>>(P, S);
-    } else {
-        if (INV) inv_strided_body<SA, IntArith<false>>(P, S); else fwd_strided_body<SA, IntArith<false>>(P, S);
-    }
-}
 
 template <int SA>
-void launch_strided(bool inverse, dim3 grid_lp, const NttArgs& P, cudaStream_t st) {
+__device__ __forceinline__ void prefetch_tile(u64* sbuf, const u64* gtile, uint32_t tid) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t p = 2 * (i * kThreads + tid);
+        __pipeline_memcpy_async(sbuf + p, gtile + StridedCfg<SA>::goff(p), 16);
+    }
+}
+
+// reduction mask of a forward window whose first stage is kernel stage G0: stages 2, 5 of the kernel reduce
+__host__ __device__ constexpr int fwd_mask(int G0) {
+    return ((G0 % 3 == 2) ? 1 : 0) | (((G0 + 1) % 3 == 2) ? 2 : 0) | (((G0 + 2) % 3 == 2) ? 4 : 0) | (((G0 + 3) % 3 == 2) ? 8 : 0);
+}
+
+template <int SA, bool INV, class A>
+__device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles) {
     typedef StridedCfg<SA> C;
-    dim3 grid(256 / C::CW, grid_lp.y, grid_lp.z);
-    if (inverse) ntt_strided<SA, true><<<grid, C::THREADS, 0, st>>>(P);
-    else ntt_strided<SA, false><<<grid, C::THREADS, 0, st>>>(P);
+    typedef typename A::V V;
+    const uint32_t tid = threadIdx.x;
+    const int limb = blockIdx.y, poly = blockIdx.z;
+    A ar;
+    ar.init(P, P.start_mod_idx + limb);
+    u64* g = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN) +
+             (size_t)blockIdx.x * tiles * C::CW;
+    const uint32_t b1 = ((tid >> 4) << 8) | (tid & 15);          // window 1: v[j] at b1 | j << 4
+    const TwGlobal<A> tw0{ar, 1u}, tw1{ar, 16u + (tid >> 4)};
+    V a[16];
+    prefetch_tile<SA>(S, g, tid);
+    __pipeline_commit();
+    for (int t = 0; t < tiles; t++) {
+        u64* s = S + (t & 1) * kTile;
+        u64* gt = g + (size_t)t * C::CW;
+        __syncthreads();                                          // everybody is done with the other buffer
+        if (t + 1 < tiles) prefetch_tile<SA>(S + ((t + 1) & 1) * kTile, gt + C::CW, tid);
+        __pipeline_commit();
+        __pipeline_wait_prior(1);
+        __syncthreads();
+        if (!INV) {
+            // window 0: v[j] at idx j*256 + tid; one twiddle set for the whole grid
+#pragma unroll
+            for (int j = 0; j < 16; j++) a[j] = ar.from_canonical(s[j * 256 + tid]);
+            fwd16<0, 4, fwd_mask(0), A>(ar, a, tw0);
+            if (C::NST1 > 0) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) s[j * 256 + tid] = ar.to_word(a[j]);
+                __syncthreads();
+#pragma unroll
+                for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[b1 | (j << 4)]);
+                fwd16<0, C::NST1, fwd_mask(4), A>(ar, a, tw1);
+#pragma unroll
+                for (int j = 0; j < 16; j++) gt[C::goff(b1 | (j << 4))] = ar.to_word(a[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) gt[C::goff(j * 256 + tid)] = ar.to_word(a[j]);
+            }
+        } else {
+            if (C::NST1 > 0) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[b1 | (j << 4)]);
+                inv16<0, C::NST1, A>(ar, a, tw1);
+#pragma unroll
+                for (int j = 0; j < 16; j++) s[b1 | (j << 4)] = ar.to_word(a[j]);
+                __syncthreads();
+            }
+#pragma unroll
+            for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[j * 256 + tid]);
+            inv16<0, 4, A>(ar, a, tw0);
+            // Final scaling: the last stage's twiddle psiinv[1] already carries N^-1 for the upper half (a[8..15]);
+            // the lower half is multiplied by N^-1 here (src/ckks/include/ntt_60bit.cuh:890-898).
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const u64 r = j < 8 ? ar.canonical_inv_lo(a[j]) : ar.canonical_inv_hi(a[j]);
+                gt[C::goff(j * 256 + tid)] = r;
+            }
+        }
+    }
+}
+
+// grid: (group of `tiles` tiles, limb, polynomial)
+template <int SA, bool INV>
+__global__ void __launch_bounds__(kThreads, 2) ntt_strided(NttArgs P, int tiles) {
+    extern __shared__ __align__(16) u64 S[];       // 2 buffers x 4096 words
+    const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
+    if (q < kF64Bound) strided_body<SA, INV, F64Arith>(P, S, tiles);
+    else if (q < kLazyBound) strided_body<SA, INV, IntArith<true>>(P, S, tiles);
+    else strided_body<SA, INV, IntArith<false>>(P, S, tiles);
+}
+
+constexpr size_t kSmemStrided = 2 * kTile * sizeof(u64);
+constexpr size_t kSmemContig = 3 * kTile * sizeof(u64);
+
+template <int SA>
+int launch_strided(bool inverse, int ntile, int tiles, int mod_num, int poly_num, const NttArgs& P, cudaStream_t st) {
+    dim3 grid(ntile / tiles, mod_num, poly_num);
+    if (inverse) {
+        CKB_CUDA(cudaFuncSetAttribute(ntt_strided<SA, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemStrided));
+        ntt_strided<SA, true><<<grid, kThreads, kSmemStrided, st>>>(P, tiles);
+    } else {
+        CKB_CUDA(cudaFuncSetAttribute(ntt_strided<SA, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemStrided));
+        ntt_strided<SA, false><<<grid, kThreads, kSmemStrided, st>>>(P, tiles);
+    }
+    return CKKS_B200_OK;
+}
+
+int launch_contig(bool inverse, int ntile, int walk, int mod_num, int poly_num, const NttArgs& P, cudaStream_t st) {
+    dim3 grid(ntile, mod_num, (poly_num + walk - 1) / walk);
+    if (inverse) {
+        CKB_CUDA(cudaFuncSetAttribute(ntt_contig<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemContig));
+        ntt_contig<true><<<grid, kThreads, kSmemContig, st>>>(P, poly_num, walk);
+    } else {
+        CKB_CUDA(cudaFuncSetAttribute(ntt_contig<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemContig));
+        ntt_contig<false><<<grid, kThreads, kSmemContig, st>>>(P, poly_num, walk);
+    }
+    return CKKS_B200_OK;
 }
 
 int run_ntt(ckks_b200_context* c, u64* d_data, int start_limb_off, int start_mod_idx, int poly_num,
@@ -543,37 +613,30 @@ int run_ntt(ckks_b200_context* c, u64* d_data, int start_limb_off, int start_mod
     P.start_mod_idx = start_mod_idx;
     P.poly_mod_len = poly_mod_len;
 
-    dim3 grid_c(c->N / (kChunk * kChunksPerCta), mod_num, poly_num);
-    auto strided = [&]() {
+    // A CTA walks over several tiles (strided phase) or polynomials (contiguous phase) so that its prefetch has
+    // something to run ahead of, unless the call is so small that walking would leave SMs without a CTA: then more,
+    // shorter CTAs.
+    static int sms = 0;
+    if (sms == 0 && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device) != cudaSuccess) sms = 148;
+    const int ntile = c->N / kTile;
+    const long transforms = (long)mod_num * poly_num;
+    int tiles = ntile >= 4 ? 4 : ntile;
+    while (tiles > 1 && transforms * (ntile / tiles) < 2L * sms) tiles >>= 1;
+    int walk = poly_num >= 8 ? 8 : poly_num;
+    while (walk > 1 && (long)ntile * mod_num * ((poly_num + walk - 1) / walk) < 4L * sms) walk = (walk + 1) / 2;
+    auto strided = [&]() -> int {
         switch (c->logN - 8) {
-            case 4: launch_strided<4>(inverse, grid_c, P, st); break;
-            case 5: launch_strided<5>(inverse, grid_c, P, st); break;
-            case 6: launch_strided<6>(inverse, grid_c, P, st); break;
-            case 7: launch_strided<7>(inverse, grid_c, P, st); break;
-            case 8: launch_strided<8>(inverse, grid_c, P, st); break;
+            case 4: return launch_strided<4>(inverse, ntile, tiles, mod_num, poly_num, P, st);
+            case 5: return launch_strided<5>(inverse, ntile, tiles, mod_num, poly_num, P, st);
+            case 6: return launch_strided<6>(inverse, ntile, tiles, mod_num, poly_num, P, st);
+            case 7: return launch_strided<7>(inverse, ntile, tiles, mod_num, poly_num, P, st);
+            default: return launch_strided<8>(inverse, ntile, tiles, mod_num, poly_num, P, st);
         }
     };
-    // the contiguous kernel walks over several tiles per CTA so that its prefetch has something to run ahead of
-    const int ntile = c->N / (kChunk * kChunksPerCta);
-    // ... unless the call is so small that walking would leave SMs without a CTA: then more, shorter CTAs
-    int tiles = ntile >= 4 ? 4 : ntile;
-    {
-        static int sms = 0;
-        if (sms == 0 && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device) != cudaSuccess) sms = 148;
-        const long transforms = (long)mod_num * poly_num;
-        while (tiles > 1 && transforms * (ntile / tiles) < 2L * sms) tiles >>= 1;
-    }
-    const size_t smem_c = 2 * kChunk * kChunksPerCta * sizeof(u64);
-    dim3 grid_k(ntile / tiles, mod_num, poly_num);
-    if (!inverse) {
-        strided();
-        CKB_CUDA(cudaFuncSetAttribute(ntt_contig<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c));
-        ntt_contig<false><<<grid_k, kThreadsB, smem_c, st>>>(P, tiles);
-    } else {
-        CKB_CUDA(cudaFuncSetAttribute(ntt_contig<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c));
-        ntt_contig<true><<<grid_k, kThreadsB, smem_c, st>>>(P, tiles);
-        strided();
-    }
+    int rc = inverse ? launch_contig(true, ntile, walk, mod_num, poly_num, P, st) : strided();
+    if (rc) return rc;
+    rc = inverse ? strided() : launch_contig(false, ntile, walk, mod_num, poly_num, P, st);
+    if (rc) return rc;
     count_launch(2);
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
