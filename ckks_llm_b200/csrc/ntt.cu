@@ -109,6 +109,8 @@ struct IntArith {
             b = shoup_lazy(t, w.x, w.y, q);
         }
     }
+    // last inverse stage: the same butterfly; N^-1 follows in canonical_inv_lo
+    __device__ __forceinline__ void gs_last(V& a, V& b, TW w) const { gs<true>(a, b, w); }
     // any lazy forward value -> [0, q)
     __device__ __forceinline__ u64 canonical_fwd(V x) const {
         if (LAZY) return csub(x - __umul64hi(x, qinv64) * q, q);
@@ -126,12 +128,13 @@ struct F64Arith {
     typedef double V;
     typedef double TW;
     double q, u, ninv;
+    long long qi;
     const double* tw;
     __device__ __forceinline__ void init(const NttArgs& P, int mod) {
-        const u64 qi = P.moduli[mod];
+        qi = (long long)P.moduli[mod];
         q = (double)qi;
         u = __drcp_rn(q);
-        const u64 ni = P.ninv[mod].x;
+        const long long ni = (long long)P.ninv[mod].x;
         ninv = ni > qi / 2 ? -(double)(qi - ni) : (double)ni;
         tw = P.tw_d + ((size_t)mod << P.logN);
     }
@@ -160,7 +163,8 @@ struct F64Arith {
     }
     // Forward: a is reduced on one stage in three (R); with bound B on the inputs a stage
     // yields B + T(B) without and 0.51q + T(B) with the reduction, T(B) = q/2 + 3B/16, so
-    // the cycle (R, -, -) keeps every value below 3.5q < 2^52.
+    // the cycle (-, -, R) starting from canonical inputs keeps every value below 3.5q < 2^52,
+    // and a transform whose last stage reduces ends below 1.7q.
     template <bool R>
     __device__ __forceinline__ void ct(V& a, V& b, TW w) const {
         double t = mulmod(b, w);
@@ -168,21 +172,35 @@ struct F64Arith {
         a = __dadd_rn(s, t);
         b = __dadd_rn(s, -t);
     }
-    // Inverse: the sum is reduced on every stage; products then stay below 0.8q and
-    // differences below 1.6q.
+    // Inverse: the difference goes through the product (below q/2 + 3|d|/16), the sum is reduced on two stages in
+    // three (R).  With S the bound on the inputs, |d| <= 2S must stay below 2^52 = 4q: the cycle (R, R, -) from
+    // canonical inputs keeps S below 1.93q.
     template <bool R>
     __device__ __forceinline__ void gs(V& a, V& b, TW w) const {
         double s = __dadd_rn(a, b), d = __dadd_rn(a, -b);
-        a = reduce(s);
+        a = R ? reduce(s) : s;
         b = mulmod(d, w);
     }
+    // Last inverse stage: N^-1 is due on both outputs.  The table's psiinv[1] carries it for the difference
+    // (src/ckks/include/Utils.cuh:190-201); the sum gets it as its own product, which also reduces it.
+    __device__ __forceinline__ void gs_last(V& a, V& b, TW w) const {
+        double s = __dadd_rn(a, b), d = __dadd_rn(a, -b);
+        a = mulmod(s, ninv);
+        b = mulmod(d, w);
+    }
+    // An integer-valued double below 2^51 in magnitude as a two's-complement integer: 1.5 * 2^52 + x has x in its
+    // low mantissa bits.
+    __device__ __forceinline__ long long to_int(V x) const {
+        return __double_as_longlong(__dadd_rn(x, 6755399441055744.0)) - 0x4338000000000000ll;
+    }
+    // |x| < 2q -> [0, q), on the integer pipe (the FP64 pipe is what these kernels wait for)
     __device__ __forceinline__ u64 canonical(V x) const {
-        x = reduce(x);
-        if (x < 0.0) x = __dadd_rn(x, q);
-        return (u64)__double_as_longlong(__dadd_rn(x, 4503599627370496.0)) & 0x000FFFFFFFFFFFFFull;
+        u64 v = (u64)(to_int(x) + 2 * qi);               // (0, 4q)
+        v = v >= 2 * (u64)qi ? v - 2 * (u64)qi : v;
+        return v >= (u64)qi ? v - (u64)qi : v;
     }
     __device__ __forceinline__ u64 canonical_fwd(V x) const { return canonical(x); }
-    __device__ __forceinline__ u64 canonical_inv_lo(V x) const { return canonical(mulmod(x, ninv)); }
+    __device__ __forceinline__ u64 canonical_inv_lo(V x) const { return canonical(x); }      // gs_last applied N^-1
     __device__ __forceinline__ u64 canonical_inv_hi(V x) const { return canonical(x); }
 };
 
@@ -290,14 +308,15 @@ __device__ __forceinline__ void fwd16(const A& ar, typename A::V (&v)[16], const
     }
 }
 
-// The same stages undone, bottom bit first.
-template <int S0, int S1, class A, class TWS>
+// The same stages undone, bottom bit first.  RM as above (the inverse reduces its sums on the marked stages);
+// LAST: stage 0 of this window is the last stage of the transform and applies N^-1.
+template <int S0, int S1, int RM, bool LAST, class A, class TWS>
 __device__ __forceinline__ void inv16(const A& ar, typename A::V (&v)[16], const TWS& tws) {
     if (S0 <= 3 && 3 < S1) {
         typename A::TW w[8];
         tws.template get<3>(w);
 #pragma unroll
-        for (int h = 0; h < 8; h++) ar.template gs<false>(v[2 * h], v[2 * h + 1], w[h]);
+        for (int h = 0; h < 8; h++) ar.template gs<(RM & 8) != 0>(v[2 * h], v[2 * h + 1], w[h]);
     }
     if (S0 <= 2 && 2 < S1) {
         typename A::TW w[4];
@@ -305,7 +324,7 @@ __device__ __forceinline__ void inv16(const A& ar, typename A::V (&v)[16], const
 #pragma unroll
         for (int h = 0; h < 4; h++)
 #pragma unroll
-            for (int j = 0; j < 2; j++) ar.template gs<false>(v[4 * h + j], v[4 * h + j + 2], w[h]);
+            for (int j = 0; j < 2; j++) ar.template gs<(RM & 4) != 0>(v[4 * h + j], v[4 * h + j + 2], w[h]);
     }
     if (S0 <= 1 && 1 < S1) {
         typename A::TW w[2];
@@ -313,14 +332,31 @@ __device__ __forceinline__ void inv16(const A& ar, typename A::V (&v)[16], const
 #pragma unroll
         for (int h = 0; h < 2; h++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) ar.template gs<false>(v[8 * h + j], v[8 * h + j + 4], w[h]);
+            for (int j = 0; j < 4; j++) ar.template gs<(RM & 2) != 0>(v[8 * h + j], v[8 * h + j + 4], w[h]);
     }
     if (S0 <= 0 && 0 < S1) {
         typename A::TW w[1];
         tws.template get<0>(w);
 #pragma unroll
-        for (int j = 0; j < 8; j++) ar.template gs<false>(v[j], v[j + 8], w[0]);
+        for (int j = 0; j < 8; j++) {
+            if (LAST) ar.gs_last(v[j], v[j + 8], w[0]);
+            else ar.template gs<(RM & 1) != 0>(v[j], v[j + 8], w[0]);
+        }
     }
+}
+
+// Reduction masks.  Forward: a stage reduces when the number of stages after it is a multiple of three, so the last
+// stage does (the results end below 1.7q) and at most three stages in a row do not (3.5q from canonical inputs or
+// from the 1.7q a reducing stage leaves); the very first stage has nothing to reduce.  REM = stages of the transform
+// after stage 0 of the window.  Inverse: the stage executed as number e of the transform (0 = first) reduces unless
+// e % 3 == 2.
+__host__ __device__ constexpr int fwd_mask(int REM, bool first_window) {
+    return ((REM % 3 == 0 && !first_window) ? 1 : 0) | (((REM - 1) % 3 == 0) ? 2 : 0) | (((REM - 2) % 3 == 0) ? 4 : 0) |
+           (((REM - 3) % 3 == 0) ? 8 : 0);
+}
+// a window whose stages 3, 2, 1, 0 are executed as numbers E3, E3+1, E3+2, E3+3
+__host__ __device__ constexpr int inv_mask(int E3) {
+    return ((E3 % 3 != 2) ? 8 : 0) | (((E3 + 1) % 3 != 2) ? 4 : 0) | (((E3 + 2) % 3 != 2) ? 2 : 0) | (((E3 + 3) % 3 != 2) ? 1 : 0);
 }
 
 constexpr int kTile = 4096;            // words per tile
@@ -387,9 +423,9 @@ __device__ __forceinline__ void contig_body(const NttArgs& P, u64* S, int poly0,
             // window A, chunk bits 7..4: p = j*16 + l
 #pragma unroll
             for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[j * 16 + (l ^ ((j & 7) << 1))]);
-            // kernel stages 0 (reducing), 1, 2, 3 (reducing)
-            if constexpr (STAGED) fwd16<0, 4, 1 | 8, A>(ar, a, TwSharedA{stw, c});
-            else fwd16<0, 4, 1 | 8, A>(ar, a, TwGlobal<A>{ar, (N + x0) >> 8});
+            // the last eight stages of the transform: seven follow the first of them
+            if constexpr (STAGED) fwd16<0, 4, fwd_mask(7, false), A>(ar, a, TwSharedA{stw, c});
+            else fwd16<0, 4, fwd_mask(7, false), A>(ar, a, TwGlobal<A>{ar, (N + x0) >> 8});
 #pragma unroll
             for (int j = 0; j < 16; j++) s[j * 16 + (l ^ ((j & 7) << 1))] = ar.to_word(a[j]);
             __syncwarp();
@@ -401,9 +437,8 @@ __device__ __forceinline__ void contig_body(const NttArgs& P, u64* S, int poly0,
                 a[2 * m] = ar.from_word(w.x);
                 a[2 * m + 1] = ar.from_word(w.y);
             }
-            // stages 4, 5, 6 (reducing), 7
-            if constexpr (STAGED) fwd16<0, 4, 4, A>(ar, a, TwSharedB{stw, c * 16 + l});
-            else fwd16<0, 4, 4, A>(ar, a, TwGlobal<A>{ar, ((N + x0) >> 4) + l});
+            if constexpr (STAGED) fwd16<0, 4, fwd_mask(3, false), A>(ar, a, TwSharedB{stw, c * 16 + l});
+            else fwd16<0, 4, fwd_mask(3, false), A>(ar, a, TwGlobal<A>{ar, ((N + x0) >> 4) + l});
             // A lane holds 16 consecutive words; storing them from here would touch 32 different 128-byte lines
             // per instruction.  They go back through the chunk's buffer and leave with 16 lanes per line.
 #pragma unroll
@@ -420,16 +455,18 @@ __device__ __forceinline__ void contig_body(const NttArgs& P, u64* S, int poly0,
                 a[2 * m] = ar.from_canonical(w.x);
                 a[2 * m + 1] = ar.from_canonical(w.y);
             }
-            if constexpr (STAGED) inv16<0, 4, A>(ar, a, TwSharedB{stw, c * 16 + l});
-            else inv16<0, 4, A>(ar, a, TwGlobal<A>{ar, ((N + x0) >> 4) + l});
+            // executed as stages 0..3 of the inverse
+            if constexpr (STAGED) inv16<0, 4, inv_mask(0), false, A>(ar, a, TwSharedB{stw, c * 16 + l});
+            else inv16<0, 4, inv_mask(0), false, A>(ar, a, TwGlobal<A>{ar, ((N + x0) >> 4) + l});
 #pragma unroll
             for (int m = 0; m < 8; m++) s2[m ^ (l & 7)] = make_ulonglong2(ar.to_word(a[2 * m]), ar.to_word(a[2 * m + 1]));
             __syncwarp();
             // window A: p = j*16 + l
 #pragma unroll
             for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[j * 16 + (l ^ ((j & 7) << 1))]);
-            if constexpr (STAGED) inv16<0, 4, A>(ar, a, TwSharedA{stw, c});
-            else inv16<0, 4, A>(ar, a, TwGlobal<A>{ar, (N + x0) >> 8});
+            // stages 4..7
+            if constexpr (STAGED) inv16<0, 4, inv_mask(4), false, A>(ar, a, TwSharedA{stw, c});
+            else inv16<0, 4, inv_mask(4), false, A>(ar, a, TwGlobal<A>{ar, (N + x0) >> 8});
             // values stay lazy; the strided phase finishes the transform
 #pragma unroll
             for (int j = 0; j < 16; j++) gl[x0 + j * 16 + l] = ar.to_word(a[j]);
@@ -477,11 +514,6 @@ __device__ __forceinline__ void prefetch_tile(u64* sbuf, const u64* gtile, uint3
     }
 }
 
-// reduction mask of a forward window whose first stage is kernel stage G0: stages 2, 5 of the kernel reduce
-__host__ __device__ constexpr int fwd_mask(int G0) {
-    return ((G0 % 3 == 2) ? 1 : 0) | (((G0 + 1) % 3 == 2) ? 2 : 0) | (((G0 + 2) % 3 == 2) ? 4 : 0) | (((G0 + 3) % 3 == 2) ? 8 : 0);
-}
-
 template <int SA, bool INV, class A>
 __device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles) {
     typedef StridedCfg<SA> C;
@@ -509,14 +541,14 @@ __device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles
             // window 0: v[j] at idx j*256 + tid; one twiddle set for the whole grid
 #pragma unroll
             for (int j = 0; j < 16; j++) a[j] = ar.from_canonical(s[j * 256 + tid]);
-            fwd16<0, 4, fwd_mask(0), A>(ar, a, tw0);
+            fwd16<0, 4, fwd_mask(8 + SA - 1, true), A>(ar, a, tw0);
             if (C::NST1 > 0) {
 #pragma unroll
                 for (int j = 0; j < 16; j++) s[j * 256 + tid] = ar.to_word(a[j]);
                 __syncthreads();
 #pragma unroll
                 for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[b1 | (j << 4)]);
-                fwd16<0, C::NST1, fwd_mask(4), A>(ar, a, tw1);
+                fwd16<0, C::NST1, fwd_mask(8 + SA - 5, false), A>(ar, a, tw1);
 #pragma unroll
                 for (int j = 0; j < 16; j++) gt[C::goff(b1 | (j << 4))] = ar.to_word(a[j]);
             } else {
@@ -527,16 +559,18 @@ __device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles
             if (C::NST1 > 0) {
 #pragma unroll
                 for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[b1 | (j << 4)]);
-                inv16<0, C::NST1, A>(ar, a, tw1);
+                // window 1 runs its NST1 stages as numbers 8.. of the inverse: its stage NST1-1 first
+                inv16<0, C::NST1, inv_mask(8 + C::NST1 - 4), false, A>(ar, a, tw1);
 #pragma unroll
                 for (int j = 0; j < 16; j++) s[b1 | (j << 4)] = ar.to_word(a[j]);
                 __syncthreads();
             }
 #pragma unroll
             for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[j * 256 + tid]);
-            inv16<0, 4, A>(ar, a, tw0);
+            inv16<0, 4, inv_mask(8 + C::NST1), true, A>(ar, a, tw0);
             // Final scaling: the last stage's twiddle psiinv[1] already carries N^-1 for the upper half (a[8..15]);
-            // the lower half is multiplied by N^-1 here (src/ckks/include/ntt_60bit.cuh:890-898).
+            // the lower half still needs it (src/ckks/include/ntt_60bit.cuh:890-898): the integer back ends multiply
+            // here, the FP64 back end did in its last butterfly.
 #pragma unroll
             for (int j = 0; j < 16; j++) {
                 const u64 r = j < 8 ? ar.canonical_inv_lo(a[j]) : ar.canonical_inv_hi(a[j]);
@@ -546,9 +580,10 @@ __device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles
     }
 }
 
-// grid: (group of `tiles` tiles, limb, polynomial)
+// grid: (group of `tiles` tiles, limb, polynomial).  Three CTAs per SM (80 registers, no spills): the CTA-wide
+// barriers of this phase leave the FP64 pipe idle unless other CTAs fill in.
 template <int SA, bool INV>
-__global__ void __launch_bounds__(kThreads, 2) ntt_strided(NttArgs P, int tiles) {
+__global__ void __launch_bounds__(kThreads, 3) ntt_strided(NttArgs P, int tiles) {
     extern __shared__ __align__(16) u64 S[];       // 2 buffers x 4096 words
     const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
     if (q < kF64Bound) strided_body<SA, INV, F64Arith>(P, S, tiles);

@@ -133,3 +133,32 @@ def test_argument_errors(cuda_device):
     with pytest.raises(capi.CkksB200Error):
         Context_23(12, [], [q[0] + 2], [])           # not a prime = 1 mod 2N
     ctx.close()
+
+
+@pytest.mark.parametrize("logN", [12, 14, 16])
+def test_extreme_residues(oracle, cuda_device, logN):
+    """Inputs that push the lazily reduced intermediate values of the transforms to their bounds: every residue q-1,
+    residues alternating between 0 and q-1 at every stride, single spikes.  Moduli just below 2^50 (the FP64 back
+    end at its widest), one just below 2^57 and one of 60 bits (the two integer back ends)."""
+    N = 1 << logN
+    q = params.ntt_primes(50, 2 * N, 2) + params.ntt_primes(57, 2 * N, 1) + params.ntt_primes(60, 2 * N, 1)
+    ctx = Context_23(logN, [], q, [])
+    T = oracle.NttTables(N, q)
+    qa = np.array(q, dtype=np.uint64)[:, None]
+    x = np.arange(N, dtype=np.uint64)[None, :]
+    pats = [np.broadcast_to(qa - np.uint64(1), (len(q), N)).copy()]
+    for b in range(0, logN, 3):
+        pats.append(np.where((x >> np.uint64(b)) & np.uint64(1), qa - np.uint64(1), np.uint64(0)).astype(np.uint64))
+    spike = np.zeros((len(q), N), dtype=np.uint64)
+    spike[:, 0] = (qa - np.uint64(1))[:, 0]
+    spike[:, N - 1] = 1
+    pats.append(spike)
+    data = np.stack(pats)
+    n = len(pats)
+    for inverse in (False, True):
+        d = as_u64_tensor(data, ctx.device)
+        (ctx.FromNTTInplace if inverse else ctx.ToNTTInplace)(d, 0, 0, n, len(q), len(q))
+        exp = data.copy()
+        oracle.ntt_batch(exp, T, 0, 0, n, len(q), len(q), inverse=inverse)
+        assert np.array_equal(to_u64_numpy(d), exp), inverse
+    ctx.close()
