@@ -8,8 +8,11 @@ A step is one pass of the named kernel family over one batch of seeded synthetic
 resident in HBM.  Default workload: the BERT-base-shaped PCMM (768x768 weights ~N(0,0.02)
 at scale 2^40, 768 feature ciphertexts, N=2^16, N1=128, rank 512, 20 limbs of 50-bit
 primes, ciphertext words uniform in [0,q_i)).  With N>1 ranks (torchrun) every rank
-multiplies its own block of 128 tokens: no data-path collective, weak scaling.
-Prints one JSON line (rank 0).
+multiplies its own block of 128 tokens: no data-path collective, weak scaling.  After
+that headline the default run also does, at every N, the LLaMA-7B-shaped multiply
+(4096x4096, 24 limbs) as ONE job split by column range over the N ranks, with the two
+ways of bringing the output together (config.llama_job), and the batched NTT on every
+rank (config.ntt_ranks).  Prints one JSON line (rank 0).
 """
 import argparse
 import json
@@ -26,14 +29,23 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 
 PCMM_CFG = dict(logN=16, N1=128, rank=512, M=768, K=768, limbs=20, q_bits=50, w_std=0.02, scaler=float(1 << 40))
+PCMM_WORKLOAD = ("bert-base PCMM 768x768 (W~N(0,0.02) at 2^40), 768 ciphertexts x 20 limbs x 65664 words, "
+                 "N=2^16, N1=128, rank 512, 50-bit limbs")
 NTT_CFG = dict(logN=16, limbs=40, q_bits=50, polys=32)
 MODUP_CFG = dict(logN=16, q_num=24, q_bits=50, t_num=12, t_bits=60, alpha=8, batch=32)
 SW, SC = 5, 7          # byte planes the PCMM workload needs: 40-bit signed weights, 50-bit residues
 # DRAM traffic (bytes) from ncu captures of the --small cases, per unit of work
 PCMM_TRAFFIC_PER_LIMB = (709.12e6 + 766.83e6) / 2                    # pcmm_umma_kernel<5,7,false>, 768x768, per limb
-NTT_TRAFFIC_PER_XFORM = {"forward": (167.90e6 + 113.26e6 + 196.91e6 + 112.88e6) / 320,
-                         "inverse": (202.12e6 + 113.41e6 + 167.91e6 + 108.10e6) / 320}
+NTT_TRAFFIC_PER_XFORM = {"forward": (167.93e6 + 110.85e6 + 188.73e6 + 108.05e6) / 320,
+                         "inverse": (188.73e6 + 108.17e6 + 167.94e6 + 108.42e6) / 320}
 MODUP_TRAFFIC_PER_POLY = (100.74e6 + 96.33e6) / 8
+# FP64 instructions per 16 values of a whole transform of 16 stages on the FP64 back end (8 per forward butterfly:
+# six for the exact product, an add and a subtract; a three-operation range reduction on five of the stages; one
+# conversion in, one out; the inverse reduces its sums on ten of fifteen stages and pays two products per
+# butterfly in the last one), and the rate one SM sub-partition issues them at (measured with eight independent
+# fma chains per warp: 0.46 warp instructions per clock, 59 lanes per clock per SM).
+NTT_FP64_PER_16 = {"forward": 1176, "inverse": 1344}
+FP64_WARP_INSTR_PER_CLK_PER_SMSP = 0.46
 
 
 def measured_peaks():
@@ -139,6 +151,20 @@ def cpu_pcmm_sample(q, X, W, Cw, rows=128, cols=16384):
             res[:rows])
 
 
+def ccmm_side(path):
+    """python/ccmm.py of the reference, run as it is and timed by wall clock.  It simulates a rotation-based
+    ciphertext-ciphertext matrix multiply on plaintext integers (python/ccmm.py:144-336): a different algorithm from the
+    PCMM benched here, reported as a labelled side number only.  The file is not part of this repository; without a path
+    to it the entry says so."""
+    label = "plaintext CCMM simulation, not PCMM"
+    if not path or not os.path.exists(path):
+        return {"label": label, "unavailable": "python/ccmm.py of the reference is not on this box (pass --ccmm PATH where it is)"}
+    t0 = time.perf_counter()
+    r = subprocess.run([sys.executable, path], capture_output=True, text=True, cwd=os.path.dirname(path) or ".")
+    return {"label": label, "seconds": time.perf_counter() - t0, "exit": r.returncode, "cores": 1,
+            "what": "python ccmm.py as shipped (NumPy, one process)"}
+
+
 def run_reference(args):
     """The reference has no CPU implementation of this path and its CUDA build needs NTL;
     the CPU restatement (oracle/) is timed instead, on all host threads, on a bounded
@@ -167,7 +193,7 @@ def run_reference(args):
         value = rows * (cols / Cw) / dt
         metric, unit = "pcmm_ct_rows_per_sec", "ct-rows/s"
         sample = f"{rows} rows x {cols} of {Cw} columns x {c['limbs']} limbs, K={c['K']} per step"
-        workload = "bert-base 768x768 PCMM, N=2^16, N1=128, 20x50-bit limbs"
+        workload = PCMM_WORKLOAD
     else:
         n = NTT_CFG
         N = 1 << n["logN"]
@@ -224,9 +250,16 @@ def bench_ntt(torch, device, steps, warmup, peaks):
         torch.cuda.synchronize(device)
         ms = e0.elapsed_time(e1) / steps
         gbs = xforms * 16 * N / (ms * 1e-3) / 1e9
+        # what the FP64 pipe alone allows at the maximum SM clock, as a fraction of the same HBM peak
+        sm_clk = 1.965e9
+        fp64_s = NTT_FP64_PER_16[name] / 16.0 * N / 32.0 * xforms / (FP64_WARP_INSTR_PER_CLK_PER_SMSP * 4 * 148 * sm_clk)
         res[name] = {"limb_xforms_per_sec": xforms / (ms * 1e-3), "ms_per_step": ms,
                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                   "frac": gbs / peaks["hbm_gbs"],
+                                  "attainable_frac": min(0.5, xforms * 16 * N / fp64_s / 1e9 / peaks["hbm_gbs"]),
+                                  "attainable_note": "the lower of 0.5 (two kernels: the data crosses HBM twice) and what the FP64 "
+                                                     "pipe allows at %d FP64 instructions per 16 values and 0.46 warp instructions "
+                                                     "per clock per scheduler at 1965 MHz (%.3f ms)" % (NTT_FP64_PER_16[name], fp64_s * 1e3),
                                   "traffic": NTT_TRAFFIC_PER_XFORM[name] * xforms,
                                   "traffic_note": "dram read+write of the two kernels in the ncu capture of 320 limb-transforms, scaled by units",
                                   "note": "two kernels per transform; achieved = 16*N bytes per limb-xform / time"}}
@@ -484,6 +517,126 @@ def bench_pcmm_shape(torch, device, steps, warmup, peaks, name, rank=0, world=1,
     return res
 
 
+
+LLAMA_JOB = dict(N1=2048, rank=32, M=4096, K=4096, limbs=24, split_one_gpu=8,
+                 what="LLaMA-7B PCMM 4096x4096 (W~N(0,0.02) at 2^40), 4096 ciphertexts x 24 limbs x 67584 words, N=2^16, N1=2048, rank 32")
+
+
+def bench_llama_job(torch, device, rank, world, dist, steps, small=False):
+    """BASELINE configs[4] as one job: every rank holds the ciphertexts and multiplies its column range of all 4096 rows
+    (all 24 limbs of a column stay on one GPU, so the fused rescale needs no exchange).  Timed: the whole job on one GPU
+    (its columns in eight chunks), the sharded multiply alone, the multiply followed by an NCCL all-gather of the output
+    (every rank ends with everything), and the multiply whose epilogue stores each output row straight into the buffer of
+    the row's owner (every rank ends with all columns of its 1/N of the rows, the unit the packing step consumes).  The
+    two ways of bringing the output together are compared word for word on every rank's own rows."""
+    from ckks_llm_b200 import capi, params, shard as sharding
+    from ckks_llm_b200.host import MLWECiphertext, PCMM_Context, PCMM_Scheme
+    c = dict(LLAMA_JOB)
+    if small:
+        c.update(M=512, K=512, limbs=4)
+    N = 1 << 16
+    q = params.ntt_primes(50, 2 * N, c["limbs"])
+    Cw = (c["rank"] + 1) * c["N1"]
+    M, K, limbs = c["M"], c["K"], c["limbs"]
+    torch.cuda.empty_cache()
+    # ciphertexts + output + byte planes of one column chunk; every rank must have the room or all skip together
+    need = 8 * limbs * Cw * (K + M) + limbs * (Cw // c["split_one_gpu"] + 64) * ((K + 63) // 64 * 64) * 8 + (1 << 30)
+    roomy = torch.tensor([1 if torch.cuda.mem_get_info(device)[0] > need else 0], device=device)
+    if world > 1:
+        dist.all_reduce(roomy, op=dist.ReduceOp.MIN)
+    if not bool(roomy.item()):
+        return {"skipped": "a rank has less than %.0f GB of free device memory" % (need / 1e9)}
+    g = torch.Generator(device=device).manual_seed(6)             # the same ciphertexts on every rank
+    X = torch.empty((K, limbs, Cw), dtype=torch.int64, device=device)
+    for i, qi in enumerate(q):
+        X[:, i, :] = torch.randint(0, qi, (K, Cw), generator=g, device=device, dtype=torch.int64)
+    W = torch.randn((M, K), generator=g, device=device, dtype=torch.float32) * 0.02
+    pc = PCMM_Context(c["N1"], c["rank"], [], q, device=device.index)
+    sch = PCMM_Scheme(pc, algo=capi.PCMM_TENSOR)
+    sch.ppmm_output = torch.empty(M * limbs * Cw, dtype=torch.int64, device=device)
+    out_full = sch.ppmm_output.view(M, limbs, Cw)
+    cts = [MLWECiphertext(c["N1"], limbs - 1, limbs - 1, c["rank"], 1.0, cipher=X[n].reshape(-1)) for n in range(K)]
+    scaler = float(1 << 40)
+    sch.prepare_weights(W, M, K, scaler)                           # the weights of a layer are prepared once
+
+    def multiply(c0, c1):
+        sch.PPMM(None, cts, M, K, c["N1"], K, scaler=scaler, col_begin=c0, col_end=c1, copy_back=False)
+
+    def timed(fn, n):
+        fn()
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms = e0.elapsed_time(e1) / n
+        if world > 1:
+            tt = torch.tensor([ms], device=device)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        return ms
+
+    n = max(1, min(steps, 3))
+    one_ranges = sharding.column_ranges(Cw, c["split_one_gpu"])
+    one_gpu_ms = timed(lambda: [multiply(a, b) for a, b in one_ranges], 1 if world > 1 else n)
+    res = {"job": c["what"] if not small else "column-sharded PCMM 512x512, 4 limbs (small case)", "ranks": world,
+           "one_gpu_ms": one_gpu_ms, "one_gpu_ct_rows_per_sec": M / (one_gpu_ms * 1e-3),
+           "one_gpu_note": "all columns on one GPU in eight chunks (on N > 1 ranks every rank runs it at the same time; the slowest counts)"}
+    int8_ops = 2.0 * SW * SC * M * K * Cw * limbs
+    res["one_gpu_frac_of_int8_peak"] = int8_ops / (one_gpu_ms * 1e-3) / 1e12 / (2.0 * measured_peaks()["bf16_tflops"])
+    sch.check()
+    if world > 1:
+        ranges = sharding.column_ranges(Cw, world)
+        c0, c1 = ranges[rank]
+        res["multiply_ms"] = timed(lambda: multiply(c0, c1), n)
+        # (1) multiply, then NCCL all-gather of the column ranges: every rank ends with the whole output
+        def mult_gather():
+            multiply(c0, c1)
+            sharding.gather_output(out_full, ranges, rows_per_step=256)
+        res["with_gather_ms"] = timed(mult_gather, 1)
+        r0, r1 = pc.row_owner_range(M, world, rank)
+
+        def checksums():
+            mine = out_full[r0:r1].reshape(-1)
+            return [int(mine.sum().item()), int(mine[::4099].sum().item()), int(mine[::65537].sum().item())]
+        want = checksums()
+        # (2) the epilogue stores every row into its owner's buffer only (plain peer stores over NVLink)
+        peers, bases = sharding.open_peer_buffers(sch.ppmm_output)
+        out_full[r0:r1].zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        pc.set_row_owners([peers.get(r, 0) for r in range(world)], rank)
+        res["with_row_scatter_ms"] = timed(lambda: multiply(c0, c1), n)
+        sch.check()
+        dist.barrier()
+        got = checksums()
+        ok = torch.tensor([1 if got == want else 0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        res["outputs_match"] = bool(ok.item())
+        pc.set_row_owners([], 0)
+        dist.barrier()
+        sharding.close_peer_buffers(device.index, bases)
+        res["speedup_vs_one_gpu"] = one_gpu_ms / res["with_row_scatter_ms"]
+        res["speedup_multiply_only"] = one_gpu_ms / res["multiply_ms"]
+        res["speedup_with_gather"] = one_gpu_ms / res["with_gather_ms"]
+        res["ct_rows_per_sec"] = M / (res["with_row_scatter_ms"] * 1e-3)
+        res["bytes_sent_per_rank"] = {"row_scatter": int((M - (r1 - r0)) * limbs * (c1 - c0) * 8),
+                                      "all_gather_received": int(M * limbs * (Cw - (c1 - c0)) * 8)}
+        res["note"] = ("speedup_vs_one_gpu counts the multiply with the row scatter fused into it: afterwards every rank holds "
+                       "all columns of its rows; with_gather_ms is the multiply plus NCCL's all-gather (every rank holds everything)")
+    else:
+        res["multiply_ms"] = one_gpu_ms
+        res["speedup_vs_one_gpu"] = 1.0
+    pc.close()
+    del cts, X, out_full
+    sch.ppmm_output = None
+    torch.cuda.empty_cache()
+    return res
+
 def bench_pcmm_from_rlwe(torch, device, steps, warmup, sch, pc, cts, W, q, ppmm_ms):
     """The pipeline's pair of calls (Bert.cuh:249-254: rlweCipherDecompose of two ciphertexts into 512 + 256 MLWE
     ciphertexts, then PPMM) at the headline shape, as two steps and as the one call whose slicing pre-pass reads the
@@ -670,8 +823,9 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--ccmm", default=None, help="path of the reference's python/ccmm.py, timed as a labelled side number")
     ap.add_argument("--host-chunks", type=int, default=0, help="column chunks of the host-buffer call (0 = the library's choice)")
-    ap.add_argument("--no-side", action="store_true", help="skip the NTT / ModUp side measurements")
+    ap.add_argument("--no-side", action="store_true", help="skip the side measurements (NTT, ModUp, ..., the sharded LLaMA-shaped job)")
     ap.add_argument("--only-rlwe-side", action="store_true",
                     help="of the side measurements run only the decompose-and-multiply comparison (profiling)")
     ap.add_argument("--small", action="store_true",
@@ -768,18 +922,19 @@ def main():
         if rank == 0 and world == 1 and not args.no_side:
             extra["pcmm_from_rlwe"] = bench_pcmm_from_rlwe(torch, device, args.steps, args.warmup, sch, pc, cts, W, q, ms)
         metric, unit = "pcmm_ct_rows_per_sec", "ct-rows/s"
-        workload = ("bert-base PCMM 768x768 (W~N(0,0.02) at 2^40), 768 ciphertexts x 20 limbs x 65664 words, "
-                    "N=2^16, N1=128, rank 512, 50-bit limbs")
+        workload = PCMM_WORKLOAD
         cfg = {"workload": workload, "tokens_per_gpu": c["N1"], "sharding": "one 128-token block per GPU, no collective",
                "l2_policy": "inputs (8.07 GB ciphertext + 8.07 GB output) larger than L2"}
 
         e2e, cpu = None, None
         do_e2e = not args.no_e2e
+        out_bytes = c["M"] * c["limbs"] * Cw * 8
         if do_e2e:
-            # every rank needs 16 GB of pinned host memory; skip (and say so) if the host cannot give it
+            # every rank needs pinned host memory for its result (and, on one GPU, for the MLWE form of the inputs too);
+            # skip (and say so) if the host cannot give it
             try:
                 import psutil
-                need = (X.numel() * 8 + c["M"] * c["limbs"] * Cw * 8) * world * 1.25
+                need = (out_bytes + (X.numel() * 8 if world == 1 else 0)) * world * 1.25
                 if psutil.virtual_memory().available < need:
                     do_e2e = False
             except ImportError:
@@ -789,52 +944,96 @@ def main():
                 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
                 do_e2e = bool(flag.item())
         if do_e2e:
-            # same call through the C ABI with HOST buffers: H2D of W and X and D2H of the result per step
-            Xh = torch.empty(X.shape, dtype=torch.int64).pin_memory()
-            Xh.copy_(X)
+            L = capi.load()
+            n_e2e = max(1, min(args.steps, 3))
             Wh = W.cpu().pin_memory()
             outh = torch.empty((c["M"], c["limbs"], Cw), dtype=torch.int64).pin_memory()
-            del cts, X
-            sch.ppmm_output = None
-            torch.cuda.empty_cache()
-            L = capi.load()
             if args.host_chunks:
                 pc.set_host_chunks(args.host_chunks)
 
-            def host_step():
-                capi.check(L.ckks_b200_pcmm_ppmm_host(pc._h, Wh.data_ptr(), Xh.data_ptr(), outh.data_ptr(), c["M"], c["K"],
-                                                      c["N1"], c["K"], c["scaler"], capi.PCMM_TENSOR))
-            host_step()
-            n_e2e = max(1, min(args.steps, 3))
-            barrier()
-            t0 = time.perf_counter()
-            for _ in range(n_e2e):
-                host_step()
-            barrier()
-            dt = (time.perf_counter() - t0) / n_e2e
-            if world > 1:
-                tt = torch.tensor([dt], device=device, dtype=torch.float64)
-                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-                dt = float(tt.item())
-            e2e = {"value": world * c["M"] / dt, "unit": unit, "h2d_bytes_per_step": int(Xh.numel() * 8 + Wh.numel() * 4),
+            def timed_host(fn):
+                fn()
+                barrier()
+                t0 = time.perf_counter()
+                for _ in range(n_e2e):
+                    fn()
+                barrier()
+                dt = (time.perf_counter() - t0) / n_e2e
+                if world > 1:
+                    tt = torch.tensor([dt], device=device, dtype=torch.float64)
+                    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                    dt = float(tt.item())
+                return dt
+
+            e2e_mlwe = None
+            if world == 1:
+                # (a) the multiply's own entry point with HOST buffers: the 768 MLWE ciphertexts (8.07 GB) go in
+                Xh = torch.empty(X.shape, dtype=torch.int64).pin_memory()
+                Xh.copy_(X)
+                del cts, X
+                sch.ppmm_output = None
+                torch.cuda.empty_cache()
+                dt = timed_host(lambda: capi.check(L.ckks_b200_pcmm_ppmm_host(
+                    pc._h, Wh.data_ptr(), Xh.data_ptr(), outh.data_ptr(), c["M"], c["K"], c["N1"], c["K"], c["scaler"], capi.PCMM_TENSOR)))
+                e2e_mlwe = {"value": c["M"] / dt, "unit": unit, "h2d_bytes_per_step": int(Xh.numel() * 8 + Wh.numel() * 4),
+                            "d2h_bytes_per_step": int(outh.numel() * 8), "ms_per_step": dt * 1e3, "steps": n_e2e,
+                            "call": "ckks_b200_pcmm_ppmm_host (MLWE ciphertexts in pinned host buffers)"}
+                if rank == 0 and not args.no_cpu:
+                    rows_s, cols_s = 128, 16384
+                    Xd = Xh[:, :, :cols_s].contiguous()
+                    v, dt_cpu, cores, sample, ref_words = cpu_pcmm_sample(q, Xd, Wh, Cw, rows_s, cols_s)
+                    cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample, "seconds": dt_cpu,
+                           "ccmm_side": ccmm_side(args.ccmm)}
+                    # the same sample doubles as the parity check of the benched configuration at its full limb count:
+                    # the words the timed host-buffer call just produced against the CPU restatement, every one of them
+                    gpu_words = outh[:rows_s, :, :cols_s].numpy().view(np.uint64)
+                    equal = bool(np.array_equal(gpu_words, ref_words))
+                    cfg["parity"] = {"rows": rows_s, "cols": cols_s, "limbs": c["limbs"], "equal": equal,
+                                     "against": "CPU restatement of the reference kernel (oracle/), same inputs"}
+                    if not equal:
+                        bad = int((gpu_words != ref_words).sum())
+                        raise SystemExit(f"parity failure: {bad} of {ref_words.size} words of the benched multiply differ from the oracle")
+                del Xh
+            else:
+                del cts, X
+                sch.ppmm_output = None
+                torch.cuda.empty_cache()
+            # (b) the reference's pair of calls, rlweCipherDecompose x2 + PPMM (Bert.cuh:249-254), as one call with HOST
+            # buffers: the two RLWE ciphertexts (42 MB) go in, the same 768 x 20-limb product comes out.  This is the
+            # end-to-end figure: what a caller of the pipeline step pays.
+            N_, L_ = 1 << c["logN"], c["limbs"] - 1
+            gsrc = torch.Generator().manual_seed(1000 + rank)
+            srcs = []
+            for _ in range(2):
+                rl = torch.empty((2, L_ + 1, N_), dtype=torch.int64)
+                for i, qi in enumerate(q):
+                    rl[:, i, :] = torch.randint(0, qi, (2, N_), generator=gsrc, dtype=torch.int64)
+                srcs.append(rl.pin_memory())
+            arr = (capi.RlweSource * 2)()
+            for kx, (rl, num, off) in enumerate(((srcs[0], 512, 0), (srcs[1], 256, 512))):
+                arr[kx].d_rlwe, arr[kx].L, arr[kx].mlwe_num, arr[kx].offset = rl.data_ptr(), L_, num, off
+            dt = timed_host(lambda: capi.check(L.ckks_b200_pcmm_ppmm_rlwe_host(
+                pc._h, Wh.data_ptr(), arr, 2, outh.data_ptr(), c["M"], c["K"], c["N1"], c["K"], c["scaler"])))
+            e2e = {"value": world * c["M"] / dt, "unit": unit,
+                   "h2d_bytes_per_step": int(sum(r.numel() for r in srcs) * 8 + Wh.numel() * 4),
                    "d2h_bytes_per_step": int(outh.numel() * 8), "ms_per_step": dt * 1e3, "steps": n_e2e,
-                   "call": "ckks_b200_pcmm_ppmm_host (pinned host buffers, per rank)",
-                   "cpus_bound_per_rank": numa}
-            if rank == 0 and world == 1 and not args.no_cpu:
-                rows_s, cols_s = 128, 16384
-                Xd = Xh[:, :, :cols_s].contiguous()
-                v, dt_cpu, cores, sample, ref_words = cpu_pcmm_sample(q, Xd, Wh, Cw, rows_s, cols_s)
-                cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample, "seconds": dt_cpu}
-                # the same sample doubles as the parity check of the benched configuration at its full limb count:
-                # the words the timed host-buffer call just produced against the CPU restatement, every one of them
-                gpu_words = outh[:rows_s, :, :cols_s].numpy().view(np.uint64)
-                equal = bool(np.array_equal(gpu_words, ref_words))
-                cfg["parity"] = {"rows": rows_s, "cols": cols_s, "limbs": c["limbs"], "equal": equal,
-                                 "against": "CPU restatement of the reference kernel (oracle/), same inputs"}
-                if not equal:
-                    bad = int((gpu_words != ref_words).sum())
-                    raise SystemExit(f"parity failure: {bad} of {ref_words.size} words of the benched multiply differ from the oracle")
+                   "call": "ckks_b200_pcmm_ppmm_rlwe_host (RLWE ciphertexts and weights in, product out, pinned host buffers, per rank)",
+                   "cpus_bound_per_rank": numa, "mlwe_inputs": e2e_mlwe}
+            # its words against the device-side call on the same sources (which the tests pin to the oracle)
+            dsrc = [r.to(device) for r in srcs]
+            for kx in range(2):
+                arr[kx].d_rlwe = dsrc[kx].data_ptr()
+            out_dev = torch.empty(c["M"] * c["limbs"] * Cw, dtype=torch.int64, device=device)
+            capi.check(L.ckks_b200_pcmm_ppmm_rlwe(pc._h, W.data_ptr(), arr, 2, out_dev.data_ptr(), c["M"], c["K"], c["N1"], c["K"],
+                                                  c["scaler"], 0, Cw, None))
+            sch.check()
+            same = bool(torch.equal(out_dev.view(c["M"], c["limbs"], Cw), outh.to(device)))
+            e2e["equals_device_call"] = same
+            if not same:
+                raise SystemExit("the host-buffer decompose-and-multiply call and the device call differ")
+            del out_dev, dsrc, outh
         pc.close()
+        torch.cuda.empty_cache()
         if rank == 0 and world == 1 and not args.no_side and not args.only_rlwe_side:
             try:
                 extra["ntt"] = bench_ntt(torch, device, max(args.steps, 10), args.warmup, peaks)
@@ -842,8 +1041,33 @@ def main():
                 extra["levels"] = bench_levels(torch, device, max(args.steps, 10), args.warmup, peaks)
                 extra["keyswitch"] = bench_keyswitch(torch, device, max(args.steps, 10), args.warmup, peaks)
                 extra["ringpack"] = bench_ringpack(torch, device, max(args.steps, 10), args.warmup, peaks)
+                # the second metric and the ModUp figure inside the roofline object as well
+                for key, src_ in (("ntt_fwd", extra["ntt"]["forward"]), ("ntt_inv", extra["ntt"]["inverse"])):
+                    roof[key] = {"value": src_["limb_xforms_per_sec"], "unit": "limb-xforms/s", "ms": src_["ms_per_step"],
+                                 "frac": src_["roofline"]["frac"], "attainable_frac": src_["roofline"]["attainable_frac"], "bound": "hbm"}
+                roof["modup"] = {"value": extra["modup"]["polys_per_sec"], "unit": "polys/s", "ms": extra["modup"]["ms_per_step"],
+                                 "frac": extra["modup"]["roofline"]["frac"], "bound": "hbm"}
             except Exception as ex:           # the headline stays valid without the side measurements
                 extra["side_error"] = repr(ex)
+        if not args.no_side and not args.only_rlwe_side:
+            if world > 1:
+                # the second metric at N ranks: every rank transforms its own 32 polynomials x 40 limbs (no exchange)
+                r = bench_ntt(torch, device, max(args.steps, 10), args.warmup, peaks)
+                nt = {}
+                for name in ("forward", "inverse"):
+                    tt = torch.tensor([r[name]["ms_per_step"]], device=device)
+                    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                    ms_n = float(tt.item())
+                    xf = NTT_CFG["polys"] * NTT_CFG["limbs"]
+                    nt[name] = {"limb_xforms_per_sec": world * xf / (ms_n * 1e-3), "ms_per_step": ms_n,
+                                "frac_per_gpu": xf * 16 * (1 << NTT_CFG["logN"]) / (ms_n * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+                nt["sharding"] = "each rank its own polynomials, no collective (weak scaling)"
+                cfg["ntt_ranks"] = nt
+                roof["ntt_fwd"] = {"value": nt["forward"]["limb_xforms_per_sec"], "unit": "limb-xforms/s, all ranks", "ms": nt["forward"]["ms_per_step"],
+                                   "frac": nt["forward"]["frac_per_gpu"], "bound": "hbm"}
+                roof["ntt_inv"] = {"value": nt["inverse"]["limb_xforms_per_sec"], "unit": "limb-xforms/s, all ranks", "ms": nt["inverse"]["ms_per_step"],
+                                   "frac": nt["inverse"]["frac_per_gpu"], "bound": "hbm"}
+            cfg["llama_job"] = bench_llama_job(torch, device, rank, world, dist if world > 1 else None, args.steps, small=args.small)
     else:
         sampler = ClockSampler(local_rank)
         barrier()
