@@ -36,6 +36,45 @@ def unit_ranges(count, world):
     return out
 
 
+def row_owner_ranges(rows, world):
+    """Rows [begin, end) of every rank when the output rows of a column-sharded PCMM are dealt to owners: equal
+    contiguous runs of ceil(rows / world) rounded up to a multiple of 32, the rule of ckks_b200_pcmm_set_row_owners."""
+    per = ((rows + world - 1) // world + 31) // 32 * 32
+    return [(min(per * r, rows), min(per * (r + 1), rows)) for r in range(world)]
+
+
+def scatter_rows_to_owners(out_full, col_ranges, group=None):
+    """The exchange the PCMM's row-owner epilogue performs with peer stores, as point-to-point messages: for
+    transports without peer memory (and for tests on CPU ranks).  out_full: [M][limbs][C] on every rank with this
+    rank's columns valid for ALL rows; on return this rank holds all columns of ITS rows (other rows are
+    unchanged).  Every rank sends (world-1)/world of its part and receives as much."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    rows = row_owner_ranges(out_full.shape[0], world)
+    c0, c1 = col_ranges[rank]
+    r0, r1 = rows[rank]
+    sends, recvs, ops = [], [], []
+    for peer in range(world):
+        if peer == rank:
+            continue
+        p0, p1 = rows[peer]
+        a, b = col_ranges[peer]
+        if p1 > p0 and c1 > c0:
+            buf = out_full[p0:p1, :, c0:c1].contiguous()
+            sends.append(buf)
+            ops.append(dist.P2POp(dist.isend, buf, peer, group))
+        if r1 > r0 and b > a:
+            buf = torch.empty((r1 - r0, out_full.shape[1], b - a), dtype=out_full.dtype, device=out_full.device)
+            recvs.append((a, b, buf))
+            ops.append(dist.P2POp(dist.irecv, buf, peer, group))
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    for a, b, buf in recvs:
+        out_full[r0:r1, :, a:b] = buf
+    return rows[rank]
+
+
 def gather_output(out_full, ranges, group=None, rows_per_step=None):
     """All-gather the column ranges of a PCMM output.
 

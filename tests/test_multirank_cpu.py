@@ -25,6 +25,15 @@ def test_column_ranges_cover_and_align():
     assert shard.unit_ranges(20, 8) == [(0, 3), (3, 6), (6, 9), (9, 12), (12, 14), (14, 16), (16, 18), (18, 20)]
 
 
+def test_row_owner_ranges_follow_the_library_rule():
+    """Equal runs of ceil(M / world) rounded up to 32 rows (the rule of ckks_b200_pcmm_row_owner_range, which the GPU test
+    of the row-owner epilogue checks against the library)."""
+    assert shard.row_owner_ranges(4096, 8) == [(512 * r, 512 * (r + 1)) for r in range(8)]
+    assert shard.row_owner_ranges(150, 3) == [(0, 64), (64, 128), (128, 150)]
+    assert shard.row_owner_ranges(40, 2) == [(0, 32), (32, 40)]
+    assert shard.row_owner_ranges(20, 4) == [(0, 20), (20, 20), (20, 20), (20, 20)]
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -39,7 +48,7 @@ def _worker(rank, world, port, ret):
     from oracle import oracle as O
     q = params.ntt_primes(50, 1 << 13, 3)
     rng = np.random.default_rng(0)                 # same inputs on both ranks
-    M, K, N1, k = 8, 16, 32, 2                     # width 96: three tiles over two ranks (ragged)
+    M, K, N1, k = 40, 16, 32, 2                    # width 96: three tiles over two ranks (ragged); rows 0..31 and 32..39
     Cw = (k + 1) * N1
     W = rng.uniform(-1, 1, (M, K)).astype(np.float32)
     X = np.stack([H.uniform_residues(rng, q, (Cw,)) for _ in range(K)])
@@ -48,9 +57,16 @@ def _worker(rank, world, port, ret):
     out = torch.zeros((M, len(q), Cw), dtype=torch.int64)
     part = O.ppmm(W, np.ascontiguousarray(X[:, :, c0:c1]), q, float(1 << 40))
     out[:, :, c0:c1] = torch.from_numpy(part.view(np.int64))
-    shard.gather_output(out, ranges)
     full = O.ppmm(W, X, q, float(1 << 40))
-    ret[rank] = bool(np.array_equal(out.numpy().view(np.uint64), full))
+    # rows to their owners: this rank ends with all columns of its rows and nothing new elsewhere
+    own = out.clone()
+    r0, r1 = shard.scatter_rows_to_owners(own, ranges)
+    ok_rows = bool(np.array_equal(own[r0:r1].numpy().view(np.uint64), full[r0:r1]))
+    mask = torch.ones_like(own, dtype=torch.bool)
+    mask[r0:r1] = False
+    ok_rest = bool(torch.equal(own[mask], out[mask]))
+    shard.gather_output(out, ranges)
+    ret[rank] = bool(np.array_equal(out.numpy().view(np.uint64), full)) and ok_rows and ok_rest
     dist.destroy_process_group()
 
 
