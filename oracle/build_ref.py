@@ -10,7 +10,8 @@ import os
 import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("CKKS_REFERENCE_ROOT", "/root/reference")
+# the reference tree: named by CKKS_REFERENCE_ROOT, else a directory `reference` beside this repository
+REF_ROOT = os.environ.get("CKKS_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 REF_INC = os.path.join(REF_ROOT, "src", "ckks", "include")
 OUT_DIR = os.path.join(HERE, "_ref")
 LIB = os.path.join(OUT_DIR, "libref_driver.so")
