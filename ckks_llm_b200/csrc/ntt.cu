@@ -532,11 +532,10 @@ __device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles
     for (int t = 0; t < tiles; t++) {
         u64* s = S + (t & 1) * kTile;
         u64* gt = g + (size_t)t * C::CW;
-        __syncthreads();                                          // everybody is done with the other buffer
-        if (t + 1 < tiles) prefetch_tile<SA>(S + ((t + 1) & 1) * kTile, gt + C::CW, tid);
+        __pipeline_wait_prior(0);                                 // this thread's copies of tile t have landed
+        __syncthreads();                                          // ... and everybody's; everybody is also done with tile t-1,
+        if (t + 1 < tiles) prefetch_tile<SA>(S + ((t + 1) & 1) * kTile, gt + C::CW, tid);   // whose buffer takes tile t+1
         __pipeline_commit();
-        __pipeline_wait_prior(1);
-        __syncthreads();
         if (!INV) {
             // window 0: v[j] at idx j*256 + tid; one twiddle set for the whole grid
 #pragma unroll

@@ -343,6 +343,17 @@ class PCMM_Context:
             pass
 
 
+def ppmm_scaler(q_ringpack, scale, target_scale=float(1 << 49)):
+    """scaler = (long)(q_last * target / scale): PPMM_kernel.cuh:283-284 writes q_ringpack[1], the last of the reference's
+    two moduli and the one its kernel rescales by; with more limbs that is the last one."""
+    return float(int(q_ringpack[-1] * target_scale / scale))
+
+
+def ppmm_scale_after(q_ringpack, scale, scaler):
+    """The scale PPMM leaves on its ciphertexts (PPMM_kernel.cuh:346)."""
+    return scale * scaler / q_ringpack[-1]
+
+
 class PCMM_Scheme:
     """PPMM of the reference's PCMM_Scheme (src/ckks/include/pcmm/PCMM_Scheme.h:12-48)."""
 
@@ -356,8 +367,7 @@ class PCMM_Scheme:
     def scaler_for(self, scale, target_scale=float(1 << 49)):
         """scaler = (long)(q_last * target / scale): PPMM_kernel.cuh:283-284 writes q_ringpack[1], the last of the
         reference's two moduli and the one its kernel rescales by; with more limbs that is the last one."""
-        q_last = self.pcmm_context.q_ringpack[-1]
-        return float(int(q_last * target_scale / scale))
+        return ppmm_scaler(self.pcmm_context.q_ringpack, scale, target_scale)
 
     def prepare_weights(self, plain_mat, mat_M, mat_N, scaler):
         """Scale and slice a weight matrix once (ckks_b200_pcmm_prepare_weights); PPMM / decomposeAndPPMM calls that pass
@@ -396,9 +406,8 @@ class PCMM_Scheme:
         if copy_back:
             capi.check(self.lib.ckks_b200_pcmm_copy_back(
                 pc._h, self.ppmm_output.data_ptr(), ptrs, min(mlwe_num, mat_M), 1, _stream_ptr(pc.device)))
-            q_last = pc.q_ringpack[-1]
             for c in mlwe_cipher_decomposed[:mlwe_num]:
-                c.scale = c.scale * scaler / q_last
+                c.scale = ppmm_scale_after(pc.q_ringpack, c.scale, scaler)
         return out
 
     def rlweCipherDecompose(self, rlwe_cipher, mlwe_cipher_decomposed, mlwe_num, offset, ntt_domain=True):
@@ -453,9 +462,8 @@ class PCMM_Scheme:
         if copy_back:
             ptrs = (C.c_void_p * max(mlwe_num, 1))(*[c.cipher_device.data_ptr() for c in mlwe_cipher_decomposed[:mlwe_num]])
             capi.check(self.lib.ckks_b200_pcmm_copy_back(pc._h, self.ppmm_output.data_ptr(), ptrs, min(mlwe_num, mat_M), 1, st_ptr))
-            q_last = pc.q_ringpack[-1]
             for c in mlwe_cipher_decomposed[:mlwe_num]:
-                c.scale = sources[0][0].scale * scaler / q_last
+                c.scale = ppmm_scale_after(pc.q_ringpack, sources[0][0].scale, scaler)
         return out
 
     def addRepakcingKey(self, keys_device):

@@ -207,6 +207,16 @@ public:
     ~PCMM_Context() { ckks_b200_pcmm_destroy(b200); }
 };
 
+// scaler = (long)(q_last * target / scale) and the scale PPMM leaves, scale * scaler / q_last
+// (PPMM_kernel.cuh:283-284,346 write q_ringpack[1], the last of the reference's two moduli and the one its kernel
+// rescales by; with more limbs that is the last one).
+inline long ppmm_scaler(const std::vector<uint64_tt>& q_ringpack, long double scale, long double target = (long double)(1LL << 49)) {
+    return (long)((long double)q_ringpack.back() * target / scale);
+}
+inline long double ppmm_scale_after(const std::vector<uint64_tt>& q_ringpack, long double scale, long scaler) {
+    return scale * scaler / (long double)q_ringpack.back();
+}
+
 class PCMM_Scheme {
 public:
     PCMM_Context& pcmm_context;
@@ -234,15 +244,13 @@ public:
             ptrs[i] = (const uint64_t*)mlwe_cipher_decomposed[i]->cipher_device;
             wptrs[i] = (uint64_t*)mlwe_cipher_decomposed[i]->cipher_device;
         }
-        // scaler = (long)(q_ringpack[1] * 2^49 / scale)   (PPMM_kernel.cuh:283-284)
-        const long double q_div = (long double)pcmm_context.q_ringpack[pcmm_context.ringpack_q_count > 1 ? 1 : 0];
-        const long scaler = (long)(q_div * (long double)(1LL << 49) / mlwe_cipher_decomposed[0]->scale);
+        const long scaler = ppmm_scaler(pcmm_context.q_ringpack, mlwe_cipher_decomposed[0]->scale);
         check(ckks_b200_pcmm_ppmm(pcmm_context.b200, plain_mat, ptrs.data(), (uint64_t*)ppmm_output, mat_M, mat_N, mat_K,
                                   mlwe_num, (double)scaler, 0, C, algo, stream));
         const int rows_back = mlwe_num < mat_M ? mlwe_num : mat_M;
         check(ckks_b200_pcmm_copy_back(pcmm_context.b200, (const uint64_t*)ppmm_output, wptrs.data(), rows_back, 1, stream));
         for (int i = 0; i < mlwe_num; i++)
-            mlwe_cipher_decomposed[i]->scale = mlwe_cipher_decomposed[i]->scale * scaler / q_div;
+            mlwe_cipher_decomposed[i]->scale = ppmm_scale_after(pcmm_context.q_ringpack, mlwe_cipher_decomposed[i]->scale, scaler);
     }
 
     // rlweCipherDecompose of every source (PCMM_Scheme.cuh:90-125) feeding PPMM, as the one call that never
@@ -261,15 +269,14 @@ public:
                 throw std::runtime_error("cudaMalloc failed");
             ppmm_output_rows = mat_M;
         }
-        const long double q_div = (long double)pcmm_context.q_ringpack[pcmm_context.ringpack_q_count > 1 ? 1 : 0];
-        const long scaler = (long)(q_div * (long double)(1LL << 49) / scale);
+        const long scaler = ppmm_scaler(pcmm_context.q_ringpack, scale);
         check(ckks_b200_pcmm_ppmm_rlwe(pcmm_context.b200, plain_mat, sources.data(), (int)sources.size(),
                                        (uint64_t*)ppmm_output, mat_M, mat_N, mat_K, mlwe_num, (double)scaler, 0, C, stream));
         std::vector<uint64_t*> wptrs(mlwe_num);
         for (int i = 0; i < mlwe_num; i++) wptrs[i] = (uint64_t*)mlwe_cipher_decomposed[i]->cipher_device;
         const int rows_back = mlwe_num < mat_M ? mlwe_num : mat_M;
         check(ckks_b200_pcmm_copy_back(pcmm_context.b200, (const uint64_t*)ppmm_output, wptrs.data(), rows_back, 1, stream));
-        for (int i = 0; i < mlwe_num; i++) mlwe_cipher_decomposed[i]->scale = scale * scaler / q_div;
+        for (int i = 0; i < mlwe_num; i++) mlwe_cipher_decomposed[i]->scale = ppmm_scale_after(pcmm_context.q_ringpack, scale, scaler);
     }
 };
 

@@ -64,3 +64,35 @@ def test_compat_driver_matches_oracle(oracle, cuda_device, tmp_path):
     assert np.array_equal(out, ref)
     assert np.array_equal(ct5, ref[5, 0])
     assert abs(ratio - 1.0) < 1e-12          # scale * scaler / q1 with scaler == q1
+
+
+def test_mirrors_agree_on_the_scale_bookkeeping(tmp_path):
+    """The C++ shim, the source-level compat classes and the Python mirror derive the PPMM scaler and the scale it leaves
+    from the LAST ring-pack modulus (the one the kernel rescales by): identical at the reference's two moduli, and equal
+    to one another at three."""
+    from ckks_llm_b200 import host
+    src = tmp_path / "scale.cu"
+    src.write_text(r"""
+#include <cstdio>
+#include "ckks_b200/compat.hpp"
+int main() {
+    std::vector<ckks_b200::uint64_tt> q = {%dULL, %dULL, %dULL};
+    for (int n = 2; n <= 3; n++) {
+        std::vector<ckks_b200::uint64_tt> qq(q.begin(), q.begin() + n);
+        long double scale = 562949953421312.0L * 3 / 2;
+        long s = ckks_b200::ppmm_scaler(qq, scale);
+        printf("%%ld %%.6Lf\n", s, ckks_b200::ppmm_scale_after(qq, scale, s));
+    }
+    return 0;
+}
+""" % tuple(params.ntt_primes(50, 1 << 17, 3)))
+    exe = tmp_path / "scale"
+    subprocess.run(["nvcc", "-std=c++17", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    lines = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split("\n")
+    q = params.ntt_primes(50, 1 << 17, 3)
+    scale = float(1 << 49) * 1.5
+    for n, ln in zip((2, 3), lines):
+        s_cpp, after_cpp = ln.split()
+        s_py = host.ppmm_scaler(q[:n], scale)
+        assert int(s_cpp) == int(s_py)
+        assert abs(float(after_cpp) - host.ppmm_scale_after(q[:n], scale, s_py)) / float(after_cpp) < 1e-12
