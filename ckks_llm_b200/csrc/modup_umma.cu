@@ -10,9 +10,14 @@
 // and with c_{k,j,b} cut into bytes too this is an unsigned 8-bit matrix product:
 //     D[x][k*8+a] = sum_{(j,b)} rb_{j,b}[x] * byte_a(c_{k,j,b}) ,   K = 8*alpha,  N = 8*t_num .
 // One UMMA (M = 128 coefficients) per 32 bytes of K does it; the s32 results stay below 2^23.
-// Each thread then recombines its row, sum_a D_a 2^(8a) < 2^80, reduces it modulo t_k with an
-// FP64 quotient estimate (t_k in [2^40, 2^62)), subtracts the overflow term from a small table and
-// stores.  What is left on the integer pipes is the alpha Shoup products that make rb_j.
+// Each thread then recombines its row, sum_a D_a 2^(8a) < 2^80, adds the negated overflow term from a
+// small table, reduces the sum modulo t_k with one FP64 quotient estimate (t_k in [2^40, 2^62)) and
+// stores.
+//
+// With source moduli below 2^50 rb_j comes off the FP64 pipe as a value in (-0.7 q_j, 0.7 q_j); q_j is
+// added to every one of them instead of to the negative ones only, and the overflow count rises by the
+// number of limbs so treated: rb_j + q_j contributes one more Qblk to the sum, which the table entry for
+// the larger count takes away again.  The residues are those of the canonical rb_j.
 //
 // The result is the exact residue.  The reference (and the CUDA-core kernel in modup.cu) forms
 // the difference in 128 bits, which equals the exact residue unless the sum falls below
@@ -57,6 +62,7 @@ struct BconvArgs {
     uint32_t N;
     int blocks, batch, tg, npad;
     int tgt_limit;                // target k of block blk exists iff blk*tg + k < tgt_limit
+    int xshift;                   // log2 of the tiles per limb, N / 128
     long long wait_budget;        // clock cycles a wait on a group's mbarrier may take
     int withhold;                 // test switch: group 0 of CTA 0 leaves out the commit of its first tile
     size_t in_batch, in_blk, out_batch, out_blk;      // strides in words; limb j / target k sits j*N / k*N further
@@ -107,39 +113,43 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
     const int b_tile = KSTEPS * P.npad * 32;
     uint8_t* sA = smem + g * A_TILE;
     uint8_t* sB = smem + GROUPS * A_TILE;                                   // [blocks][KSTEPS][npad*32]
-    u64* s_q = reinterpret_cast<u64*>(sB + P.blocks * b_tile);             // [blocks][APAD]  source moduli
-    ulonglong2* s_hinv = reinterpret_cast<ulonglong2*>(s_q + P.blocks * APAD);   // [blocks][APAD]
-    u64* s_vt = reinterpret_cast<u64*>(s_hinv + P.blocks * APAD);          // [blocks][APAD+1][T]  (v*F + post) mod r
-    u64* s_t = s_vt + P.blocks * (APAD + 1) * T;                           // [blocks][T]  target moduli (0: none)
-    double* s_tinv = reinterpret_cast<double*>(s_t + P.blocks * T);        // [blocks][T]
-    double* s_qd = s_tinv + P.blocks * T;                                  // [blocks][APAD]  m_j as a double
-    double* s_qinv = s_qd + P.blocks * APAD;                               // [blocks][APAD]  1/m_j (0 where there is no limb)
-    double* s_wd = s_qinv + P.blocks * APAD;                               // [blocks][APAD]  hat_j^-1 mod m_j, centred
-    u64* s_pre = reinterpret_cast<u64*>(s_wd + P.blocks * APAD);           // [blocks][APAD]
+    const int BA = P.blocks * APAD, NV = 2 * APAD + 1;
+    double2* s_f = reinterpret_cast<double2*>(sB + P.blocks * b_tile);     // [blocks][APAD][2]  {m_j, 1/m_j}, {w_j, 2^52 + m_j}
+    ulonglong2* s_hinv = reinterpret_cast<ulonglong2*>(s_f + 2 * BA);      // [blocks][APAD]  {hat_j^-1 mod m_j, shoup}
+    ulonglong2* s_tk = s_hinv + BA;                                        // [blocks][T]  {t_k (0: none), bits of 2^32 / t_k}
+    u64* s_q = reinterpret_cast<u64*>(s_tk + P.blocks * T);                // [blocks][APAD]  source moduli (1: none)
+    u64* s_pre = s_q + BA;                                                 // [blocks][APAD]
+    u64* s_nv = s_pre + BA;                                                // [blocks][NV][T]  -(v*F + post) mod t_k
+    int* s_nlive = reinterpret_cast<int*>(s_nv + P.blocks * NV * T);       // [blocks]  limbs of the digit (they come first)
 
     for (int i = tid; i < P.blocks * b_tile / 16; i += THREADS)
         reinterpret_cast<uint4*>(sB)[i] = reinterpret_cast<const uint4*>(P.planes)[i];
-    for (int i = tid; i < P.blocks * APAD; i += THREADS) {
+    for (int i = tid; i < BA; i += THREADS) {
         const u64 mj = P.src_mod[i];
         const bool live = mj != 1;
         s_q[i] = mj;
         s_hinv[i] = live ? P.src_hinv[i] : make_ulonglong2(0, 0);
         s_pre[i] = live ? P.src_pre[i] : 0;
-        s_qd[i] = (double)mj;
-        s_qinv[i] = live ? 1.0 / (double)mj : 0.0;
         const u64 w = live ? P.src_hinv[i].x : 0;
-        s_wd[i] = w > mj / 2 ? -(double)(mj - w) : (double)w;
+        // without a limb: w = 0 and 1/m = 0 make rb = 0 and leave the count alone
+        s_f[2 * i] = make_double2((double)mj, live ? 1.0 / (double)mj : 0.0);
+        s_f[2 * i + 1] = make_double2(w > mj / 2 ? -(double)(mj - w) : (double)w,
+                                      4503599627370496.0 + (live && F64Q ? (double)mj : 0.0));
+    }
+    for (int i = tid; i < P.blocks; i += THREADS) {
+        int n = 0;
+        for (int j = 0; j < APAD; j++) n += P.src_mod[i * APAD + j] != 1;
+        s_nlive[i] = n;
     }
     for (int i = tid; i < P.blocks * T; i += THREADS) {
         const int blk = i / T, k = i % T;
         const bool live = blk * T + k < P.tgt_limit && P.tgt_mod[i] != 0;
         const u64 rk = live ? P.tgt_mod[i] : 0;
-        s_t[i] = rk;
-        s_tinv[i] = live ? 1.0 / (double)rk : 0.0;
+        s_tk[i] = make_ulonglong2(rk, (u64)__double_as_longlong(live ? 4294967296.0 / (double)rk : 0.0));
         u64 acc = live ? P.tgt_post[i] : 0;
         const u64 f = live ? P.tgt_f[i] : 0;
-        for (int v = 0; v <= APAD; v++) {
-            s_vt[(blk * (APAD + 1) + v) * T + k] = acc;
+        for (int v = 0; v < NV; v++) {
+            s_nv[(blk * NV + v) * T + k] = acc ? rk - acc : 0;
             acc += f;                        // f, acc < r < 2^62: no overflow
             if (acc >= rk) acc -= rk;
         }
@@ -162,59 +172,63 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
     const uint32_t a16 = smem_u32(sA) >> 4, b16 = smem_u32(sB) >> 4;
     const uint32_t idesc = instr_desc(P.npad, false);
 
-    const long tiles_x = P.N / TM;
-    const long total = (long)P.batch * P.blocks * tiles_x;
-    const long stride = (long)gridDim.x * GROUPS;
-    long tile = (long)blockIdx.x * GROUPS + g;
+    const uint32_t total = (uint32_t)P.batch * P.blocks << P.xshift;
+    const uint32_t stride = gridDim.x * GROUPS;
+    uint32_t tile = blockIdx.x * GROUPS + g;
 
-    // residues of a tile's coefficient r, one per limb of its digit (zero beyond the digit)
-    auto load_tile = [&](long tl, u64 (&x)[APAD]) {
-        const long xt = tl % tiles_x;
-        const long rest = tl / tiles_x;
-        const int blk = (int)(rest % P.blocks);
-        const long bt = rest / P.blocks;
-        const u64* src = P.in + (size_t)bt * P.in_batch + (size_t)blk * P.in_blk + xt * TM + r;
+    // where a tile's coefficient r sits: its digit, its first source limb, its first target
+    auto locate = [&](uint32_t tl, int& blk, const u64*& src, u64*& dst) {
+        const uint32_t xt = tl & ((1u << P.xshift) - 1), rest = tl >> P.xshift;
+        const uint32_t bt = rest / (uint32_t)P.blocks;
+        blk = (int)(rest - bt * P.blocks);
+        src = P.in + (size_t)bt * P.in_batch + (size_t)blk * P.in_blk + xt * TM + r;
+        dst = P.out + (size_t)bt * P.out_batch + (size_t)blk * P.out_blk + xt * TM + r;
+    };
+    // residues of that coefficient, one per limb of its digit (zero beyond the digit)
+    auto load_tile = [&](const u64* src, int blk, u64 (&x)[APAD]) {
+        const int nl = s_nlive[blk];
 #pragma unroll
-        for (int j = 0; j < APAD; j++) x[j] = s_q[blk * APAD + j] != 1 ? src[(size_t)j * P.N] : 0;
+        for (int j = 0; j < APAD; j++) x[j] = j < nl ? src[(size_t)j * P.N] : 0;
     };
 
     u64 cur[APAD];
-    if (tile < total) load_tile(tile, cur);
+    int blk = 0, blk_next = 0;
+    const u64 *src = nullptr;
+    u64 *dst = nullptr, *dst_next = nullptr;
+    if (tile < total) {
+        locate(tile, blk, src, dst);
+        load_tile(src, blk, cur);
+    }
     uint32_t phase = 0;
     bool ok = true;
     // byte offset of this thread's row inside a K step: 8-row group, row in the group
     const uint32_t row_off = (uint32_t)(r >> 3) * 256 + (uint32_t)(r & 7) * 16;
     while (tile < total && ok) {
-        const long xt = tile % tiles_x;
-        const long rest = tile / tiles_x;
-        const int blk = (int)(rest % P.blocks);
-        const long bt = rest / P.blocks;
-
         // ---- rb_j, the overflow count, and this coefficient's row of the byte matrix ----
         // The reference's count is v = trunc(sum_j rb_j / q_j) with IEEE divisions added in limb
         // order.  est = sum_j rb_j * (1/q_j) differs from that sum by less than 2^-46, so both
         // truncate alike unless est sits within 2^-40 of an integer; only then are the divisions made.
-        double est = 0.0;
+        // On the FP64 path rb_j is kept signed in the sum and q_j added to every limb of the digit, so the
+        // count starts at the number of limbs.
+        double est = F64Q ? (double)s_nlive[blk] : 0.0;
 #pragma unroll
         for (int j = 0; j < APAD; j++) {
             u64 rb;
-            double rbd;
+            const double2 f0 = s_f[2 * (blk * APAD + j)];              // {q, 1/q}
             if (F64Q) {
-                const double q = s_qd[blk * APAD + j], u = s_qinv[blk * APAD + j], w = s_wd[blk * APAD + j];
+                const double2 f1 = s_f[2 * (blk * APAD + j) + 1];      // {w, 2^52 + q}
                 const double x = small_to_double(cur[j]);
-                const double h = __dmul_rn(x, w);
-                const double l = __fma_rn(x, w, -h);
-                const double c = __dadd_rn(__fma_rn(h, u, 6755399441055744.0), -6755399441055744.0);
-                rbd = __dadd_rn(__fma_rn(-c, q, h), l);
-                if (rbd < 0.0) rbd = __dadd_rn(rbd, q);
-                rb = (u64)__double_as_longlong(__dadd_rn(rbd, 4503599627370496.0)) & 0x000FFFFFFFFFFFFFull;
+                const double h = __dmul_rn(x, f1.x);
+                const double l = __fma_rn(x, f1.x, -h);
+                const double c = __dadd_rn(__fma_rn(h, f0.y, 6755399441055744.0), -6755399441055744.0);
+                const double rbd = __dadd_rn(__fma_rn(-c, f0.x, h), l);          // in (-0.7q, 0.7q)
+                est = __fma_rn(rbd, f0.y, est);
+                rb = (u64)__double_as_longlong(__dadd_rn(rbd, f1.y)) & 0x000FFFFFFFFFFFFFull;   // rbd + q, below 2^51
             } else {
                 const ulonglong2 hi = s_hinv[blk * APAD + j];
                 rb = shoup_mul(cur[j] + s_pre[blk * APAD + j], hi.x, hi.y, s_q[blk * APAD + j]);   // exact for any 64-bit operand
-                rbd = (double)rb;
+                est = __fma_rn((double)rb, f0.y, est);
             }
-            // beyond the digit w = 0 and 1/q = 0: rb = 0 and est is unchanged
-            est = fma(rbd, s_qinv[blk * APAD + j], est);
             // K index j*8+b: step j/4, K half (j%4)/2, byte offset (j%2)*8 inside the 16-byte row
             *reinterpret_cast<u64*>(sA + (j / 4) * (TM * 32) + ((j % 4) / 2) * 128 + row_off + (j % 2) * 8) = rb;
         }
@@ -223,16 +237,25 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
             const double frac = est - (double)v;
             if (frac < 0x1p-40 || frac > 1.0 - 0x1p-40) {
                 double vv = 0.0;
+                int added = 0;
                 for (int j = 0; j < APAD; j++) {
-                    const u64 rb = *reinterpret_cast<const u64*>(sA + (j / 4) * (TM * 32) + ((j % 4) / 2) * 128 + row_off + (j % 2) * 8);
-                    vv += __ddiv_rn((double)rb, s_qd[blk * APAD + j]);      // rb = 0 beyond the digit: adds 0.0
+                    u64 rb = *reinterpret_cast<const u64*>(sA + (j / 4) * (TM * 32) + ((j % 4) / 2) * 128 + row_off + (j % 2) * 8);
+                    const u64 q = s_q[blk * APAD + j];
+                    if (F64Q && rb >= q) {                                   // the stored value is the canonical one or q more
+                        rb -= q;
+                        added++;
+                    }
+                    vv += __ddiv_rn((double)rb, (double)q);                  // rb = 0 beyond the digit: adds 0.0
                 }
-                v = (int)vv;
+                v = (int)vv + added;
             }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        const long next = tile + stride;
-        if (next < total) load_tile(next, cur);
+        const uint32_t next = tile + stride;
+        if (next < total) {
+            locate(next, blk_next, src, dst_next);
+            load_tile(src, blk_next, cur);
+        }
         group_sync(1 + g);
         if (r == 0) {
             tc_fence_after();
@@ -250,12 +273,10 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
         if (!ok) break;
         tc_fence_after();
 
-        // ---- this coefficient's row: recombine, reduce, subtract the overflow term, store ----
+        // ---- this coefficient's row: recombine, add the negated overflow term, reduce, store ----
         const uint32_t taddr = tmem_g + ((uint32_t)((warp & 3) * 32) << 16);
-        u64* dst = P.out + (size_t)bt * P.out_batch + (size_t)blk * P.out_blk + xt * TM + r;
-        const u64* vt = s_vt + (blk * (APAD + 1) + v) * T;
-        const u64* tmod = s_t + blk * T;
-        const double* tinv = s_tinv + blk * T;
+        const u64* nv = s_nv + (blk * NV + v) * T;
+        const ulonglong2* tk2 = s_tk + blk * T;
         for (int k0 = 0; k0 < T; k0 += 4) {
             int32_t D[4][8];
 #pragma unroll
@@ -270,21 +291,22 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
                                mad_wide((uint32_t)D[u][1], 1u << 8, (u64)(uint32_t)D[u][0])));
                 const u64 g1 = mad_wide((uint32_t)D[u][7], 1u << 24, mad_wide((uint32_t)D[u][6], 1u << 16,
                                mad_wide((uint32_t)D[u][5], 1u << 8, (u64)(uint32_t)D[u][4])));
-                const u64 lo = g0 + (g1 << 32);              // the row's value modulo 2^64
-                const double val = fma(small_to_double(g1), 4294967296.0, small_to_double(g0));   // the value, to 53 bits
-                const u64 tk = tmod[k];
-                if (tk == 0) continue;                       // no such target in this block
-                const double qd = val * tinv[k] + 4503599627370496.0;        // nearest integer quotient (< 2^40)
+                const ulonglong2 tt = tk2[k];                // {t_k, 2^32 / t_k}
+                const u64 s0 = g0 + nv[k];                   // below 2^63
+                const u64 lo = s0 + (g1 << 32);              // the sum modulo 2^64
+                const u64 top = g1 + (s0 >> 32);             // the sum / 2^32, below 2^49
+                // nearest integer to top * 2^32 / t_k: within 1/2 + 2^-7 of the quotient of the sum
+                const double qd = __fma_rn(small_to_double(top), __longlong_as_double((long long)tt.y), 4503599627370496.0);
                 const u64 qh = (u64)__double_as_longlong(qd) & 0xFFFFFFFFFFFFFull;
-                u64 res = lo - qh * tk;                      // in (-t/2 - 1, t/2 + 1) modulo 2^64
-                if ((long long)res < 0) res += tk;
-                const u64 sub = vt[k];
-                res = res >= sub ? res - sub : res + tk - sub;
-                dst[(size_t)k * P.N] = res;
+                u64 res = lo - qh * tt.x;                    // in (-0.51 t, 0.51 t) modulo 2^64
+                if ((long long)res < 0) res += tt.x;
+                if (tt.x != 0) dst[(size_t)k * P.N] = res;   // no such target in this block otherwise
             }
         }
         tc_fence_before();
         tile = next;
+        blk = blk_next;
+        dst = dst_next;
     }
     if (!ok && r == 0) atomicExch(&abort_flag, 1);
 
@@ -300,17 +322,23 @@ template <int APAD, bool F64Q, int NG>
 int launch_groups(ckks_b200_context* c, const BconvArgs& P, cudaStream_t st) {
     constexpr int GROUPS = NG, THREADS = 128 * NG;
     constexpr int KSTEPS = APAD * 8 / 32;
+    // operand tiles, byte planes, then the tables in the kernel's order: 32 + 16 + 8 + 8 bytes per source limb,
+    // 16 per target, the negated overflow terms and the limb counts
     const size_t smem = (size_t)GROUPS * KSTEPS * TM * 32 + (size_t)P.blocks * KSTEPS * P.npad * 32 +
-                        (size_t)P.blocks * APAD * (8 + 16) + (size_t)P.blocks * (APAD + 1) * P.tg * 8 +
-                        (size_t)P.blocks * P.tg * 16 + (size_t)P.blocks * APAD * 32;
+                        (size_t)P.blocks * APAD * 64 + (size_t)P.blocks * P.tg * 16 +
+                        (size_t)P.blocks * (2 * APAD + 1) * P.tg * 8 + (size_t)P.blocks * 4;
     CKB_REQUIRE(smem <= 200 * 1024, CKKS_B200_ERR_UNSUPPORTED, "ModUp tables of %zu bytes do not fit shared memory", smem);
     CKB_CUDA(cudaFuncSetAttribute(bconv_umma_kernel<APAD, F64Q, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int sms = 0;
     CKB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device));
     const long total = (long)P.batch * P.blocks * (P.N / TM);
+    CKB_REQUIRE(total < (1l << 31) && (P.N & (P.N - 1)) == 0, CKKS_B200_ERR_UNSUPPORTED,
+                "ModUp of %ld tiles (N = %u) is beyond the kernel's 32-bit tile index", total, P.N);
     const long want = (total + GROUPS - 1) / GROUPS;
     const int grid = (int)(want < sms ? want : sms);
     BconvArgs Q = P;
+    Q.xshift = 0;
+    while ((TM << Q.xshift) < (int)P.N) Q.xshift++;
     Q.wait_budget = c->wait_budget > 0 ? c->wait_budget : WAIT_BUDGET;
     Q.withhold = c->withhold_commit;
     c->withhold_commit = 0;                                 // the test switch arms one launch
