@@ -19,7 +19,7 @@ SYMBOLS = [
     "ckks_b200_ntt_forward", "ckks_b200_ntt_inverse",
     "ckks_b200_ntt_forward_host", "ckks_b200_ntt_inverse_host",
     "ckks_b200_modup_qj_to_t", "ckks_b200_modup_qj_to_t_host", "ckks_b200_modup_set_algo", "ckks_b200_context_check",
-    "ckks_b200_context_set_wait_budget", "ckks_b200_context_test_withhold_commit",
+    "ckks_b200_context_set_wait_budget", "ckks_b200_context_test_withhold_commit", "ckks_b200_context_test_exact_count",
     "ckks_b200_rescale", "ckks_b200_modup_q0_to_ql", "ckks_b200_rescale_batch", "ckks_b200_modup_q0_to_ql_batch",
     "ckks_b200_external_product_t", "ckks_b200_ntt_inverse_ext", "ckks_b200_modup_t_to_pql",
     "ckks_b200_moddown_pql_to_ql", "ckks_b200_keyswitch", "ckks_b200_mult", "ckks_b200_conjugate", "ckks_b200_rotate",
@@ -104,6 +104,7 @@ def load():
     L.ckks_b200_pcmm_ppmm_static.argtypes = [vp, C.POINTER(vp), vp, i, i, i, i, i, i, u64p, i, dbl, vp]
     L.ckks_b200_context_set_wait_budget.argtypes = [vp, C.c_longlong]
     L.ckks_b200_context_test_withhold_commit.argtypes = [vp, i]
+    L.ckks_b200_context_test_exact_count.argtypes = [vp, i]
     L.ckks_b200_pcmm_prepare_weights.argtypes = [vp, vp, i, i, dbl, vp]
     L.ckks_b200_pcmm_ppmm_rlwe_host.argtypes = [vp, vp, C.POINTER(RlweSource), i, vp, i, i, i, i, dbl]
     L.ckks_b200_pcmm_set_wait_budget.argtypes = [vp, C.c_longlong]

@@ -71,6 +71,7 @@ struct ckks_b200_context {
     int modup_algo = 0;                      // CKKS_B200_MODUP_AUTO / _TENSOR / _SIMT
     int* d_flags = nullptr;                  // [16] [1] = site of a device-side wait that ran out
     long long wait_budget = 0;               // clock cycles a device-side wait may take (0: the library's default)
+    int exact_count = 0;                     // test switch of ckks_b200_context_test_exact_count
     int withhold_commit = 0;                 // test switch of ckks_b200_context_test_withhold_commit, consumed by one launch
     int* h_flags = nullptr;                  // pinned mirror
 

@@ -134,6 +134,12 @@ extern "C" int ckks_b200_context_test_withhold_commit(ckks_b200_context* c, int 
     return CKKS_B200_OK;
 }
 
+extern "C" int ckks_b200_context_test_exact_count(ckks_b200_context* c, int on) {
+    CKB_REQUIRE(c != nullptr, CKKS_B200_ERR_ARG, "null handle");
+    c->exact_count = on ? 1 : 0;
+    return CKKS_B200_OK;
+}
+
 // Synchronise `stream` and report whether a bounded device-side wait of a tensor-core
 // ModUp on this context ran out since the last check.
 extern "C" int ckks_b200_context_check(ckks_b200_context* c, void* stream) {

@@ -63,6 +63,8 @@ struct BconvArgs {
     int blocks, batch, tg, npad;
     int tgt_limit;                // target k of block blk exists iff blk*tg + k < tgt_limit
     int xshift;                   // log2 of the tiles per limb, N / 128
+    bool fast;                    // the conditions of the kernel's FAST form hold
+    double near;                  // the count is redone with divisions when the estimate is this close to an integer
     long long wait_budget;        // clock cycles a wait on a group's mbarrier may take
     int withhold;                 // test switch: group 0 of CTA 0 leaves out the commit of its first tile
     size_t in_batch, in_blk, out_batch, out_blk;      // strides in words; limb j / target k sits j*N / k*N further
@@ -97,7 +99,9 @@ __device__ __forceinline__ u64 mad_wide(uint32_t a, uint32_t b, u64 c) {
 // (exact: h + l = x*w with h = fl(x*w), l the FMA remainder; h - c*q is a small integer for
 // c = rint(h/q); w is kept centred, |w| <= q/2, so the result stays within (-0.7q, 0.7q)).
 // Otherwise rb_j is a 64-bit Shoup product.
-template <int APAD, bool F64Q, int NG>
+// FAST: every block has all tg targets, tg is a multiple of four and every target modulus is at least 2^49, so
+// the quotient of the 81-bit sum fits 32 bits and nothing in the epilogue is conditional.
+template <int APAD, bool F64Q, int NG, bool FAST>
 __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
     constexpr int GROUPS = NG, THREADS = 128 * NG, GROUP_COLS = NG == 5 ? 96 : 128;
     constexpr int KSTEPS = APAD * 8 / 32;
@@ -176,6 +180,7 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
     const uint32_t stride = gridDim.x * GROUPS;
     uint32_t tile = blockIdx.x * GROUPS + g;
 
+    const uint32_t limb_bytes = P.N * 8;
     // where a tile's coefficient r sits: its digit, its first source limb, its first target
     auto locate = [&](uint32_t tl, int& blk, const u64*& src, u64*& dst) {
         const uint32_t xt = tl & ((1u << P.xshift) - 1), rest = tl >> P.xshift;
@@ -188,7 +193,8 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
     auto load_tile = [&](const u64* src, int blk, u64 (&x)[APAD]) {
         const int nl = s_nlive[blk];
 #pragma unroll
-        for (int j = 0; j < APAD; j++) x[j] = j < nl ? src[(size_t)j * P.N] : 0;
+        for (int j = 0; j < APAD; j++)
+            x[j] = j < nl ? *reinterpret_cast<const u64*>(mad_wide((uint32_t)j, limb_bytes, (u64)src)) : 0;
     };
 
     u64 cur[APAD];
@@ -235,7 +241,7 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
         int v = (int)est;
         {
             const double frac = est - (double)v;
-            if (frac < 0x1p-40 || frac > 1.0 - 0x1p-40) {
+            if (frac < P.near || frac > 1.0 - P.near) {
                 double vv = 0.0;
                 int added = 0;
                 for (int j = 0; j < APAD; j++) {
@@ -285,7 +291,7 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 const int k = k0 + u;
-                if (k >= T) break;
+                if (!FAST && k >= T) break;
                 // sum_a D_a 2^(8a) in two halves of four (each below 2^48)
                 const u64 g0 = mad_wide((uint32_t)D[u][3], 1u << 24, mad_wide((uint32_t)D[u][2], 1u << 16,
                                mad_wide((uint32_t)D[u][1], 1u << 8, (u64)(uint32_t)D[u][0])));
@@ -297,10 +303,17 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
                 const u64 top = g1 + (s0 >> 32);             // the sum / 2^32, below 2^49
                 // nearest integer to top * 2^32 / t_k: within 1/2 + 2^-7 of the quotient of the sum
                 const double qd = __fma_rn(small_to_double(top), __longlong_as_double((long long)tt.y), 4503599627370496.0);
-                const u64 qh = (u64)__double_as_longlong(qd) & 0xFFFFFFFFFFFFFull;
-                u64 res = lo - qh * tt.x;                    // in (-0.51 t, 0.51 t) modulo 2^64
+                u64 res;                                     // in (-0.51 t, 0.51 t) modulo 2^64
+                if (FAST) {
+                    const uint32_t qh = (uint32_t)__double2loint(qd);
+                    res = lo - (mad_wide(qh, (uint32_t)tt.x, 0) + ((u64)(qh * (uint32_t)(tt.x >> 32)) << 32));
+                } else {
+                    const u64 qh = (u64)__double_as_longlong(qd) & 0xFFFFFFFFFFFFFull;
+                    res = lo - qh * tt.x;
+                }
                 if ((long long)res < 0) res += tt.x;
-                if (tt.x != 0) dst[(size_t)k * P.N] = res;   // no such target in this block otherwise
+                if (FAST || tt.x != 0)                       // no such target in this block otherwise
+                    *reinterpret_cast<u64*>(mad_wide((uint32_t)k, limb_bytes, (u64)dst)) = res;
             }
         }
         tc_fence_before();
@@ -318,7 +331,7 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
     }
 }
 
-template <int APAD, bool F64Q, int NG>
+template <int APAD, bool F64Q, int NG, bool FAST>
 int launch_groups(ckks_b200_context* c, const BconvArgs& P, cudaStream_t st) {
     constexpr int GROUPS = NG, THREADS = 128 * NG;
     constexpr int KSTEPS = APAD * 8 / 32;
@@ -328,7 +341,7 @@ int launch_groups(ckks_b200_context* c, const BconvArgs& P, cudaStream_t st) {
                         (size_t)P.blocks * APAD * 64 + (size_t)P.blocks * P.tg * 16 +
                         (size_t)P.blocks * (2 * APAD + 1) * P.tg * 8 + (size_t)P.blocks * 4;
     CKB_REQUIRE(smem <= 200 * 1024, CKKS_B200_ERR_UNSUPPORTED, "ModUp tables of %zu bytes do not fit shared memory", smem);
-    CKB_CUDA(cudaFuncSetAttribute(bconv_umma_kernel<APAD, F64Q, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CKB_CUDA(cudaFuncSetAttribute(bconv_umma_kernel<APAD, F64Q, NG, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int sms = 0;
     CKB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device));
     const long total = (long)P.batch * P.blocks * (P.N / TM);
@@ -341,8 +354,9 @@ int launch_groups(ckks_b200_context* c, const BconvArgs& P, cudaStream_t st) {
     while ((TM << Q.xshift) < (int)P.N) Q.xshift++;
     Q.wait_budget = c->wait_budget > 0 ? c->wait_budget : WAIT_BUDGET;
     Q.withhold = c->withhold_commit;
+    Q.near = c->exact_count ? 0.75 : 0x1p-40;               // 0.75: every estimate counts as close
     c->withhold_commit = 0;                                 // the test switch arms one launch
-    bconv_umma_kernel<APAD, F64Q, NG><<<grid, THREADS, smem, st>>>(Q);
+    bconv_umma_kernel<APAD, F64Q, NG, FAST><<<grid, THREADS, smem, st>>>(Q);
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
@@ -351,8 +365,9 @@ int launch_groups(ckks_b200_context* c, const BconvArgs& P, cudaStream_t st) {
 template <int APAD, bool F64Q>
 int launch(ckks_b200_context* c, const BconvArgs& P, cudaStream_t st) {
     // the accumulator loads run in groups of four targets, so five groups need 8*ceil4(t_num) <= 96
-    if ((P.tg + 3) / 4 * 32 <= 96) return launch_groups<APAD, F64Q, 5>(c, P, st);
-    return launch_groups<APAD, F64Q, 4>(c, P, st);
+    const bool five = (P.tg + 3) / 4 * 32 <= 96;
+    if (P.fast) return five ? launch_groups<APAD, F64Q, 5, true>(c, P, st) : launch_groups<APAD, F64Q, 4, true>(c, P, st);
+    return five ? launch_groups<APAD, F64Q, 5, false>(c, P, st) : launch_groups<APAD, F64Q, 4, false>(c, P, st);
 }
 
 template <bool F64Q>
@@ -397,6 +412,8 @@ int modup_tensor(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int b
     P.out_blk = (size_t)T * c->N;
     bool q_small = true;
     for (int i = 0; i < c->q_num; i++) q_small = q_small && c->moduli[c->p_num + i] < (1ull << 50);
+    P.fast = T % 4 == 0;                                // every digit is converted to all t moduli
+    for (int k = 0; k < T; k++) P.fast = P.fast && c->moduli[c->p_num + c->q_num + k] >= (1ull << 49);
     return q_small ? launch_apad<true>(c, P, c->tc_kpad, st) : launch_apad<false>(c, P, c->tc_kpad, st);
 }
 
@@ -430,6 +447,7 @@ int modup_t_tensor(ckks_b200_context* c, u64* d_out, const u64* d_in, int l, int
     P.in_blk = (size_t)c->t_num * c->N;
     P.out_batch = P.in_batch;
     P.out_blk = (size_t)gamma * c->N;
+    P.fast = false;                                     // the last block may have fewer than gamma targets
     return launch_apad<false>(c, P, tb.kpad, st);
 }
 

@@ -130,6 +130,10 @@ class Context_23:
         """Test support: the next tensor-core ModUp leaves out one completion signal so that a wait runs out."""
         capi.check(self.lib.ckks_b200_context_test_withhold_commit(self._h, int(bool(on))))
 
+    def test_exact_count(self, on=True):
+        """Test support: every coefficient of a tensor-core ModUp takes the overflow count from IEEE divisions."""
+        capi.check(self.lib.ckks_b200_context_test_exact_count(self._h, int(bool(on))))
+
     # host-buffer forms (numpy uint64 arrays, transformed in place / returned)
     def ToNTTInplace_host(self, host_a, start_poly_idx, start_mod_idx, poly_num, mod_num, poly_mod_len):
         assert host_a.dtype == np.uint64 and host_a.flags.c_contiguous

@@ -107,6 +107,12 @@ int ckks_b200_context_set_wait_budget(ckks_b200_context* ctx, long long cycles);
  * ckks_b200_context_check returns CKKS_B200_ERR_TIMEOUT (the output of that launch is then incomplete).  Nothing
  * faults or hangs; set a short budget first.  The switch arms one launch. */
 int ckks_b200_context_test_withhold_commit(ckks_b200_context* ctx, int on);
+/* Test support for the overflow count of the tensor-core conversions (no reference counterpart).  The kernel takes
+ * the count from a sum of products with reciprocals and repeats it with the reference's IEEE divisions
+ * (BasisConv.cuh:121-131) only where that sum lies within 2^-40 of an integer, which random inputs practically never
+ * reach.  With on != 0 every coefficient takes the division path, so a parity test covers it.  Stays set until
+ * cleared. */
+int ckks_b200_context_test_exact_count(ckks_b200_context* ctx, int on);
 
 /* ---- level changes around the PCMM ------------------------------------------
  * d_cipher is the reference's Ciphertext buffer, a limbs then b limbs, each [L+1][N], NTT

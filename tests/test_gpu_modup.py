@@ -11,13 +11,15 @@ pytestmark = pytest.mark.gpu
 
 
 def _run(oracle, logN, alpha, q_num, t_num, l, batch, seed, q_bits=50, t_bits=60, algos=("tensor", "simt", "auto"),
-         edge=False):
+         edge=False, exact_count=False):
     """Both kernels (the tcgen05 byte-plane product and the 64-bit CUDA-core one) against the oracle."""
     N = 1 << logN
     p = params.ntt_primes(q_bits + 1, 2 * N, alpha)
     q = params.ntt_primes(q_bits, 2 * N, q_num)
     t = params.ntt_primes(t_bits, 2 * N, t_num)
     ctx = Context_23(logN, p, q, t)
+    if exact_count:
+        ctx.test_exact_count()
     rng = np.random.default_rng(seed)
     inp = np.stack([H.uniform_residues(rng, q, (N,)) for _ in range(batch)])
     if edge:
@@ -73,6 +75,21 @@ def test_digit_sizes_off_the_mma_step(oracle, cuda_device):
 
 def test_wide_q_limbs(oracle, cuda_device):
     _run(oracle, 12, 4, 8, 6, 7, 2, seed=9, q_bits=59, t_bits=61)
+
+
+def test_narrow_targets(oracle, cuda_device):
+    """Targets below 2^49: the quotient of the 81-bit sum no longer fits 32 bits, the kernel's general form runs."""
+    _run(oracle, 12, 4, 8, 4, 7, 2, seed=11, t_bits=44, algos=("tensor", "simt"))
+    _run(oracle, 12, 4, 8, 8, 7, 1, seed=12, q_bits=58, t_bits=42, algos=("tensor", "simt"))
+
+
+def test_overflow_count_from_divisions(oracle, cuda_device):
+    """The tensor-core kernel takes the overflow count from a sum of products with reciprocals and falls back to the
+    reference's IEEE divisions only next to an integer, which random inputs do not reach: the test switch sends every
+    coefficient down the division path, for both ways of forming rb_j, extreme residues included."""
+    _run(oracle, 12, 8, 16, 12, 15, 2, seed=13, algos=("tensor",), edge=True, exact_count=True)
+    _run(oracle, 12, 4, 10, 3, 8, 2, seed=14, algos=("tensor",), exact_count=True)
+    _run(oracle, 12, 4, 8, 6, 7, 2, seed=15, q_bits=59, t_bits=61, algos=("tensor",), edge=True, exact_count=True)
 
 
 def test_tensor_kernel_refuses_what_it_cannot_reduce(oracle, cuda_device):
