@@ -1029,6 +1029,18 @@ def main():
             sch.check()
             same = bool(torch.equal(out_dev.view(c["M"], c["limbs"], Cw), outh.to(device)))
             e2e["equals_device_call"] = same
+            # what the bus alone takes for the result, on this host and into this buffer: the floor under ms_per_step
+            flat = outh.view(-1)
+            best = None
+            for _ in range(3):
+                torch.cuda.synchronize(device)
+                t0 = time.perf_counter()
+                flat.copy_(out_dev, non_blocking=True)
+                torch.cuda.synchronize(device)
+                dt_copy = time.perf_counter() - t0
+                best = dt_copy if best is None or dt_copy < best else best
+            e2e["copy_out_alone_ms"] = best * 1e3
+            e2e["copy_out_alone_gbs"] = out_bytes / best / 1e9
             if not same:
                 raise SystemExit("the host-buffer decompose-and-multiply call and the device call differ")
             del out_dev, dsrc, outh
