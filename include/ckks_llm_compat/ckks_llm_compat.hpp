@@ -780,6 +780,17 @@ inline void print_device_array(double* data, int num, const char* vname) {
     for (double v : h) printf("%.8f, ", v);
     printf("...]\n");
 }
+// residues: the first words of each of mod_num limbs of N words (Utils.cuh:362-380)
+inline void print_device_array(uint64_tt* data, int N, int mod_num, const char* vname) {
+    const int show = N < 16 ? N : 16;
+    printf("%s = [", vname);
+    for (int i = 0; i < mod_num; i++) {
+        std::vector<uint64_tt> h = ckks_llm_compat::download(data + (size_t)i * N, (size_t)show);
+        printf("[");
+        for (uint64_tt v : h) printf("%llu, ", v);
+        printf("],\n");
+    }
+}
 struct PrecisionStats {
     double min_log2 = 0, avg_log2 = 0, max_err = 0;
     std::string String() const {

@@ -96,3 +96,13 @@ def test_bert_layer_flow_decrypts(cuda_device):
     r = _run(["bert"])
     assert r.returncode == 0, r.stdout + r.stderr
     assert "realData_coeffShift: not defined by the reference" in r.stdout
+
+
+def test_reference_programs_build_unmodified():
+    """Where the reference tree is present: its own driver programs for this path (test_rlwe_decomp.cu,
+    ntt_throughput.cu) compile, unmodified, with nothing but -I into the header tree, and link against the library."""
+    import build_ref_callers
+    if not os.path.isdir(build_ref_callers.REF_ROOT):
+        pytest.skip("the reference tree is not on this machine")
+    built = build_ref_callers.build_ref_callers()
+    assert set(built) == set(build_ref_callers.PROGRAMS)
