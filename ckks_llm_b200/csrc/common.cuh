@@ -40,6 +40,35 @@ const char* get_error();
 extern std::atomic<long> g_launches;
 inline void count_launch(long n = 1) { g_launches += n; }
 
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch, for the chains of short kernels (transforms, level changes, key switching): a
+// kernel launched with launch_after() may be scheduled while the kernel before it in the stream is still running.
+// It sets up what does not depend on that kernel (indices, constant tables, tensor memory) and calls
+// wait_for_previous_kernel() before it touches anything else in global memory; the wait returns once the previous
+// kernel has completed and its writes are visible.  The previous kernel opens the door with let_next_kernel_start()
+// (without it the dependent is scheduled when the previous kernel ends, as usual); launched the ordinary way, both
+// calls pass straight through.  Only kernels that wait may be launched with launch_after().
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ void wait_for_previous_kernel() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <class... Params, class... Args>
+inline cudaError_t launch_after(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+#endif
+
 // RAII guard: make `device` current for the duration of a call, then restore.
 struct DeviceGuard {
     int prev = -1;

@@ -25,7 +25,9 @@ __global__ void __launch_bounds__(kThreads) external_product_kernel(u64* __restr
                                                                     const ulonglong2* __restrict__ t_mu) {
     const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
     const int k = blockIdx.y, blk = blockIdx.z;
+    let_next_kernel_start();
     if (x >= N) return;
+    wait_for_previous_kernel();
     const size_t half_swk = (size_t)R * t_num * dnum * N, half_out = (size_t)R * t_num * N;
     u64 lo0 = 0, hi0 = 0, lo1 = 0, hi1 = 0;
     for (int i = 0; i < cipher_blocks; i++) {
@@ -59,7 +61,9 @@ template <int TMAX>
 __global__ void __launch_bounds__(kThreads) modup_t_kernel(ModUpTArgs P) {
     const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
     const int blk = blockIdx.y, c = blockIdx.z;
+    let_next_kernel_start();
     if (x >= P.N) return;
+    wait_for_previous_kernel();
     const size_t half = (size_t)P.R * P.t_num * P.N;
     const u64* src = P.in + c * half + (size_t)blk * P.t_num * P.N + x;
     u64 rb[TMAX];
@@ -114,7 +118,9 @@ template <int PMAX>
 __global__ void __launch_bounds__(kThreads) moddown_kernel(ModDownArgs P, int l) {
     const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
     const int c = blockIdx.y;
+    let_next_kernel_start();
     if (x >= P.N) return;
+    wait_for_previous_kernel();
     const u64* src = P.in + (size_t)c * P.R * P.t_num * P.N + x;
     u64 rb[PMAX];
 #pragma unroll
@@ -248,9 +254,8 @@ extern "C" int ckks_b200_external_product_t(ckks_b200_context* c, uint64_t* d_ou
     const int blocks = (c->p_num + l + 1 + gamma - 1) / gamma;
     const int dnum = c->q_num / c->p_num;
     dim3 grid((c->N + kThreads - 1) / kThreads, c->t_num, blocks);
-    external_product_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(
-        (u64*)d_out, (const u64*)d_cipher_t, (const u64*)d_swk, c->N, c->t_num, R, cipher_blocks, dnum,
-        c->d_moduli + c->p_num + c->q_num, c->d_t_mu);
+    CKB_CUDA(launch_after(external_product_kernel, grid, dim3(kThreads), 0, (cudaStream_t)stream, (u64*)d_out, (const u64*)d_cipher_t,
+                          (const u64*)d_swk, c->N, c->t_num, R, cipher_blocks, dnum, c->d_moduli + c->p_num + c->q_num, c->d_t_mu));
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
@@ -302,9 +307,9 @@ extern "C" int ckks_b200_modup_t_to_pql(ckks_b200_context* c, uint64_t* d_out, c
     P.R = (c->p_num + c->q_num + gamma - 1) / gamma;
     const int blocks = (c->p_num + l + 1 + gamma - 1) / gamma;
     dim3 grid((c->N + kThreads - 1) / kThreads, blocks, batch);
-    if (c->t_num <= 4) modup_t_kernel<4><<<grid, kThreads, 0, (cudaStream_t)stream>>>(P);
-    else if (c->t_num <= 8) modup_t_kernel<8><<<grid, kThreads, 0, (cudaStream_t)stream>>>(P);
-    else modup_t_kernel<16><<<grid, kThreads, 0, (cudaStream_t)stream>>>(P);
+    if (c->t_num <= 4) CKB_CUDA(launch_after(modup_t_kernel<4>, grid, dim3(kThreads), 0, (cudaStream_t)stream, P));
+    else if (c->t_num <= 8) CKB_CUDA(launch_after(modup_t_kernel<8>, grid, dim3(kThreads), 0, (cudaStream_t)stream, P));
+    else CKB_CUDA(launch_after(modup_t_kernel<16>, grid, dim3(kThreads), 0, (cudaStream_t)stream, P));
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
@@ -333,9 +338,9 @@ extern "C" int ckks_b200_moddown_pql_to_ql(ckks_b200_context* c, uint64_t* d_out
     P.t_num = c->t_num;
     P.R = (c->p_num + c->q_num + gamma - 1) / gamma;
     dim3 grid((c->N + kThreads - 1) / kThreads, batch);
-    if (c->p_num <= 4) moddown_kernel<4><<<grid, kThreads, 0, (cudaStream_t)stream>>>(P, l);
-    else if (c->p_num <= 8) moddown_kernel<8><<<grid, kThreads, 0, (cudaStream_t)stream>>>(P, l);
-    else moddown_kernel<16><<<grid, kThreads, 0, (cudaStream_t)stream>>>(P, l);
+    if (c->p_num <= 4) CKB_CUDA(launch_after(moddown_kernel<4>, grid, dim3(kThreads), 0, (cudaStream_t)stream, P, l));
+    else if (c->p_num <= 8) CKB_CUDA(launch_after(moddown_kernel<8>, grid, dim3(kThreads), 0, (cudaStream_t)stream, P, l));
+    else CKB_CUDA(launch_after(moddown_kernel<16>, grid, dim3(kThreads), 0, (cudaStream_t)stream, P, l));
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;

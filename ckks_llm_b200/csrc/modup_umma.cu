@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
     const int tid = threadIdx.x, warp = tid >> 5;
     const int g = tid >> 7, r = tid & 127;
     const int T = P.tg;
+    let_next_kernel_start();          // its set-up may overlap this kernel; its own wait keeps it off the data
     const int b_tile = KSTEPS * P.npad * 32;
     uint8_t* sA = smem + g * A_TILE;
     uint8_t* sB = smem + GROUPS * A_TILE;                                   // [blocks][KSTEPS][npad*32]
@@ -201,6 +202,7 @@ __global__ void __launch_bounds__(128 * NG, 1) bconv_umma_kernel(BconvArgs P) {
     int blk = 0, blk_next = 0;
     const u64 *src = nullptr;
     u64 *dst = nullptr, *dst_next = nullptr;
+    wait_for_previous_kernel();       // the tables above are constants of the context; the residues are not
     if (tile < total) {
         locate(tile, blk, src, dst);
         load_tile(src, blk, cur);
@@ -356,7 +358,7 @@ int launch_groups(ckks_b200_context* c, const BconvArgs& P, cudaStream_t st) {
     Q.withhold = c->withhold_commit;
     Q.near = c->exact_count ? 0.75 : 0x1p-40;               // 0.75: every estimate counts as close
     c->withhold_commit = 0;                                 // the test switch arms one launch
-    bconv_umma_kernel<APAD, F64Q, NG, FAST><<<grid, THREADS, smem, st>>>(Q);
+    CKB_CUDA(launch_after(bconv_umma_kernel<APAD, F64Q, NG, FAST>, dim3(grid), dim3(THREADS), smem, st, Q));
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;

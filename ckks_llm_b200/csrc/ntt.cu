@@ -406,6 +406,7 @@ __device__ __forceinline__ void contig_body(const NttArgs& P, u64* S, int poly0,
     auto gpoly = [&](int t) { return P.data + (((size_t)(poly0 + t) * P.poly_mod_len + P.start_limb_off + limb) << P.logN); };
     V a[16];
     if (STAGED) stage_twiddles(const_cast<double*>(stw), P.tw_d + ((size_t)(P.start_mod_idx + limb) << P.logN), N, xt, tid, kThreads);
+    wait_for_previous_kernel();
     prefetch_chunks(sbuf, gpoly(0) + xwarp, lane);
     __pipeline_commit();
     for (int t = 0; t < npoly; t++) {
@@ -478,6 +479,7 @@ __device__ __forceinline__ void contig_body(const NttArgs& P, u64* S, int poly0,
 template <bool INV>
 __global__ void __launch_bounds__(kThreads, 2) ntt_contig(NttArgs P, int poly_num, int walk) {
     extern __shared__ __align__(16) u64 S[];       // 2 buffers x 4096 words, then the tile's twiddles
+    let_next_kernel_start();
     const int poly0 = blockIdx.z * walk;
     const int npoly = poly_num - poly0 < walk ? poly_num - poly0 : walk;
     const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
@@ -527,6 +529,7 @@ __device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles
     const uint32_t b1 = ((tid >> 4) << 8) | (tid & 15);          // window 1: v[j] at b1 | j << 4
     const TwGlobal<A> tw0{ar, 1u}, tw1{ar, 16u + (tid >> 4)};
     V a[16];
+    wait_for_previous_kernel();
     prefetch_tile<SA>(S, g, tid);
     __pipeline_commit();
     for (int t = 0; t < tiles; t++) {
@@ -584,6 +587,7 @@ __device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles
 template <int SA, bool INV>
 __global__ void __launch_bounds__(kThreads, 3) ntt_strided(NttArgs P, int tiles) {
     extern __shared__ __align__(16) u64 S[];       // 2 buffers x 4096 words
+    let_next_kernel_start();
     const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
     if (q < kF64Bound) strided_body<SA, INV, F64Arith>(P, S, tiles);
     else if (q < kLazyBound) strided_body<SA, INV, IntArith<true>>(P, S, tiles);
@@ -593,29 +597,26 @@ __global__ void __launch_bounds__(kThreads, 3) ntt_strided(NttArgs P, int tiles)
 constexpr size_t kSmemStrided = 2 * kTile * sizeof(u64);
 constexpr size_t kSmemContig = 3 * kTile * sizeof(u64);
 
+// Both kernels of a transform are launched as programmatic dependents of whatever kernel precedes them in the
+// stream: they wait for it (wait_for_previous_kernel) after their set-up, before the first access to the data.
+template <class... Params, class... Args>
+int launch_kernel(void (*kernel)(Params...), dim3 grid, size_t smem, cudaStream_t st, Args... args) {
+    CKB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CKB_CUDA(launch_after(kernel, grid, dim3(kThreads), smem, st, args...));
+    return CKKS_B200_OK;
+}
+
 template <int SA>
 int launch_strided(bool inverse, int ntile, int tiles, int mod_num, int poly_num, const NttArgs& P, cudaStream_t st) {
     dim3 grid(ntile / tiles, mod_num, poly_num);
-    if (inverse) {
-        CKB_CUDA(cudaFuncSetAttribute(ntt_strided<SA, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemStrided));
-        ntt_strided<SA, true><<<grid, kThreads, kSmemStrided, st>>>(P, tiles);
-    } else {
-        CKB_CUDA(cudaFuncSetAttribute(ntt_strided<SA, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemStrided));
-        ntt_strided<SA, false><<<grid, kThreads, kSmemStrided, st>>>(P, tiles);
-    }
-    return CKKS_B200_OK;
+    return inverse ? launch_kernel(ntt_strided<SA, true>, grid, kSmemStrided, st, P, tiles)
+                   : launch_kernel(ntt_strided<SA, false>, grid, kSmemStrided, st, P, tiles);
 }
 
 int launch_contig(bool inverse, int ntile, int walk, int mod_num, int poly_num, const NttArgs& P, cudaStream_t st) {
     dim3 grid(ntile, mod_num, (poly_num + walk - 1) / walk);
-    if (inverse) {
-        CKB_CUDA(cudaFuncSetAttribute(ntt_contig<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemContig));
-        ntt_contig<true><<<grid, kThreads, kSmemContig, st>>>(P, poly_num, walk);
-    } else {
-        CKB_CUDA(cudaFuncSetAttribute(ntt_contig<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemContig));
-        ntt_contig<false><<<grid, kThreads, kSmemContig, st>>>(P, poly_num, walk);
-    }
-    return CKKS_B200_OK;
+    return inverse ? launch_kernel(ntt_contig<true>, grid, kSmemContig, st, P, poly_num, walk)
+                   : launch_kernel(ntt_contig<false>, grid, kSmemContig, st, P, poly_num, walk);
 }
 
 int run_ntt(ckks_b200_context* c, u64* d_data, int start_limb_off, int start_mod_idx, int poly_num,

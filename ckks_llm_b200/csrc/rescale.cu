@@ -32,7 +32,9 @@ __global__ void __launch_bounds__(kThreads) rescale_spread_kernel(u64* __restric
                                                                   const u64* __restrict__ qinv64) {
     const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
     const int c = blockIdx.y;
+    let_next_kernel_start();
     if (x >= N) return;
+    wait_for_previous_kernel();
     const u64 v = cipher[((size_t)c * stride + l) * N + x];
     for (int i = 0; i < l; i++) buf[((size_t)c * stride + i) * N + x] = reduce64(v, q[i], qinv64[i]);
 }
@@ -43,7 +45,9 @@ __global__ void __launch_bounds__(kThreads) rescale_combine_kernel(u64* __restri
                                                                    const ulonglong2* __restrict__ qlinv) {
     const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
     const int i = blockIdx.y, c = blockIdx.z;
+    let_next_kernel_start();
     if (x >= N) return;
+    wait_for_previous_kernel();
     const size_t idx = ((size_t)c * stride + i) * N + x;
     const u64 qi = q[i];
     const u64 d = csub(cipher[idx] + qi - buf[idx], qi);          // both operands are canonical
@@ -59,7 +63,9 @@ __global__ void __launch_bounds__(kThreads) modup_q0_kernel(u64* __restrict__ ci
                                                             u64 scale_up) {
     const uint32_t x = blockIdx.x * kThreads + threadIdx.x;
     const int c = blockIdx.y;
+    let_next_kernel_start();
     if (x >= N) return;
+    wait_for_previous_kernel();
     const u64 q0 = q[0];
     const u64 v = cipher[(size_t)c * stride * N + x];
     for (int i = 0; i < target_level; i++) {
@@ -91,14 +97,15 @@ extern "C" int ckks_b200_rescale_batch(ckks_b200_context* c, uint64_t* d_ciphers
     if (rc) return rc;
     const u64* q = c->d_moduli + K;
     dim3 g1((c->N + kThreads - 1) / kThreads, polys);
-    rescale_spread_kernel<<<g1, kThreads, 0, st>>>(c->resc_buf, (const u64*)d_ciphers, c->N, stride, l, q, c->d_qinv64 + K);
+    CKB_CUDA(launch_after(rescale_spread_kernel, g1, dim3(kThreads), 0, st, c->resc_buf, (const u64*)d_ciphers, (uint32_t)c->N, stride, l, q,
+                          (const u64*)(c->d_qinv64 + K)));
     count_launch();
     CKB_CUDA(cudaGetLastError());
     rc = ckks_b200_ntt_forward(c, (uint64_t*)c->resc_buf, 0, K, polys, l, stride, stream);
     if (rc) return rc;
     dim3 g2((c->N + kThreads - 1) / kThreads, l, polys);
-    rescale_combine_kernel<<<g2, kThreads, 0, st>>>((u64*)d_ciphers, c->resc_buf, c->N, stride, l, q,
-                                                    c->d_qlinv + (size_t)l * c->q_num);
+    CKB_CUDA(launch_after(rescale_combine_kernel, g2, dim3(kThreads), 0, st, (u64*)d_ciphers, c->resc_buf, c->N, stride, l, q,
+                          c->d_qlinv + (size_t)l * c->q_num));
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return CKKS_B200_OK;
@@ -122,8 +129,8 @@ extern "C" int ckks_b200_modup_q0_to_ql_batch(ckks_b200_context* c, uint64_t* d_
     int rc = ckks_b200_ntt_inverse(c, d_ciphers, 0, K, polys, 1, stride, stream);
     if (rc) return rc;
     dim3 g((c->N + kThreads - 1) / kThreads, polys);
-    modup_q0_kernel<<<g, kThreads, 0, st>>>((u64*)d_ciphers, c->N, stride, target_level, c->d_moduli + K, c->d_qinv64 + K,
-                                            (u64)scale_up);
+    CKB_CUDA(launch_after(modup_q0_kernel, g, dim3(kThreads), 0, st, (u64*)d_ciphers, c->N, stride, target_level, c->d_moduli + K,
+                          c->d_qinv64 + K, (u64)scale_up));
     count_launch();
     CKB_CUDA(cudaGetLastError());
     return ckks_b200_ntt_forward(c, d_ciphers, 0, K, polys, target_level + 1, stride, stream);
