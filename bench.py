@@ -38,7 +38,7 @@ SW, SC = 5, 7          # byte planes the PCMM workload needs: 40-bit signed weig
 PCMM_TRAFFIC_PER_LIMB = (709.12e6 + 766.83e6) / 2                    # pcmm_umma_kernel<5,7,false>, 768x768, per limb
 NTT_TRAFFIC_PER_XFORM = {"forward": (167.93e6 + 110.85e6 + 188.73e6 + 108.05e6) / 320,
                          "inverse": (188.73e6 + 108.17e6 + 167.94e6 + 108.42e6) / 320}
-MODUP_TRAFFIC_PER_POLY = (100.74e6 + 96.33e6) / 8
+MODUP_TRAFFIC_PER_POLY = (100.73e6 + 94.82e6) / 8
 # FP64 instructions per 16 values of a whole transform of 16 stages on the FP64 back end (8 per forward butterfly:
 # six for the exact product, an add and a subtract; a three-operation range reduction on five of the stages; one
 # conversion in, one out; the inverse reduces its sums on ten of fifteen stages and pays two products per
