@@ -269,6 +269,52 @@ def bench_ntt(torch, device, steps, warmup, peaks):
     return res
 
 
+def bench_ntt_limb_sharded(torch, device, rank, world, dist, steps, warmup):
+    """The same batch (32 polynomials x 40 limbs, one copy per rank, limb-major) with the LIMBS dealt to the ranks: every
+    rank transforms its limbs of all polynomials, then the limbs are all-gathered over NCCL so that every rank holds the
+    whole transformed batch (strong scaling; the exchange is what it costs)."""
+    from ckks_llm_b200 import params, shard
+    from ckks_llm_b200.host import Context_23
+    n = NTT_CFG
+    N = 1 << n["logN"]
+    q = params.ntt_primes(n["q_bits"], 2 * N, n["limbs"])
+    ctx = Context_23(n["logN"], [], q, [], device=device.index)
+    g = torch.Generator(device=device).manual_seed(1)
+    data = torch.empty((n["limbs"], n["polys"], N), dtype=torch.int64, device=device)     # [limb][poly][N]
+    for i, qi in enumerate(q):
+        data[i] = torch.randint(0, qi, (n["polys"], N), generator=g, device=device, dtype=torch.int64)
+    ranges = shard.unit_ranges(n["limbs"], world)
+    a, b = ranges[rank]
+
+    def transform():
+        for i in range(a, b):
+            ctx.ToNTTInplace(data[i], 0, i, n["polys"], 1, 1)        # limb i of every polynomial: 32 limb-transforms
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        tt = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    ms_t = timed(transform)
+    ms_g = timed(lambda: (transform(), shard.gather_limbs(data, ranges)))
+    ctx.close()
+    xf = n["polys"] * n["limbs"]
+    return {"sharding": "limbs dealt to ranks, all polynomials on every rank; NCCL all-gather of the limbs afterwards",
+            "transform_ms": ms_t, "with_gather_ms": ms_g, "limb_xforms_per_sec": xf / (ms_t * 1e-3),
+            "limb_xforms_per_sec_with_gather": xf / (ms_g * 1e-3),
+            "gather_bytes_received_per_rank": int(xf * N * 8 * (world - 1) / world)}
+
+
 def bench_modup(torch, device, steps, warmup, peaks):
     from ckks_llm_b200 import params
     from ckks_llm_b200.host import Context_23
@@ -1074,6 +1120,7 @@ def main():
                     nt[name] = {"limb_xforms_per_sec": world * xf / (ms_n * 1e-3), "ms_per_step": ms_n,
                                 "frac_per_gpu": xf * 16 * (1 << NTT_CFG["logN"]) / (ms_n * 1e-3) / 1e9 / peaks["hbm_gbs"]}
                 nt["sharding"] = "each rank its own polynomials, no collective (weak scaling)"
+                nt["limb_sharded"] = bench_ntt_limb_sharded(torch, device, rank, world, dist, max(args.steps, 10), args.warmup)
                 cfg["ntt_ranks"] = nt
                 roof["ntt_fwd"] = {"value": nt["forward"]["limb_xforms_per_sec"], "unit": "limb-xforms/s, all ranks", "ms": nt["forward"]["ms_per_step"],
                                    "frac": nt["forward"]["frac_per_gpu"], "bound": "hbm"}

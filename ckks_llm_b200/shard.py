@@ -101,6 +101,31 @@ def gather_output(out_full, ranges, group=None, rows_per_step=None):
     return out_full
 
 
+def gather_limbs(limb_major, limb_ranges, group=None):
+    """All-gather the limbs of a batch of polynomials transformed limb by limb on different ranks.
+
+    limb_major: [limbs][polys][N] tensor on every rank (limb-major, so that a rank's limbs are one contiguous block)
+    in which only this rank's limbs (limb_ranges[rank]) are valid.  On return every rank holds all limbs.  Equal ranges
+    go out as one in-place all-gather; ragged ones are padded to the largest."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    sizes = [b - a for a, b in limb_ranges]
+    if len(set(sizes)) == 1 and limb_ranges[0][0] == 0 and sizes[0] * world == limb_major.shape[0]:
+        a, b = limb_ranges[rank]
+        dist.all_gather_into_tensor(limb_major, limb_major[a:b], group=group)
+        return limb_major
+    wmax = max(sizes)
+    mine = torch.zeros((wmax,) + tuple(limb_major.shape[1:]), dtype=limb_major.dtype, device=limb_major.device)
+    a, b = limb_ranges[rank]
+    mine[:b - a] = limb_major[a:b]
+    parts = torch.empty((world * wmax,) + tuple(limb_major.shape[1:]), dtype=limb_major.dtype, device=limb_major.device)
+    dist.all_gather_into_tensor(parts, mine, group=group)
+    for r, (x, y) in enumerate(limb_ranges):
+        if r != rank and y > x:
+            limb_major[x:y] = parts[r * wmax:r * wmax + (y - x)]
+    return limb_major
+
+
 def open_peer_buffers(t, group=None):
     """Maps the other ranks' copies of a CUDA tensor into this process for kernels on this rank's GPU.
 

@@ -4,6 +4,7 @@ import os
 import socket
 
 import numpy as np
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -76,6 +77,50 @@ def test_two_ranks_column_sharded_ppmm_gloo():
     ret = ctx.Manager().dict()
     port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert all(ret[r] for r in range(world))
+
+
+def _limb_worker(rank, world, port, limbs, ret):
+    """Every rank transforms its own limbs of the same batch (with the CPU restatement standing in for the GPU) and
+    the limbs are gathered: all ranks must end with the transform of the whole batch."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle import oracle as O
+    N, polys = 256, 3
+    q = params.ntt_primes(40, 2 * N, limbs)
+    T = O.NttTables(N, q)
+    rng = np.random.default_rng(5)
+    data = np.stack([np.stack([rng.integers(0, qi, N, dtype=np.uint64) for qi in q]) for _ in range(polys)])   # [poly][limb][N]
+    want = data.copy()
+    O.ntt_batch(want, T, 0, 0, polys, limbs, limbs)
+    ranges = shard.unit_ranges(limbs, world)
+    a, b = ranges[rank]
+    mine = data.copy()
+    if b > a:
+        O.ntt_batch(mine, T, a, a, polys, b - a, limbs)          # limbs [a, b) of every polynomial
+    limb_major = torch.from_numpy(np.ascontiguousarray(mine.transpose(1, 0, 2)).view(np.int64)).clone()
+    for i in range(limbs):
+        if not a <= i < b:
+            limb_major[i] = -1                                    # what this rank did not compute is not valid
+    shard.gather_limbs(limb_major, ranges)
+    got = limb_major.numpy().view(np.uint64).transpose(1, 0, 2)
+    ret[rank] = bool(np.array_equal(got, want))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("limbs", [4, 5])
+def test_two_ranks_limb_sharded_transform_gloo(limbs):
+    """Equal limb ranges take the in-place all-gather, ragged ones (5 limbs on 2 ranks) the padded one."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_limb_worker, args=(r, world, port, limbs, ret)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
