@@ -261,7 +261,18 @@ struct TwSharedB {
 // The strided phase takes its twiddles from the first 256 entries of the limb's table whatever the tile (stage s of
 // window 0 uses entries 2^s .. 2^(s+1)-1, window 1 those from 16 on): they sit in shared memory, copied once per CTA.
 constexpr int kTwStrided = 256;
-struct TwSharedS {
+template <class TW>
+struct TwSharedS {                           // 16-byte twiddles of the integer back ends: one load each
+    const TW* base;
+    uint32_t widx;
+    template <int s>
+    __device__ __forceinline__ void get(TW (&w)[1 << s]) const {
+#pragma unroll
+        for (int h = 0; h < (1 << s); h++) w[h] = base[(widx << s) + h];
+    }
+};
+template <>
+struct TwSharedS<double> {                   // doubles: two per load
     const double* base;
     uint32_t widx;
     template <int s>
@@ -550,13 +561,10 @@ __device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles
     u64* g = P.data + (((size_t)poly * P.poly_mod_len + P.start_limb_off + limb) << P.logN) +
              (size_t)blockIdx.x * tiles * C::CW;
     const uint32_t b1 = ((tid >> 4) << 8) | (tid & 15);          // window 1: v[j] at b1 | j << 4
-    constexpr bool STAGED = StagesTwiddles<A>::value;
-    const TwGlobal<A> tw0{ar, 1u}, tw1{ar, 16u + (tid >> 4)};
-    double* stw = reinterpret_cast<double*>(S + 2 * kTile);
-    if constexpr (STAGED) {
-        if (tid < kTwStrided) stw[tid] = ar.twiddle(tid);        // visible after the first barrier of the tile loop
-    }
-    const TwSharedS sw0{stw, 1u}, sw1{stw, 16u + (tid >> 4)};
+    typedef typename A::TW TW;
+    TW* stw = reinterpret_cast<TW*>(S + 2 * kTile);
+    if (tid < kTwStrided) stw[tid] = ar.twiddle(tid);            // visible after the first barrier of the tile loop
+    const TwSharedS<TW> sw0{stw, 1u}, sw1{stw, 16u + (tid >> 4)};
     V a[16];
     wait_for_previous_kernel();
     prefetch_tile<SA>(S, g, tid);
@@ -572,16 +580,14 @@ __device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles
             // window 0: v[j] at idx j*256 + tid; one twiddle set for the whole grid
 #pragma unroll
             for (int j = 0; j < 16; j++) a[j] = ar.from_canonical(s[j * 256 + tid]);
-            if constexpr (STAGED) fwd16<0, 4, fwd_mask(8 + SA - 1, true), A>(ar, a, sw0);
-            else fwd16<0, 4, fwd_mask(8 + SA - 1, true), A>(ar, a, tw0);
+            fwd16<0, 4, fwd_mask(8 + SA - 1, true), A>(ar, a, sw0);
             if (C::NST1 > 0) {
 #pragma unroll
                 for (int j = 0; j < 16; j++) s[j * 256 + tid] = ar.to_word(a[j]);
                 __syncthreads();
 #pragma unroll
                 for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[b1 | (j << 4)]);
-                if constexpr (STAGED) fwd16<0, C::NST1, fwd_mask(8 + SA - 5, false), A>(ar, a, sw1);
-                else fwd16<0, C::NST1, fwd_mask(8 + SA - 5, false), A>(ar, a, tw1);
+                fwd16<0, C::NST1, fwd_mask(8 + SA - 5, false), A>(ar, a, sw1);
 #pragma unroll
                 for (int j = 0; j < 16; j++) gt[C::goff(b1 | (j << 4))] = ar.to_word(a[j]);
             } else {
@@ -593,16 +599,14 @@ __device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles
 #pragma unroll
                 for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[b1 | (j << 4)]);
                 // window 1 runs its NST1 stages as numbers 8.. of the inverse: its stage NST1-1 first
-                if constexpr (STAGED) inv16<0, C::NST1, inv_mask(8 + C::NST1 - 4), false, A>(ar, a, sw1);
-                else inv16<0, C::NST1, inv_mask(8 + C::NST1 - 4), false, A>(ar, a, tw1);
+                inv16<0, C::NST1, inv_mask(8 + C::NST1 - 4), false, A>(ar, a, sw1);
 #pragma unroll
                 for (int j = 0; j < 16; j++) s[b1 | (j << 4)] = ar.to_word(a[j]);
                 __syncthreads();
             }
 #pragma unroll
             for (int j = 0; j < 16; j++) a[j] = ar.from_word(s[j * 256 + tid]);
-            if constexpr (STAGED) inv16<0, 4, inv_mask(8 + C::NST1), true, A>(ar, a, sw0);
-            else inv16<0, 4, inv_mask(8 + C::NST1), true, A>(ar, a, tw0);
+            inv16<0, 4, inv_mask(8 + C::NST1), true, A>(ar, a, sw0);
             // Final scaling: the last stage's twiddle psiinv[1] already carries N^-1 for the upper half (a[8..15]);
             // the lower half still needs it (src/ckks/include/ntt_60bit.cuh:890-898): the integer back ends multiply
             // here, the FP64 back end did in its last butterfly.
@@ -619,7 +623,7 @@ __device__ __forceinline__ void strided_body(const NttArgs& P, u64* S, int tiles
 // barriers of this phase leave the FP64 pipe idle unless other CTAs fill in.
 template <int SA, bool INV>
 __global__ void __launch_bounds__(kThreads, 3) ntt_strided(NttArgs P, int tiles) {
-    extern __shared__ __align__(16) u64 S[];       // 2 buffers x 4096 words, then 256 twiddles
+    extern __shared__ __align__(16) u64 S[];       // 2 buffers x 4096 words, then 256 twiddles of up to 16 bytes
     let_next_kernel_start();
     const u64 q = P.moduli[P.start_mod_idx + blockIdx.y];
     if (q < kF64Bound) strided_body<SA, INV, F64Arith>(P, S, tiles);
@@ -627,7 +631,7 @@ __global__ void __launch_bounds__(kThreads, 3) ntt_strided(NttArgs P, int tiles)
     else strided_body<SA, INV, IntArith<false>>(P, S, tiles);
 }
 
-constexpr size_t kSmemStrided = (2 * kTile + kTwStrided) * sizeof(u64);
+constexpr size_t kSmemStrided = (2 * kTile + 2 * kTwStrided) * sizeof(u64);
 constexpr size_t kSmemContig = 3 * kTile * sizeof(u64);
 
 // Both kernels of a transform are launched as programmatic dependents of whatever kernel precedes them in the
