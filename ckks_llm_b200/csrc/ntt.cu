@@ -127,12 +127,13 @@ struct IntArith {
 struct F64Arith {
     typedef double V;
     typedef double TW;
-    double q, u, ninv;
+    double q, u, ninv, to_pos;
     long long qi;
     const double* tw;
     __device__ __forceinline__ void init(const NttArgs& P, int mod) {
         qi = (long long)P.moduli[mod];
         q = (double)qi;
+        to_pos = 4503599627370496.0 + 2.0 * q;                   // 2^52 + 2q, an integer below 2^53
         u = __drcp_rn(q);
         const long long ni = (long long)P.ninv[mod].x;
         ninv = ni > qi / 2 ? -(double)(qi - ni) : (double)ni;
@@ -188,14 +189,10 @@ struct F64Arith {
         a = mulmod(s, ninv);
         b = mulmod(d, w);
     }
-    // An integer-valued double below 2^51 in magnitude as a two's-complement integer: 1.5 * 2^52 + x has x in its
-    // low mantissa bits.
-    __device__ __forceinline__ long long to_int(V x) const {
-        return __double_as_longlong(__dadd_rn(x, 6755399441055744.0)) - 0x4338000000000000ll;
-    }
-    // |x| < 2q -> [0, q), on the integer pipe (the FP64 pipe is what these kernels wait for)
+    // |x| < 2q -> [0, q).  x + 2q lies in (0, 4q), below 2^52, so adding 2^52 + 2q leaves it in the mantissa as an
+    // integer; the two conditional subtractions run on the integer pipe (the FP64 pipe is what these kernels wait for).
     __device__ __forceinline__ u64 canonical(V x) const {
-        u64 v = (u64)(to_int(x) + 2 * qi);               // (0, 4q)
+        u64 v = (u64)__double_as_longlong(__dadd_rn(x, to_pos)) & 0x000FFFFFFFFFFFFFull;
         v = v >= 2 * (u64)qi ? v - 2 * (u64)qi : v;
         return v >= (u64)qi ? v - (u64)qi : v;
     }
